@@ -1,0 +1,202 @@
+/*
+ * lattice_q4.h - C ABI of the B200 (sm_100a) backend for Lattice's Q4 weight-only
+ * linear layer with the LoRA delta fused in and the optional QuaRot activation
+ * rotation in the prologue.
+ *
+ * The reference (ohdearquant/lattice, Rust) has no FFI for this path: its Q4
+ * matmul seam is a set of inherent methods on the Metal engine state.  Each
+ * entry point below names the reference call site it stands in for (paths are
+ * relative to the reference project root); a Rust `extern "C"` block binds
+ * these one to one.
+ *
+ * Conventions
+ *   - every function returns an lq4_status (0 = ok) and never aborts;
+ *   - pointers are DEVICE pointers unless the parameter name starts with `h_`;
+ *   - `stream` is a cudaStream_t passed as void*; calls are asynchronous on it
+ *     unless stated otherwise;
+ *   - a context belongs to one device and one owning host thread (the reference
+ *     keeps its GPU state on a single worker thread:
+ *     crates/inference/src/serve/metal_worker.rs:1-34).  Calls that share a
+ *     context must be ordered on one stream: its workspace is reused per call.
+ *   - weights use the reference's on-disk block layout unchanged: row-major
+ *     [n][k/32] blocks of 20 bytes {f16 scale, f16 bias, 16 bytes of nibbles,
+ *     low nibble first}, w = nibble * scale + bias
+ *     (crates/inference/src/weights/q4_weights.rs:3-45, 65-92).
+ */
+#ifndef LATTICE_Q4_H
+#define LATTICE_Q4_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t lq4_status;
+
+enum {
+    LQ4_OK = 0,
+    LQ4_ERR_NULL = 1,          /* a required pointer is NULL */
+    LQ4_ERR_K = 2,             /* k == 0 or k % 32 != 0 (the reference panics here) */
+    LQ4_ERR_OVERFLOW = 3,      /* m*k, n*k or m*n does not fit */
+    LQ4_ERR_ALIGN = 4,         /* pointer alignment below the documented minimum */
+    LQ4_ERR_DTYPE = 5,
+    LQ4_ERR_LORA = 6,          /* rank == 0, non-finite scale, or NULL factor */
+    LQ4_ERR_ROT = 7,           /* rotation dim != k or not a power of two */
+    LQ4_ERR_BAD_BLOCK = 8,     /* a block's scale is not finite-positive or its bias not finite */
+    LQ4_ERR_CUDA = 9,          /* a CUDA runtime call failed; see lq4_last_error() */
+    LQ4_ERR_UNSUPPORTED = 10,  /* shape outside what this build handles */
+    LQ4_ERR_DEVICE = 11,       /* a kernel reported a failed bounded wait */
+    LQ4_ERR_FORMAT = 12,       /* malformed .q4 image */
+    LQ4_ERR_IO = 13,
+    LQ4_ERR_SHAPE = 14,        /* shape / length mismatch */
+    LQ4_ERR_NOSPACE = 15       /* request exceeds a fixed capacity */
+};
+
+enum { LQ4_DTYPE_F32 = 0, LQ4_DTYPE_BF16 = 1 };
+enum { LQ4_QUANT_ASYMMETRIC = 0, LQ4_QUANT_SYMMETRIC = 1 };
+
+/* Which kernel family lq4_linear picks.  AUTO is the product path. */
+enum {
+    LQ4_PATH_AUTO = 0,
+    LQ4_PATH_GEMV_MMA = 1,       /* m <= 16: TMA-staged stream-K decode kernel */
+    LQ4_PATH_GEMV_GENERIC = 2,   /* any alignment, any k % 32 == 0; slow */
+    LQ4_PATH_GEMM_TC = 3         /* m > 16: tcgen05 / TMEM tensor-core kernel */
+};
+
+typedef struct lq4_ctx lq4_ctx;
+typedef struct lq4_weights lq4_weights;
+typedef struct lq4_lora lq4_lora;
+
+/* One LoRA projection: y += scale * B (A x).  A is [rank, k] row-major, B is
+ * [n, rank] row-major, both f32 on the device
+ * (crates/tune/src/lora/mod.rs:124-137, crates/tune/src/lora/apply.rs:48-93). */
+typedef struct {
+    const float* a;
+    const float* b;
+    uint32_t rank;
+    float scale;
+} lq4_lora_desc;
+
+/* Online randomized Hadamard rotation x' = H (D x) applied to every activation
+ * row before the matmul; `signs` holds k entries of +1/-1 (f32, device)
+ * (crates/inference/src/quant/quarot/hadamard.rs:176-209). */
+typedef struct {
+    const float* signs;
+    uint32_t dim;
+} lq4_rot_desc;
+
+typedef struct {
+    const void* x;        /* [m, k] row-major activations, f32 or bf16 */
+    int32_t x_dtype;      /* LQ4_DTYPE_* */
+    uint32_t m, n, k;
+    const uint8_t* w;     /* Q4 payload for rows [0, n): the header is already skipped;
+                             an N-shard or a row slice of a fused matrix is addressed by
+                             adding n0 * (k/32) * 20 bytes.  4-byte aligned at least;
+                             16-byte aligned with k % 128 == 0 for the fast kernels. */
+    float* y;             /* [m, n] f32, OVERWRITTEN */
+    uint64_t ldy;         /* elements between consecutive rows of y; 0 means n */
+    const lq4_lora_desc* lora;   /* NULL = no adapter for this projection */
+    const lq4_rot_desc* rot;     /* NULL = no online rotation */
+    int32_t path;         /* LQ4_PATH_* */
+} lq4_linear_args;
+
+/* ---- context ----------------------------------------------------------- */
+
+/* Creates the per-device state (workspace, status word) on `device`.  Allocates. */
+lq4_status lq4_ctx_create(int32_t device, lq4_ctx** out);
+void lq4_ctx_destroy(lq4_ctx* ctx);
+/* Grows the workspace so that a later lq4_linear of this shape allocates nothing. */
+lq4_status lq4_ctx_reserve(lq4_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t rank);
+/* Synchronises `stream` and returns LQ4_ERR_DEVICE if any kernel launched through
+ * this context gave up on a bounded wait since the last call; clears the flag. */
+lq4_status lq4_ctx_check(lq4_ctx* ctx, void* stream);
+/* Number of kernels this library has launched through `ctx` so far. */
+uint64_t lq4_ctx_launch_count(const lq4_ctx* ctx);
+const char* lq4_last_error(void);
+const char* lq4_status_string(lq4_status s);
+int32_t lq4_abi_version(void);
+
+/* ---- the hot path ------------------------------------------------------- */
+
+/* y = x Wq4^T (+ LoRA) with the optional rotation of x first.
+ * Replaces dispatch_gemm_q4 / dispatch_gemm_q4_at / dispatch_matmul_q4
+ * (crates/inference/src/forward/metal_qwen35/inner/dispatch.rs:148-229, 1037-1097)
+ * with dispatch_lora_if_active (.../inner/layers/mod.rs:15-51) folded into the same
+ * launch.  m == 0 or n == 0 is a no-op; k == 0 or k % 32 != 0 returns LQ4_ERR_K. */
+lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* args, void* stream);
+
+/* Same call with HOST activations and HOST output: copies x to the device,
+ * runs lq4_linear, copies y back and waits for it.  Weights and LoRA factors
+ * stay device resident, as the reference keeps them in GPU-visible buffers for
+ * the model's lifetime (crates/inference/src/forward/metal_qwen35.rs:599-702). */
+lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* args_with_host_x_y, void* stream);
+
+/* Standalone y[m, d_out] += scale * B (A x): the two-dispatch form of
+ * dispatch_lora_if_active, for fused outputs where two adapters write two
+ * column ranges of one y (gate||up, qkv||z). */
+lq4_status lq4_lora_apply(lq4_ctx* ctx, const void* x, int32_t x_dtype, uint32_t m, uint32_t k,
+                          float* y, uint32_t n, uint64_t ldy, const lq4_lora_desc* lora, void* stream);
+
+/* Dequantizes n_blocks blocks to 32 * n_blocks floats, bit-identical to
+ * dequantize_q4_to_f32 (crates/inference/src/weights/q4_weights.rs:558-571). */
+lq4_status lq4_dequant_f32(const uint8_t* payload, uint64_t n_blocks, float* out, void* stream);
+
+/* Quantizes `len` f32 values in flat 32-element chunks (last one zero padded),
+ * bit-identical to quantize_f32_to_q4 (asymmetric) and to quantize_f64_to_q4 on
+ * f32-representable input (symmetric)
+ * (crates/inference/src/weights/q4_weights.rs:239-295, 470-487, 514-553).
+ * `status_out` (device int32, may be NULL) receives LQ4_ERR_BAD_BLOCK if a block
+ * had a non-finite input or unrepresentable metadata. */
+lq4_status lq4_quantize_f32(const float* data, uint64_t len, int32_t mode, uint8_t* payload,
+                            int32_t* status_out, void* stream);
+
+/* Applies x' = H (D x) to `rows` rows of length `dim` (a power of two <= 16384),
+ * f32 in and out, bit-identical to RandomizedHadamard::apply
+ * (crates/inference/src/quant/quarot/hadamard.rs:197-209). */
+lq4_status lq4_hadamard_rows(const float* x, float* out, uint32_t rows, const lq4_rot_desc* rot, void* stream);
+
+/* Fills `signs` with the +1/-1 diagonal of RandomizedHadamard::new(seed, dim)
+ * (crates/inference/src/quant/quarot/hadamard.rs:114-139). */
+lq4_status lq4_rot_signs_from_seed(uint64_t seed, uint32_t dim, float* signs, void* stream);
+
+/* ---- resident objects ---------------------------------------------------- */
+
+/* Validates every block (scale finite and > 0, bias finite) on the host and only
+ * then copies the payload into a 256-byte aligned device allocation: the
+ * counterpart of mmap_q4_weight (crates/inference/src/forward/metal_qwen35.rs:660-702;
+ * rule: crates/inference/src/weights/ingress.rs:542-560).  Synchronous. */
+lq4_status lq4_weights_upload(const uint8_t* h_payload, uint64_t n, uint64_t k, lq4_weights** out);
+/* Loads a `.q4` file ("KHQ4", version 2): header, exact extent, optional
+ * expected shape (pass ndim 0 to skip), block validity
+ * (crates/inference/src/weights/q4_weights.rs:709-868). */
+lq4_status lq4_weights_load_q4_file(const char* h_path, const uint64_t* h_expected_shape,
+                                    uint32_t expected_ndim, lq4_weights** out);
+const uint8_t* lq4_weights_payload(const lq4_weights* w);
+uint64_t lq4_weights_rows(const lq4_weights* w);
+uint64_t lq4_weights_cols(const lq4_weights* w);
+void lq4_weights_free(lq4_weights* w);
+
+/* Copies host LoRA factors to the device after the checks load_lora_adapter makes
+ * per projection: rank > 0, d_in > 0, d_out > 0, finite scale, A and B element
+ * counts equal rank*d_in and d_out*rank, sizes fit u32
+ * (crates/inference/src/forward/metal_qwen35.rs:3806-3986).  Synchronous. */
+lq4_status lq4_lora_upload(const float* h_a, uint64_t a_len, const float* h_b, uint64_t b_len,
+                           uint64_t rank, uint64_t d_in, uint64_t d_out, float scale, lq4_lora** out);
+/* Fills `desc` with the device pointers of rows [n0, n1) of B (all of A). */
+lq4_status lq4_lora_desc_for_rows(const lq4_lora* l, uint64_t n0, uint64_t n1, lq4_lora_desc* desc);
+void lq4_lora_free(lq4_lora* l);
+
+/* ---- N-sharding ----------------------------------------------------------- */
+
+/* Column-parallel split of the n output rows over `world` ranks: rank r owns rows
+ * [n0, n1) = [r*n/world, (r+1)*n/world) and its payload starts `byte_offset` bytes
+ * into the full payload - the qw_extra_offset addressing of dispatch_gemm_q4_at. */
+lq4_status lq4_shard_plan(uint64_t n, uint64_t k, uint32_t world, uint32_t rank,
+                          uint64_t* n0, uint64_t* n1, uint64_t* byte_offset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LATTICE_Q4_H */

@@ -1,0 +1,338 @@
+"""Host-side mirror of the reference's Q4 matmul seam, over the C ABI.
+
+The reference exposes no plugin interface for this path: the seam is a set of methods
+on its Metal engine state.  The methods below keep those names, argument meaning and
+error behaviour so that call sites (and tests) read like the reference's:
+
+* ``dispatch_matmul_q4`` / ``dispatch_gemm_q4`` / ``dispatch_gemm_q4_at``
+  (crates/inference/src/forward/metal_qwen35/inner/dispatch.rs:148-229, 1037-1097)
+* ``dispatch_lora_if_active`` (crates/inference/src/forward/metal_qwen35/inner/layers/mod.rs:15-51)
+* ``load_lora_adapter`` / ``unload_lora_adapter`` / ``LoraLayerData``
+  (crates/inference/src/forward/metal_qwen35.rs:1699-1716, 3806-3986, 4063-4075)
+* ``Q4WeightBuf`` (crates/inference/src/forward/metal_qwen35.rs:599-702)
+
+Buffers are torch CUDA tensors (device memory only); ``*_offset`` arguments are byte
+offsets into them, as the Metal encoder takes them.  All compute is in the CUDA library;
+nothing here falls back to PyTorch or to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import LinearArgs, LoraDesc, Lq4Error, RotDesc, check
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Q4WeightBuf:
+    """Device-resident Q4 payload of one ``[n, k]`` weight in the reference block layout."""
+
+    def __init__(self, handle: int, n: int, k: int):
+        self._handle = handle
+        self.n, self.k = n, k
+        self.payload_ptr = _lib.lib().lq4_weights_payload(handle)
+        self.payload_bytes = n * (k // 32) * 20
+
+    @classmethod
+    def from_host_payload(cls, payload: np.ndarray, n: int, k: int) -> "Q4WeightBuf":
+        """Validates every block's scale/bias on the host, then copies to the device."""
+        p = np.ascontiguousarray(payload, dtype=np.uint8).reshape(-1)
+        if p.size != n * (k // 32) * 20:
+            raise ValueError(f"payload has {p.size} bytes, expected {n * (k // 32) * 20} for [{n}, {k}]")
+        h = C.c_void_p()
+        check(_lib.lib().lq4_weights_upload(p.ctypes.data_as(C.c_void_p), n, k, C.byref(h)))
+        return cls(h.value, n, k)
+
+    @classmethod
+    def from_q4_file(cls, path: str, expected_shape: Optional[Tuple[int, int]] = None) -> "Q4WeightBuf":
+        h = C.c_void_p()
+        if expected_shape is None:
+            check(_lib.lib().lq4_weights_load_q4_file(path.encode(), None, 0, C.byref(h)))
+        else:
+            shp = (C.c_uint64 * len(expected_shape))(*expected_shape)
+            check(_lib.lib().lq4_weights_load_q4_file(path.encode(), shp, len(expected_shape), C.byref(h)))
+        L = _lib.lib()
+        return cls(h.value, int(L.lq4_weights_rows(h)), int(L.lq4_weights_cols(h)))
+
+    @classmethod
+    def from_device_payload(cls, payload: torch.Tensor, n: int, k: int) -> "Q4WeightBuf":
+        """Wraps bytes that are already on the device (e.g. produced by ``quantize``); not validated."""
+        assert payload.is_cuda and payload.dtype == torch.uint8 and payload.numel() >= n * (k // 32) * 20
+        self = cls.__new__(cls)
+        self._handle = None
+        self._keep = payload
+        self.n, self.k = n, k
+        self.payload_ptr = payload.data_ptr()
+        self.payload_bytes = n * (k // 32) * 20
+        return self
+
+    def free(self) -> None:
+        if getattr(self, "_handle", None):
+            _lib.lib().lq4_weights_free(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+@dataclass
+class LoraLayerData:
+    """Input data for one LoRA projection: A row-major ``(rank, d_in)``, B row-major ``(d_out, rank)``."""
+    layer_idx: int
+    module: str
+    a: np.ndarray
+    b: np.ndarray
+    rank: int
+    d_in: int
+    d_out: int
+
+
+@dataclass
+class _LoraProjection:
+    handle: int
+    rank: int
+    d_in: int
+    d_out: int
+
+
+@dataclass
+class _LoraAdapter:
+    projections: List[Dict[str, _LoraProjection]]
+    scale: float
+    max_rank: int = 0
+
+
+class CudaQ4Backend:
+    """One instance per device and owning thread, like the reference's GPU state."""
+
+    def __init__(self, device: int = 0, num_hidden_layers: int = 1,
+                 projection_shapes: Optional[Dict[str, Tuple[int, int]]] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("CudaQ4Backend needs a CUDA device; there is no CPU path")
+        self.device = device
+        torch.cuda.set_device(device)
+        h = C.c_void_p()
+        check(_lib.lib().lq4_ctx_create(device, C.byref(h)))
+        self._ctx = h.value
+        self.num_hidden_layers = num_hidden_layers
+        # module name -> (d_in, d_out); None disables the model-shape check of load_lora_adapter
+        self.projection_shapes = projection_shapes
+        self.lora: Optional[_LoraAdapter] = None
+
+    def close(self) -> None:
+        if self._ctx:
+            self.unload_lora_adapter()
+            _lib.lib().lq4_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- bookkeeping ------------------------------------------------------
+    @property
+    def launch_count(self) -> int:
+        return int(_lib.lib().lq4_ctx_launch_count(self._ctx))
+
+    def check_device_status(self) -> None:
+        """Synchronises the current stream and raises if a kernel gave up on a bounded wait."""
+        check(_lib.lib().lq4_ctx_check(self._ctx, _stream()))
+
+    def reserve(self, m: int, n: int, k: int, rank: int = 0) -> None:
+        check(_lib.lib().lq4_ctx_reserve(self._ctx, m, n, k, rank))
+
+    # ---- the seam -----------------------------------------------------------
+    def _linear(self, x_ptr: int, x_dtype: int, w_ptr: int, y_ptr: int, m: int, n: int, k: int, ldy: int = 0,
+                lora: Optional[LoraDesc] = None, rot: Optional[RotDesc] = None, path: int = _lib.PATH_AUTO,
+                host: bool = False) -> None:
+        args = LinearArgs(x_ptr, x_dtype, m, n, k, w_ptr, y_ptr, ldy,
+                          C.pointer(lora) if lora is not None else None,
+                          C.pointer(rot) if rot is not None else None, path)
+        fn = _lib.lib().lq4_linear_host if host else _lib.lib().lq4_linear
+        check(fn(self._ctx, C.byref(args), _stream()))
+
+    @staticmethod
+    def _require_k(name: str, k: int) -> None:
+        # the reference asserts here: dispatch.rs:185-188
+        if k <= 0 or k % 32 != 0:
+            raise ValueError(f"{name} requires K to be non-zero and divisible by 32, got {k}")
+
+    @staticmethod
+    def _dtype_of(x: torch.Tensor) -> int:
+        if x.dtype == torch.float32:
+            return _lib.DTYPE_F32
+        if x.dtype == torch.bfloat16:
+            return _lib.DTYPE_BF16
+        raise TypeError(f"activations must be float32 or bfloat16, got {x.dtype}")
+
+    def dispatch_gemm_q4_at(self, x: torch.Tensor, x_offset: int, qw: Q4WeightBuf, qw_extra_offset: int,
+                            y: torch.Tensor, y_offset: int, m: int, n: int, k: int, *,
+                            lora: Optional[LoraDesc] = None, rot: Optional[RotDesc] = None,
+                            ldy: int = 0, path: int = _lib.PATH_AUTO) -> None:
+        """``y[m, n] = x[m, k] . Wq4[n, k]^T`` (overwrites y); ``qw_extra_offset`` bytes into the payload."""
+        if m == 0 or n == 0:
+            return
+        self._require_k("dispatch_gemm_q4_at", k)
+        assert x.is_cuda and y.is_cuda and y.dtype == torch.float32
+        self._linear(x.data_ptr() + x_offset, self._dtype_of(x), qw.payload_ptr + qw_extra_offset,
+                     y.data_ptr() + y_offset, m, n, k, ldy, lora, rot, path)
+
+    def dispatch_gemm_q4(self, x: torch.Tensor, x_offset: int, qw: Q4WeightBuf, y: torch.Tensor, y_offset: int,
+                         m: int, n: int, k: int, **kw) -> None:
+        if m == 0 or n == 0:
+            return
+        self._require_k("dispatch_gemm_q4", k)
+        self.dispatch_gemm_q4_at(x, x_offset, qw, 0, y, y_offset, m, n, k, **kw)
+
+    def dispatch_matmul_q4(self, x: torch.Tensor, qw: Q4WeightBuf, y: torch.Tensor, m: int, n: int, k: int, **kw) -> None:
+        """Decode-step form (m == 1 in the reference)."""
+        self.dispatch_gemm_q4(x, 0, qw, y, 0, m, n, k, **kw)
+
+    # ---- LoRA ------------------------------------------------------------------
+    def load_lora_adapter(self, layers: List[LoraLayerData], scale: float, quarot_seed: Optional[int] = None) -> None:
+        """Copies the adapter to the device after the reference's load-time checks."""
+        if self.lora is not None:
+            raise Lq4Error(_lib.ERR_LORA, "LoRA adapter already loaded; call unload_lora_adapter first")
+        if len(layers) == 0:
+            raise Lq4Error(_lib.ERR_LORA, "load_lora_adapter: layers must not be empty")
+        if not math.isfinite(scale):
+            raise Lq4Error(_lib.ERR_LORA, f"load_lora_adapter: scale must be finite, got {scale}")
+        if quarot_seed is not None:
+            raise Lq4Error(_lib.ERR_UNSUPPORTED, "adapter rotation for a QuaRot base is not built yet: "
+                                                 "rotate A/B before loading")
+        projections: List[Dict[str, _LoraProjection]] = [dict() for _ in range(self.num_hidden_layers)]
+        max_rank = 0
+        try:
+            for layer in layers:
+                if layer.rank == 0:
+                    raise Lq4Error(_lib.ERR_LORA, f"load_lora_adapter: layer {layer.layer_idx} module "
+                                                  f"'{layer.module}' has rank=0")
+                if layer.d_in == 0 or layer.d_out == 0:
+                    raise Lq4Error(_lib.ERR_LORA, f"load_lora_adapter: layer {layer.layer_idx} module "
+                                                  f"'{layer.module}' has zero dimension")
+                if layer.layer_idx >= self.num_hidden_layers:
+                    raise Lq4Error(_lib.ERR_SHAPE, f"load_lora_adapter: layer_idx {layer.layer_idx} >= "
+                                                   f"num_hidden_layers {self.num_hidden_layers}")
+                if self.projection_shapes is not None:
+                    if layer.module not in self.projection_shapes:
+                        raise Lq4Error(_lib.ERR_LORA, f"unknown LoRA module '{layer.module}'")
+                    exp = self.projection_shapes[layer.module]
+                    if (layer.d_in, layer.d_out) != exp:
+                        raise Lq4Error(_lib.ERR_SHAPE, f"load_lora_adapter: layer {layer.layer_idx} module "
+                                                       f"'{layer.module}' has (d_in={layer.d_in}, d_out={layer.d_out}) "
+                                                       f"but model expects (d_in={exp[0]}, d_out={exp[1]})")
+                if layer.module in projections[layer.layer_idx]:
+                    raise Lq4Error(_lib.ERR_LORA, f"load_lora_adapter: duplicate projection for layer "
+                                                  f"{layer.layer_idx} module '{layer.module}'")
+                a = np.ascontiguousarray(layer.a, dtype=np.float32).reshape(-1)
+                b = np.ascontiguousarray(layer.b, dtype=np.float32).reshape(-1)
+                h = C.c_void_p()
+                # A/B length, overflow and u32 checks happen in the library
+                check(_lib.lib().lq4_lora_upload(a.ctypes.data_as(C.c_void_p), a.size, b.ctypes.data_as(C.c_void_p),
+                                                 b.size, layer.rank, layer.d_in, layer.d_out, scale, C.byref(h)))
+                projections[layer.layer_idx][layer.module] = _LoraProjection(h.value, layer.rank, layer.d_in, layer.d_out)
+                max_rank = max(max_rank, layer.rank)
+        except Exception:
+            for d in projections:
+                for pr in d.values():
+                    _lib.lib().lq4_lora_free(pr.handle)
+            raise
+        self.lora = _LoraAdapter(projections, float(scale), max_rank)
+
+    def unload_lora_adapter(self) -> None:
+        if self.lora is not None:
+            for d in self.lora.projections:
+                for pr in d.values():
+                    _lib.lib().lq4_lora_free(pr.handle)
+            self.lora = None
+
+    def has_lora_adapter(self) -> bool:
+        return self.lora is not None
+
+    def get_projection(self, layer_idx: int, module: str) -> Optional[_LoraProjection]:
+        if self.lora is None or layer_idx >= len(self.lora.projections):
+            return None
+        return self.lora.projections[layer_idx].get(module)
+
+    def lora_desc(self, layer_idx: int, module: str, n0: int = 0, n1: Optional[int] = None) -> Optional[LoraDesc]:
+        """Descriptor to pass as ``lora=`` so the delta is added inside the matmul launch."""
+        pr = self.get_projection(layer_idx, module)
+        if pr is None:
+            return None
+        d = LoraDesc()
+        check(_lib.lib().lq4_lora_desc_for_rows(pr.handle, n0, pr.d_out if n1 is None else n1, C.byref(d)))
+        return d
+
+    def dispatch_lora_if_active(self, x: torch.Tensor, x_byte_offset: int, y: torch.Tensor, y_byte_offset: int,
+                                layer_idx: int, module: str, m: int = 1, ldy: int = 0) -> None:
+        """``y[0..d_out] += scale * B (A x)``; no-op without an adapter or a projection for this module."""
+        pr = self.get_projection(layer_idx, module)
+        if pr is None:
+            return
+        d = self.lora_desc(layer_idx, module)
+        check(_lib.lib().lq4_lora_apply(self._ctx, x.data_ptr() + x_byte_offset, self._dtype_of(x), m, pr.d_in,
+                                        y.data_ptr() + y_byte_offset, pr.d_out, ldy, C.byref(d), _stream()))
+
+    # ---- helpers on device tensors ------------------------------------------------
+    def dequantize(self, payload: torch.Tensor, n_blocks: int) -> torch.Tensor:
+        out = torch.empty(n_blocks * 32, dtype=torch.float32, device=payload.device)
+        check(_lib.lib().lq4_dequant_f32(payload.data_ptr(), n_blocks, out.data_ptr(), _stream()))
+        return out
+
+    def quantize(self, data: torch.Tensor, symmetric: bool = False) -> torch.Tensor:
+        """Flat 32-chunk quantizer on the device; raises if a block was not representable."""
+        assert data.is_cuda and data.dtype == torch.float32 and data.is_contiguous()
+        n = data.numel()
+        out = torch.empty(((n + 31) // 32) * 20, dtype=torch.uint8, device=data.device)
+        st = torch.zeros(1, dtype=torch.int32, device=data.device)
+        check(_lib.lib().lq4_quantize_f32(data.data_ptr(), n, int(symmetric), out.data_ptr(), st.data_ptr(), _stream()))
+        if int(st.item()) != 0:
+            raise Lq4Error(_lib.ERR_BAD_BLOCK, "a block had a non-finite value or unrepresentable scale/bias")
+        return out
+
+    def rot_signs(self, seed: int, dim: int) -> torch.Tensor:
+        s = torch.empty(dim, dtype=torch.float32, device=f"cuda:{self.device}")
+        check(_lib.lib().lq4_rot_signs_from_seed(seed & (2 ** 64 - 1), dim, s.data_ptr(), _stream()))
+        return s
+
+    @staticmethod
+    def rot_desc(signs: torch.Tensor) -> RotDesc:
+        assert signs.is_cuda and signs.dtype == torch.float32
+        return RotDesc(signs.data_ptr(), signs.numel())
+
+    def hadamard_rows(self, x: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+        out = torch.empty_like(x)
+        rot = self.rot_desc(signs)
+        check(_lib.lib().lq4_hadamard_rows(x.data_ptr(), out.data_ptr(), x.numel() // signs.numel(), C.byref(rot), _stream()))
+        return out
+
+    def linear(self, x: torch.Tensor, qw: Q4WeightBuf, *, lora: Optional[LoraDesc] = None,
+               rot: Optional[RotDesc] = None, path: int = _lib.PATH_AUTO, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Convenience wrapper: ``x`` is ``[m, k]`` on the device, returns ``[m, n]`` f32."""
+        m, k = x.shape
+        y = out if out is not None else torch.empty((m, qw.n), dtype=torch.float32, device=x.device)
+        self.dispatch_gemm_q4(x.contiguous(), 0, qw, y, 0, m, qw.n, k, lora=lora, rot=rot, path=path)
+        return y
+
+    def linear_host(self, x: np.ndarray, qw: Q4WeightBuf, y: np.ndarray, *, lora: Optional[LoraDesc] = None,
+                    rot: Optional[RotDesc] = None) -> None:
+        """End-to-end call with HOST activations and output (copies inside the call, waits for y)."""
+        m, k = x.shape
+        self._require_k("linear_host", k)
+        dt = _lib.DTYPE_F32 if x.dtype == np.float32 else _lib.DTYPE_BF16
+        self._linear(x.ctypes.data, dt, qw.payload_ptr, y.ctypes.data, m, qw.n, k, 0, lora, rot, host=True)

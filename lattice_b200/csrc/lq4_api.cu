@@ -1,0 +1,613 @@
+// C ABI: argument validation, workspace management and kernel selection.
+// Validation happens before any launch and mirrors the reference's call-site
+// contract: m == 0 or n == 0 is a no-op, k must be a non-zero multiple of 32
+// (crates/inference/src/forward/metal_qwen35/inner/dispatch.rs:181-188), element
+// counts are overflow-checked first (crates/inference/src/forward/cpu/gemm_validate.rs:1-60).
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "lq4_gemm.cuh"
+#include "lq4_kernels.cuh"
+
+using namespace lq4;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+lq4_status fail(lq4_status s, const std::string& msg) {
+    g_last_error = msg;
+    return s;
+}
+lq4_status cuda_fail(cudaError_t e, const char* what) {
+    return fail(LQ4_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define LQ4_CUDA(call)                                        \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #call); \
+    } while (0)
+
+struct Buf {
+    void* p = nullptr;
+    size_t cap = 0;
+};
+
+}  // namespace
+
+struct lq4_ctx {
+    int device = 0;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    int32_t* status = nullptr;    // device status word
+    uint32_t* tsync = nullptr;    // {arrived, finished} of the LoRA partial exchange
+    Buf xrot, xs, sx, t, tpart, partials, tickets, hx, hy, gemm;
+    bool allow_grow = true;
+    int pdl = 1;
+};
+
+struct lq4_weights {
+    uint8_t* payload = nullptr;
+    uint64_t rows = 0, cols = 0;
+    int device = 0;
+};
+
+struct lq4_lora {
+    float* a = nullptr;
+    float* b = nullptr;
+    uint64_t rank = 0, d_in = 0, d_out = 0;
+    float scale = 0.0f;
+};
+
+namespace {
+
+// Grows `b` to at least `bytes`.  Growing frees the old allocation, so the stream
+// that may still use it is drained first.
+lq4_status ensure(lq4_ctx* ctx, Buf& b, size_t bytes, bool zero, cudaStream_t s) {
+    if (bytes <= b.cap) return LQ4_OK;
+    if (!ctx->allow_grow) return fail(LQ4_ERR_NOSPACE, "workspace too small and growth is disabled");
+    LQ4_CUDA(cudaStreamSynchronize(s));
+    if (b.p) LQ4_CUDA(cudaFree(b.p));
+    b.p = nullptr;
+    b.cap = 0;
+    size_t cap = (bytes + 255) / 256 * 256;
+    LQ4_CUDA(cudaMalloc(&b.p, cap));
+    if (zero) LQ4_CUDA(cudaMemset(b.p, 0, cap));
+    b.cap = cap;
+    return LQ4_OK;
+}
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline bool is_pow2(uint64_t v) { return v && !(v & (v - 1)); }
+
+bool mul_overflows(uint64_t a, uint64_t b, uint64_t limit) { return a != 0 && b > limit / a; }
+
+lq4_status validate_linear(const lq4_linear_args* a) {
+    if (!a) return fail(LQ4_ERR_NULL, "args is NULL");
+    if (a->m == 0 || a->n == 0) return LQ4_OK;
+    if (a->k == 0 || a->k % 32 != 0)
+        return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32, got " + std::to_string(a->k));
+    const uint64_t lim = (uint64_t)1 << 40;
+    if (mul_overflows(a->m, a->k, lim) || mul_overflows(a->n, a->k, lim) || mul_overflows(a->m, a->n, lim))
+        return fail(LQ4_ERR_OVERFLOW, "m*k, n*k or m*n exceeds the supported element count");
+    if (!a->x || !a->w || !a->y) return fail(LQ4_ERR_NULL, "x, w and y must be non-NULL");
+    if (a->x_dtype != LQ4_DTYPE_F32 && a->x_dtype != LQ4_DTYPE_BF16) return fail(LQ4_ERR_DTYPE, "unknown x_dtype");
+    if (!aligned(a->w, 4) || !aligned(a->y, 4) || !aligned(a->x, a->x_dtype == LQ4_DTYPE_F32 ? 4 : 2))
+        return fail(LQ4_ERR_ALIGN, "w and y need 4-byte alignment, x its element alignment");
+    if (a->ldy != 0 && a->ldy < a->n) return fail(LQ4_ERR_SHAPE, "ldy is smaller than n");
+    if (a->lora) {
+        const lq4_lora_desc* l = a->lora;
+        if (!l->a || !l->b) return fail(LQ4_ERR_LORA, "LoRA factor pointer is NULL");
+        if (l->rank == 0) return fail(LQ4_ERR_LORA, "LoRA rank is 0");
+        if (!std::isfinite(l->scale)) return fail(LQ4_ERR_LORA, "LoRA scale must be finite");
+        if (!aligned(l->a, 4) || !aligned(l->b, 4)) return fail(LQ4_ERR_ALIGN, "LoRA factors need 4-byte alignment");
+    }
+    if (a->rot) {
+        if (!a->rot->signs) return fail(LQ4_ERR_ROT, "rotation signs pointer is NULL");
+        if (a->rot->dim != a->k) return fail(LQ4_ERR_ROT, "rotation dim must equal k");
+        if (!is_pow2(a->k) || a->k > 16384) return fail(LQ4_ERR_ROT, "rotation needs k a power of two <= 16384");
+    }
+    if (a->path < LQ4_PATH_AUTO || a->path > LQ4_PATH_GEMM_TC) return fail(LQ4_ERR_UNSUPPORTED, "unknown path");
+    return LQ4_OK;
+}
+
+// One call of the decode kernel for at most 16 tokens.
+lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dtype, const float* signs,
+                        uint32_t m, float* y, uint64_t ldy, cudaStream_t s) {
+    GemvParams p{};
+    p.w = a->w; p.y = y; p.ldy = ldy;
+    p.m = m; p.n = a->n; p.k = a->k;
+    p.kb = a->k / 32; p.kg = p.kb / kGemvGranuleBlocks;
+    p.tiles = (a->n + kGemvTileRows - 1) / kGemvTileRows;
+    p.nt = (2 * m + 7) / 8;
+    p.gmax = p.nt == 1 ? 2 * m : 8;
+    p.status = ctx->status;
+    if (a->lora) {
+        p.la = a->lora->a; p.lb = a->lora->b; p.rank = a->lora->rank; p.lscale = a->lora->scale;
+    }
+    const uint64_t total = (uint64_t)p.tiles * p.kg;
+    const int grid = (int)(total < (uint64_t)ctx->sm_count ? total : (uint64_t)ctx->sm_count);
+    lq4_status st;
+    if ((st = ensure(ctx, ctx->partials, (size_t)grid * 2 * kGemvTileRows * p.nt * 4 * sizeof(float), false, s))) return st;
+    if ((st = ensure(ctx, ctx->tickets, (size_t)p.tiles * 8 * sizeof(uint32_t), true, s))) return st;
+    p.partials = (float*)ctx->partials.p;
+    p.tickets = (uint32_t*)ctx->tickets.p;
+
+    const bool resident = gemv_resident_fits(m, a->k, signs != nullptr);
+    if (resident) {
+        p.x = x; p.x_dtype = x_dtype; p.signs = signs;
+        if (p.rank) {
+            if ((st = ensure(ctx, ctx->tpart, (size_t)grid * m * p.rank * sizeof(float), false, s))) return st;
+            p.tpart = (float*)ctx->tpart.p;
+            p.tsync = ctx->tsync;
+        }
+        p.use_pdl = ctx->pdl;
+        const size_t smem = gemv_plan_smem(p, true);
+        if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "resident plan does not fit");
+        LQ4_CUDA(launch_gemv_mma(p, true, smem, grid, s));
+        ctx->launches += 1;
+        return LQ4_OK;
+    }
+    // staged variant: rotation (if any) was applied by the caller into the workspace
+    if ((st = ensure(ctx, ctx->xs, (size_t)p.kb * p.nt * p.gmax * 64, false, s))) return st;
+    if ((st = ensure(ctx, ctx->sx, (size_t)p.kb * p.nt * 16, false, s))) return st;
+    launch_prep_xs(x, x_dtype, m, a->k, p.nt, p.gmax, (uint8_t*)ctx->xs.p, (float*)ctx->sx.p, s);
+    ctx->launches += 1;
+    if (p.rank) {
+        if ((st = ensure(ctx, ctx->t, (size_t)m * p.rank * sizeof(float), false, s))) return st;
+        launch_lora_t(x, x_dtype, m, a->k, p.la, p.rank, (float*)ctx->t.p, s);
+        ctx->launches += 1;
+        p.t_g = (const float*)ctx->t.p;
+    }
+    p.xs_g = (const uint8_t*)ctx->xs.p;
+    p.sx_g = (const float*)ctx->sx.p;
+    p.use_pdl = 0;
+    const size_t smem = gemv_plan_smem(p, false);
+    if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "staged plan does not fit");
+    LQ4_CUDA(launch_gemv_mma(p, false, smem, grid, s));
+    ctx->launches += 1;
+    return LQ4_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t lq4_abi_version(void) { return 1; }
+
+const char* lq4_last_error(void) { return g_last_error.c_str(); }
+
+const char* lq4_status_string(lq4_status s) {
+    switch (s) {
+        case LQ4_OK: return "ok";
+        case LQ4_ERR_NULL: return "null pointer";
+        case LQ4_ERR_K: return "k must be a non-zero multiple of 32";
+        case LQ4_ERR_OVERFLOW: return "element count overflow";
+        case LQ4_ERR_ALIGN: return "misaligned pointer";
+        case LQ4_ERR_DTYPE: return "unknown dtype";
+        case LQ4_ERR_LORA: return "invalid LoRA descriptor";
+        case LQ4_ERR_ROT: return "invalid rotation descriptor";
+        case LQ4_ERR_BAD_BLOCK: return "invalid Q4 block metadata";
+        case LQ4_ERR_CUDA: return "CUDA error";
+        case LQ4_ERR_UNSUPPORTED: return "unsupported shape or path";
+        case LQ4_ERR_DEVICE: return "device-side bounded wait failed";
+        case LQ4_ERR_FORMAT: return "malformed .q4 file";
+        case LQ4_ERR_IO: return "I/O error";
+        case LQ4_ERR_SHAPE: return "shape mismatch";
+        case LQ4_ERR_NOSPACE: return "capacity exceeded";
+        default: return "unknown status";
+    }
+}
+
+lq4_status lq4_ctx_create(int32_t device, lq4_ctx** out) {
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    *out = nullptr;
+    int count = 0;
+    LQ4_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return fail(LQ4_ERR_UNSUPPORTED, "no such CUDA device");
+    LQ4_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop{};
+    LQ4_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(LQ4_ERR_UNSUPPORTED, "this library contains sm_100a code only; device is sm_" +
+                                             std::to_string(prop.major) + std::to_string(prop.minor));
+    lq4_ctx* ctx = new lq4_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    LQ4_CUDA(cudaMalloc(&ctx->status, 256));
+    LQ4_CUDA(cudaMemset(ctx->status, 0, 256));
+    ctx->tsync = reinterpret_cast<uint32_t*>(ctx->status) + 16;
+    const char* env = getenv("LQ4_DISABLE_PDL");
+    if (env && env[0] == '1') ctx->pdl = 0;
+    *out = ctx;
+    return lq4_ctx_reserve(ctx, 16, 32768, 32768, 128);
+}
+
+void lq4_ctx_destroy(lq4_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->sx, &ctx->t, &ctx->tpart, &ctx->partials, &ctx->tickets, &ctx->hx,
+                   &ctx->hy, &ctx->gemm})
+        if (b->p) cudaFree(b->p);
+    if (ctx->status) cudaFree(ctx->status);
+    delete ctx;
+}
+
+lq4_status lq4_ctx_reserve(lq4_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t rank) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    LQ4_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t s = 0;
+    const uint32_t mm = m < 16 ? m : 16;
+    const uint32_t nt = (2 * mm + 7) / 8, kb = k / 32;
+    const size_t G = ctx->sm_count;
+    lq4_status st;
+    if ((st = ensure(ctx, ctx->xrot, (size_t)m * k * 4, false, s))) return st;
+    if ((st = ensure(ctx, ctx->xs, (size_t)kb * nt * 8 * 64, false, s))) return st;
+    if ((st = ensure(ctx, ctx->sx, (size_t)kb * nt * 16, false, s))) return st;
+    if ((st = ensure(ctx, ctx->t, (size_t)m * rank * 4 + 256, false, s))) return st;
+    if ((st = ensure(ctx, ctx->tpart, G * 4 * (size_t)(rank ? rank : 1) * 4, false, s))) return st;
+    if ((st = ensure(ctx, ctx->partials, G * 2 * kGemvTileRows * nt * 4 * 4, false, s))) return st;
+    if ((st = ensure(ctx, ctx->tickets, ((size_t)n + 127) / 128 * 8 * 4, true, s))) return st;
+    if ((st = ensure(ctx, ctx->hx, (size_t)m * k * 4, false, s))) return st;
+    if ((st = ensure(ctx, ctx->hy, (size_t)m * n * 4, false, s))) return st;
+    if (m > 16) {
+        const size_t need = gemm_workspace_bytes(m, n, k, rank);
+        if ((st = ensure(ctx, ctx->gemm, need, false, s))) return st;
+    }
+    return LQ4_OK;
+}
+
+lq4_status lq4_ctx_check(lq4_ctx* ctx, void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    cudaStream_t s = (cudaStream_t)stream;
+    int32_t h = 0;
+    LQ4_CUDA(cudaMemcpyAsync(&h, ctx->status, 4, cudaMemcpyDeviceToHost, s));
+    LQ4_CUDA(cudaStreamSynchronize(s));
+    if (h != 0) {
+        cudaMemsetAsync(ctx->status, 0, 4, s);
+        cudaStreamSynchronize(s);
+        return fail(LQ4_ERR_DEVICE, "kernel reported a failed bounded wait, status bits " + std::to_string(h));
+    }
+    return LQ4_OK;
+}
+
+uint64_t lq4_ctx_launch_count(const lq4_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    lq4_status st = validate_linear(a);
+    if (st) return st;
+    if (a->m == 0 || a->n == 0) return LQ4_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint64_t ldy = a->ldy ? a->ldy : a->n;
+    const uint32_t rank = a->lora ? a->lora->rank : 0;
+
+    const bool fast_layout = (a->k % 128 == 0) && aligned(a->w, 16) && aligned(a->x, 16) && rank <= kGemvMaxRank;
+    int path = a->path;
+    if (path == LQ4_PATH_AUTO) {
+        if (!fast_layout) path = LQ4_PATH_GEMV_GENERIC;
+        else if (a->m <= kGemvMaxM) path = LQ4_PATH_GEMV_MMA;
+        else path = gemm_supported(a->m, a->n, a->k, rank) ? LQ4_PATH_GEMM_TC : LQ4_PATH_GEMV_MMA;
+    }
+    if (path != LQ4_PATH_GEMV_GENERIC && !fast_layout)
+        return fail(LQ4_ERR_ALIGN, "fast paths need k % 128 == 0, 16-byte aligned w and x, rank <= 128");
+
+    const void* x = a->x;
+    int x_dtype = a->x_dtype;
+    const float* signs = a->rot ? a->rot->signs : nullptr;
+
+    // The decode kernel rotates in its own prologue when the row fits; otherwise the
+    // rotation runs as a kernel of its own into the workspace.
+    const bool in_kernel_rot = signs && path == LQ4_PATH_GEMV_MMA && a->m <= kGemvMaxM &&
+                               gemv_resident_fits(a->m, a->k, true);
+    if (signs && !in_kernel_rot) {
+        if ((st = ensure(ctx, ctx->xrot, (size_t)a->m * a->k * 4, false, s))) return st;
+        LQ4_CUDA(launch_hadamard_rows(x, x_dtype, signs, a->k, a->m, (float*)ctx->xrot.p, s));
+        ctx->launches += 1;
+        x = ctx->xrot.p;
+        x_dtype = LQ4_DTYPE_F32;
+        signs = nullptr;
+    }
+
+    if (path == LQ4_PATH_GEMV_MMA) {
+        for (uint32_t m0 = 0; m0 < a->m; m0 += kGemvMaxM) {
+            const uint32_t mc = a->m - m0 < (uint32_t)kGemvMaxM ? a->m - m0 : (uint32_t)kGemvMaxM;
+            const size_t esz = x_dtype == LQ4_DTYPE_F32 ? 4 : 2;
+            const void* xc = static_cast<const uint8_t*>(x) + (size_t)m0 * a->k * esz;
+            if ((st = run_gemv_mma(ctx, a, xc, x_dtype, signs, mc, a->y + (size_t)m0 * ldy, ldy, s))) return st;
+        }
+        return LQ4_OK;
+    }
+    if (path == LQ4_PATH_GEMM_TC) {
+        if (!gemm_supported(a->m, a->n, a->k, rank)) return fail(LQ4_ERR_UNSUPPORTED, "shape not handled by the tensor-core kernel");
+        const size_t need = gemm_workspace_bytes(a->m, a->n, a->k, rank);
+        if ((st = ensure(ctx, ctx->gemm, need, false, s))) return st;
+        int launches = 0;
+        std::string err;
+        cudaError_t e = launch_gemm_tc(x, x_dtype, a->w, a->y, ldy, a->m, a->n, a->k,
+                                       a->lora ? a->lora->a : nullptr, a->lora ? a->lora->b : nullptr, rank,
+                                       a->lora ? a->lora->scale : 0.0f, ctx->gemm.p, ctx->gemm.cap, ctx->status,
+                                       ctx->sm_count, s, &launches, &err);
+        ctx->launches += launches;
+        if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, "tensor-core GEMM: " + err + ": " + cudaGetErrorString(e));
+        return LQ4_OK;
+    }
+    // generic
+    const float* t = nullptr;
+    if (rank) {
+        if ((st = ensure(ctx, ctx->t, (size_t)a->m * rank * 4, false, s))) return st;
+        launch_lora_t(x, x_dtype, a->m, a->k, a->lora->a, rank, (float*)ctx->t.p, s);
+        ctx->launches += 1;
+        t = (const float*)ctx->t.p;
+    }
+    launch_gemv_generic(x, x_dtype, a->w, a->y, ldy, a->m, a->n, a->k, t, a->lora ? a->lora->b : nullptr, rank,
+                        a->lora ? a->lora->scale : 0.0f, 0, s);
+    ctx->launches += 1;
+    LQ4_CUDA(cudaGetLastError());
+    return LQ4_OK;
+}
+
+lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (!a) return fail(LQ4_ERR_NULL, "args is NULL");
+    if (a->m == 0 || a->n == 0) return LQ4_OK;
+    if (!a->x || !a->y) return fail(LQ4_ERR_NULL, "x and y must be non-NULL");
+    if (a->k == 0 || a->k % 32 != 0) return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t esz = a->x_dtype == LQ4_DTYPE_BF16 ? 2 : 4;
+    const size_t xbytes = (size_t)a->m * a->k * esz, ybytes = (size_t)a->m * a->n * 4;
+    lq4_status st;
+    if ((st = ensure(ctx, ctx->hx, xbytes, false, s))) return st;
+    if ((st = ensure(ctx, ctx->hy, ybytes, false, s))) return st;
+    LQ4_CUDA(cudaMemcpyAsync(ctx->hx.p, a->x, xbytes, cudaMemcpyHostToDevice, s));
+    lq4_linear_args d = *a;
+    d.x = ctx->hx.p;
+    d.y = (float*)ctx->hy.p;
+    d.ldy = a->n;
+    if ((st = lq4_linear(ctx, &d, stream))) return st;
+    const uint64_t ldy = a->ldy ? a->ldy : a->n;
+    if (ldy == a->n) {
+        LQ4_CUDA(cudaMemcpyAsync(a->y, ctx->hy.p, ybytes, cudaMemcpyDeviceToHost, s));
+    } else {
+        LQ4_CUDA(cudaMemcpy2DAsync(a->y, ldy * 4, ctx->hy.p, (size_t)a->n * 4, (size_t)a->n * 4, a->m,
+                                   cudaMemcpyDeviceToHost, s));
+    }
+    LQ4_CUDA(cudaStreamSynchronize(s));
+    return LQ4_OK;
+}
+
+lq4_status lq4_lora_apply(lq4_ctx* ctx, const void* x, int32_t x_dtype, uint32_t m, uint32_t k, float* y, uint32_t n,
+                          uint64_t ldy, const lq4_lora_desc* lora, void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (!lora) return LQ4_OK;   // no adapter for this projection: no-op, as in the reference
+    if (m == 0 || n == 0) return LQ4_OK;
+    if (!x || !y || !lora->a || !lora->b) return fail(LQ4_ERR_NULL, "x, y and the LoRA factors must be non-NULL");
+    if (lora->rank == 0 || !std::isfinite(lora->scale)) return fail(LQ4_ERR_LORA, "rank 0 or non-finite scale");
+    if (k == 0) return fail(LQ4_ERR_K, "k must be non-zero");
+    if (x_dtype != LQ4_DTYPE_F32 && x_dtype != LQ4_DTYPE_BF16) return fail(LQ4_ERR_DTYPE, "unknown x_dtype");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (ldy == 0) ldy = n;
+    lq4_status st;
+    if ((st = ensure(ctx, ctx->t, (size_t)m * lora->rank * 4, false, s))) return st;
+    launch_lora_t(x, x_dtype, m, k, lora->a, lora->rank, (float*)ctx->t.p, s);
+    launch_gemv_generic(x, x_dtype, nullptr, y, ldy, m, n, k, (const float*)ctx->t.p, lora->b, lora->rank,
+                        lora->scale, 1, s);
+    ctx->launches += 2;
+    LQ4_CUDA(cudaGetLastError());
+    return LQ4_OK;
+}
+
+lq4_status lq4_dequant_f32(const uint8_t* payload, uint64_t n_blocks, float* out, void* stream) {
+    if (n_blocks == 0) return LQ4_OK;
+    if (!payload || !out) return fail(LQ4_ERR_NULL, "payload and out must be non-NULL");
+    if (!aligned(payload, 4) || !aligned(out, 16)) return fail(LQ4_ERR_ALIGN, "payload needs 4-byte, out 16-byte alignment");
+    int dev = 0, sms = 0;
+    LQ4_CUDA(cudaGetDevice(&dev));
+    LQ4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    launch_dequant(payload, n_blocks, out, sms, (cudaStream_t)stream);
+    LQ4_CUDA(cudaGetLastError());
+    return LQ4_OK;
+}
+
+lq4_status lq4_quantize_f32(const float* data, uint64_t len, int32_t mode, uint8_t* payload, int32_t* status_out,
+                            void* stream) {
+    if (len == 0) return LQ4_OK;
+    if (!data || !payload) return fail(LQ4_ERR_NULL, "data and payload must be non-NULL");
+    if (mode != LQ4_QUANT_ASYMMETRIC && mode != LQ4_QUANT_SYMMETRIC) return fail(LQ4_ERR_UNSUPPORTED, "unknown mode");
+    if (!aligned(payload, 4) || !aligned(data, 4)) return fail(LQ4_ERR_ALIGN, "data and payload need 4-byte alignment");
+    int dev = 0, sms = 0;
+    LQ4_CUDA(cudaGetDevice(&dev));
+    LQ4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    launch_quantize(data, len, mode == LQ4_QUANT_SYMMETRIC, payload, status_out, sms, (cudaStream_t)stream);
+    LQ4_CUDA(cudaGetLastError());
+    return LQ4_OK;
+}
+
+lq4_status lq4_hadamard_rows(const float* x, float* out, uint32_t rows, const lq4_rot_desc* rot, void* stream) {
+    if (rows == 0) return LQ4_OK;
+    if (!x || !out || !rot || !rot->signs) return fail(LQ4_ERR_NULL, "x, out and rot->signs must be non-NULL");
+    if (!is_pow2(rot->dim) || rot->dim > 16384) return fail(LQ4_ERR_ROT, "rotation needs a power-of-two dim <= 16384");
+    LQ4_CUDA(launch_hadamard_rows(x, LQ4_DTYPE_F32, rot->signs, rot->dim, rows, out, (cudaStream_t)stream));
+    return LQ4_OK;
+}
+
+lq4_status lq4_rot_signs_from_seed(uint64_t seed, uint32_t dim, float* signs, void* stream) {
+    if (dim == 0) return LQ4_OK;
+    if (!signs) return fail(LQ4_ERR_NULL, "signs is NULL");
+    launch_rot_signs(seed, dim, signs, (cudaStream_t)stream);
+    LQ4_CUDA(cudaGetLastError());
+    return LQ4_OK;
+}
+
+// ---- resident objects ---------------------------------------------------------
+
+static float f16_bits_to_f32_host(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 0x1f, f = h & 0x3ff;
+    uint32_t bits;
+    if (e == 0) {
+        if (f == 0) bits = sign;
+        else {
+            int ue = -14;
+            uint32_t m = f;
+            while (!(m & 0x400)) { m <<= 1; --ue; }
+            bits = sign | ((uint32_t)(ue + 127) << 23) | ((m & 0x3ff) << 13);
+        }
+    } else if (e == 0x1f) bits = sign | 0x7f800000u | (f << 13);
+    else bits = sign | ((e + 112) << 23) | (f << 13);
+    float v;
+    memcpy(&v, &bits, 4);
+    return v;
+}
+
+static lq4_status check_blocks(const uint8_t* payload, uint64_t n_blocks) {
+    for (uint64_t b = 0; b < n_blocks; ++b) {
+        uint16_t sb, bb;
+        memcpy(&sb, payload + b * 20, 2);
+        memcpy(&bb, payload + b * 20 + 2, 2);
+        const float sc = f16_bits_to_f32_host(sb), bi = f16_bits_to_f32_host(bb);
+        if (!(std::isfinite(sc) && sc > 0.0f) || !std::isfinite(bi))
+            return fail(LQ4_ERR_BAD_BLOCK, "block " + std::to_string(b) + " has a non-finite or non-positive scale, or a non-finite bias");
+    }
+    return LQ4_OK;
+}
+
+lq4_status lq4_weights_upload(const uint8_t* h_payload, uint64_t n, uint64_t k, lq4_weights** out) {
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    *out = nullptr;
+    if (!h_payload) return fail(LQ4_ERR_NULL, "payload is NULL");
+    if (k == 0 || k % 32 != 0) return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32");
+    if (n == 0) return fail(LQ4_ERR_SHAPE, "n must be non-zero");
+    if (mul_overflows(n, k / 32, ((uint64_t)1 << 40) / 20)) return fail(LQ4_ERR_OVERFLOW, "payload too large");
+    const uint64_t nb = n * (k / 32);
+    lq4_status st = check_blocks(h_payload, nb);   // before the bytes are published to the GPU
+    if (st) return st;
+    lq4_weights* w = new lq4_weights();
+    w->rows = n; w->cols = k;
+    cudaGetDevice(&w->device);
+    cudaError_t e = cudaMalloc(&w->payload, nb * 20 + 256);
+    if (e == cudaSuccess) e = cudaMemcpy(w->payload, h_payload, nb * 20, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (w->payload) cudaFree(w->payload);
+        delete w;
+        return cuda_fail(e, "weights upload");
+    }
+    *out = w;
+    return LQ4_OK;
+}
+
+lq4_status lq4_weights_load_q4_file(const char* h_path, const uint64_t* h_expected_shape, uint32_t expected_ndim,
+                                    lq4_weights** out) {
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    *out = nullptr;
+    if (!h_path) return fail(LQ4_ERR_NULL, "path is NULL");
+    FILE* f = fopen(h_path, "rb");
+    if (!f) return fail(LQ4_ERR_IO, std::string("cannot open ") + h_path);
+    std::vector<uint8_t> img;
+    fseek(f, 0, SEEK_END);
+    const long len = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    if (len < 0) { fclose(f); return fail(LQ4_ERR_IO, "cannot size file"); }
+    img.resize((size_t)len);
+    const size_t got = len ? fread(img.data(), 1, (size_t)len, f) : 0;
+    fclose(f);
+    if (got != (size_t)len) return fail(LQ4_ERR_IO, "short read");
+    if (img.size() < 12 || memcmp(img.data(), "KHQ4", 4) != 0) return fail(LQ4_ERR_FORMAT, "invalid magic: not a .q4 file");
+    uint32_t ver, ndim;
+    memcpy(&ver, img.data() + 4, 4);
+    memcpy(&ndim, img.data() + 8, 4);
+    if (ver == 1) return fail(LQ4_ERR_FORMAT, "legacy .q4 file (v1 symmetric 18-byte blocks): re-quantize");
+    if (ver != 2) return fail(LQ4_ERR_FORMAT, "unsupported .q4 version " + std::to_string(ver));
+    if (ndim == 0 || ndim > 8 || img.size() < 20 + 8ull * ndim) return fail(LQ4_ERR_FORMAT, "bad ndim or truncated header");
+    std::vector<uint64_t> shape(ndim);
+    uint64_t prod = 1;
+    for (uint32_t i = 0; i < ndim; ++i) {
+        memcpy(&shape[i], img.data() + 12 + 8 * i, 8);
+        if (mul_overflows(prod, shape[i], (uint64_t)1 << 48)) return fail(LQ4_ERR_OVERFLOW, "shape product overflows");
+        prod *= shape[i];
+    }
+    uint64_t original_len;
+    memcpy(&original_len, img.data() + 12 + 8 * ndim, 8);
+    const uint64_t off = 20 + 8ull * ndim, nb = (original_len + 31) / 32;
+    if (prod != original_len) return fail(LQ4_ERR_SHAPE, "shape product does not equal original_len");
+    if (img.size() < off + nb * 20) return fail(LQ4_ERR_FORMAT, "file truncated below the Q4 block payload");
+    if (img.size() > off + nb * 20) return fail(LQ4_ERR_FORMAT, "file has trailing bytes after the Q4 block payload");
+    if (expected_ndim) {
+        if (expected_ndim != ndim) return fail(LQ4_ERR_SHAPE, "rank differs from the expected shape");
+        for (uint32_t i = 0; i < ndim; ++i)
+            if (h_expected_shape[i] != shape[i]) return fail(LQ4_ERR_SHAPE, "shape differs from the expected shape");
+    }
+    if (ndim != 2) return fail(LQ4_ERR_UNSUPPORTED, "a linear layer needs a 2-D tensor");
+    if (shape[1] == 0 || shape[1] % 32 != 0) return fail(LQ4_ERR_K, "row length must be a non-zero multiple of 32");
+    return lq4_weights_upload(img.data() + off, shape[0], shape[1], out);
+}
+
+const uint8_t* lq4_weights_payload(const lq4_weights* w) { return w ? w->payload : nullptr; }
+uint64_t lq4_weights_rows(const lq4_weights* w) { return w ? w->rows : 0; }
+uint64_t lq4_weights_cols(const lq4_weights* w) { return w ? w->cols : 0; }
+void lq4_weights_free(lq4_weights* w) {
+    if (!w) return;
+    if (w->payload) cudaFree(w->payload);
+    delete w;
+}
+
+lq4_status lq4_lora_upload(const float* h_a, uint64_t a_len, const float* h_b, uint64_t b_len, uint64_t rank,
+                           uint64_t d_in, uint64_t d_out, float scale, lq4_lora** out) {
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    *out = nullptr;
+    if (!h_a || !h_b) return fail(LQ4_ERR_NULL, "A and B must be non-NULL");
+    if (!std::isfinite(scale)) return fail(LQ4_ERR_LORA, "scale must be finite");
+    if (rank == 0) return fail(LQ4_ERR_LORA, "rank=0");
+    if (d_in == 0 || d_out == 0) return fail(LQ4_ERR_LORA, "zero dimension");
+    if (rank > UINT32_MAX || d_in > UINT32_MAX || d_out > UINT32_MAX) return fail(LQ4_ERR_OVERFLOW, "rank, d_in or d_out exceeds u32");
+    if (mul_overflows(rank, d_in, UINT64_MAX / 4) || mul_overflows(d_out, rank, UINT64_MAX / 4))
+        return fail(LQ4_ERR_OVERFLOW, "rank*d_in or d_out*rank overflows");
+    if (a_len != rank * d_in) return fail(LQ4_ERR_LORA, "A length != rank*d_in");
+    if (b_len != d_out * rank) return fail(LQ4_ERR_LORA, "B length != d_out*rank");
+    lq4_lora* l = new lq4_lora();
+    l->rank = rank; l->d_in = d_in; l->d_out = d_out; l->scale = scale;
+    cudaError_t e = cudaMalloc(&l->a, a_len * 4);
+    if (e == cudaSuccess) e = cudaMalloc(&l->b, b_len * 4);
+    if (e == cudaSuccess) e = cudaMemcpy(l->a, h_a, a_len * 4, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(l->b, h_b, b_len * 4, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        lq4_lora_free(l);
+        return cuda_fail(e, "lora upload");
+    }
+    *out = l;
+    return LQ4_OK;
+}
+
+lq4_status lq4_lora_desc_for_rows(const lq4_lora* l, uint64_t n0, uint64_t n1, lq4_lora_desc* desc) {
+    if (!l || !desc) return fail(LQ4_ERR_NULL, "lora and desc must be non-NULL");
+    if (n0 > n1 || n1 > l->d_out) return fail(LQ4_ERR_SHAPE, "row range outside [0, d_out]");
+    desc->a = l->a;
+    desc->b = l->b + n0 * l->rank;
+    desc->rank = (uint32_t)l->rank;
+    desc->scale = l->scale;
+    return LQ4_OK;
+}
+
+void lq4_lora_free(lq4_lora* l) {
+    if (!l) return;
+    if (l->a) cudaFree(l->a);
+    if (l->b) cudaFree(l->b);
+    delete l;
+}
+
+lq4_status lq4_shard_plan(uint64_t n, uint64_t k, uint32_t world, uint32_t rank, uint64_t* n0, uint64_t* n1,
+                          uint64_t* byte_offset) {
+    if (!n0 || !n1 || !byte_offset) return fail(LQ4_ERR_NULL, "output pointers must be non-NULL");
+    if (world == 0 || rank >= world) return fail(LQ4_ERR_SHAPE, "rank must be below world");
+    if (k == 0 || k % 32 != 0) return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32");
+    *n0 = n * rank / world;
+    *n1 = n * (rank + 1) / world;
+    *byte_offset = *n0 * (k / 32) * 20;
+    return LQ4_OK;
+}
+
+}  // extern "C"

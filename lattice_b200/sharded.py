@@ -1,0 +1,61 @@
+"""Column-parallel N-sharding of one Q4 linear over the ranks of a process group.
+
+Output rows are independent and every row's blocks are contiguous, so rank r of G owns
+rows ``[r*n/G, (r+1)*n/G)``: a byte range of the payload (the ``qw_extra_offset``
+addressing of the reference's ``dispatch_gemm_q4_at``,
+crates/inference/src/forward/metal_qwen35/inner/dispatch.rs:1037-1097) plus the same
+rows of LoRA ``B``.  Activations, LoRA ``A`` and the rotation signs are replicated.  The
+only exchange step is the all-gather of the output slices.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+def shard_plan(n: int, k: int, world: int, rank: int) -> Tuple[int, int, int]:
+    """(n0, n1, payload byte offset) of `rank`'s row range; validated by the library."""
+    n0, n1, off = C.c_uint64(), C.c_uint64(), C.c_uint64()
+    _lib.check(_lib.lib().lq4_shard_plan(n, k, world, rank, C.byref(n0), C.byref(n1), C.byref(off)))
+    return int(n0.value), int(n1.value), int(off.value)
+
+
+class ShardedLinear:
+    """Runs ``compute(x) -> y_local[m, n1 - n0]`` on this rank and gathers ``y[m, n]`` on every rank."""
+
+    def __init__(self, n: int, k: int, compute: Callable[[torch.Tensor], torch.Tensor],
+                 group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n, self.k = n, k
+        self.n0, self.n1, self.byte_offset = shard_plan(n, k, self.world, self.rank)
+        self.sizes: List[int] = []
+        for r in range(self.world):
+            a, b, _ = shard_plan(n, k, self.world, r)
+            self.sizes.append(b - a)
+        self.compute = compute
+        self._gather_buf: Optional[torch.Tensor] = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y_local = self.compute(x)
+        m = y_local.shape[0]
+        assert y_local.shape[1] == self.n1 - self.n0
+        if self.world == 1:
+            return y_local
+        if len(set(self.sizes)) == 1:
+            # equal shards: one all_gather into a [world, m, n/world] buffer, then a strided view
+            if self._gather_buf is None or self._gather_buf.shape[1] != m:
+                self._gather_buf = torch.empty((self.world, m, self.sizes[0]), dtype=y_local.dtype, device=y_local.device)
+            dist.all_gather_into_tensor(self._gather_buf, y_local.contiguous(), group=self.group)
+            if m == 1:
+                return self._gather_buf.view(1, self.n)
+            return self._gather_buf.permute(1, 0, 2).reshape(m, self.n)
+        parts = [torch.empty((m, s), dtype=y_local.dtype, device=y_local.device) for s in self.sizes]
+        dist.all_gather(parts, y_local.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)

@@ -1,0 +1,124 @@
+"""No-GPU checks of the C ABI: the library loads, exports every symbol the header declares,
+and rejects bad arguments before touching the device."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+import oracle
+from lattice_b200 import _lib, build as lq4_build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    lq4_build.build()
+    return _lib.lib()
+
+
+def test_header_symbols_all_exported(L):
+    hdr = open(os.path.join(ROOT, "include", "lattice_q4.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)          # declarations only, not prose
+    declared = set(re.findall(r"\b(lq4_[a-z0-9_]+)\s*\(", hdr))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    for name in declared:
+        assert getattr(L, name) is not None
+    assert L.lq4_abi_version() >= 1
+
+
+def test_shard_plan(L):
+    n0, n1, off = C.c_uint64(), C.c_uint64(), C.c_uint64()
+    for n, k in [(17408, 5120), (5120, 17408), (1024, 5120), (11008, 4096), (3584, 1024), (100, 64)]:
+        prev = 0
+        for world in (1, 2, 4, 8):
+            prev = 0
+            for r in range(world):
+                assert L.lq4_shard_plan(n, k, world, r, C.byref(n0), C.byref(n1), C.byref(off)) == _lib.OK
+                assert n0.value == prev and n1.value == n * (r + 1) // world
+                assert off.value == n0.value * (k // 32) * 20
+                prev = n1.value
+            assert prev == n
+    assert L.lq4_shard_plan(64, 64, 0, 0, C.byref(n0), C.byref(n1), C.byref(off)) == _lib.ERR_SHAPE
+    assert L.lq4_shard_plan(64, 64, 2, 2, C.byref(n0), C.byref(n1), C.byref(off)) == _lib.ERR_SHAPE
+    assert L.lq4_shard_plan(64, 48, 2, 0, C.byref(n0), C.byref(n1), C.byref(off)) == _lib.ERR_K
+    assert L.lq4_shard_plan(64, 64, 2, 0, None, C.byref(n1), C.byref(off)) == _lib.ERR_NULL
+
+
+def test_lora_upload_validation_happens_before_any_copy(L):
+    a = np.zeros(8, np.float32)
+    b = np.zeros(8, np.float32)
+    h = C.c_void_p()
+    pa, pb = a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p)
+    up = L.lq4_lora_upload
+    assert up(pa, 8, pb, 8, 0, 4, 4, 1.0, C.byref(h)) == _lib.ERR_LORA           # rank 0
+    assert up(pa, 8, pb, 8, 2, 0, 4, 1.0, C.byref(h)) == _lib.ERR_LORA           # zero dim
+    assert up(pa, 8, pb, 8, 2, 4, 4, float("nan"), C.byref(h)) == _lib.ERR_LORA  # non-finite scale
+    assert up(pa, 7, pb, 8, 2, 4, 4, 1.0, C.byref(h)) == _lib.ERR_LORA           # A length
+    assert up(pa, 8, pb, 9, 2, 4, 4, 1.0, C.byref(h)) == _lib.ERR_LORA           # B length
+    assert up(pa, 8, pb, 8, 2 ** 33, 4, 4, 1.0, C.byref(h)) == _lib.ERR_OVERFLOW
+    assert up(None, 8, pb, 8, 2, 4, 4, 1.0, C.byref(h)) == _lib.ERR_NULL
+    assert h.value is None
+    assert b"rank" in L.lq4_last_error() or L.lq4_last_error() != b""
+
+
+def test_weights_upload_rejects_bad_blocks_on_the_host(L):
+    w = (np.random.default_rng(0).standard_normal(64 * 4) * 0.02).astype(np.float32)
+    p = oracle.quantize_f32_to_q4(w)
+    h = C.c_void_p()
+    bad = p.copy()
+    bad[2 * 20:2 * 20 + 2] = 0                      # scale == 0
+    assert L.lq4_weights_upload(bad.ctypes.data_as(C.c_void_p), 4, 64, C.byref(h)) == _lib.ERR_BAD_BLOCK
+    bad = p.copy()
+    bad[5 * 20 + 2:5 * 20 + 4] = np.frombuffer((0x7E00).to_bytes(2, "little"), np.uint8)   # bias NaN
+    assert L.lq4_weights_upload(bad.ctypes.data_as(C.c_void_p), 4, 64, C.byref(h)) == _lib.ERR_BAD_BLOCK
+    assert b"block 5" in L.lq4_last_error()
+    bad = p.copy()
+    bad[20:22] = np.frombuffer((0xBC00).to_bytes(2, "little"), np.uint8)                   # scale -1
+    assert L.lq4_weights_upload(bad.ctypes.data_as(C.c_void_p), 4, 64, C.byref(h)) == _lib.ERR_BAD_BLOCK
+    assert L.lq4_weights_upload(p.ctypes.data_as(C.c_void_p), 4, 48, C.byref(h)) == _lib.ERR_K
+    assert L.lq4_weights_upload(None, 4, 64, C.byref(h)) == _lib.ERR_NULL
+    assert h.value is None
+
+
+def test_q4_file_loader_rejects_malformed_files(L, tmp_path, golden_dir):
+    import json
+    fx = json.load(open(os.path.join(golden_dir, "reference_q4_fixtures.json")))["k_proj"]
+    img = bytes.fromhex(fx["hex"])
+    h = C.c_void_p()
+
+    def load(data, shape=None):
+        p = tmp_path / "t.q4"
+        p.write_bytes(data)
+        if shape is None:
+            return L.lq4_weights_load_q4_file(str(p).encode(), None, 0, C.byref(h))
+        arr = (C.c_uint64 * len(shape))(*shape)
+        return L.lq4_weights_load_q4_file(str(p).encode(), arr, len(shape), C.byref(h))
+
+    assert load(b"KHQ5" + img[4:]) == _lib.ERR_FORMAT
+    assert load(img[:4] + (1).to_bytes(4, "little") + img[8:]) == _lib.ERR_FORMAT      # legacy v1
+    assert load(img[:4] + (3).to_bytes(4, "little") + img[8:]) == _lib.ERR_FORMAT
+    assert load(img[:-1]) == _lib.ERR_FORMAT and b"truncated" in L.lq4_last_error()
+    assert load(img + b"\0") == _lib.ERR_FORMAT and b"trailing" in L.lq4_last_error()
+    assert load(img, (1, 64)) == _lib.ERR_SHAPE
+    assert load(img, (32,)) == _lib.ERR_SHAPE
+    bad = bytearray(img)
+    bad[36:38] = (0).to_bytes(2, "little")                                              # scale == 0
+    assert load(bytes(bad)) == _lib.ERR_BAD_BLOCK
+    assert L.lq4_weights_load_q4_file(b"/nonexistent/x.q4", None, 0, C.byref(h)) == _lib.ERR_IO
+    assert h.value is None
+
+
+def test_entry_points_reject_null_and_bad_shapes_without_a_device(L):
+    assert L.lq4_linear(None, None, None) == _lib.ERR_NULL
+    assert L.lq4_ctx_reserve(None, 1, 1, 32, 0) == _lib.ERR_NULL
+    assert L.lq4_ctx_check(None, None) == _lib.ERR_NULL
+    assert L.lq4_dequant_f32(None, 4, None, None) == _lib.ERR_NULL
+    assert L.lq4_dequant_f32(None, 0, None, None) == _lib.OK
+    assert L.lq4_quantize_f32(None, 0, 0, None, None, None) == _lib.OK
+    assert L.lq4_quantize_f32(None, 32, 0, None, None, None) == _lib.ERR_NULL
+    assert L.lq4_status_string(_lib.ERR_K).startswith(b"k must")
+    assert L.lq4_ctx_launch_count(None) == 0

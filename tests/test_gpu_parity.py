@@ -1,0 +1,307 @@
+"""GPU parity: every result of the CUDA library, called through its C ABI, against the CPU oracle.
+
+Bit-exact for bytes and dequantized weights; |y - y_ref| <= 1e-3 * (|y_ref| + rms(y_ref)) for outputs.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle
+from lattice_b200 import _lib, synth
+from tests._cases import make_case, tol_ratio
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def be():
+    from lattice_b200 import CudaQ4Backend
+    b = CudaQ4Backend(0)
+    yield b
+    b.check_device_status()
+    b.close()
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def run_case(be, case, path=_lib.PATH_AUTO, bf16=False, repeat=1):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    qw = Q4WeightBuf.from_host_payload(case["payload"], case["n"], case["k"])
+    x = dev(case["x"]).to(torch.bfloat16) if bf16 else dev(case["x"])
+    keep = []
+    lora = None
+    if case["lora"] is not None:
+        a, b, s = case["lora"]
+        ad, bd = dev(a), dev(b)
+        keep += [ad, bd]
+        lora = LoraDesc(ad.data_ptr(), bd.data_ptr(), case["rank"], s)
+    rot = None
+    if case["signs"] is not None:
+        sd = dev(case["signs"])
+        keep.append(sd)
+        rot = be.rot_desc(sd)
+    ys = []
+    for _ in range(repeat):
+        y = torch.full((case["m"], case["n"]), float("nan"), dtype=torch.float32, device="cuda")
+        be.dispatch_gemm_q4(x, 0, qw, y, 0, case["m"], case["n"], case["k"], lora=lora, rot=rot, path=path)
+        ys.append(y.cpu().numpy())
+    be.check_device_status()
+    qw.free()
+    return ys if repeat > 1 else ys[0]
+
+
+# ---------------------------------------------------------------- bytes and integers
+def test_dequant_bit_exact(be):
+    w = synth.weights(1, 3584, 1024)
+    p = oracle.quantize_f32_to_q4(w)
+    got = be.dequantize(dev(p), p.size // 20).cpu().numpy()
+    want = oracle.dequantize_q4_to_f32(p)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # arbitrary nibbles with edge metadata: subnormal scale, negative bias, largest finite values
+    rng = np.random.default_rng(7)
+    raw = rng.integers(0, 256, size=(4096, 20), dtype=np.uint8)
+    scales = np.array([0x0001, 0x03FF, 0x0400, 0x3C00, 0x7BFF, 0x2E66], np.uint16)
+    biases = np.array([0x0000, 0x8000, 0xFBFF, 0x7BFF, 0x8001, 0xB800], np.uint16)
+    meta = np.stack([scales[rng.integers(0, 6, 4096)], biases[rng.integers(0, 6, 4096)]], 1)
+    raw[:, :4] = meta.view(np.uint8).reshape(4096, 4)
+    got = be.dequantize(dev(raw.reshape(-1)), 4096).cpu().numpy()
+    want = oracle.dequantize_q4_to_f32(raw.reshape(-1))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("symmetric", [False, True])
+def test_quantize_bit_exact(be, symmetric):
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal(32 * 4000 + 7) * 0.02).astype(np.float32)      # ragged tail of 7
+    w[32 * 5:32 * 6] = 0.0                                                    # zero-range block
+    w[32 * 9:32 * 10] = np.float32(1e-38)                                     # underflowing range
+    w[32 * 11] = 7.0; w[32 * 11 + 1] = -7.0
+    w[32 * 13:32 * 14] = np.float32(0.5) * np.arange(-16, 16, dtype=np.float32)   # exact .5 ties
+    got = be.quantize(dev(w), symmetric).cpu().numpy()
+    want = oracle.quantize_f32_to_q4(w, symmetric)
+    assert got.tobytes() == want.tobytes()
+    bad = w.copy(); bad[100] = np.inf
+    with pytest.raises(_lib.Lq4Error):
+        be.quantize(dev(bad), symmetric)
+    big = np.zeros(64, np.float32); big[3] = 1.0e7                            # scale overflows f16
+    with pytest.raises(_lib.Lq4Error):
+        be.quantize(dev(big), symmetric)
+
+
+def test_golden_q4_files_from_device_quantizer(be, golden_dir):
+    import json, os
+    fxs = json.load(open(os.path.join(golden_dir, "reference_q4_fixtures.json")))
+    for name in ("gate_proj", "k_proj"):
+        fx = fxs[name]
+        n = int(np.prod(fx["shape"]))
+        vals = np.array([float(((i * 37 + fx["seed"] * 13) % 200) - 100) / 4.0 for i in range(n)], np.float32)
+        vals = ((vals.view(np.uint32) >> 16) << 16).view(np.float32)
+        payload = be.quantize(dev(vals)).cpu().numpy()
+        assert oracle.q4_file_bytes(fx["shape"], n, payload) == bytes.fromhex(fx["hex"])
+
+
+def test_hadamard_and_signs_bit_exact(be):
+    for dim, rows in [(32, 3), (4096, 5), (16384, 2), (2, 1)]:
+        signs = oracle.signs_from_seed(synth.QUAROT_DEFAULT_SEED ^ dim, dim)
+        sd = be.rot_signs(synth.QUAROT_DEFAULT_SEED ^ dim, dim)
+        assert np.array_equal(sd.cpu().numpy(), signs)
+        x = synth.activations(5, rows, dim, extra=dim)
+        got = be.hadamard_rows(dev(x), sd).cpu().numpy()
+        want = np.stack([oracle.rh_apply(signs, r) for r in x])
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+# ---------------------------------------------------------------- the linear layer
+def test_config1_decode_no_lora(be):
+    case = make_case(1, 1, 1024, 3584)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+@pytest.mark.parametrize("m", [1, 8])
+def test_config2_lora_r16(be, m):
+    case = make_case(2, m, 1024, 3584, rank=16, alpha=32.0)
+    ys = run_case(be, case, repeat=3)
+    for y in ys:
+        assert tol_ratio(y, case["y_ref"]) <= 1.0
+    assert all(np.array_equal(ys[0], y) for y in ys[1:]), "repeated launches must be bit-identical"
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+@pytest.mark.parametrize("k,n", [(5120, 1024), (17408, 640), (5120, 2176)])
+def test_config3_large_layers_lora(be, m, k, n):
+    case = make_case(3, m, k, n, rank=16, alpha=32.0, extra=k // 7 + n)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+def test_config3_full_size_up_projection(be):
+    case = make_case(3, 1, 5120, 17408, rank=16, alpha=32.0)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_config5_quarot_decode(be, m):
+    case = make_case(5, m, 4096, 1376, quarot=True)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+    # the rotation must matter: without it the answer is far away
+    plain = dict(case, signs=None)
+    assert tol_ratio(run_case(be, plain), case["y_ref"]) > 10.0
+
+
+def test_quarot_with_rotated_adapter(be):
+    case = make_case(5, 2, 1024, 256, rank=8, alpha=16.0, quarot=True, extra=3)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+@pytest.mark.parametrize("m,k,n,rank", [(1, 128, 1, 0), (1, 128, 130, 4), (2, 256, 127, 0), (4, 16384, 128, 16),
+                                         (3, 2048, 300, 5), (5, 384, 129, 128), (16, 128, 257, 3), (9, 640, 64, 0)])
+def test_ragged_shapes_and_split_k(be, m, k, n, rank):
+    case = make_case(9, m, k, n, rank=rank, alpha=2.0 * rank, extra=m * 1000 + n)
+    for path in (_lib.PATH_AUTO, _lib.PATH_GEMV_GENERIC):
+        y = run_case(be, case, path=path)
+        assert tol_ratio(y, case["y_ref"]) <= 1.0, path
+
+
+@pytest.mark.parametrize("m,k,n,rank", [(1, 32, 5, 0), (3, 96, 37, 3), (2, 160, 64, 0), (20, 64, 40, 2)])
+def test_generic_path_takes_any_k_multiple_of_32(be, m, k, n, rank):
+    case = make_case(8, m, k, n, rank=rank, alpha=4.0, extra=k)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+def test_bf16_activations_decode(be):
+    case = make_case(4, 4, 1024, 512, rank=16, alpha=32.0, bf16_x=True)
+    y = run_case(be, case, bf16=True)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+def test_edge_scale_activations(be):
+    # the reference's +-500 activation case (metal_qwen35.rs:23530-23692): relative error far below 2 %
+    case = make_case(7, 2, 1024, 256, x_scale=500.0)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+    assert np.max(np.abs(y - case["y_ref"])) / np.max(np.abs(case["y_ref"])) < 0.02
+
+
+def test_row_slice_addressing_and_strided_output(be):
+    """dispatch_gemm_q4_at: a byte offset into the payload selects a row range (an N-shard)."""
+    from lattice_b200 import Q4WeightBuf
+    case = make_case(6, 2, 1024, 512)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], 512, 1024)
+    x = dev(case["x"])
+    y = torch.zeros((2, 512), dtype=torch.float32, device="cuda")
+    row_bytes = (1024 // 32) * 20
+    # two halves written into one output with ldy = 512 (the fused gate||up pattern)
+    be.dispatch_gemm_q4_at(x, 0, qw, 0, y, 0, 2, 256, 1024, ldy=512)
+    be.dispatch_gemm_q4_at(x, 0, qw, 256 * row_bytes, y, 256 * 4, 2, 256, 1024, ldy=512)
+    assert tol_ratio(y.cpu().numpy(), case["y_ref"]) <= 1.0
+    # x offset: second token only
+    y1 = torch.zeros((1, 512), dtype=torch.float32, device="cuda")
+    be.dispatch_gemm_q4(x, 1024 * 4, qw, y1, 0, 1, 512, 1024)
+    assert tol_ratio(y1.cpu().numpy(), case["y_ref"][1:2]) <= 1.0
+    be.check_device_status()
+
+
+def test_call_site_contract(be):
+    from lattice_b200 import Q4WeightBuf
+    case = make_case(6, 1, 128, 16)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], 16, 128)
+    x = dev(case["x"])
+    y = torch.full((1, 16), 5.0, dtype=torch.float32, device="cuda")
+    be.dispatch_gemm_q4(x, 0, qw, y, 0, 0, 16, 128)          # m == 0: no-op
+    be.dispatch_gemm_q4(x, 0, qw, y, 0, 1, 0, 128)           # n == 0: no-op
+    assert torch.all(y == 5.0)
+    for bad_k in (0, 48, 100):
+        with pytest.raises(ValueError, match="divisible by 32"):
+            be.dispatch_gemm_q4(x, 0, qw, y, 0, 1, 16, bad_k)
+    # the C entry point itself reports the same condition as a status, never aborts
+    args = _lib.LinearArgs(x.data_ptr(), 0, 1, 16, 48, qw.payload_ptr, y.data_ptr(), 0, None, None, 0)
+    assert _lib.lib().lq4_linear(be._ctx, C.byref(args), None) == _lib.ERR_K
+    args = _lib.LinearArgs(x.data_ptr(), 0, 1, 16, 128, qw.payload_ptr, y.data_ptr(), 8, None, None, 0)
+    assert _lib.lib().lq4_linear(be._ctx, C.byref(args), None) == _lib.ERR_SHAPE   # ldy < n
+    be.dispatch_matmul_q4(x, qw, y, 1, 16, 128)              # overwrites, does not accumulate
+    assert tol_ratio(y.cpu().numpy(), case["y_ref"]) <= 1.0
+
+
+def test_lora_adapter_lifecycle_and_standalone_dispatch(be):
+    from lattice_b200 import LoraLayerData
+    k, n, r = 256, 96, 4
+    a, b = synth.lora_factors(2, r, k, n, extra=1)
+    layers = [LoraLayerData(0, "q_proj", a, b, r, k, n)]
+    with pytest.raises(_lib.Lq4Error, match="must not be empty"):
+        be.load_lora_adapter([], 2.0)
+    with pytest.raises(_lib.Lq4Error, match="finite"):
+        be.load_lora_adapter(layers, float("inf"))
+    with pytest.raises(_lib.Lq4Error, match="rank=0"):
+        be.load_lora_adapter([LoraLayerData(0, "q_proj", a, b, 0, k, n)], 2.0)
+    with pytest.raises(_lib.Lq4Error):
+        be.load_lora_adapter([LoraLayerData(0, "q_proj", a[:-1], b, r, k, n)], 2.0)      # A length
+    with pytest.raises(_lib.Lq4Error, match="duplicate"):
+        be.load_lora_adapter(layers + layers, 2.0)
+    with pytest.raises(_lib.Lq4Error, match="num_hidden_layers"):
+        be.load_lora_adapter([LoraLayerData(3, "q_proj", a, b, r, k, n)], 2.0)
+    assert not be.has_lora_adapter()
+    be.load_lora_adapter(layers, 2.0)
+    with pytest.raises(_lib.Lq4Error, match="already loaded"):
+        be.load_lora_adapter(layers, 2.0)
+    x = synth.activations(2, 3, k, extra=5)
+    y0 = synth.activations(2, 3, n, extra=6)
+    y = dev(y0)
+    be.dispatch_lora_if_active(dev(x), 0, y, 0, 0, "k_proj", m=3)      # no projection: no-op
+    assert np.array_equal(y.cpu().numpy(), y0)
+    be.dispatch_lora_if_active(dev(x), 0, y, 0, 0, "q_proj", m=3)
+    want = y0.copy()
+    for i in range(3):
+        oracle.apply_lora(a, b, r, k, n, 2.0, x[i], want[i])
+    assert np.max(np.abs(y.cpu().numpy() - want)) < 1e-5
+    be.unload_lora_adapter()
+    be.dispatch_lora_if_active(dev(x), 0, y, 0, 0, "q_proj", m=3)      # unloaded: no-op
+    assert np.max(np.abs(y.cpu().numpy() - want)) < 1e-5
+
+
+def test_host_buffer_entry_point_matches_device_path(be):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    case = make_case(2, 1, 1024, 3584, rank=16, alpha=32.0)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], 3584, 1024)
+    a, b, s = case["lora"]
+    ad, bd = dev(a), dev(b)
+    lora = LoraDesc(ad.data_ptr(), bd.data_ptr(), 16, s)
+    xh = torch.from_numpy(case["x"]).pin_memory()
+    yh = torch.empty((1, 3584), dtype=torch.float32).pin_memory()
+    be.linear_host(xh.numpy(), qw, yh.numpy(), lora=lora)
+    y_dev = be.linear(dev(case["x"]), qw, lora=lora).cpu().numpy()
+    assert np.array_equal(yh.numpy(), y_dev)
+    assert tol_ratio(yh.numpy(), case["y_ref"]) <= 1.0
+
+
+def test_q4_file_round_trip_to_device(be, tmp_path):
+    from lattice_b200 import Q4WeightBuf
+    case = make_case(1, 1, 256, 64)
+    path = tmp_path / "w.q4"
+    path.write_bytes(oracle.q4_file_bytes([64, 256], 64 * 256, case["payload"]))
+    qw = Q4WeightBuf.from_q4_file(str(path), (64, 256))
+    assert (qw.n, qw.k) == (64, 256)
+    y = be.linear(dev(case["x"]), qw).cpu().numpy()
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+    with pytest.raises(_lib.Lq4Error):
+        Q4WeightBuf.from_q4_file(str(path), (64, 128))
+
+
+def test_launches_are_counted(be):
+    from lattice_b200 import Q4WeightBuf
+    case = make_case(1, 1, 128, 16)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], 16, 128)
+    before = be.launch_count
+    be.linear(dev(case["x"]), qw)
+    assert be.launch_count == before + 1      # m = 1 runs as a single fused kernel
