@@ -1,0 +1,433 @@
+#!/usr/bin/env python
+"""Benchmark of the Q4(+LoRA) linear hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Headline workload (config.workload): the large-layer decode set of BASELINE.json's configs[2]
+- per "layer" the four projections 5120->5120, 5120->1024, 5120->17408, 17408->5120 with Q4
+weights quantized from N(0, 0.02^2) and a LoRA adapter of rank 16 on every projection, one
+token (M = 1) - repeated over `--layers` layers with distinct weights (4 x 131 MB by default,
+several times the 126 MB L2, so every launch streams its weights from HBM).  One step is one
+pass over all of them.  metric = weight-streaming rate in GB/s on ALGORITHMIC bytes
+(payload + LoRA factors + x + y, each once); with N GPUs the output rows of every projection
+are sharded over the ranks and the slices are all-gathered over NCCL.
+
+Data are seeded synthetic tensors of those shapes (no dataset exists for this path).
+The reference arm (--impl reference) times the CPU restatement of the reference's own
+path (pre-dequantized f32 weights -> matmul_bt -> apply_lora) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+
+METRIC = "Q4 linear weight GB/s at M=1 (large-layer decode set, LoRA r=16)"
+UNIT = "GB/s"
+LORA_RANK, LORA_ALPHA = 16, 32.0
+SHAPES = [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)]      # (k, n)
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu
+# capture summarised in profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(m, n, k, rank):
+    return n * (k // 32) * 20 + 4 * rank * (k + n) + m * k * 4 + m * n * 4
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0)), float(d.get("bf16_tflops_sustained", 0)), "measured"
+    return FALLBACK_HBM_GBS, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- reference arm
+def cpu_token_set(threads: int, layer):
+    """One token-set on the CPU oracle: per projection matmul_bt over pre-dequantized f32 weights
+    followed by apply_lora, output rows split over `threads` host threads."""
+    import oracle
+    from concurrent.futures import ThreadPoolExecutor
+
+    def part(job):
+        x, w, a, b, scale, n0, n1, k = job
+        y = oracle.matmul_bt(x, w[n0:n1], 1, k, n1 - n0)
+        out = np.ascontiguousarray(y[0])
+        oracle.apply_lora(a, b[n0:n1], LORA_RANK, k, n1 - n0, scale, x[0], out)
+        return out
+
+    jobs = []
+    for (k, n), (x, w, a, b, scale) in zip(SHAPES, layer):
+        for t in range(threads):
+            jobs.append((x, w, a, b, scale, n * t // threads, n * (t + 1) // threads, k))
+    if threads == 1:
+        return [part(j) for j in jobs]
+    with ThreadPoolExecutor(threads) as ex:
+        return list(ex.map(part, jobs))
+
+
+def make_cpu_layer(seed: int):
+    import oracle
+    rng = np.random.default_rng(seed)
+    layer = []
+    for (k, n) in SHAPES:
+        w = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+        wd = oracle.dequantize_q4_to_f32(oracle.quantize_f32_to_q4(w)).reshape(n, k)   # load-time, untimed
+        x = rng.standard_normal((1, k), dtype=np.float32)
+        a = rng.standard_normal((LORA_RANK, k), dtype=np.float32) * np.float32(0.02)
+        b = rng.standard_normal((n, LORA_RANK), dtype=np.float32) * np.float32(0.02)
+        layer.append((x, wd, a, b, oracle.effective_scale(LORA_RANK, LORA_ALPHA)))
+    return layer
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    threads = os.cpu_count() or 1
+    layer = make_cpu_layer(1)
+    set_bytes = sum(algorithmic_bytes(1, n, k, LORA_RANK) for k, n in SHAPES)
+    for _ in range(args.warmup):
+        cpu_token_set(threads, layer)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_token_set(threads, layer)
+    dt = time.perf_counter() - t0
+    val = set_bytes * args.steps / dt / 1e9
+    sample = (f"each step = one token-set (4 projections, M=1, LoRA r=16) of the workload's {args.layers} layers; "
+              f"weights pre-dequantized to f32 at load as the reference's CPU path holds them; "
+              f"matmul_bt kernel {oracle.matmul_bt_kernel(1, 5120, 5120)}; output rows split over {threads} threads")
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, 1),
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(args, world):
+    return {"workload": "configs[2] large-layer decode set: (5120->5120, 5120->1024, 5120->17408, 17408->5120) "
+                        f"x {args.layers} layers, M={args.m}, Q4 weights ~N(0,0.02^2), LoRA r={LORA_RANK} alpha={LORA_ALPHA:g}",
+            "m": args.m, "layers": args.layers, "lora_rank": LORA_RANK,
+            "parallelism": f"N-sharded column-parallel x{world} + NCCL all-gather" if world > 1 else "single GPU",
+            "l2": "inputs larger than L2: every launch streams distinct weights, "
+                  f"{args.layers * 131.072:.0f} MB of Q4 payload per step per job"}
+
+
+# ----------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from lattice_b200 import CudaQ4Backend, Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    from lattice_b200.sharded import shard_plan
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank)
+    be = CudaQ4Backend(local_rank)
+    m = args.m
+    scale = LORA_ALPHA / LORA_RANK
+
+    # ---- build the synthetic model: every rank holds its row range of every projection
+    layers = []
+    gen = torch.Generator(device=dev)
+    for li in range(args.layers):
+        projs = []
+        for si, (k, n) in enumerate(SHAPES):
+            n0, n1, _ = shard_plan(n, k, world, rank)
+            nl = n1 - n0
+            gen.manual_seed(1000003 * li + 101 * si + 7 * rank + 1)
+            w = torch.randn((nl, k), generator=gen, device=dev, dtype=torch.float32) * 0.02
+            payload = be.quantize(w.reshape(-1))
+            del w
+            gen.manual_seed(5000011 * li + 211 * si + 3)          # A is replicated: same seed on every rank
+            a = torch.randn((LORA_RANK, k), generator=gen, device=dev) * 0.02
+            gen.manual_seed(7000003 * li + 307 * si + 13 * rank + 5)
+            b = torch.randn((nl, LORA_RANK), generator=gen, device=dev) * 0.02
+            projs.append(dict(k=k, n=n, nl=nl, qw=Q4WeightBuf.from_device_payload(payload, nl, k), a=a, b=b,
+                              lora=LoraDesc(a.data_ptr(), b.data_ptr(), LORA_RANK, scale)))
+        layers.append(projs)
+    gen.manual_seed(99)
+    xs = {k: torch.randn((m, k), generator=gen, device=dev) for k in (5120, 17408)}
+    y_local = {si: torch.empty((m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
+    y_full = {si: torch.empty((world, m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
+    torch.cuda.synchronize()
+
+    def step():
+        for projs in layers:
+            for si, p in enumerate(projs):
+                be.dispatch_gemm_q4(xs[p["k"]], 0, p["qw"], y_local[si], 0, m, p["nl"], p["k"], lora=p["lora"])
+                if world > 1:
+                    dist.all_gather_into_tensor(y_full[si], y_local[si])
+
+    # pinned host buffers for the end-to-end variant
+    hx = {k: torch.randn((m, k)).pin_memory() for k in (5120, 17408)}
+    hy = {si: torch.empty((world, m, layers[0][si]["nl"])).pin_memory() for si in range(len(SHAPES))}
+    dx = {k: torch.empty((m, k), device=dev) for k in (5120, 17408)}
+
+    def e2e_step():
+        for projs in layers:
+            for si, p in enumerate(projs):
+                if world == 1:
+                    # the C ABI's host-buffer entry point: H2D of x, kernel, D2H of y, wait
+                    be.linear_host(hx[p["k"]].numpy(), p["qw"], hy[si].numpy().reshape(m, p["nl"]), lora=p["lora"])
+                else:
+                    dx[p["k"]].copy_(hx[p["k"]], non_blocking=True)
+                    be.dispatch_gemm_q4(dx[p["k"]], 0, p["qw"], y_local[si], 0, m, p["nl"], p["k"], lora=p["lora"])
+                    dist.all_gather_into_tensor(y_full[si], y_local[si])
+                    hy[si].copy_(y_full[si], non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = be.launch_count
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, be.launch_count - l0
+
+    per_step_bytes = args.layers * sum(algorithmic_bytes(m, n, k, LORA_RANK) for k, n in SHAPES)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, launches = timed(step, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    be.check_device_status()
+    e2e_ms, _ = timed(e2e_step, max(1, min(args.steps, 20)), 3)
+    e2e_steps = max(1, min(args.steps, 20))
+    be.check_device_status()
+
+    value = per_step_bytes * args.steps / (ms * 1e-3) / 1e9
+    e2e_value = per_step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    hbm_peak, tc_peak, tc_sust, which = measured_peaks()
+    n_lin = args.layers * len(SHAPES)
+    # the step's launches are all the decode kernel (one per projection at m <= 4), so the average
+    # launch duration is the event time over the launches, and algorithmic bytes per launch divide
+    # the same way; per GPU each rank streams 1/world of the bytes
+    avg_launch_us = ms * 1e3 / (args.steps * n_lin)
+    achieved = (per_step_bytes / world) * args.steps / (ms * 1e-3) / 1e9
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32 accumulate over int4 codes x f16-split f32 activations", "data": "synthetic",
+            "config": workload_config(args, world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / e2e_steps,
+                    "h2d_bytes_per_step": int(args.layers * sum(m * k * 4 for k, _ in SHAPES)),
+                    "d2h_bytes_per_step": int(args.layers * sum(m * n * 4 for _, n in SHAPES))},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<1,true> (one launch per projection)",
+                         "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
+                         "avg_launch_us": avg_launch_us, "algorithmic_bytes_per_launch": per_step_bytes / world / n_lin,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+            "clocks": clocks}
+
+    if rank == 0 and world == 1 and not args.no_aux:
+        line["aux"] = aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust)
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(layers[0])
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(gpu_layer):
+    """Times the oracle on the host on ONE token-set built from the first layer's own Q4 payload."""
+    import oracle
+    import torch
+    layer = []
+    for p in gpu_layer:
+        k, n = p["k"], p["nl"]
+        payload = p["qw"]._keep.cpu().numpy()
+        wd = oracle.dequantize_q4_to_f32(payload).reshape(n, k)           # load-time, untimed
+        x = np.random.default_rng(3).standard_normal((1, k), dtype=np.float32)
+        layer.append((x, wd, p["a"].cpu().numpy(), p["b"].cpu().numpy(), LORA_ALPHA / LORA_RANK))
+    set_bytes = sum(algorithmic_bytes(1, n, k, LORA_RANK) for k, n in SHAPES)
+    cpu_token_set(1, layer)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        cpu_token_set(1, layer)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > 12.0 or reps >= 200:
+            break
+    return {"value": set_bytes * reps / dt / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"{reps} repeats of one token-set (4 projections of layer 0, M=1, LoRA r=16), single thread as "
+                      f"the reference's matmul_bt is; kernel {oracle.matmul_bt_kernel(1, 5120, 5120)}; "
+                      f"f32 weights pre-dequantized at load (untimed)", "ms_per_token_set": dt / reps * 1e3}
+
+
+def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
+    """Secondary configurations, each timed with CUDA events over distinct weight copies."""
+    import torch
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    out = {}
+    gen = torch.Generator(device=dev)
+
+    def bench_linear(name, m, k, n, rank, copies, reps, rot=False, x_dtype=torch.float32):
+        qws, keep = [], []
+        for c in range(copies):
+            gen.manual_seed(31 * c + k + n)
+            w = torch.randn((n, k), generator=gen, device=dev) * 0.02
+            payload = be.quantize(w.reshape(-1), symmetric=rot)
+            keep.append(payload)
+            qws.append(Q4WeightBuf.from_device_payload(payload, n, k))
+            del w
+        lora = None
+        if rank:
+            a = torch.randn((rank, k), generator=gen, device=dev) * 0.02
+            b = torch.randn((n, rank), generator=gen, device=dev) * 0.02
+            keep += [a, b]
+            lora = LoraDesc(a.data_ptr(), b.data_ptr(), rank, 2.0)
+        rd = None
+        if rot:
+            signs = be.rot_signs(0xCAFEBABEDEADBEEF, k)
+            keep.append(signs)
+            rd = be.rot_desc(signs)
+        x = torch.randn((m, k), generator=gen, device=dev).to(x_dtype)
+        y = torch.empty((m, n), device=dev)
+        for i in range(3):
+            be.dispatch_gemm_q4(x, 0, qws[i % copies], y, 0, m, n, k, lora=lora, rot=rd)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            be.dispatch_gemm_q4(x, 0, qws[i % copies], y, 0, m, n, k, lora=lora, rot=rd)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        xb = 2 if x_dtype == torch.bfloat16 else 4
+        byts = n * (k // 32) * 20 + 4 * rank * (k + n) + m * k * xb + m * n * 4
+        flops = 2 * m * n * k + 2 * m * rank * (k + n)
+        out[name] = {"us_per_call": us, "GB/s": byts / us / 1e3, "frac_hbm": byts / us / 1e3 / hbm_peak,
+                     "TFLOP/s": flops / us / 1e6, "weight_copies": copies}
+        if m >= 64 and tc_peak:
+            out[name]["frac_bf16_burst"] = flops / us / 1e6 / tc_peak
+            out[name]["frac_bf16_sustained"] = flops / us / 1e6 / tc_sust
+
+    try:
+        bench_linear("config1_M1_K1024_N3584_cold", 1, 1024, 3584, 0, 128, 512)
+        bench_linear("config1_M1_K1024_N3584_warm", 1, 1024, 3584, 0, 1, 512)
+        bench_linear("config2_M1_lora16_cold", 1, 1024, 3584, 16, 128, 512)
+        bench_linear("config2_M8_lora16_cold", 8, 1024, 3584, 16, 128, 512)
+        for mm in (4, 16):
+            for (k, n) in SHAPES:
+                bench_linear(f"config3_M{mm}_{k}to{n}_lora16", mm, k, n, 16, 4, 40)
+        bench_linear("config5_quarot_M1_K4096_N11008", 1, 4096, 11008, 0, 8, 200, rot=True)
+        bench_linear("config4_prefill_M2048_K5120_N17408_lora64_bf16", 2048, 5120, 17408, 64, 1, 5,
+                     x_dtype=torch.bfloat16)
+        bench_linear("config5_quarot_M512_K4096_N11008", 512, 4096, 11008, 0, 1, 5, rot=True)
+    except Exception as e:                                   # an aux failure must not hide the headline
+        out["error"] = repr(e)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--no-aux", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
