@@ -39,6 +39,10 @@ struct Buf {
 
 }  // namespace
 
+namespace lq4 {
+void set_last_error(const char* msg) { g_last_error = msg ? msg : ""; }
+}  // namespace lq4
+
 struct lq4_ctx {
     int device = 0;
     int sm_count = 0;

@@ -6,6 +6,10 @@
 
 namespace lq4 {
 
+// ---- lq4_api.cu ---------------------------------------------------------------
+// Stores the message lq4_last_error() returns on the calling thread.
+void set_last_error(const char* msg);
+
 // ---- lq4_aux.cu ---------------------------------------------------------------
 void launch_dequant(const uint8_t* payload, uint64_t n_blocks, float* out, int sm_count, cudaStream_t s);
 void launch_quantize(const float* data, uint64_t len, int symmetric, uint8_t* payload, int32_t* status,
