@@ -1,0 +1,122 @@
+// lq4_linear_decode_noalloc: the decode projection for callers that must not allocate.
+//
+// Who needs it: an engine that claimed all device memory for its own pool at start-up (a
+// later cudaMalloc fails or eats into another tenant's share), and a latency-critical decode
+// loop in which the device-wide synchronisation hidden inside cudaMalloc/cudaFree would
+// stall every stream.  Neither can create an lq4_ctx, whose workspace lives in cudaMalloc'd
+// buffers.  Here the kernel's scratch (stream-K partial sums and tickets, the LoRA partial
+// exchange, the status word) sits in a fixed array that is part of the loaded module instead.
+#include <cmath>
+#include <mutex>
+
+#include "lq4_kernels.cuh"
+
+namespace {
+
+using namespace lq4;
+
+// Capacity of the built-in scratch.  Every GPU that loads this library holds these bytes
+// until the process exits.
+constexpr uint32_t kNaMaxGrid = 160;        // CTAs (one per SM; B200 has 148)
+constexpr uint32_t kNaMaxM = 4;             // tokens per call
+constexpr uint32_t kNaMaxN = 32768;         // output rows per call
+constexpr uint32_t kNaMaxRank = 64;         // LoRA rank
+constexpr size_t kNaCtrlBytes = 256 + (size_t)(kNaMaxN / kGemvTileRows) * 8 * 4;                  // status, counters, tickets
+constexpr size_t kNaPartialBytes = (size_t)kNaMaxGrid * 2 * kGemvTileRows * 4 * sizeof(float);    // 655,360
+constexpr size_t kNaTpartBytes = (size_t)kNaMaxGrid * kNaMaxM * kNaMaxRank * sizeof(float);       // 163,840
+constexpr size_t kNaScratchBytes = ((kNaCtrlBytes + 255) / 256) * 256 + kNaPartialBytes + kNaTpartBytes;
+
+// In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNaScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mu;
+unsigned char* g_scratch_ptr[kMaxDevices] = {nullptr};
+int g_sm_count[kMaxDevices] = {0};
+
+}  // namespace
+
+// Declared in include/lattice_q4.h.
+extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* stream) {
+    auto fail = [](lq4_status s, const char* msg) {
+        set_last_error(msg);          // read back with lq4_last_error()
+        return s;
+    };
+    if (!a) return fail(LQ4_ERR_NULL, "args is NULL");
+    if (a->m == 0 || a->n == 0) return LQ4_OK;
+    if (a->k == 0 || a->k % 32 != 0) return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32");
+    if (!a->x || !a->w || !a->y) return fail(LQ4_ERR_NULL, "x, w and y must be non-NULL");
+    if (a->x_dtype != LQ4_DTYPE_F32 && a->x_dtype != LQ4_DTYPE_BF16) return fail(LQ4_ERR_DTYPE, "unknown x_dtype");
+    if (a->m > kNaMaxM) return fail(LQ4_ERR_NOSPACE, "lq4_linear_decode_noalloc handles at most 4 tokens per call");
+    if (a->n > kNaMaxN) return fail(LQ4_ERR_NOSPACE, "lq4_linear_decode_noalloc handles at most 32768 output rows per call");
+    const uint32_t rank = a->lora ? a->lora->rank : 0;
+    if (a->lora) {
+        if (!a->lora->a || !a->lora->b || rank == 0 || !std::isfinite(a->lora->scale))
+            return fail(LQ4_ERR_LORA, "invalid LoRA descriptor");
+        if (rank > kNaMaxRank) return fail(LQ4_ERR_NOSPACE, "lq4_linear_decode_noalloc handles LoRA rank up to 64");
+    }
+    if (a->k % 128 != 0 || (reinterpret_cast<uintptr_t>(a->w) & 15) || (reinterpret_cast<uintptr_t>(a->x) & 15) ||
+        (reinterpret_cast<uintptr_t>(a->y) & 3))
+        return fail(LQ4_ERR_ALIGN, "needs k % 128 == 0 and 16-byte aligned w and x");
+    if (a->ldy != 0 && a->ldy < a->n) return fail(LQ4_ERR_SHAPE, "ldy is smaller than n");
+    const float* signs = nullptr;
+    if (a->rot) {
+        if (!a->rot->signs || a->rot->dim != a->k || (a->k & (a->k - 1))) return fail(LQ4_ERR_ROT, "invalid rotation descriptor");
+        signs = a->rot->signs;
+    }
+    if (!gemv_resident_fits(a->m, a->k, signs != nullptr))
+        return fail(LQ4_ERR_NOSPACE, "m * k too large: the activation row(s) must fit in shared memory for this entry point");
+
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return fail(LQ4_ERR_UNSUPPORTED, "device index out of range");
+    unsigned char* base;
+    int sms;
+    {
+        // Set-up, once per device, with that device current: resolve the device address of the array.
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!g_scratch_ptr[dev]) {
+            unsigned char* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
+            int n = 0;
+            e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
+            g_sm_count[dev] = n;
+            g_scratch_ptr[dev] = p;
+        }
+        base = g_scratch_ptr[dev];
+        sms = g_sm_count[dev];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+
+    GemvParams p{};
+    p.w = a->w; p.y = a->y; p.ldy = a->ldy ? a->ldy : a->n;
+    p.m = a->m; p.n = a->n; p.k = a->k;
+    p.kb = a->k / 32; p.kg = p.kb / kGemvGranuleBlocks;
+    p.tiles = (a->n + kGemvTileRows - 1) / kGemvTileRows;
+    p.nt = 1; p.gmax = 2 * a->m;
+    p.x = a->x; p.x_dtype = a->x_dtype; p.signs = signs;
+    if (a->lora) { p.la = a->lora->a; p.lb = a->lora->b; p.rank = rank; p.lscale = a->lora->scale; }
+    const uint64_t total = (uint64_t)p.tiles * p.kg;
+    uint64_t grid = total < (uint64_t)sms ? total : (uint64_t)sms;
+    if (grid > kNaMaxGrid) grid = kNaMaxGrid;
+
+    // carve the array: [status | counters | tickets] [partials] [LoRA partials]
+    p.status = reinterpret_cast<int32_t*>(base);
+    p.tsync = reinterpret_cast<uint32_t*>(base + 64);
+    p.tickets = reinterpret_cast<uint32_t*>(base + 256);
+    unsigned char* q = base + ((kNaCtrlBytes + 255) / 256) * 256;
+    p.partials = reinterpret_cast<float*>(q);
+    p.tpart = reinterpret_cast<float*>(q + kNaPartialBytes);
+    p.use_pdl = 0;
+    // The array keeps whatever the previous call left: the counters and tickets must start at zero.
+    e = cudaMemsetAsync(base, 0, kNaCtrlBytes, s);
+    if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
+    const size_t smem = gemv_plan_smem(p, true);
+    if (!smem) return fail(LQ4_ERR_NOSPACE, "shared-memory plan does not fit");
+    e = launch_gemv_mma(p, true, smem, (int)grid, s);
+    if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
+    return LQ4_OK;
+}

@@ -1,0 +1,94 @@
+"""lq4_linear_decode_noalloc: the entry point for callers that may not allocate device memory
+(an engine that gave all of it to its own pool, or a decode loop that cannot take the
+device-wide synchronisation cudaMalloc implies).  It must give what lq4_linear gives.
+
+Collected last on purpose: a run that stops at the first failure has then already run every
+other test.  The test owns no state from the others and passes alone in a fresh process too.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from lattice_b200 import _lib
+from tests._cases import make_case, tol_ratio
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _run_both(be, case):
+    """Returns (y from lq4_linear, y from lq4_linear_decode_noalloc) for one projection."""
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LinearArgs, LoraDesc, RotDesc
+    L = _lib.lib()
+    qw = Q4WeightBuf.from_host_payload(case["payload"], case["n"], case["k"])
+    x = _dev(case["x"])
+    keep, lora, rot = [], None, None
+    if case["lora"] is not None:
+        a, b, s = case["lora"]
+        ad, bd = _dev(a), _dev(b)
+        keep += [ad, bd]
+        lora = LoraDesc(ad.data_ptr(), bd.data_ptr(), case["rank"], s)
+    if case["signs"] is not None:
+        sd = _dev(case["signs"])
+        keep.append(sd)
+        rot = RotDesc(sd.data_ptr(), sd.numel())
+    stream = torch.cuda.current_stream().cuda_stream
+    m, n, k = case["m"], case["n"], case["k"]
+    y_ref = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    be.dispatch_gemm_q4(x, 0, qw, y_ref, 0, m, n, k, lora=lora, rot=rot)
+    y_new = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    args = LinearArgs(x.data_ptr(), 0, m, n, k, qw.payload_ptr, y_new.data_ptr(), 0,
+                      C.pointer(lora) if lora is not None else None,
+                      C.pointer(rot) if rot is not None else None, 0)
+    _lib.check(L.lq4_linear_decode_noalloc(C.byref(args), stream))
+    torch.cuda.synchronize()
+    be.check_device_status()
+    out = (y_ref.cpu().numpy(), y_new.cpu().numpy())
+    qw.free()
+    return out
+
+
+def test_noalloc_entry_point_matches_lq4_linear_on_two_calls_in_a_row():
+    from lattice_b200 import CudaQ4Backend
+    be = CudaQ4Backend(0)
+    try:
+        # two different shapes back to back: whatever the first call leaves in the shared
+        # scratch (partial sums, tickets, LoRA partials) must not leak into the second
+        cases = [make_case(3, 1, 5120, 1024, rank=16, alpha=32.0, extra=41),      # split-k tiles + LoRA
+                 make_case(5, 2, 1024, 300, rank=8, alpha=16.0, quarot=True, extra=42)]   # rotation, ragged n
+        for rep in range(2):
+            for case in cases:
+                y_old, y_new = _run_both(be, case)
+                assert tol_ratio(y_new, y_old) <= 1.0
+                assert tol_ratio(y_new, case["y_ref"]) <= 1.0
+    finally:
+        be.close()
+
+
+def test_noalloc_entry_point_rejects_what_exceeds_its_fixed_scratch():
+    from lattice_b200._lib import LinearArgs, LoraDesc
+    L = _lib.lib()
+    x = torch.zeros((8, 1024), device="cuda")
+    w = torch.zeros(64 * 32 * 20, dtype=torch.uint8, device="cuda")
+    y = torch.zeros((8, 64), device="cuda")
+
+    def call(m=1, n=64, k=1024, lora=None):
+        args = LinearArgs(x.data_ptr(), 0, m, n, k, w.data_ptr(), y.data_ptr(), 0,
+                          C.pointer(lora) if lora is not None else None, None, 0)
+        return L.lq4_linear_decode_noalloc(C.byref(args), None)
+
+    assert call(m=5) == _lib.ERR_NOSPACE and b"at most 4 tokens" in L.lq4_last_error()
+    assert call(n=40000) == _lib.ERR_NOSPACE
+    assert call(k=32768) == _lib.ERR_NOSPACE          # the activation row no longer fits in shared memory
+    big = LoraDesc(x.data_ptr(), x.data_ptr(), 65, 1.0)
+    assert call(lora=big) == _lib.ERR_NOSPACE
+    assert call(k=96) == _lib.ERR_ALIGN
+    assert call(k=40) == _lib.ERR_K
+    assert call(m=0) == _lib.OK
+    assert L.lq4_linear_decode_noalloc(None, None) == _lib.ERR_NULL
