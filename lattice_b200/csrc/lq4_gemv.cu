@@ -23,82 +23,13 @@
 // the partial projection A x over its own slice of k in the prologue and the CTAs
 // exchange the partials through global memory; in the staged variant a small
 // preparation kernel has produced the activation fragments and t = A x beforehand.
-#include "lq4_kernels.cuh"
+#include "lq4_gemv_common.cuh"
 
 namespace lq4 {
 
 namespace {
 
-constexpr uint32_t kFull = 0xffffffffu;
-constexpr int kConsumerThreads = 256;
-constexpr int kBarConsumers = 1;   // named barrier id used by the 8 consumer warps
-
-__device__ __forceinline__ uint64_t range_begin(uint64_t c, uint64_t total, uint64_t grid) {
-    return (c * total) / grid;
-}
-
-// CTA whose range contains position `pos` (every CTA owns at least one granule).
-__device__ __forceinline__ uint32_t owner_of(uint64_t pos, uint64_t total, uint64_t grid) {
-    uint64_t c = (pos * grid) / total;
-    while (c + 1 < grid && range_begin(c + 1, total, grid) <= pos) ++c;
-    return (uint32_t)c;
-}
-
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-__device__ __forceinline__ uint32_t pack_h2(__half a, __half b) {
-    return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
-}
-
-// Loads eight consecutive activations (16-byte aligned) as f32.
-__device__ __forceinline__ void load8(const void* x, int dtype, size_t idx, float (&v)[8]) {
-    if (dtype == LQ4_DTYPE_BF16) {
-        const uint4 r = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + idx);
-        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            v[2 * i] = __uint_as_float(w[i] << 16);
-            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-        }
-    } else {
-        const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + idx);
-        const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + idx + 4);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    }
-}
-
-// Turns eight activations k = 8o .. 8o+7 of one token into the two 16-byte B-operand
-// fragments (hi limb, lo limb) the consumer threads load, and returns their sum.
-// Fragment order {(k0,k4), (k1,k5), (k2,k6), (k3,k7)} mirrors nibbles_to_h2().
-__device__ __forceinline__ float make_fragments(const float (&v)[8], uint4& fh, uint4& fl) {
-    __half h[8], l[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) split_f16(v[i], h[i], l[i]);
-    fh = make_uint4(pack_h2(h[0], h[4]), pack_h2(h[1], h[5]), pack_h2(h[2], h[6]), pack_h2(h[3], h[7]));
-    fl = make_uint4(pack_h2(l[0], l[4]), pack_h2(l[1], l[5]), pack_h2(l[2], l[6]), pack_h2(l[3], l[7]));
-    return ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-}
-
-// Writes fragments and block sums of token slot `mp` for octet `o` (8 activations).
-// Layout: fragments [kb][nt][gmax columns][4 quads][16 B]; sums [kb][nt][4 tokens].
-__device__ __forceinline__ void store_fragments(uint8_t* xs, float* sx, uint32_t NT, uint32_t gmax, uint32_t mp,
-                                                uint32_t o, bool active, const float (&v)[8]) {
-    uint4 fh, fl;
-    float s = make_fragments(v, fh, fl);
-    s += __shfl_xor_sync(kFull, s, 1);
-    s += __shfl_xor_sync(kFull, s, 2);
-    if (!active) return;
-    const uint32_t kbi = o >> 2, tt = o & 3, ntile = mp >> 2, ghi = (mp & 3) * 2;
-    uint8_t* dst = xs + ((size_t)(kbi * NT + ntile) * gmax + ghi) * 64 + tt * 16;
-    *reinterpret_cast<uint4*>(dst) = fh;
-    *reinterpret_cast<uint4*>(dst + 64) = fl;
-    if (tt == 0) sx[(size_t)(kbi * NT + ntile) * 4 + (mp & 3)] = s;
-}
+using namespace gemv;
 
 // ---------------------------------------------------------------------------
 // Resident-variant prologue, run by the 256 consumer threads: optional Hadamard
@@ -173,7 +104,7 @@ __device__ void resident_prologue(const GemvParams& p, uint8_t* smem, int ctid) 
                     load8(p.x, p.x_dtype, (size_t)mp * K + (size_t)o * 8, v);
                 }
             }
-            store_fragments(xs, sx, NT, p.gmax, mp, o, active, v);
+            store_fragments(xs, sx, NT, p.gmax, mp, o, active, v, NT * 4);
         }
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
@@ -453,6 +384,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
 static inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 size_t gemv_plan_smem(GemvParams& p, bool resident) {
+    if (resident) return decode_plan_smem(p);
     uint32_t off = 128;                       // 2 x 8 mbarriers
     p.off_t = off;
     off += align_up(p.m * p.rank * 4, 128);
@@ -486,13 +418,13 @@ size_t gemv_plan_smem(GemvParams& p, bool resident) {
 }
 
 bool gemv_resident_fits(uint32_t m, uint32_t k, bool rot) {
-    if (m == 0 || m > 4) return false;
+    if (m == 0 || m > 4 || k % 128 != 0) return false;
     GemvParams q{};
-    q.m = m; q.k = k; q.kb = k / 32; q.nt = 1; q.gmax = 2 * m; q.rank = kGemvMaxRank;
+    q.m = m; q.n = 1u << 20; q.k = k; q.kb = k / 32; q.nt = 1; q.gmax = 2 * m; q.rank = kGemvMaxRank;
+    q.tiles = q.n / kGemvTileRows;
     static float dummy;
     q.signs = rot ? &dummy : nullptr;
-    const size_t need = gemv_plan_smem(q, true);
-    return need != 0 && q.nstages >= 3;
+    return decode_plan_smem(q) != 0;
 }
 
 template <int NT, bool RESIDENT>
@@ -518,12 +450,7 @@ static cudaError_t launch_one(const GemvParams& p, size_t smem, int grid, cudaSt
 }
 
 cudaError_t launch_gemv_mma(const GemvParams& p, bool resident, size_t smem, int grid, cudaStream_t s) {
-    if (resident) {
-        switch (p.nt) {
-            case 1: return launch_one<1, true>(p, smem, grid, s);
-            default: return cudaErrorInvalidValue;
-        }
-    }
+    if (resident) return launch_decode(p, smem, grid, s);
     switch (p.nt) {
         case 1: return launch_one<1, false>(p, smem, grid, s);
         case 2: return launch_one<2, false>(p, smem, grid, s);
@@ -545,7 +472,7 @@ __global__ void __launch_bounds__(256) prep_xs_kernel(const void* __restrict__ x
     const bool active = o < k / 8;
     float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (active && mp < m) load8(x, x_dtype, (size_t)mp * k + (size_t)o * 8, v);
-    store_fragments(xs, sx, NT, gmax, mp, o, active, v);
+    store_fragments(xs, sx, NT, gmax, mp, o, active, v, NT * 4);
 }
 
 void launch_prep_xs(const void* x, int x_dtype, uint32_t m, uint32_t k, uint32_t nt, uint32_t gmax, uint8_t* xs_g,

@@ -63,7 +63,19 @@ struct GemvParams {
     // shared-memory offsets (bytes from the dynamic smem base)
     uint32_t off_t, off_stage, stage_bytes, off_stage_xs, off_stage_sx, off_xs, off_sx, off_xrot;
     uint32_t use_pdl;
+    // resident decode kernel (lq4_decode.cu)
+    uint32_t stage_blocks;  // Q4 blocks of one row per pipeline stage: 20, 12 or 4
+    uint32_t spt;           // stages per tile = ceil(kb / stage_blocks)
+    int32_t sm_count;       // 0: plan for a full GPU
 };
+
+// ---- lq4_decode.cu ---------------------------------------------------------------
+// Resident decode kernel (m <= 4): picks the stage length, fills the shared-memory offsets of
+// `p` and returns the dynamic shared memory needed (0 if the activation rows do not fit).
+size_t decode_plan_smem(GemvParams& p);
+// Work units (tile, stage) of a planned launch; the grid is min(#SM, units).
+uint64_t decode_units(const GemvParams& p);
+cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s);
 
 // Fills the smem-dependent fields of `p` and returns the dynamic shared memory the
 // launch needs, or 0 if the shape does not fit the requested variant.
