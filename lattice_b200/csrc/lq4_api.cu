@@ -136,7 +136,7 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
     const uint64_t total = (uint64_t)p.tiles * p.kg;
     const int grid = (int)(total < (uint64_t)ctx->sm_count ? total : (uint64_t)ctx->sm_count);
     lq4_status st;
-    if ((st = ensure(ctx, ctx->partials, (size_t)grid * 2 * kGemvTileRows * p.nt * 4 * sizeof(float), false, s))) return st;
+    if ((st = ensure(ctx, ctx->partials, (size_t)grid * 2 * kGemvTileRows * p.nt * 4 * sizeof(float), true, s))) return st;
     if ((st = ensure(ctx, ctx->tickets, (size_t)p.tiles * 8 * sizeof(uint32_t), true, s))) return st;
     p.partials = (float*)ctx->partials.p;
     p.tickets = (uint32_t*)ctx->tickets.p;
@@ -145,14 +145,17 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
     if (resident) {
         p.x = x; p.x_dtype = x_dtype; p.signs = signs;
         if (p.rank) {
-            if ((st = ensure(ctx, ctx->tpart, (size_t)grid * m * p.rank * sizeof(float), false, s))) return st;
+            if ((st = ensure(ctx, ctx->tpart, (size_t)grid * m * p.rank * 8, true, s))) return st;
             p.tpart = (float*)ctx->tpart.p;
-            p.tsync = ctx->tsync;
         }
+        p.tsync = ctx->tsync;      // launch generation and end-of-launch counter: always needed
         p.use_pdl = ctx->pdl;
+        p.sm_count = ctx->sm_count;
         const size_t smem = gemv_plan_smem(p, true);
         if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "resident plan does not fit");
-        LQ4_CUDA(launch_gemv_mma(p, true, smem, grid, s));
+        const uint64_t units = decode_units(p);
+        const int dgrid = (int)(units < (uint64_t)ctx->sm_count ? units : (uint64_t)ctx->sm_count);
+        LQ4_CUDA(launch_gemv_mma(p, true, smem, dgrid, s));
         ctx->launches += 1;
         return LQ4_OK;
     }
@@ -254,8 +257,8 @@ lq4_status lq4_ctx_reserve(lq4_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uin
     if ((st = ensure(ctx, ctx->xs, (size_t)kb * nt * 8 * 64, false, s))) return st;
     if ((st = ensure(ctx, ctx->sx, (size_t)kb * nt * 16, false, s))) return st;
     if ((st = ensure(ctx, ctx->t, (size_t)m * rank * 4 + 256, false, s))) return st;
-    if ((st = ensure(ctx, ctx->tpart, G * 4 * (size_t)(rank ? rank : 1) * 4, false, s))) return st;
-    if ((st = ensure(ctx, ctx->partials, G * 2 * kGemvTileRows * nt * 4 * 4, false, s))) return st;
+    if ((st = ensure(ctx, ctx->tpart, G * 4 * (size_t)(rank ? rank : 1) * 8, true, s))) return st;
+    if ((st = ensure(ctx, ctx->partials, G * 2 * kGemvTileRows * nt * 4 * 4, true, s))) return st;
     if ((st = ensure(ctx, ctx->tickets, ((size_t)n + 127) / 128 * 8 * 4, true, s))) return st;
     if ((st = ensure(ctx, ctx->hx, (size_t)m * k * 4, false, s))) return st;
     if ((st = ensure(ctx, ctx->hy, (size_t)m * n * 4, false, s))) return st;

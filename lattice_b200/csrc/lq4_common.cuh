@@ -21,18 +21,16 @@ constexpr int kDevErrBarrierTimeout = 1;   // an mbarrier wait hit its time limi
 constexpr int kDevErrGridWaitTimeout = 2;  // waiting for other CTAs' LoRA partials timed out
 constexpr int kDevErrTmem = 4;
 
-// Every device-side wait gives up after this many nanoseconds of %globaltimer.
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+// Every device-side wait gives up after this many SM clock cycles (about two seconds).  The
+// SM-local %clock64 is used because it is cheap to read inside a polling loop.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+__device__ __forceinline__ long long wait_clock() { return clock64(); }
+__device__ __forceinline__ bool wait_expired(long long t0) { return clock64() - t0 > kWaitLimitCycles; }
 
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -62,11 +60,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: returns false (and the caller records an error) once the time limit passes.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    const long long t0 = wait_clock();
     for (;;) {
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+        if (wait_expired(t0)) return false;
     }
 }
 

@@ -37,6 +37,7 @@ constexpr int kBigGranules = kBigBlocks / kGemvGranuleBlocks;    // 5
 constexpr uint32_t kSlotBytes = kGemvTileRows * kBigBlocks * kBlockBytes;      // 51,200
 constexpr uint32_t kSmallBytes = kGemvTileRows * kSmallBlocks * kBlockBytes;   // 10,240
 constexpr int kMaxStages = 8;
+constexpr uint32_t kZeroOffset = 2 * kMaxStages * 8;   // 32 zero bytes after the mbarriers
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
                                             uint64_t* bar, uint64_t policy) {
@@ -47,9 +48,85 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// Cross-CTA messages are 8-byte {value, tag} pairs written with one store: the tag arrives with
+// the value, so neither side needs a fence (a gpu-scope fence here would wait for the hundreds of
+// kilobytes of weight loads the SM has in flight).  The tag is the launch generation.
+__device__ __forceinline__ void msg_store(uint2* p, float v, uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 msg_load(const uint2* p) {
+    uint2 r;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    return r;
+}
+// Polls until the message carries `tag`; false after the time limit.
+__device__ __forceinline__ bool msg_wait(const uint2* p, uint32_t tag, float& v) {
+    uint2 r = msg_load(p);
+    if (r.y != tag) {
+        const long long t0 = wait_clock();
+        do {
+            r = msg_load(p);
+            if (r.y == tag) break;
+        } while (!wait_expired(t0));
+    }
+    v = __uint_as_float(r.x);
+    return r.y == tag;
+}
+
+// u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
+__device__ __forceinline__ void imma_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr float kLimb1Ratio = 254.0f;    // limb 1 is in units of scale / 254
+
+__device__ __forceinline__ uint32_t pack_s8x4(float a, float b, float c, float d) {
+    return ((uint32_t)(int)a & 0xffu) | (((uint32_t)(int)b & 0xffu) << 8) | (((uint32_t)(int)c & 0xffu) << 16) |
+           (((uint32_t)(int)d & 0xffu) << 24);
+}
+
+// Activations of one Q4 block (32 values, four threads with eight each) become two int8 limbs
+// with a common f32 scale s = max|x| / 127:  x ~= s * (l0 + l1 / 254), |l0|, |l1| <= 127, so the
+// representation error is below max|x| / 64516.  The integer dot products with the 4-bit codes
+// are then exact.  Bytes are stored in the order the MMA B operand wants them: per nibble word
+// {k0,k2,k4,k6} then {k1,k3,k5,k7}.  `sx` receives {s, sum of the 32 activations}.
+__device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT, uint32_t mp, uint32_t o,
+                                            bool active, const float (&v)[8]) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
+    sum += __shfl_xor_sync(kFull, sum, 1);
+    sum += __shfl_xor_sync(kFull, sum, 2);
+    if (!active) return;
+    const bool tiny = !(amax > 1e-30f);
+    const float s0 = tiny ? 1.0f : amax * (1.0f / 127.0f);
+    const float inv0 = tiny ? 0.0f : 127.0f / amax;
+    const float inv1 = inv0 * kLimb1Ratio;
+    float l0[8], l1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        l0[i] = fminf(fmaxf(rintf(v[i] * inv0), -127.0f), 127.0f);
+        const float r = fmaf(-l0[i], s0, v[i]);
+        l1[i] = fminf(fmaxf(rintf(r * inv1), -127.0f), 127.0f);
+    }
+    const uint32_t blk = o >> 2, j = o & 3;
+    uint8_t* dst = xs + ((size_t)blk * MT + mp) * 64 + j * 8;
+    *reinterpret_cast<uint2*>(dst) =
+        make_uint2(pack_s8x4(l0[0], l0[2], l0[4], l0[6]), pack_s8x4(l0[1], l0[3], l0[5], l0[7]));
+    *reinterpret_cast<uint2*>(dst + 32) =
+        make_uint2(pack_s8x4(l1[0], l1[2], l1[4], l1[6]), pack_s8x4(l1[1], l1[3], l1[5], l1[7]));
+    if (j == 0) sx[(size_t)blk * MT + mp] = make_float2(s0, sum);
+}
+
 // Prologue of the 256 consumer threads: rotation, LoRA partial projection, activation limbs.
 template <int MT>
-__device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
+__device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, uint32_t tag) {
     const uint32_t K = p.k, M = p.m;
     const int cw = ctid >> 5, lane = ctid & 31;
     float* xrot = reinterpret_cast<float*>(smem + p.off_xrot);
@@ -90,18 +167,13 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
             }
 #pragma unroll
             for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
-            if (lane == 0) {
-                p.tpart[(size_t)blockIdx.x * pairs + pr] = s;
-                __threadfence();
-            }
+            if (lane == 0) msg_store(reinterpret_cast<uint2*>(p.tpart) + (size_t)blockIdx.x * pairs + pr, s, tag);
         }
-        named_bar_sync(kBarConsumers, kConsumerThreads);
-        if (ctid == 0) atomicAdd(p.tsync, 1u);
     }
 
-    // limbs: [block][token][hi, lo][64 B]; block sums: [block][token]
+    // limbs: [block][token][limb 0, limb 1][32 B]; per-block info {scale, sum}: [block][token]
     uint8_t* xs = smem + p.off_xs;
-    float* sx = reinterpret_cast<float*>(smem + p.off_sx);
+    float2* sx = reinterpret_cast<float2*>(smem + p.off_sx);
     const uint32_t noct = K / 8;
     for (uint32_t mp = 0; mp < (uint32_t)MT; ++mp) {
         // four octets per thread and pass: all global loads are issued before the first use
@@ -124,7 +196,7 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const uint32_t o = o0 + u * kConsumerThreads + ctid;
-                store_fragments(xs, sx, 1, 2 * MT, mp, o, o < noct, v[u], MT);
+                store_limbs(xs, sx, MT, mp, o, o < noct, v[u]);
             }
         }
     }
@@ -150,6 +222,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
         }
         s_err = 0;
         s_twait_failed = 0;
+        for (int i = 0; i < 8; ++i) reinterpret_cast<uint32_t*>(smem + kZeroOffset)[i] = 0;
         mbar_fence_init();
     }
     __syncthreads();
@@ -157,7 +230,10 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
 
     const uint64_t G = gridDim.x;
     const uint64_t total = (uint64_t)p.tiles * p.kg;
-    const uint64_t r0 = range_begin(blockIdx.x, total, G), r1 = range_begin(blockIdx.x + 1, total, G);
+    // whole-tile mode hands out entire tiles (no partial sums); otherwise equal shares of granules
+    const uint64_t r0 = p.whole_tiles ? range_begin(blockIdx.x, p.tiles, G) * p.kg : range_begin(blockIdx.x, total, G);
+    const uint64_t r1 = p.whole_tiles ? range_begin(blockIdx.x + 1, p.tiles, G) * p.kg
+                                      : range_begin(blockIdx.x + 1, total, G);
     uint32_t issued = 0;
 
     if (warp == 8) {
@@ -195,50 +271,40 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
         const int g = lane >> 2, t = lane & 3;
         float* t_s = reinterpret_cast<float*>(smem + p.off_t);
         if (p.use_pdl) pdl_wait_prior_grids();
-        decode_prologue<MT>(p, smem, tid);
-        bool t_ready = p.rank == 0;
+        // launch generation: bumped once at the end of every launch, so a message written by an
+        // earlier launch never carries the current tag
+        const uint32_t tag = *reinterpret_cast<volatile const uint32_t*>(p.tsync) + 1u;
+        decode_prologue<MT>(p, smem, tid, tag);
 
+        // Sums every CTA's partial projection: one warp per (token, rank) pair, lanes poll different
+        // CTAs' messages, then a fixed shuffle tree adds them (same result whatever the arrival order).
         auto gather_t = [&]() {
-            if (tid == 0) {
-                const unsigned long long t0 = globaltimer_ns();
-                while (ld_acquire_u32(p.tsync) < (uint32_t)G) {
-                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-                        s_twait_failed = 1;
-                        atomicOr(p.status, kDevErrGridWaitTimeout);
-                        break;
-                    }
-                    __nanosleep(64);
-                }
-            }
-            named_bar_sync(kBarConsumers, kConsumerThreads);
-            // one warp per (token, rank) pair: lanes fetch different CTAs' partials at once, then a
-            // fixed shuffle tree adds them (same result whatever the arrival order)
             const uint32_t pairs = p.m * p.rank;
-            const bool failed = s_twait_failed != 0;
+            const uint2* msgs = reinterpret_cast<const uint2*>(p.tpart);
             for (uint32_t pr = warp; pr < pairs; pr += 8) {
                 float s = 0.0f;
-                if (!failed)
-                    for (uint32_t c = lane; c < (uint32_t)G; c += 32) s += __ldcg(p.tpart + (size_t)c * pairs + pr);
+                bool good = true;
+                for (uint32_t c = lane; c < (uint32_t)G; c += 32) {
+                    float v;
+                    good = msg_wait(msgs + (size_t)c * pairs + pr, tag, v) && good;
+                    s += v;
+                }
+                if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
 #pragma unroll
                 for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
                 if (lane == 0) t_s[pr] = s;
             }
             named_bar_sync(kBarConsumers, kConsumerThreads);
-            if (tid == 0) {
-                const uint32_t old = atomicAdd(p.tsync + 1, 1u);
-                if (old == (uint32_t)G - 1) {     // last reader re-arms both counters
-                    p.tsync[0] = 0;
-                    p.tsync[1] = 0;
-                    __threadfence();
-                }
-            }
-            t_ready = true;
         };
+        // The ring keeps filling while this waits for the other CTAs' partial projections.
+        if (p.rank) gather_t();
 
-        // this lane supplies B-operand registers only for the column pair of its own block
+        // A lane supplies B-operand registers only for the column pair (limb 0, limb 1) of its own
+        // block; every other lane reads a block of zeros, so that its columns contribute nothing.
         const bool has_b = (g >> 1) == t;
-        const uint8_t* xs_lane = smem + p.off_xs + (size_t)(g & 1) * 64;
-        const float* sx_all = reinterpret_cast<const float*>(smem + p.off_sx);
+        const uint8_t* xs_lane = smem + p.off_xs + (size_t)(g & 1) * 32;
+        const uint8_t* zeros = smem + kZeroOffset;
+        const float2* sx_all = reinterpret_cast<const float2*>(smem + p.off_sx);
 
         uint32_t it = 0;
         bool ok = true;
@@ -252,6 +318,14 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
             float acc[MT][2];
 #pragma unroll
             for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = 0.0f;
+            if (p.rank && g0 == 0) {
+                // this CTA will finish the tile: pull the warp's 16 rows of LoRA B towards L2 now
+                const uint32_t rfirst = tile * kGemvTileRows + warp * 16;
+                const uint32_t rows = rfirst < p.n ? min(16u, p.n - rfirst) : 0u;
+                const char* bb = reinterpret_cast<const char*>(p.lb + (size_t)rfirst * p.rank);
+                for (uint32_t off = lane * 128; off < rows * p.rank * 4; off += 32 * 128)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(bb + off));
+            }
 
             for (uint32_t gs = g0; gs < g1; ++it) {
                 const bool big = g1 - gs >= (uint32_t)kBigGranules;
@@ -271,41 +345,41 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                     uint32_t w0[4], w1[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) { w0[j] = q0[1 + j]; w1[j] = q1[1 + j]; }
-                    uint4 bf[MT][4];
-                    float sxv[MT];
+                    uint4 bq[MT][2];
+                    float2 info[MT];
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const uint8_t* xb = xs_lane + ((size_t)blk * MT + mt) * 128;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            bf[mt][j] = has_b ? *reinterpret_cast<const uint4*>(xb + j * 16) : make_uint4(0, 0, 0, 0);
-                        sxv[mt] = sx_all[(size_t)blk * MT + mt];
+                        const uint8_t* xb = has_b ? xs_lane + ((size_t)blk * MT + mt) * 64 : zeros;
+                        bq[mt][0] = *reinterpret_cast<const uint4*>(xb);
+                        bq[mt][1] = *reinterpret_cast<const uint4*>(xb + 16);
+                        info[mt] = sx_all[(size_t)blk * MT + mt];
                     }
-                    float ca[MT][4], cb[MT][4];
+                    int c[MT][4];
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) ca[mt][i] = cb[mt][i] = 0.0f;
+                    for (int mt = 0; mt < MT; ++mt) c[mt][0] = c[mt][1] = c[mt][2] = c[mt][3] = 0;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        uint32_t a1[4], a2[4];
-                        nibbles_to_h2(w0[j], a1[0], a1[2], a2[0], a2[2]);
-                        nibbles_to_h2(w1[j], a1[1], a1[3], a2[1], a2[3]);
+                        // bytes {n0,n2,n4,n6} fill k-slots 4t..4t+3, bytes {n1,n3,n5,n7} slots 4t+16..4t+19
+                        uint32_t a[4];
+                        a[0] = w0[j] & 0x0F0F0F0Fu;
+                        a[1] = w1[j] & 0x0F0F0F0Fu;
+                        a[2] = (w0[j] >> 4) & 0x0F0F0F0Fu;
+                        a[3] = (w1[j] >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
-                            mma_16816(ca[mt], a1, bf[mt][j].x, bf[mt][j].y, ca[mt]);
-                            mma_16816(cb[mt], a2, bf[mt][j].z, bf[mt][j].w, cb[mt]);
+                            const uint4 q = bq[mt][j >> 1];
+                            imma_16832(c[mt], a, (j & 1) ? q.z : q.x, (j & 1) ? q.w : q.y);
                         }
                     }
                     const float d0 = h2f_bits(meta0 & 0xffffu), b0 = h2f_bits(meta0 >> 16);
                     const float d1 = h2f_bits(meta1 & 0xffffu), b1 = h2f_bits(meta1 >> 16);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        // columns 2t (hi limb) and 2t+1 (lo limb) hold this thread's block
-                        const float dot0 = (ca[mt][0] + cb[mt][0]) + (ca[mt][1] + cb[mt][1]);
-                        const float dot1 = (ca[mt][2] + cb[mt][2]) + (ca[mt][3] + cb[mt][3]);
-                        acc[mt][0] = fmaf(d0, dot0, fmaf(b0, sxv[mt], acc[mt][0]));
-                        acc[mt][1] = fmaf(d1, dot1, fmaf(b1, sxv[mt], acc[mt][1]));
+                        // columns 2t (limb 0) and 2t+1 (limb 1) hold this thread's block: exact integers
+                        const float dot0 = fmaf((float)c[mt][1], 1.0f / kLimb1Ratio, (float)c[mt][0]);
+                        const float dot1 = fmaf((float)c[mt][3], 1.0f / kLimb1Ratio, (float)c[mt][2]);
+                        acc[mt][0] = fmaf(d0 * info[mt].x, dot0, fmaf(b0, info[mt].y, acc[mt][0]));
+                        acc[mt][1] = fmaf(d1 * info[mt].x, dot1, fmaf(b1, info[mt].y, acc[mt][1]));
                     }
                 }
                 __syncwarp();
@@ -313,7 +387,6 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 gs += ngr;
             }
             if (!ok) break;
-            if (!t_ready) gather_t();
 
             // each thread of a quad covered blocks = t (mod 4): add the four
             float v[MT][2];
@@ -328,46 +401,40 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 }
             }
             const bool complete = (g0 == 0 && g1 == p.kg);
-            if (!complete) {
-                const uint32_t slot = (tile == (uint32_t)(r0 / p.kg)) ? 0u : 1u;
-                float* dst = p.partials + ((size_t)(blockIdx.x * 2 + slot) * kGemvTileRows + warp * 16) * MT;
+            if (!complete && g0 != 0) {
+                // Contributor: this CTA's range starts inside the tile, so this is its first segment.
+                // Publish the partial sums and leave; the ticket add is a release, no reply is needed.
+                uint2* dst = reinterpret_cast<uint2*>(p.partials) + ((size_t)blockIdx.x * kGemvTileRows + warp * 16) * MT;
                 if (t == 0) {
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        dst[g * MT + mt] = v[mt][0];
-                        dst[(g + 8) * MT + mt] = v[mt][1];
+                        msg_store(dst + g * MT + mt, v[mt][0], tag);
+                        msg_store(dst + (g + 8) * MT + mt, v[mt][1], tag);
                     }
                 }
-                __threadfence();
-                __syncwarp();
-                uint32_t last = 0, c_first = 0, c_last = 0;
-                if (lane == 0) {
-                    c_first = owner_of((uint64_t)tile * p.kg, total, G);
-                    c_last = owner_of((uint64_t)(tile + 1) * p.kg - 1, total, G);
-                    const uint32_t old = atomicAdd(&p.tickets[tile * 8 + warp], 1u);
-                    last = (old == c_last - c_first) ? 1u : 0u;
-                    if (last) p.tickets[tile * 8 + warp] = 0;
-                }
-                last = __shfl_sync(kFull, last, 0);
-                if (!last) continue;
-                c_first = __shfl_sync(kFull, c_first, 0);
-                c_last = __shfl_sync(kFull, c_last, 0);
-                __threadfence();
-                // lanes fetch different CTAs' partials (all 16 rows each) in one round trip, a fixed
-                // shuffle tree adds them, then every lane picks the rows it finishes
+                continue;
+            }
+            if (!complete) {
+                // Finisher: the CTA that owns the tile's first k part reaches it at the END of its own
+                // range, when the contributors (who met the tile at the START of theirs) are long done.
+                // The wait below is bounded and normally falls through at once.
+                const uint32_t c_last = owner_of((uint64_t)(tile + 1) * p.kg - 1, total, G);
+                // lanes poll different CTAs' messages (all 16 rows each), a fixed shuffle tree adds
+                // them: the sum does not depend on arrival order
                 float part[16 * MT];
 #pragma unroll
                 for (int i = 0; i < 16 * MT; ++i) part[i] = 0.0f;
-                for (uint32_t c = c_first + lane; c <= c_last; c += 32) {
-                    const uint32_t sl = ((uint32_t)(range_begin(c, total, G) / p.kg) == tile) ? 0u : 1u;
-                    const float4* src = reinterpret_cast<const float4*>(
-                        p.partials + ((size_t)(c * 2 + sl) * kGemvTileRows + warp * 16) * MT);
+                bool good = true;
+                for (uint32_t c = blockIdx.x + 1 + lane; c <= c_last; c += 32) {
+                    const uint2* src = reinterpret_cast<const uint2*>(p.partials) + ((size_t)c * kGemvTileRows + warp * 16) * MT;
 #pragma unroll
-                    for (int i = 0; i < 4 * MT; ++i) {
-                        const float4 q = __ldcg(src + i);
-                        part[4 * i] += q.x; part[4 * i + 1] += q.y; part[4 * i + 2] += q.z; part[4 * i + 3] += q.w;
+                    for (int i = 0; i < 16 * MT; ++i) {
+                        float q;
+                        good = msg_wait(src + i, tag, q) && good;
+                        part[i] += q;
                     }
                 }
+                if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
 #pragma unroll
                 for (int i = 0; i < 16 * MT; ++i) {
 #pragma unroll
@@ -375,40 +442,48 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    v[mt][0] = v[mt][1] = 0.0f;
 #pragma unroll
                     for (int r = 0; r < 8; ++r) {        // select without dynamic register indexing
-                        if (r == g) { v[mt][0] = part[r * MT + mt]; v[mt][1] = part[(r + 8) * MT + mt]; }
+                        if (r == g) { v[mt][0] += part[r * MT + mt]; v[mt][1] += part[(r + 8) * MT + mt]; }
                     }
                 }
             }
 
-            // epilogue: quad thread t finishes token t (LoRA term, store)
+            // epilogue: LoRA term (the quad splits the rank), then quad thread t stores token t
             const uint32_t rowa = tile * kGemvTileRows + warp * 16 + g, rowb = rowa + 8;
+            if (p.rank) {
+                float la[MT], lb2[MT];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) la[mt] = lb2[mt] = 0.0f;
+                const float* bra = p.lb + (size_t)(rowa < p.n ? rowa : 0) * p.rank;
+                const float* brb = p.lb + (size_t)(rowb < p.n ? rowb : 0) * p.rank;
+#pragma unroll 4
+                for (uint32_t j = t; j < p.rank; j += 4) {
+                    const float ba = __ldg(bra + j), bb = __ldg(brb + j);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const float tv = t_s[mt * p.rank + j];
+                        la[mt] = fmaf(ba, tv, la[mt]);
+                        lb2[mt] = fmaf(bb, tv, lb2[mt]);
+                    }
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    la[mt] += __shfl_xor_sync(kFull, la[mt], 1);
+                    la[mt] += __shfl_xor_sync(kFull, la[mt], 2);
+                    lb2[mt] += __shfl_xor_sync(kFull, lb2[mt], 1);
+                    lb2[mt] += __shfl_xor_sync(kFull, lb2[mt], 2);
+                    v[mt][0] += p.lscale * la[mt];
+                    v[mt][1] += p.lscale * lb2[mt];
+                }
+            }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 if (mt != t || (uint32_t)mt >= p.m) continue;
-                float y0 = v[mt][0], y1 = v[mt][1];
-                if (p.rank) {
-                    const float* tt = t_s + mt * p.rank;
-                    if (rowa < p.n) {
-                        const float* br = p.lb + (size_t)rowa * p.rank;
-                        float dsum = 0.0f;
-                        for (uint32_t j = 0; j < p.rank; ++j) dsum = fmaf(__ldg(br + j), tt[j], dsum);
-                        y0 += p.lscale * dsum;
-                    }
-                    if (rowb < p.n) {
-                        const float* br = p.lb + (size_t)rowb * p.rank;
-                        float dsum = 0.0f;
-                        for (uint32_t j = 0; j < p.rank; ++j) dsum = fmaf(__ldg(br + j), tt[j], dsum);
-                        y1 += p.lscale * dsum;
-                    }
-                }
-                if (rowa < p.n) p.y[(size_t)mt * p.ldy + rowa] = y0;
-                if (rowb < p.n) p.y[(size_t)mt * p.ldy + rowb] = y1;
+                if (rowa < p.n) p.y[(size_t)mt * p.ldy + rowa] = v[mt][0];
+                if (rowb < p.n) p.y[(size_t)mt * p.ldy + rowb] = v[mt][1];
             }
         }
-        if (ok && !t_ready) gather_t();
         if (!ok) {
             if (lane == 0) atomicOr(p.status, kDevErrBarrierTimeout);
             s_err = 1;
@@ -418,6 +493,14 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
     // After a failed wait some TMA loads may still be in flight towards this CTA's shared
     // memory: wait (bounded) for the stages that were issued before leaving.
     __syncthreads();
+    if (tid == 0) {
+        // the last CTA to get here (all of them have read the generation by now) advances it
+        const uint32_t old = atomicAdd(p.tsync + 1, 1u);
+        if (old == (uint32_t)G - 1) {
+            p.tsync[1] = 0;
+            p.tsync[0] = p.tsync[0] + 1u;
+        }
+    }
     if (s_err && warp == 8 && lane == 0) {
         const uint32_t first = issued > NST ? issued - NST : 0;
         for (uint32_t j = first; j < issued; ++j) mbar_wait(&full[j % NST], (j / NST) & 1u);
@@ -485,7 +568,7 @@ cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtenso
 size_t decode_plan_smem(GemvParams& p) {
     if (p.m == 0 || p.m > 4 || p.kb == 0 || p.kb % kGemvGranuleBlocks != 0) return 0;
     const uint32_t MT = p.m;
-    uint32_t off = 2 * kMaxStages * 8;            // mbarriers
+    uint32_t off = 2 * kMaxStages * 8 + 128;      // mbarriers, then the block of zeros
     p.off_t = off;
     off += align_up(p.m * p.rank * 4, 128);
     p.off_xrot = 0;
@@ -494,9 +577,9 @@ size_t decode_plan_smem(GemvParams& p) {
         off += align_up(p.m * p.k * 4, 128);
     }
     p.off_xs = off;
-    off += align_up(p.kb * MT * 128, 128);
+    off += align_up(p.kb * MT * 64, 128);
     p.off_sx = off;
-    off += align_up(p.kb * MT * 4, 128);
+    off += align_up(p.kb * MT * 8, 128);
     p.off_stage = off;
     p.stage_bytes = kSlotBytes;
     p.off_stage_xs = p.off_stage_sx = 0;
@@ -506,10 +589,14 @@ size_t decode_plan_smem(GemvParams& p) {
     if (nst > 4) nst = 4;
     p.nstages = nst;
     p.kg = p.kb / kGemvGranuleBlocks;
+    // Whole tiles per CTA need no cross-CTA sums; take that when it keeps at least 88 % of the SMs busy.
+    const uint64_t sms = p.sm_count > 0 ? (uint64_t)p.sm_count : 148;
+    const uint64_t rounds = (p.tiles + sms - 1) / sms;
+    p.whole_tiles = (rounds > 0 && (double)p.tiles / (double)(rounds * sms) >= 0.88) ? 1u : 0u;
     return (size_t)off + (size_t)nst * kSlotBytes;
 }
 
-uint64_t decode_units(const GemvParams& p) { return (uint64_t)p.tiles * p.kg; }
+uint64_t decode_units(const GemvParams& p) { return p.whole_tiles ? (uint64_t)p.tiles : (uint64_t)p.tiles * p.kg; }
 
 cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s) {
     CUtensorMap big, small;

@@ -1,14 +1,583 @@
+// Prefill path (m > 16): Y[m, n] = X[m, k] * Wq4[n, k]^T (+ LoRA) on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+// The product is computed transposed, D[n, m] = W[n, :] . X[m, :], so that the 128 TMEM lanes
+// are weight rows and the columns are tokens: the epilogue then stores 32 consecutive output
+// features per warp instruction (coalesced along n).
+//
+//   CTA tile      128 weight rows x TT tokens (TT = 256 with f16-exact activations, 128 when the
+//                 activations are carried as two f16 limbs), K loop in blocks of 64
+//   warp 0        TMA producer: activation tiles (and the dense LoRA tiles) -> shared memory
+//   warp 1        TMEM allocation, then one elected lane issues tcgen05.mma / tcgen05.commit
+//   warps 2..5    dequantizers: read 2 Q4 blocks per weight row from global memory, convert
+//                 in registers (magic-number int4 -> f16, one HFMA2 per pair for q*d+b) and
+//                 write the 128 x 64 f16 tile in the 128-byte-swizzled K-major layout the MMA reads
+//   warps 6..9    epilogue: tcgen05.ld the finished accumulator, store f32 to Y
+//
+// Operands are f16 with f32 accumulation.  Dequantized weights are rounded once to f16; the
+// activations are exact in f16 when they come as bf16, and are split into hi + lo f16 limbs
+// (two MMAs on the same weight tile) when they come as f32.
+// LoRA enters as extra K blocks: D += (s*B)[n, :] . T[m, :] with T = X A^T computed beforehand
+// (f32) and both factors carried as hi/lo f16 pairs.
+//
+// Within each group of 8 consecutive k the stored order is (k0,k4,k1,k5,k2,k6,k3,k7): that is
+// the order in which the nibble extraction yields pairs, and the activation tiles are written
+// in the same order by the conversion kernel, so no shuffling is needed on either side.
 #include "lq4_gemm.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
 
 namespace lq4 {
 
-bool gemm_supported(uint32_t, uint32_t, uint32_t, uint32_t) { return false; }
-size_t gemm_workspace_bytes(uint32_t, uint32_t, uint32_t, uint32_t) { return 0; }
-cudaError_t launch_gemm_tc(const void*, int, const uint8_t*, float*, uint64_t, uint32_t, uint32_t, uint32_t,
-                           const float*, const float*, uint32_t, float, void*, size_t, int32_t*, int, cudaStream_t,
-                           int*, std::string* err) {
-    if (err) *err = "not built";
-    return cudaErrorNotSupported;
+namespace {
+
+constexpr int kTileN = 128;          // weight rows per CTA tile (TMEM lanes)
+constexpr int kBlockK = 64;          // k per pipeline stage (128 bytes of f16: one swizzle atom)
+constexpr int kStages = 4;
+constexpr uint32_t kTileABytes = kTileN * kBlockK * 2;      // 16 KB dequantized weights
+constexpr uint32_t kTileBBytes = 256 * kBlockK * 2;         // 32 KB activations (both limb modes)
+constexpr uint32_t kStageBytes = kTileABytes + kTileBBytes; // 48 KB
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], f16 inputs, f32 accumulate; issued by one thread.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// 32 lanes x 32 consecutive columns of 32-bit accumulators -> 32 registers per thread.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle; groups of
+// 8 rows are 1024 bytes apart.  Fields: start address >> 4 (bits 0-13), leading byte offset >> 4
+// (16-29, unused for swizzled K-major), stride byte offset >> 4 (32-45), descriptor version 1
+// (46-47), swizzle mode 2 = 128 B (61-63).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: f32 accumulator (bits 4-5 = 1), f16 A and B (formats 0), both
+// K-major, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+__device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
+                                              uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Byte offset of 16-byte chunk `c` (0..7) of row `r` inside a 128-byte-swizzled K-major tile.
+__device__ __forceinline__ uint32_t swz128(uint32_t r, uint32_t c) {
+    return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4);
+}
+
+// ---------------------------------------------------------------------------
+// f16 conversion of an f32/bf16 matrix [rows, cols] (cols % 8 == 0): "hi" = round to nearest,
+// optional "lo" = residual.  Each group of 8 consecutive columns is stored as
+// (c0,c4,c1,c5,c2,c6,c3,c7).  Destination rows are `dst_stride` halves apart; lo goes
+// `lo_off` halves to the right of hi (lo_off == 0: no lo limb).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) convert_rows_kernel(const void* __restrict__ x, int x_dtype, uint32_t rows,
+                                                           uint32_t cols, __half* __restrict__ dst,
+                                                           uint64_t dst_stride, uint64_t lo_off) {
+    const uint64_t opr = cols / 8, n_oct = (uint64_t)rows * opr;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t o = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; o < n_oct; o += stride) {
+        const uint64_t row = o / opr, oc = o - row * opr;
+        float v[8];
+        if (x_dtype == LQ4_DTYPE_BF16) {
+            const uint4 r = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + o * 8);
+            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+            }
+        } else {
+            const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + o * 8);
+            const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(x) + o * 8 + 4);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        }
+        __half h[8], l[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) split_f16(v[i], h[i], l[i]);
+        auto pk = [](__half a, __half b) { return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16); };
+        __half* d = dst + row * dst_stride + oc * 8;
+        *reinterpret_cast<uint4*>(d) = make_uint4(pk(h[0], h[4]), pk(h[1], h[5]), pk(h[2], h[6]), pk(h[3], h[7]));
+        if (lo_off)
+            *reinterpret_cast<uint4*>(d + lo_off) = make_uint4(pk(l[0], l[4]), pk(l[1], l[5]), pk(l[2], l[6]), pk(l[3], l[7]));
+    }
+}
+
+// dst[row][j] = hi(scale * src[row][j]), dst[row][cp + j] = lo(...), natural column order, zero
+// padding for cols <= j < cp.  dst rows are 2 * cp halves long.
+__global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict__ src, uint32_t rows, uint32_t cols,
+                                                         uint32_t cp, float scale, __half* __restrict__ dst) {
+    const uint64_t n = (uint64_t)rows * cp;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const uint64_t row = i / cp;
+        const uint32_t j = (uint32_t)(i - row * cp);
+        __half h = __float2half_rn(0.0f), l = h;
+        if (j < cols) split_f16(scale * src[row * cols + j], h, l);
+        dst[row * 2 * cp + j] = h;
+        dst[row * 2 * cp + cp + j] = l;
+    }
+}
+
+struct GemmParams {
+    const uint8_t* w;
+    float* y;
+    uint64_t ldy;
+    uint32_t m, n, k;
+    uint32_t limbs;          // 1: activations exact in f16; 2: hi + lo limbs
+    uint32_t tt;             // tokens per CTA tile = 256 / limbs
+    uint32_t n_tiles, m_tiles;
+    uint32_t kblocks;        // k / 64 (even)
+    uint32_t lora_kblocks;   // dense (f16 x f16) k blocks appended after the Q4 blocks
+    uint32_t seg_len;        // dense blocks per segment
+    uint32_t seg_a_off[4];   // column offset of each dense segment in the A-operand matrix
+    uint32_t seg_b_off[4];   // ... and in the B-operand matrix
+    int32_t* status;
+};
+
+constexpr int kRawStages = 3;                                  // each holds 128 rows x 4 blocks (two k blocks)
+constexpr uint32_t kRawBytes = kTileN * 4 * kBlockBytes;       // 10,240
+constexpr uint32_t kOffStages = 1024;                          // barriers and the TMEM pointer live below
+constexpr uint32_t kOffRaw = kOffStages + kStages * kStageBytes;
+constexpr uint32_t kGemmSmem = kOffRaw + kRawStages * kRawBytes;   // 228,352
+
+// One nibble word (8 weights of one block) -> 8 f16 weights q*d+b in the order (k0,k4,k1,k5,k2,k6,k3,k7).
+__device__ __forceinline__ uint4 dequant_word_f16(uint32_t w, __half2 d2, __half2 b2) {
+    uint32_t q04, q15, q26, q37;
+    nibbles_to_h2(w, q04, q15, q26, q37);
+    __half2 r0 = __hfma2(*reinterpret_cast<__half2*>(&q04), d2, b2);
+    __half2 r1 = __hfma2(*reinterpret_cast<__half2*>(&q15), d2, b2);
+    __half2 r2 = __hfma2(*reinterpret_cast<__half2*>(&q26), d2, b2);
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2*>(&q37), d2, b2);
+    return make_uint4(*reinterpret_cast<uint32_t*>(&r0), *reinterpret_cast<uint32_t*>(&r1),
+                      *reinterpret_cast<uint32_t*>(&r2), *reinterpret_cast<uint32_t*>(&r3));
+}
+
+constexpr int kGemmWarps = 11;       // 0 TMA (activations, LoRA), 1 MMA, 2-5 dequant, 6-9 epilogue, 10 TMA (raw Q4)
+
+__global__ void __launch_bounds__(kGemmWarps * 32, 1)
+gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+               const __grid_constant__ CUtensorMap tm_da, const __grid_constant__ CUtensorMap tm_db) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);          // [kStages]  tile operands ready
+    uint64_t* empty = full + kStages;                            // [kStages]  MMAs that read the stage are done
+    uint64_t* raw_full = empty + kStages;                        // [kRawStages]
+    uint64_t* raw_empty = raw_full + kRawStages;                 // [kRawStages]
+    uint64_t* acc_full = raw_empty + kRawStages;                 // [2] accumulator finished
+    uint64_t* acc_empty = acc_full + 2;                          // [2] accumulator drained
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    int* s_err = reinterpret_cast<int*>(tmem_ptr + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 5); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < kRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        *s_err = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_ptr, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    const uint32_t total_tiles = p.n_tiles * p.m_tiles;
+    const uint32_t nkb = p.kblocks + p.lora_kblocks;
+    const uint32_t xbytes = p.limbs * p.tt * 128;                // activation bytes per Q4 stage (32 KB)
+
+    if (warp == 0) {
+        // ---------------- TMA: activation tiles, dense LoRA tiles ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int32_t n0 = (int32_t)((tile / p.m_tiles) * kTileN), m0 = (int32_t)((tile % p.m_tiles) * p.tt);
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
+                    const uint32_t s = it % kStages;
+                    if (!mbar_wait(&empty[s], ((it / kStages) & 1u) ^ 1u)) { ok = false; break; }
+                    uint8_t* st = smem + kOffStages + s * kStageBytes;
+                    if (kb < p.kblocks) {
+                        mbar_arrive_expect_tx(&full[s], xbytes);
+                        // the converted activations hold the hi limb in columns [0, k), the lo limb in [k, 2k)
+                        tma_load_tile(st + kTileABytes, &tm_x, (int32_t)(kb * kBlockK), m0, &full[s]);
+                        if (p.limbs == 2)
+                            tma_load_tile(st + kTileABytes + p.tt * 128, &tm_x, (int32_t)(p.k + kb * kBlockK), m0, &full[s]);
+                    } else {
+                        const uint32_t d = kb - p.kblocks, seg = d / p.seg_len, within = d - seg * p.seg_len;
+                        mbar_arrive_expect_tx(&full[s], kTileABytes + p.tt * 128);
+                        tma_load_tile(st, &tm_da, (int32_t)(p.seg_a_off[seg] + within * kBlockK), n0, &full[s]);
+                        tma_load_tile(st + kTileABytes, &tm_db, (int32_t)(p.seg_b_off[seg] + within * kBlockK), m0, &full[s]);
+                    }
+                }
+            }
+            if (!ok) { atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
+        }
+    } else if (warp == 10) {
+        // ---------------- TMA: packed Q4 rows, 4 blocks (two k blocks) per load ----------------
+        if (lane == 0) {
+            uint32_t rit = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int32_t n0 = (int32_t)((tile / p.m_tiles) * kTileN);
+                for (uint32_t pr = 0; pr < p.kblocks / 2; ++pr, ++rit) {
+                    const uint32_t rs = rit % kRawStages;
+                    if (!mbar_wait(&raw_empty[rs], ((rit / kRawStages) & 1u) ^ 1u)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&raw_full[rs], kRawBytes);
+                    tma_load_tile(smem + kOffRaw + rs * kRawBytes, &tm_w, (int32_t)(pr * 20), n0, &raw_full[rs]);
+                }
+            }
+            if (!ok) { atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(kTileN, p.tt);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+                const uint32_t buf = tcount & 1u;
+                if (!mbar_wait(&acc_empty[buf], ((tcount >> 1) & 1u) ^ 1u)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * 256;
+                for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
+                    const uint32_t s = it % kStages;
+                    if (!mbar_wait(&full[s], (it / kStages) & 1u)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + kOffStages + s * kStageBytes);
+                    const uint32_t b_addr = a_addr + kTileABytes;
+                    const uint32_t nl = kb < p.kblocks ? p.limbs : 1u;
+                    for (uint32_t l = 0; l < nl; ++l) {
+                        const uint64_t da = make_smem_desc(a_addr);
+                        const uint64_t db = make_smem_desc(b_addr + l * p.tt * 128);
+#pragma unroll
+                        for (uint32_t k4 = 0; k4 < 4; ++k4)      // 16 k per MMA = 32 bytes = 2 descriptor units
+                            umma_f16(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | l | k4) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);
+                }
+                if (!ok) break;
+                umma_commit(&acc_full[buf]);
+            }
+            if (!ok) { atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
+        }
+    } else if (warp >= 2 && warp <= 5) {
+        // ---------------- dequantizers: thread r owns weight row n0 + r ----------------
+        const uint32_t r = (uint32_t)(tid - 64);
+        uint32_t it = 0, rit = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
+                const uint32_t s = it % kStages;
+                if (!mbar_wait(&empty[s], ((it / kStages) & 1u) ^ 1u)) { ok = false; break; }
+                if (kb < p.kblocks) {
+                    const uint32_t rs = rit % kRawStages;
+                    if ((kb & 1u) == 0 && !mbar_wait(&raw_full[rs], (rit / kRawStages) & 1u)) { ok = false; break; }
+                    // rows past n were zero-filled by the TMA: scale 0, bias 0, codes 0 -> weights 0
+                    const uint2* src = reinterpret_cast<const uint2*>(smem + kOffRaw + rs * kRawBytes + r * 80 + (kb & 1u) * 40);
+                    uint32_t q[10];
+#pragma unroll
+                    for (int i = 0; i < 5; ++i) { const uint2 v = src[i]; q[2 * i] = v.x; q[2 * i + 1] = v.y; }
+                    uint8_t* a_tile = smem + kOffStages + s * kStageBytes;
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        const uint32_t meta = q[5 * b];
+                        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)(meta & 0xffffu)));
+                        const __half2 b2 = __half2half2(__ushort_as_half((unsigned short)(meta >> 16)));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint4*>(a_tile + swz128(r, 4 * b + j)) = dequant_word_f16(q[5 * b + 1 + j], d2, b2);
+                    }
+                    fence_async_smem();          // generic-proxy writes -> visible to the tensor core
+                    if (kb & 1u) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+                        ++rit;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+            }
+        }
+        if (!ok) { if (lane == 0) atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
+    } else if (warp >= 6 && warp <= 9) {
+        // ---------------- epilogue: TMEM -> registers -> Y ----------------
+        const uint32_t quarter = (uint32_t)warp & 3u;            // TMEM lanes this warp may read
+        uint32_t tcount = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+            const uint32_t buf = tcount & 1u;
+            const uint32_t n = (tile / p.m_tiles) * kTileN + quarter * 32 + lane;
+            const uint32_t m0 = (tile % p.m_tiles) * p.tt;
+            if (!mbar_wait(&acc_full[buf], (tcount >> 1) & 1u)) { ok = false; break; }
+            tc_fence_after();
+            for (uint32_t c0 = 0; c0 < p.tt; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + buf * 256 + c0, v);
+                tmem_ld_wait();
+                if (n < p.n) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t m = m0 + c0 + j;
+                        if (c0 + j < p.tt && m < p.m) p.y[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        if (!ok) { if (lane == 0) atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*s_err) {
+        // a bounded wait gave up: let copies still in flight towards this CTA land before it exits
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {}
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn gemm_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// f16 matrix [rows, cols] with `stride` halves between rows; box = 64 columns x box_rows, 128-byte swizzle.
+bool make_f16_map(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t stride, uint32_t box_rows) {
+    EncodeTiledFn fn = gemm_encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {stride * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Packed weights as 4-byte words: box = 4 blocks (20 words) x 128 rows, no swizzle.
+bool make_raw_map(CUtensorMap* map, const uint8_t* w, uint32_t n, uint32_t k) {
+    EncodeTiledFn fn = gemm_encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)(k / 32) * 5, n};
+    const cuuint64_t strides[1] = {(cuuint64_t)(k / 32) * kBlockBytes};
+    const cuuint32_t box[2] = {20, (cuuint32_t)kTileN};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(w), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+struct GemmWorkspace {
+    size_t x16, al, t, tl, bl, total;
+};
+
+GemmWorkspace plan_workspace(uint32_t m, uint32_t n, uint32_t k, uint32_t rank, uint32_t limbs) {
+    GemmWorkspace ws{};
+    const uint32_t rp = round_up(rank, kBlockK);
+    size_t off = 0;
+    ws.x16 = off; off += up256((size_t)m * limbs * k * 2);
+    ws.al = off;  off += up256((size_t)rank * 2 * k * 2);
+    ws.t = off;   off += up256((size_t)m * rank * 4);
+    ws.tl = off;  off += up256((size_t)m * 2 * rp * 2);
+    ws.bl = off;  off += up256((size_t)n * 2 * rp * 2);
+    ws.total = off;
+    return ws;
+}
+
+cudaError_t launch_kernel(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tda,
+                          const CUtensorMap& tdb, int sm_count, cudaStream_t s) {
+    static bool attr_set = false;
+    const size_t smem = kGemmSmem + 1024;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const uint32_t tiles = p.n_tiles * p.m_tiles;
+    const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
+    gemm_tc_kernel<<<grid, kGemmWarps * 32, smem, s>>>(p, tx, tw, tda, tdb);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t rank) {
+    return m > 0 && n > 0 && k > 0 && k % 128 == 0 && rank <= 128;
+}
+
+size_t gemm_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, uint32_t rank) {
+    return plan_workspace(m, n, k, rank, 2).total;
+}
+
+cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* y, uint64_t ldy, uint32_t m,
+                           uint32_t n, uint32_t k, const float* la, const float* lb, uint32_t rank, float lscale,
+                           void* workspace, size_t workspace_bytes, int32_t* status, int sm_count, cudaStream_t s,
+                           int* launches, std::string* err) {
+    auto fail = [&](const char* what, cudaError_t e) {
+        if (err) *err = what;
+        return e;
+    };
+    const uint32_t limbs = x_dtype == LQ4_DTYPE_BF16 ? 1u : 2u;      // bf16 is exact in f16 (normal range)
+    const GemmWorkspace ws = plan_workspace(m, n, k, rank, limbs);
+    if (ws.total > workspace_bytes) return fail("workspace too small", cudaErrorInvalidValue);
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    __half* x16 = reinterpret_cast<__half*>(base + ws.x16);
+    const uint32_t rp = round_up(rank, kBlockK);
+    int nl = 0;
+    cudaError_t e;
+
+    // 1. activations -> f16 limbs, [m][limbs * k]
+    {
+        const uint64_t n_oct = (uint64_t)m * k / 8;
+        const unsigned blocks = (unsigned)((n_oct + 255) / 256 < (uint64_t)sm_count * 8 ? (n_oct + 255) / 256 : (uint64_t)sm_count * 8);
+        convert_rows_kernel<<<blocks, 256, 0, s>>>(x, x_dtype, m, k, x16, (uint64_t)limbs * k, limbs == 2 ? k : 0);
+        ++nl;
+    }
+    uint32_t tt = 256 / limbs;
+    if (round_up(m, 32) < tt) tt = round_up(m, 32);
+
+    CUtensorMap tm_x, tm_w, tm_da, tm_db;
+    if (!make_f16_map(&tm_x, x16, (uint64_t)limbs * k, m, (uint64_t)limbs * k, tt)) return fail("tensor map (x)", cudaErrorInvalidValue);
+    if (!make_raw_map(&tm_w, w, n, k)) return fail("tensor map (w)", cudaErrorInvalidValue);
+    tm_da = tm_x;
+    tm_db = tm_x;
+
+    GemmParams p{};
+    p.status = status;
+    if (rank) {
+        // 2. A -> [Ah | Al] in the activations' column order; 3. T = X A^T on the tensor cores (f32)
+        __half* al = reinterpret_cast<__half*>(base + ws.al);
+        float* t = reinterpret_cast<float*>(base + ws.t);
+        const uint64_t a_oct = (uint64_t)rank * k / 8;
+        convert_rows_kernel<<<(unsigned)((a_oct + 255) / 256), 256, 0, s>>>(la, LQ4_DTYPE_F32, rank, k, al, 2ull * k, k);
+        ++nl;
+        CUtensorMap tm_al, tm_x32;
+        if (!make_f16_map(&tm_al, al, 2ull * k, rank, 2ull * k, kTileN)) return fail("tensor map (A)", cudaErrorInvalidValue);
+        if (!make_f16_map(&tm_x32, x16, (uint64_t)limbs * k, m, (uint64_t)limbs * k, 32)) return fail("tensor map (x32)", cudaErrorInvalidValue);
+        GemmParams q{};
+        q.status = status;
+        q.w = w; q.y = t; q.ldy = rank; q.m = m; q.n = rank; q.k = k;
+        q.limbs = 1; q.tt = 32; q.n_tiles = (rank + kTileN - 1) / kTileN; q.m_tiles = (m + 31) / 32;
+        q.kblocks = 0;
+        q.seg_len = k / kBlockK;
+        q.seg_a_off[0] = 0; q.seg_b_off[0] = 0;          // Ah . Xh
+        q.seg_a_off[1] = k; q.seg_b_off[1] = 0;          // Al . Xh
+        q.seg_a_off[2] = 0; q.seg_b_off[2] = k;          // Ah . Xl (two-limb activations only)
+        q.lora_kblocks = (limbs == 2 ? 3u : 2u) * q.seg_len;
+        if ((e = launch_kernel(q, tm_x32, tm_w, tm_al, tm_x32, sm_count, s)) != cudaSuccess) return fail("projection GEMM launch", e);
+        ++nl;
+        // 4. hi/lo limbs of T and of s * B
+        __half* tl = reinterpret_cast<__half*>(base + ws.tl);
+        __half* bl = reinterpret_cast<__half*>(base + ws.bl);
+        split_rows_kernel<<<(unsigned)(((uint64_t)m * rp + 255) / 256), 256, 0, s>>>(t, m, rank, rp, 1.0f, tl);
+        const uint64_t bn = (uint64_t)n * rp;
+        const unsigned bblocks = (unsigned)((bn + 255) / 256 < (uint64_t)sm_count * 16 ? (bn + 255) / 256 : (uint64_t)sm_count * 16);
+        split_rows_kernel<<<bblocks, 256, 0, s>>>(lb, n, rank, rp, lscale, bl);
+        nl += 2;
+        if (!make_f16_map(&tm_da, bl, 2ull * rp, n, 2ull * rp, kTileN)) return fail("tensor map (B)", cudaErrorInvalidValue);
+        if (!make_f16_map(&tm_db, tl, 2ull * rp, m, 2ull * rp, tt)) return fail("tensor map (T)", cudaErrorInvalidValue);
+        p.seg_len = rp / kBlockK;
+        p.seg_a_off[0] = 0;  p.seg_b_off[0] = 0;         // Bh . Th
+        p.seg_a_off[1] = rp; p.seg_b_off[1] = 0;         // Bl . Th
+        p.seg_a_off[2] = 0;  p.seg_b_off[2] = rp;        // Bh . Tl
+        p.lora_kblocks = 3 * p.seg_len;
+    } else {
+        p.seg_len = 1;
+    }
+    // 5. the main product
+    p.w = w; p.y = y; p.ldy = ldy; p.m = m; p.n = n; p.k = k;
+    p.limbs = limbs; p.tt = tt;
+    p.n_tiles = (n + kTileN - 1) / kTileN;
+    p.m_tiles = (m + tt - 1) / tt;
+    p.kblocks = k / kBlockK;
+    if ((e = launch_kernel(p, tm_x, tm_w, tm_da, tm_db, sm_count, s)) != cudaSuccess) return fail("GEMM launch", e);
+    ++nl;
+    if (launches) *launches = nl;
+    return cudaSuccess;
 }
 
 }  // namespace lq4

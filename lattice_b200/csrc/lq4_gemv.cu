@@ -195,14 +195,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_mma_kernel(const GemvPar
         // Waits for every CTA's partial projection and sums them in CTA order.
         auto gather_t = [&]() {
             if (tid == 0) {
-                const unsigned long long t0 = globaltimer_ns();
+                const long long t0 = wait_clock();
                 while (ld_acquire_u32(p.tsync) < (uint32_t)G) {
-                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                    if (wait_expired(t0)) {
                         s_twait_failed = 1;
                         atomicOr(p.status, kDevErrGridWaitTimeout);
                         break;
                     }
-                    __nanosleep(64);
                 }
             }
             named_bar_sync(kBarConsumers, kConsumerThreads);

@@ -66,7 +66,8 @@ struct GemvParams {
     // resident decode kernel (lq4_decode.cu)
     uint32_t stage_blocks;  // Q4 blocks of one row per pipeline stage: 20, 12 or 4
     uint32_t spt;           // stages per tile = ceil(kb / stage_blocks)
-    int32_t sm_count;       // 0: plan for a full GPU
+    int32_t sm_count;       // SMs of the device (0: assume 148)
+    uint32_t whole_tiles;   // 1: every CTA gets entire tiles, no cross-CTA partial sums
 };
 
 // ---- lq4_decode.cu ---------------------------------------------------------------

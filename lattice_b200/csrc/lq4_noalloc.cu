@@ -23,7 +23,7 @@ constexpr uint32_t kNaMaxN = 32768;         // output rows per call
 constexpr uint32_t kNaMaxRank = 64;         // LoRA rank
 constexpr size_t kNaCtrlBytes = 256 + (size_t)(kNaMaxN / kGemvTileRows) * 8 * 4;                  // status, counters, tickets
 constexpr size_t kNaPartialBytes = (size_t)kNaMaxGrid * 2 * kGemvTileRows * 4 * sizeof(float);    // 655,360
-constexpr size_t kNaTpartBytes = (size_t)kNaMaxGrid * kNaMaxM * kNaMaxRank * sizeof(float);       // 163,840
+constexpr size_t kNaTpartBytes = (size_t)kNaMaxGrid * kNaMaxM * kNaMaxRank * 8;                   // 327,680: {value, tag} pairs
 constexpr size_t kNaScratchBytes = ((kNaCtrlBytes + 255) / 256) * 256 + kNaPartialBytes + kNaTpartBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
@@ -99,9 +99,7 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
     p.nt = 1; p.gmax = 2 * a->m;
     p.x = a->x; p.x_dtype = a->x_dtype; p.signs = signs;
     if (a->lora) { p.la = a->lora->a; p.lb = a->lora->b; p.rank = rank; p.lscale = a->lora->scale; }
-    const uint64_t total = (uint64_t)p.tiles * p.kg;
-    uint64_t grid = total < (uint64_t)sms ? total : (uint64_t)sms;
-    if (grid > kNaMaxGrid) grid = kNaMaxGrid;
+    p.sm_count = sms < (int)kNaMaxGrid ? sms : (int)kNaMaxGrid;
 
     // carve the array: [status | counters | tickets] [partials] [LoRA partials]
     p.status = reinterpret_cast<int32_t*>(base);
@@ -111,11 +109,15 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
     p.partials = reinterpret_cast<float*>(q);
     p.tpart = reinterpret_cast<float*>(q + kNaPartialBytes);
     p.use_pdl = 0;
-    // The array keeps whatever the previous call left: the counters and tickets must start at zero.
-    e = cudaMemsetAsync(base, 0, kNaCtrlBytes, s);
+    // The array keeps whatever the previous call left, on purpose: every cross-CTA message in it is
+    // tagged with the launch generation stored in the array, which each launch advances, so stale
+    // messages are never mistaken for new ones; only the status word has to start at zero.
+    e = cudaMemsetAsync(base, 0, 4, s);
     if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
     const size_t smem = gemv_plan_smem(p, true);
     if (!smem) return fail(LQ4_ERR_NOSPACE, "shared-memory plan does not fit");
+    const uint64_t units = decode_units(p);
+    const uint64_t grid = units < (uint64_t)p.sm_count ? units : (uint64_t)p.sm_count;
     e = launch_gemv_mma(p, true, smem, (int)grid, s);
     if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
     return LQ4_OK;

@@ -74,7 +74,7 @@ def test_noalloc_entry_point_matches_lq4_linear_on_two_calls_in_a_row():
 def test_noalloc_entry_point_rejects_what_exceeds_its_fixed_scratch():
     from lattice_b200._lib import LinearArgs, LoraDesc
     L = _lib.lib()
-    x = torch.zeros((8, 1024), device="cuda")
+    x = torch.zeros((8, 65536), device="cuda")
     w = torch.zeros(64 * 32 * 20, dtype=torch.uint8, device="cuda")
     y = torch.zeros((8, 64), device="cuda")
 
@@ -85,7 +85,7 @@ def test_noalloc_entry_point_rejects_what_exceeds_its_fixed_scratch():
 
     assert call(m=5) == _lib.ERR_NOSPACE and b"at most 4 tokens" in L.lq4_last_error()
     assert call(n=40000) == _lib.ERR_NOSPACE
-    assert call(k=32768) == _lib.ERR_NOSPACE          # the activation row no longer fits in shared memory
+    assert call(m=4, k=65536) == _lib.ERR_NOSPACE     # the activation rows no longer fit in shared memory
     big = LoraDesc(x.data_ptr(), x.data_ptr(), 65, 1.0)
     assert call(lora=big) == _lib.ERR_NOSPACE
     assert call(k=96) == _lib.ERR_ALIGN
