@@ -144,12 +144,16 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
     const bool resident = gemv_resident_fits(m, a->k, signs != nullptr);
     if (resident) {
         p.x = x; p.x_dtype = x_dtype; p.signs = signs;
-        if (p.rank) {
-            if ((st = ensure(ctx, ctx->tpart, (size_t)grid * m * p.rank * 8, true, s))) return st;
-            p.tpart = (float*)ctx->tpart.p;
-        }
-        p.tsync = ctx->tsync;      // launch generation and end-of-launch counter: always needed
+        p.tsync = ctx->tsync;      // launch generation and end-of-launch counter
         p.use_pdl = ctx->pdl;
+        if (p.rank) {
+            // the projection t = A x runs as a small kernel right before; the decode kernel starts
+            // streaming weights meanwhile and waits for t only before its first epilogue
+            if ((st = ensure(ctx, ctx->t, (size_t)m * p.rank * sizeof(float), false, s))) return st;
+            LQ4_CUDA(launch_lora_project(x, x_dtype, m, a->k, p.la, p.rank, (float*)ctx->t.p, p.use_pdl, s));
+            ctx->launches += 1;
+            p.t_g = (const float*)ctx->t.p;
+        }
         p.sm_count = ctx->sm_count;
         const size_t smem = gemv_plan_smem(p, true);
         if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "resident plan does not fit");
@@ -310,7 +314,7 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
 
     // The decode kernel rotates in its own prologue when the row fits; otherwise the
     // rotation runs as a kernel of its own into the workspace.
-    const bool in_kernel_rot = signs && path == LQ4_PATH_GEMV_MMA && a->m <= kGemvMaxM &&
+    const bool in_kernel_rot = signs && path == LQ4_PATH_GEMV_MMA && a->m <= kGemvMaxM && rank == 0 &&
                                gemv_resident_fits(a->m, a->k, true);
     if (signs && !in_kernel_rot) {
         if ((st = ensure(ctx, ctx->xrot, (size_t)a->m * a->k * 4, false, s))) return st;

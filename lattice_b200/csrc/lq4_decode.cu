@@ -126,9 +126,8 @@ __device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT
 
 // Prologue of the 256 consumer threads: rotation, LoRA partial projection, activation limbs.
 template <int MT>
-__device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, uint32_t tag) {
+__device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
     const uint32_t K = p.k, M = p.m;
-    const int cw = ctid >> 5, lane = ctid & 31;
     float* xrot = reinterpret_cast<float*>(smem + p.off_xrot);
     const bool rot = p.signs != nullptr;
 
@@ -150,25 +149,6 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, ui
         const float sc = __fdiv_rn(1.0f, __fsqrt_rn((float)K));
         for (uint32_t i = ctid; i < M * K; i += kConsumerThreads) xrot[i] = __fmul_rn(xrot[i], sc);
         named_bar_sync(kBarConsumers, kConsumerThreads);
-    }
-
-    if (p.rank) {
-        const uint64_t G = gridDim.x;
-        const uint32_t k0 = (uint32_t)(((uint64_t)blockIdx.x * p.kb) / G) * 32;
-        const uint32_t k1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * p.kb) / G) * 32;
-        const uint32_t pairs = M * p.rank;
-        for (uint32_t pr = cw; pr < pairs; pr += 8) {
-            const uint32_t mm = pr / p.rank, j = pr - mm * p.rank;
-            const float* arow = p.la + (size_t)j * K;
-            float s = 0.0f;
-            for (uint32_t kk = k0 + lane; kk < k1; kk += 32) {
-                const float xv = rot ? xrot[mm * K + kk] : load_act(p.x, p.x_dtype, (size_t)mm * K + kk);
-                s = fmaf(__ldg(arow + kk), xv, s);
-            }
-#pragma unroll
-            for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
-            if (lane == 0) msg_store(reinterpret_cast<uint2*>(p.tpart) + (size_t)blockIdx.x * pairs + pr, s, tag);
-        }
     }
 
     // limbs: [block][token][limb 0, limb 1][32 B]; per-block info {scale, sum}: [block][token]
@@ -269,35 +249,16 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
     } else {
         // ------------------------------ consumers ------------------------------
         const int g = lane >> 2, t = lane & 3;
-        float* t_s = reinterpret_cast<float*>(smem + p.off_t);
-        if (p.use_pdl) pdl_wait_prior_grids();
+        // With a LoRA adapter the launch before this one is the small projection kernel (t = A x),
+        // which itself waited for everything earlier before it let this grid start: x is final, and
+        // only t must be waited for, right before the first epilogue.  Without an adapter the previous
+        // launch may be the producer of x, so the wait comes first.
+        bool prior_done = false;
+        if (p.use_pdl && !p.rank) { pdl_wait_prior_grids(); prior_done = true; }
         // launch generation: bumped once at the end of every launch, so a message written by an
         // earlier launch never carries the current tag
         const uint32_t tag = *reinterpret_cast<volatile const uint32_t*>(p.tsync) + 1u;
-        decode_prologue<MT>(p, smem, tid, tag);
-
-        // Sums every CTA's partial projection: one warp per (token, rank) pair, lanes poll different
-        // CTAs' messages, then a fixed shuffle tree adds them (same result whatever the arrival order).
-        auto gather_t = [&]() {
-            const uint32_t pairs = p.m * p.rank;
-            const uint2* msgs = reinterpret_cast<const uint2*>(p.tpart);
-            for (uint32_t pr = warp; pr < pairs; pr += 8) {
-                float s = 0.0f;
-                bool good = true;
-                for (uint32_t c = lane; c < (uint32_t)G; c += 32) {
-                    float v;
-                    good = msg_wait(msgs + (size_t)c * pairs + pr, tag, v) && good;
-                    s += v;
-                }
-                if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
-#pragma unroll
-                for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
-                if (lane == 0) t_s[pr] = s;
-            }
-            named_bar_sync(kBarConsumers, kConsumerThreads);
-        };
-        // The ring keeps filling while this waits for the other CTAs' partial projections.
-        if (p.rank) gather_t();
+        decode_prologue<MT>(p, smem, tid);
 
         // A lane supplies B-operand registers only for the column pair (limb 0, limb 1) of its own
         // block; every other lane reads a block of zeros, so that its columns contribute nothing.
@@ -452,6 +413,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
             // epilogue: LoRA term (the quad splits the rank), then quad thread t stores token t
             const uint32_t rowa = tile * kGemvTileRows + warp * 16 + g, rowb = rowa + 8;
             if (p.rank) {
+                if (!prior_done) { if (p.use_pdl) pdl_wait_prior_grids(); prior_done = true; }
                 float la[MT], lb2[MT];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) la[mt] = lb2[mt] = 0.0f;
@@ -462,7 +424,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                     const float ba = __ldg(bra + j), bb = __ldg(brb + j);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const float tv = t_s[mt * p.rank + j];
+                        const float tv = __ldcg(p.t_g + mt * p.rank + j);
                         la[mt] = fmaf(ba, tv, la[mt]);
                         lb2[mt] = fmaf(bb, tv, lb2[mt]);
                     }
@@ -564,6 +526,68 @@ cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtenso
 }
 
 }  // namespace
+
+// t[tok][j] = sum_k A[j][k] * x[tok][k]: one CTA per (token, rank row), fixed reduction order.
+// Runs right before the decode kernel.  With programmatic dependent launch it first waits for the
+// work before it (the producer of x) and only then lets the decode kernel start, which may
+// therefore read x at once and needs to wait for this grid only before it uses t.
+__global__ void __launch_bounds__(256) lora_project_kernel(const void* __restrict__ x, int x_dtype, uint32_t k,
+                                                           const float* __restrict__ la, uint32_t rank,
+                                                           float* __restrict__ t, int use_pdl, int vec4) {
+    if (use_pdl) {
+        pdl_wait_prior_grids();
+        pdl_launch_dependents();
+    }
+    const uint32_t pr = blockIdx.x, tok = pr / rank, j = pr - tok * rank;
+    const float* arow = la + (size_t)j * k;
+    float s = 0.0f;
+    if (vec4) {
+        const float4* a4 = reinterpret_cast<const float4*>(arow);
+        const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)tok * k);
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < k / 4; i += 256) {
+            const float4 a = __ldg(a4 + i), b = x4[i];
+            s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
+        }
+    } else {
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < k; i += 256) s = fmaf(__ldg(arow + i), load_act(x, x_dtype, (size_t)tok * k + i), s);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __shared__ float part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) t[pr] = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+}
+
+cudaError_t launch_lora_project_impl(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
+                                     float* t, int use_pdl, cudaStream_t s) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(m * rank);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (use_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    const int vec4 = x_dtype == LQ4_DTYPE_F32 && k % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(la) & 15) == 0;
+    return cudaLaunchKernelEx(&cfg, lora_project_kernel, x, x_dtype, k, la, rank, t, use_pdl, vec4);
+}
+
+
+cudaError_t launch_lora_project(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
+                                float* t, int use_pdl, cudaStream_t s) {
+    return launch_lora_project_impl(x, x_dtype, m, k, la, rank, t, use_pdl, s);
+}
+
 
 size_t decode_plan_smem(GemvParams& p) {
     if (p.m == 0 || p.m > 4 || p.kb == 0 || p.kb % kGemvGranuleBlocks != 0) return 0;

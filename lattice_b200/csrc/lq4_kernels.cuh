@@ -77,6 +77,9 @@ size_t decode_plan_smem(GemvParams& p);
 // Work units (tile, stage) of a planned launch; the grid is min(#SM, units).
 uint64_t decode_units(const GemvParams& p);
 cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s);
+// t = A x for the decode kernel's LoRA epilogue; launched right before launch_decode.
+cudaError_t launch_lora_project(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
+                                float* t, int use_pdl, cudaStream_t s);
 
 // Fills the smem-dependent fields of `p` and returns the dynamic shared memory the
 // launch needs, or 0 if the shape does not fit the requested variant.

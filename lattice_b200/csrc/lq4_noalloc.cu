@@ -23,7 +23,7 @@ constexpr uint32_t kNaMaxN = 32768;         // output rows per call
 constexpr uint32_t kNaMaxRank = 64;         // LoRA rank
 constexpr size_t kNaCtrlBytes = 256 + (size_t)(kNaMaxN / kGemvTileRows) * 8 * 4;                  // status, counters, tickets
 constexpr size_t kNaPartialBytes = (size_t)kNaMaxGrid * 2 * kGemvTileRows * 4 * sizeof(float);    // 655,360
-constexpr size_t kNaTpartBytes = (size_t)kNaMaxGrid * kNaMaxM * kNaMaxRank * 8;                   // 327,680: {value, tag} pairs
+constexpr size_t kNaTpartBytes = 4096;                                                           // t = A x: up to 4 x 64 floats
 constexpr size_t kNaScratchBytes = ((kNaCtrlBytes + 255) / 256) * 256 + kNaPartialBytes + kNaTpartBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
@@ -64,6 +64,8 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
         if (!a->rot->signs || a->rot->dim != a->k || (a->k & (a->k - 1))) return fail(LQ4_ERR_ROT, "invalid rotation descriptor");
         signs = a->rot->signs;
     }
+    if (signs && a->lora)
+        return fail(LQ4_ERR_UNSUPPORTED, "rotation together with LoRA needs a workspace: use lq4_linear");
     if (!gemv_resident_fits(a->m, a->k, signs != nullptr))
         return fail(LQ4_ERR_NOSPACE, "m * k too large: the activation row(s) must fit in shared memory for this entry point");
 
@@ -107,7 +109,7 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
     p.tickets = reinterpret_cast<uint32_t*>(base + 256);
     unsigned char* q = base + ((kNaCtrlBytes + 255) / 256) * 256;
     p.partials = reinterpret_cast<float*>(q);
-    p.tpart = reinterpret_cast<float*>(q + kNaPartialBytes);
+    float* t_scratch = reinterpret_cast<float*>(q + kNaPartialBytes);     // t = A x, m * rank floats
     p.use_pdl = 0;
     // The array keeps whatever the previous call left, on purpose: every cross-CTA message in it is
     // tagged with the launch generation stored in the array, which each launch advances, so stale
@@ -116,6 +118,11 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
     if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
     const size_t smem = gemv_plan_smem(p, true);
     if (!smem) return fail(LQ4_ERR_NOSPACE, "shared-memory plan does not fit");
+    if (p.rank) {
+        e = launch_lora_project(a->x, a->x_dtype, a->m, a->k, p.la, p.rank, t_scratch, 0, s);
+        if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
+        p.t_g = t_scratch;
+    }
     const uint64_t units = decode_units(p);
     const uint64_t grid = units < (uint64_t)p.sm_count ? units : (uint64_t)p.sm_count;
     e = launch_gemv_mma(p, true, smem, (int)grid, s);
