@@ -33,7 +33,6 @@ using namespace gemv;
 
 constexpr int kBigBlocks = 20;                                   // blocks per row in a big stage
 constexpr int kSmallBlocks = kGemvGranuleBlocks;                 // 4
-constexpr int kBigGranules = kBigBlocks / kGemvGranuleBlocks;    // 5
 constexpr uint32_t kSlotBytes = kGemvTileRows * kBigBlocks * kBlockBytes;      // 51,200
 constexpr uint32_t kSmallBytes = kGemvTileRows * kSmallBlocks * kBlockBytes;   // 10,240
 constexpr int kMaxStages = 8;
@@ -124,6 +123,10 @@ __device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT
     if (j == 0) sx[(size_t)blk * MT + mp] = make_float2(s0, sum);
 }
 
+// Granules (4 blocks each) the next stage takes when `left` remain in the segment: 5, 3 or 1.
+// Row strides of 100, 60 and 20 words keep the consumer loads free of bank conflicts.
+__device__ __forceinline__ uint32_t stage_granules(uint32_t left) { return left >= 5 ? 5u : (left >= 3 ? 3u : 1u); }
+
 // Prologue of the 256 consumer threads: rotation, LoRA partial projection, activation limbs.
 template <int MT>
 __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
@@ -156,11 +159,12 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
     float2* sx = reinterpret_cast<float2*>(smem + p.off_sx);
     const uint32_t noct = K / 8;
     for (uint32_t mp = 0; mp < (uint32_t)MT; ++mp) {
-        // four octets per thread and pass: all global loads are issued before the first use
-        for (uint32_t o0 = 0; o0 < noct; o0 += 4 * kConsumerThreads) {
-            float v[4][8];
+        // several octets per thread and pass: all global loads are issued before the first use
+        constexpr int kBatch = MT <= 2 ? 8 : 4;
+        for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * kConsumerThreads) {
+            float v[kBatch][8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kBatch; ++u) {
                 const uint32_t o = o0 + u * kConsumerThreads + ctid;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
@@ -174,7 +178,7 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < kBatch; ++u) {
                 const uint32_t o = o0 + u * kConsumerThreads + ctid;
                 store_limbs(xs, sx, MT, mp, o, o < noct, v[u]);
             }
@@ -186,7 +190,7 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
 template <int MT>
 __global__ void __launch_bounds__(kGemvThreads, 1)
 decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
-              const __grid_constant__ CUtensorMap tm_small) {
+              const __grid_constant__ CUtensorMap tm_mid, const __grid_constant__ CUtensorMap tm_small) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
@@ -228,15 +232,15 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 const uint64_t left = r1 - pos;
                 const uint32_t g1 = (uint64_t)(p.kg - g0) < left ? p.kg : (uint32_t)(g0 + left);
                 for (uint32_t gs = g0; gs < g1; ++it) {
-                    const bool big = g1 - gs >= (uint32_t)kBigGranules;
+                    const uint32_t ngr = stage_granules(g1 - gs);
                     const uint32_t s = it % NST;
                     if (!mbar_wait(&empty[s], ((it / NST) & 1u) ^ 1u)) { ok = false; break; }
                     uint8_t* st = smem + p.off_stage + (size_t)s * kSlotBytes;
-                    mbar_arrive_expect_tx(&full[s], big ? kSlotBytes : kSmallBytes);
+                    mbar_arrive_expect_tx(&full[s], ngr * kSmallBytes);
                     // coordinates: x in 4-byte elements along the row, y = first row of the tile
-                    tma_load_2d(st, big ? &tm_big : &tm_small, (int32_t)(gs * kGemvGranuleBlocks * 5),
+                    tma_load_2d(st, ngr == 5 ? &tm_big : (ngr == 3 ? &tm_mid : &tm_small), (int32_t)(gs * kGemvGranuleBlocks * 5),
                                 (int32_t)(tile * kGemvTileRows), &full[s], pol);
-                    gs += big ? kBigGranules : 1;
+                    gs += ngr;
                 }
                 pos += g1 - g0;
             }
@@ -289,9 +293,8 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
             }
 
             for (uint32_t gs = g0; gs < g1; ++it) {
-                const bool big = g1 - gs >= (uint32_t)kBigGranules;
-                const uint32_t ngr = big ? kBigGranules : 1;
-                const uint32_t rs = big ? kBigBlocks * kBlockBytes : kSmallBlocks * kBlockBytes;
+                const uint32_t ngr = stage_granules(g1 - gs);
+                const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
                 const uint32_t s = it % NST;
                 if (!mbar_wait(&full[s], (it / NST) & 1u)) { ok = false; break; }
                 const uint8_t* st = smem + p.off_stage + (size_t)s * kSlotBytes;
@@ -503,11 +506,15 @@ bool make_weight_map(CUtensorMap* map, const uint8_t* w, uint32_t n, uint32_t kb
 inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 template <int MT>
-cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtensorMap& small, size_t smem, int grid,
-                      cudaStream_t s) {
+cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtensorMap& mid, const CUtensorMap& small,
+                      size_t smem, int grid, cudaStream_t s) {
     auto kern = decode_kernel<MT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+    static bool attr_set = false;      // one opt-in to the full shared-memory carve-out per kernel
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - 1024);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kGemvThreads);
@@ -522,7 +529,7 @@ cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtenso
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kern, p, big, small);
+    return cudaLaunchKernelEx(&cfg, kern, p, big, mid, small);
 }
 
 }  // namespace
@@ -623,14 +630,29 @@ size_t decode_plan_smem(GemvParams& p) {
 uint64_t decode_units(const GemvParams& p) { return p.whole_tiles ? (uint64_t)p.tiles : (uint64_t)p.tiles * p.kg; }
 
 cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s) {
-    CUtensorMap big, small;
-    if (!make_weight_map(&big, p.w, p.n, p.kb, kBigBlocks) || !make_weight_map(&small, p.w, p.n, p.kb, kSmallBlocks))
-        return cudaErrorInvalidValue;
+    // Encoding a tensor map costs about a microsecond of host time; weights are long-lived, so the
+    // three maps of a payload are kept in a small per-thread cache keyed by (pointer, n, k).
+    struct Entry { const uint8_t* w; uint32_t n, kb; CUtensorMap big, mid, small; };
+    thread_local Entry cache[32];
+    thread_local uint32_t next = 0;
+    Entry* hit = nullptr;
+    for (Entry& e : cache)
+        if (e.w == p.w && e.n == p.n && e.kb == p.kb) { hit = &e; break; }
+    if (!hit) {
+        Entry& e = cache[next++ % 32];
+        if (!make_weight_map(&e.big, p.w, p.n, p.kb, 20) || !make_weight_map(&e.mid, p.w, p.n, p.kb, 12) ||
+            !make_weight_map(&e.small, p.w, p.n, p.kb, 4)) {
+            e.w = nullptr;
+            return cudaErrorInvalidValue;
+        }
+        e.w = p.w; e.n = p.n; e.kb = p.kb;
+        hit = &e;
+    }
     switch (p.m) {
-        case 1: return launch_mt<1>(p, big, small, smem, grid, s);
-        case 2: return launch_mt<2>(p, big, small, smem, grid, s);
-        case 3: return launch_mt<3>(p, big, small, smem, grid, s);
-        case 4: return launch_mt<4>(p, big, small, smem, grid, s);
+        case 1: return launch_mt<1>(p, hit->big, hit->mid, hit->small, smem, grid, s);
+        case 2: return launch_mt<2>(p, hit->big, hit->mid, hit->small, smem, grid, s);
+        case 3: return launch_mt<3>(p, hit->big, hit->mid, hit->small, smem, grid, s);
+        case 4: return launch_mt<4>(p, hit->big, hit->mid, hit->small, smem, grid, s);
         default: return cudaErrorInvalidValue;
     }
 }
