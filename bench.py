@@ -220,7 +220,7 @@ def run_ours(args):
     gen.manual_seed(99)
     xs = {k: torch.randn((m, k), generator=gen, device=dev) for k in (5120, 17408)}
     y_local = {si: torch.empty((m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
-    y_full = {si: torch.empty((world, m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
+    y_full = {si: torch.empty((world * m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
     torch.cuda.synchronize()
 
     def step():
@@ -232,7 +232,7 @@ def run_ours(args):
 
     # pinned host buffers for the end-to-end variant
     hx = {k: torch.randn((m, k)).pin_memory() for k in (5120, 17408)}
-    hy = {si: torch.empty((world, m, layers[0][si]["nl"])).pin_memory() for si in range(len(SHAPES))}
+    hy = {si: torch.empty((world * m, layers[0][si]["nl"])).pin_memory() for si in range(len(SHAPES))}
     dx = {k: torch.empty((m, k), device=dev) for k in (5120, 17408)}
 
     def e2e_step():

@@ -50,12 +50,12 @@ class ShardedLinear:
             return y_local
         if len(set(self.sizes)) == 1:
             # equal shards: one all_gather into a [world, m, n/world] buffer, then a strided view
-            if self._gather_buf is None or self._gather_buf.shape[1] != m:
-                self._gather_buf = torch.empty((self.world, m, self.sizes[0]), dtype=y_local.dtype, device=y_local.device)
+            if self._gather_buf is None or self._gather_buf.shape[0] != self.world * m:
+                self._gather_buf = torch.empty((self.world * m, self.sizes[0]), dtype=y_local.dtype, device=y_local.device)
             dist.all_gather_into_tensor(self._gather_buf, y_local.contiguous(), group=self.group)
             if m == 1:
                 return self._gather_buf.view(1, self.n)
-            return self._gather_buf.permute(1, 0, 2).reshape(m, self.n)
+            return self._gather_buf.view(self.world, m, self.sizes[0]).permute(1, 0, 2).reshape(m, self.n)
         parts = [torch.empty((m, s), dtype=y_local.dtype, device=y_local.device) for s in self.sizes]
         dist.all_gather(parts, y_local.contiguous(), group=self.group)
         return torch.cat(parts, dim=1)

@@ -305,3 +305,38 @@ def test_launches_are_counted(be):
     before = be.launch_count
     be.linear(dev(case["x"]), qw)
     assert be.launch_count == before + 1      # m = 1 runs as a single fused kernel
+
+
+# ---------------------------------------------------------------- prefill (tensor-core) path
+@pytest.mark.parametrize("m,k,n,rank,bf16", [(17, 128, 128, 0, False), (64, 256, 256, 0, False),
+                                              (200, 1024, 300, 16, False), (300, 512, 520, 64, True),
+                                              (33, 1024, 129, 5, True), (1024, 1024, 640, 64, True)])
+def test_prefill_gemm_matches_oracle(be, m, k, n, rank, bf16):
+    case = make_case(4, m, k, n, rank=rank, alpha=2.0 * rank, bf16_x=bf16, extra=m + n)
+    y = run_case(be, case, bf16=bf16)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+    # the decode kernel, forced onto the same inputs in chunks of 16 tokens, agrees as well
+    if m <= 64:
+        y2 = run_case(be, case, bf16=bf16, path=_lib.PATH_GEMV_MMA)
+        assert tol_ratio(y2, case["y_ref"]) <= 1.0
+
+
+def test_config5_quarot_prefill(be):
+    case = make_case(5, 512, 4096, 1376, quarot=True)
+    y = run_case(be, case)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+def test_config4_shape_slice_prefill_lora64(be):
+    # config 4 (M=2048, K=5120, LoRA r=64, bf16 activations) on a 640-row slice of the 17408 outputs
+    case = make_case(4, 2048, 5120, 640, rank=64, alpha=128.0, bf16_x=True)
+    y = run_case(be, case, bf16=True)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+def test_prefill_edge_scale_activations(be):
+    # +-500 activations (reference: metal_qwen35.rs:23530-23692, relative error bound 2 %)
+    case = make_case(7, 72, 512, 48, x_scale=500.0)
+    y = run_case(be, case)
+    assert np.max(np.abs(y - case["y_ref"])) / np.max(np.abs(case["y_ref"])) < 0.02
+    assert tol_ratio(y, case["y_ref"]) <= 1.0

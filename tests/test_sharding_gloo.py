@@ -1,0 +1,70 @@
+"""N-sharded column-parallel path on CPU: two gloo ranks, each computes its row range with the
+oracle (the GPU kernel is exercised elsewhere), the output slices are all-gathered."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, m, k, n, rank_lora, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from lattice_b200.sharded import ShardedLinear, shard_plan
+    from tests._cases import make_case
+
+    case = make_case(3, m, k, n, rank=rank_lora, alpha=2.0 * rank_lora, extra=7)
+    n0, n1, off = shard_plan(n, k, world, rank)
+    assert off == n0 * (k // 32) * 20
+    payload = case["payload"][off: off + (n1 - n0) * (k // 32) * 20]      # the shard is a byte range
+    lora = None
+    if rank_lora:
+        a, b, s = case["lora"]
+        lora = (a, b[n0:n1], s)                                           # A replicated, rows of B sharded
+
+    def compute(x):
+        return torch.from_numpy(oracle.q4_linear(x.numpy(), payload, m, n1 - n0, k, lora=lora))
+
+    lin = ShardedLinear(n, k, compute)
+    assert (lin.n0, lin.n1) == (n0, n1)
+    y = lin.forward(torch.from_numpy(case["x"]))
+    assert y.shape == (m, n)
+    np.save(os.path.join(out_dir, f"y{rank}.npy"), y.numpy())
+    if rank == 0:
+        np.save(os.path.join(out_dir, "ref.npy"), case["y_ref"])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("m,k,n,r", [(1, 256, 96, 4), (3, 128, 70, 0)])      # 70 rows: uneven shards of 35
+def test_two_rank_sharded_linear_gathers_full_output(tmp_path, m, k, n, r):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), m, k, n, r, str(tmp_path)), nprocs=world, join=True)
+    ref = np.load(tmp_path / "ref.npy")
+    for rank in range(world):
+        y = np.load(tmp_path / f"y{rank}.npy")
+        # each shard is the same arithmetic as the matching rows of the full product
+        assert np.max(np.abs(y - ref)) < 1e-5
+
+
+def test_three_rank_uneven_plan():
+    from lattice_b200.sharded import shard_plan
+    sizes = [shard_plan(100, 64, 3, r) for r in range(3)]
+    assert [s[0] for s in sizes] == [0, 33, 66] and sizes[-1][1] == 100
