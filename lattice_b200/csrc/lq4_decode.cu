@@ -58,20 +58,6 @@ __device__ __forceinline__ uint2 msg_load(const uint2* p) {
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
     return r;
 }
-// Polls until the message carries `tag`; false after the time limit.
-__device__ __forceinline__ bool msg_wait(const uint2* p, uint32_t tag, float& v) {
-    uint2 r = msg_load(p);
-    if (r.y != tag) {
-        const long long t0 = wait_clock();
-        do {
-            r = msg_load(p);
-            if (r.y == tag) break;
-        } while (!wait_expired(t0));
-    }
-    v = __uint_as_float(r.x);
-    return r.y == tag;
-}
-
 // u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
 __device__ __forceinline__ void imma_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -129,7 +115,7 @@ __device__ __forceinline__ uint32_t stage_granules(uint32_t left) { return left 
 
 // Prologue of the 256 consumer threads: rotation, LoRA partial projection, activation limbs.
 template <int MT>
-__device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
+__device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, uint64_t r0, uint64_t r1) {
     const uint32_t K = p.k, M = p.m;
     float* xrot = reinterpret_cast<float*>(smem + p.off_xrot);
     const bool rot = p.signs != nullptr;
@@ -155,9 +141,18 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
     }
 
     // limbs: [block][token][limb 0, limb 1][32 B]; per-block info {scale, sum}: [block][token]
+    // Only the k range(s) this CTA's share of the work touches are converted: with a long k and
+    // stream-K splitting that is a fraction of the row.  Ranges are in octets (8 activations).
     uint8_t* xs = smem + p.off_xs;
     float2* sx = reinterpret_cast<float2*>(smem + p.off_sx);
-    const uint32_t noct = K / 8;
+    const uint32_t opg = kGemvGranuleBlocks * 4;              // octets per granule
+    uint32_t a0 = 0, a1 = K / 8, b0 = 0, b1 = 0;              // two octet ranges [a0,a1) and [b0,b1)
+    if (r1 - r0 < p.kg) {
+        const uint32_t g0 = (uint32_t)(r0 % p.kg), len = (uint32_t)(r1 - r0);
+        if (g0 + len <= p.kg) { a0 = g0 * opg; a1 = (g0 + len) * opg; }
+        else { a0 = g0 * opg; a1 = p.kg * opg; b0 = 0; b1 = (g0 + len - p.kg) * opg; }
+    }
+    const uint32_t na = a1 - a0, noct = na + (b1 - b0);
     for (uint32_t mp = 0; mp < (uint32_t)MT; ++mp) {
         // several octets per thread and pass: all global loads are issued before the first use
         constexpr int kBatch = MT <= 2 ? 8 : 4;
@@ -165,13 +160,14 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
             float v[kBatch][8];
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const uint32_t o = o0 + u * kConsumerThreads + ctid;
+                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t o = i < na ? a0 + i : b0 + (i - na);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[u][i] = 0.0f;
-                if (o < noct) {
+                for (int e = 0; e < 8; ++e) v[u][e] = 0.0f;
+                if (i < noct) {
                     if (rot) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) v[u][i] = xrot[mp * K + o * 8 + i];
+                        for (int e = 0; e < 8; ++e) v[u][e] = xrot[mp * K + o * 8 + e];
                     } else {
                         load8(p.x, p.x_dtype, (size_t)mp * K + (size_t)o * 8, v[u]);
                     }
@@ -179,8 +175,9 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid) {
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const uint32_t o = o0 + u * kConsumerThreads + ctid;
-                store_limbs(xs, sx, MT, mp, o, o < noct, v[u]);
+                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+                store_limbs(xs, sx, MT, mp, o, i < noct, v[u]);
             }
         }
     }
@@ -199,6 +196,14 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t NST = p.nstages;
+#ifdef LQ4_TIMELINE
+    __shared__ unsigned long long s_tl[8];
+    auto stamp = [&](int i) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); s_tl[i] = t; };
+    if (tid == 0) stamp(0);
+#define LQ4_STAMP(i) do { if (tid == 0) stamp(i); } while (0)
+#else
+#define LQ4_STAMP(i) do {} while (0)
+#endif
     if (tid == 0) {
         for (uint32_t s = 0; s < NST; ++s) {
             mbar_init(&full[s], 1);
@@ -262,7 +267,9 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
         // launch generation: bumped once at the end of every launch, so a message written by an
         // earlier launch never carries the current tag
         const uint32_t tag = *reinterpret_cast<volatile const uint32_t*>(p.tsync) + 1u;
-        decode_prologue<MT>(p, smem, tid);
+        LQ4_STAMP(1);
+        decode_prologue<MT>(p, smem, tid, r0, r1);
+        LQ4_STAMP(2);
 
         // A lane supplies B-operand registers only for the column pair (limb 0, limb 1) of its own
         // block; every other lane reads a block of zeros, so that its columns contribute nothing.
@@ -297,6 +304,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
                 const uint32_t s = it % NST;
                 if (!mbar_wait(&full[s], (it / NST) & 1u)) { ok = false; break; }
+                if (it == 0) LQ4_STAMP(3);
                 const uint8_t* st = smem + p.off_stage + (size_t)s * kSlotBytes;
                 const uint8_t* row0 = st + (warp * 16 + g) * rs + t * kBlockBytes;
                 const uint8_t* row1 = row0 + 8 * rs;
@@ -351,6 +359,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 gs += ngr;
             }
             if (!ok) break;
+            LQ4_STAMP(4);
 
             // each thread of a quad covered blocks = t (mod 4): add the four
             float v[MT][2];
@@ -391,12 +400,20 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 bool good = true;
                 for (uint32_t c = blockIdx.x + 1 + lane; c <= c_last; c += 32) {
                     const uint2* src = reinterpret_cast<const uint2*>(p.partials) + ((size_t)c * kGemvTileRows + warp * 16) * MT;
+                    // all loads of a sweep are in flight together; sweep again only while a tag is missing
+                    uint2 msg[16 * MT];
+                    const long long t0 = wait_clock();
+                    bool all = false;
+                    while (!all) {
 #pragma unroll
-                    for (int i = 0; i < 16 * MT; ++i) {
-                        float q;
-                        good = msg_wait(src + i, tag, q) && good;
-                        part[i] += q;
+                        for (int i = 0; i < 16 * MT; ++i) msg[i] = msg_load(src + i);
+                        all = true;
+#pragma unroll
+                        for (int i = 0; i < 16 * MT; ++i) all = all && (msg[i].y == tag);
+                        if (!all && wait_expired(t0)) { good = false; break; }
                     }
+#pragma unroll
+                    for (int i = 0; i < 16 * MT; ++i) part[i] += __uint_as_float(msg[i].x);
                 }
                 if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
 #pragma unroll
@@ -458,6 +475,13 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
     // After a failed wait some TMA loads may still be in flight towards this CTA's shared
     // memory: wait (bounded) for the stages that were issued before leaving.
     __syncthreads();
+#ifdef LQ4_TIMELINE
+    if (tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+        stamp(5);
+        unsigned long long* out = reinterpret_cast<unsigned long long*>(p.y + p.n) + (blockIdx.x ? 8 : 0);   // experiment builds only: y needs 128 spare bytes
+        for (int i = 0; i < 6; ++i) out[i] = s_tl[i];
+    }
+#endif
     if (tid == 0) {
         // the last CTA to get here (all of them have read the generation by now) advances it
         const uint32_t old = atomicAdd(p.tsync + 1, 1u);
