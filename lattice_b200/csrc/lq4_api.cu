@@ -302,7 +302,7 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     int path = a->path;
     if (path == LQ4_PATH_AUTO) {
         if (!fast_layout) path = LQ4_PATH_GEMV_GENERIC;
-        else if (a->m <= kGemvMaxM) path = LQ4_PATH_GEMV_MMA;
+        else if (a->m <= 4 && gemv_resident_fits(a->m, a->k, false)) path = LQ4_PATH_GEMV_MMA;   // decode kernel
         else path = gemm_supported(a->m, a->n, a->k, rank) ? LQ4_PATH_GEMM_TC : LQ4_PATH_GEMV_MMA;
     }
     if (path != LQ4_PATH_GEMV_GENERIC && !fast_layout)

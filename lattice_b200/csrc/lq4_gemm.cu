@@ -24,6 +24,7 @@
 // the order in which the nibble extraction yields pairs, and the activation tiles are written
 // in the same order by the conversion kernel, so no shuffling is needed on either side.
 #include "lq4_gemm.cuh"
+#include "lq4_kernels.cuh"
 
 #include <cuda.h>
 
@@ -259,6 +260,9 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
                     if (!mbar_wait(&empty[s], ((it / kStages) & 1u) ^ 1u)) { ok = false; break; }
                     uint8_t* st = smem + kOffStages + s * kStageBytes;
                     if (kb < p.kblocks) {
+#ifdef LQ4_EXP_NO_X
+                        if (kb != 0) { mbar_arrive(&full[s]); continue; }
+#endif
                         mbar_arrive_expect_tx(&full[s], xbytes);
                         // the converted activations hold the hi limb in columns [0, k), the lo limb in [k, 2k)
                         tma_load_tile(st + kTileABytes, &tm_x, (int32_t)(kb * kBlockK), m0, &full[s]);
@@ -340,6 +344,9 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
 #pragma unroll
                     for (int i = 0; i < 5; ++i) { const uint2 v = src[i]; q[2 * i] = v.x; q[2 * i + 1] = v.y; }
                     uint8_t* a_tile = smem + kOffStages + s * kStageBytes;
+#ifdef LQ4_EXP_NO_DEQ
+                    if (q[0] == 0x12345678u)
+#endif
 #pragma unroll
                     for (int b = 0; b < 2; ++b) {
                         const uint32_t meta = q[5 * b];
@@ -529,27 +536,33 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
     GemmParams p{};
     p.status = status;
     if (rank) {
-        // 2. A -> [Ah | Al] in the activations' column order; 3. T = X A^T on the tensor cores (f32)
-        __half* al = reinterpret_cast<__half*>(base + ws.al);
         float* t = reinterpret_cast<float*>(base + ws.t);
-        const uint64_t a_oct = (uint64_t)rank * k / 8;
-        convert_rows_kernel<<<(unsigned)((a_oct + 255) / 256), 256, 0, s>>>(la, LQ4_DTYPE_F32, rank, k, al, 2ull * k, k);
-        ++nl;
-        CUtensorMap tm_al, tm_x32;
-        if (!make_f16_map(&tm_al, al, 2ull * k, rank, 2ull * k, kTileN)) return fail("tensor map (A)", cudaErrorInvalidValue);
-        if (!make_f16_map(&tm_x32, x16, (uint64_t)limbs * k, m, (uint64_t)limbs * k, 32)) return fail("tensor map (x32)", cudaErrorInvalidValue);
-        GemmParams q{};
-        q.status = status;
-        q.w = w; q.y = t; q.ldy = rank; q.m = m; q.n = rank; q.k = k;
-        q.limbs = 1; q.tt = 32; q.n_tiles = (rank + kTileN - 1) / kTileN; q.m_tiles = (m + 31) / 32;
-        q.kblocks = 0;
-        q.seg_len = k / kBlockK;
-        q.seg_a_off[0] = 0; q.seg_b_off[0] = 0;          // Ah . Xh
-        q.seg_a_off[1] = k; q.seg_b_off[1] = 0;          // Al . Xh
-        q.seg_a_off[2] = 0; q.seg_b_off[2] = k;          // Ah . Xl (two-limb activations only)
-        q.lora_kblocks = (limbs == 2 ? 3u : 2u) * q.seg_len;
-        if ((e = launch_kernel(q, tm_x32, tm_w, tm_al, tm_x32, sm_count, s)) != cudaSuccess) return fail("projection GEMM launch", e);
-        ++nl;
+        if (m <= 32) {
+            // few tokens: one CTA per (token, rank row) dot product is quicker than a GEMM with one or two tiles
+            if ((e = launch_lora_project(x, x_dtype, m, k, la, rank, t, 0, s)) != cudaSuccess) return fail("projection launch", e);
+            ++nl;
+        } else {
+            // 2. A -> [Ah | Al] in the activations' column order; 3. T = X A^T on the tensor cores (f32)
+            __half* al = reinterpret_cast<__half*>(base + ws.al);
+            const uint64_t a_oct = (uint64_t)rank * k / 8;
+            convert_rows_kernel<<<(unsigned)((a_oct + 255) / 256), 256, 0, s>>>(la, LQ4_DTYPE_F32, rank, k, al, 2ull * k, k);
+            ++nl;
+            CUtensorMap tm_al, tm_x32;
+            if (!make_f16_map(&tm_al, al, 2ull * k, rank, 2ull * k, kTileN)) return fail("tensor map (A)", cudaErrorInvalidValue);
+            if (!make_f16_map(&tm_x32, x16, (uint64_t)limbs * k, m, (uint64_t)limbs * k, 32)) return fail("tensor map (x32)", cudaErrorInvalidValue);
+            GemmParams q{};
+            q.status = status;
+            q.w = w; q.y = t; q.ldy = rank; q.m = m; q.n = rank; q.k = k;
+            q.limbs = 1; q.tt = 32; q.n_tiles = (rank + kTileN - 1) / kTileN; q.m_tiles = (m + 31) / 32;
+            q.kblocks = 0;
+            q.seg_len = k / kBlockK;
+            q.seg_a_off[0] = 0; q.seg_b_off[0] = 0;          // Ah . Xh
+            q.seg_a_off[1] = k; q.seg_b_off[1] = 0;          // Al . Xh
+            q.seg_a_off[2] = 0; q.seg_b_off[2] = k;          // Ah . Xl (two-limb activations only)
+            q.lora_kblocks = (limbs == 2 ? 3u : 2u) * q.seg_len;
+            if ((e = launch_kernel(q, tm_x32, tm_w, tm_al, tm_x32, sm_count, s)) != cudaSuccess) return fail("projection GEMM launch", e);
+            ++nl;
+        }
         // 4. hi/lo limbs of T and of s * B
         __half* tl = reinterpret_cast<__half*>(base + ws.tl);
         __half* bl = reinterpret_cast<__half*>(base + ws.bl);
