@@ -190,9 +190,15 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    def note(msg):
+        if args.verbose:
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    note("process group ready")
     dev = torch.device("cuda", local_rank)
     be = CudaQ4Backend(local_rank)
     m = args.m
@@ -222,6 +228,7 @@ def run_ours(args):
     y_local = {si: torch.empty((m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
     y_full = {si: torch.empty((world * m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
     torch.cuda.synchronize()
+    note("synthetic model built")
 
     def step():
         for projs in layers:
@@ -253,7 +260,11 @@ def run_ours(args):
     graph_info = {"mode": "eager"}
 
     def make_graphed(fn):
-        if args.eager:
+        if args.eager or world > 1:
+            # with NCCL collectives inside the step, capture is left out: a captured all-gather did
+            # not complete on this pool, so multi-GPU steps are timed as plain calls
+            if world > 1:
+                graph_info["mode"] = "eager (multi-GPU step with NCCL all-gather)"
             return fn, None
         try:
             side = torch.cuda.Stream()
@@ -307,12 +318,15 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     step_fn, per_step_launches = make_graphed(step)
+    note("launch mode: " + graph_info["mode"])
     ms, launches = timed(step_fn, args.steps, args.warmup, per_step_launches)
+    note("device-timed leg done")
     clocks = sampler.stop() if rank == 0 else None
     be.check_device_status()
     e2e_ms, _ = timed(e2e_step, max(1, min(args.steps, 20)), 3)
     e2e_steps = max(1, min(args.steps, 20))
     be.check_device_status()
+    note("end-to-end leg done")
 
     value = per_step_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e_value = per_step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
@@ -450,6 +464,7 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
+    ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--no-aux", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
