@@ -36,10 +36,8 @@ namespace {
 
 constexpr int kTileN = 128;          // weight rows per CTA tile (TMEM lanes)
 constexpr int kBlockK = 64;          // k per pipeline stage (128 bytes of f16: one swizzle atom)
-constexpr int kStages = 4;
 constexpr uint32_t kTileABytes = kTileN * kBlockK * 2;      // 16 KB dequantized weights
 constexpr uint32_t kTileBBytes = 256 * kBlockK * 2;         // 32 KB activations (both limb modes)
-constexpr uint32_t kStageBytes = kTileABytes + kTileBBytes; // 48 KB
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
@@ -192,10 +190,16 @@ struct GemmParams {
     int32_t* status;
 };
 
-constexpr int kRawStages = 3;                                  // each holds 128 rows x 4 blocks (two k blocks)
+// A CTA works on TWO 128-row sub-tiles of the weights against one activation tile: the activation
+// tile (the operand every n-tile has to re-read from L2) is loaded once per 256 weight rows.
+constexpr int kSubTiles = 2;
+constexpr int kCtaRows = kSubTiles * kTileN;                   // 256 weight rows per CTA tile
+constexpr int kRawStages = 3;                                  // each: one sub-tile, 128 rows x 4 blocks (two k blocks)
 constexpr uint32_t kRawBytes = kTileN * 4 * kBlockBytes;       // 10,240
+constexpr int kStages2 = 3;                                    // pipeline stages of A0 | A1 | B
+constexpr uint32_t kStage2Bytes = kSubTiles * kTileABytes + kTileBBytes;   // 64 KB
 constexpr uint32_t kOffStages = 1024;                          // barriers and the TMEM pointer live below
-constexpr uint32_t kOffRaw = kOffStages + kStages * kStageBytes;
+constexpr uint32_t kOffRaw = kOffStages + kStages2 * kStage2Bytes;
 constexpr uint32_t kGemmSmem = kOffRaw + kRawStages * kRawBytes;   // 228,352
 
 // One nibble word (8 weights of one block) -> 8 f16 weights q*d+b in the order (k0,k4,k1,k5,k2,k6,k3,k7).
@@ -210,7 +214,11 @@ __device__ __forceinline__ uint4 dequant_word_f16(uint32_t w, __half2 d2, __half
                       *reinterpret_cast<uint32_t*>(&r2), *reinterpret_cast<uint32_t*>(&r3));
 }
 
-constexpr int kGemmWarps = 11;       // 0 TMA (activations, LoRA), 1 MMA, 2-5 dequant, 6-9 epilogue, 10 TMA (raw Q4)
+// warps: 0 TMA (activations, dense LoRA tiles), 1 MMA issue, 2-9 dequant sub-tile 0, 10-17 dequant
+// sub-tile 1 (thread = one weight row x one Q4 block), 18-21 epilogue (warp % 4 = TMEM lane quarter),
+// 22 TMA (packed Q4 rows)
+constexpr int kDeqWarpsPerSub = 4;      // 4: a thread converts both Q4 blocks of its row; 8: one block each
+constexpr int kGemmWarps = 2 + 2 * kDeqWarpsPerSub + 4 + 1;
 
 __global__ void __launch_bounds__(kGemmWarps * 32, 1)
 gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
@@ -218,9 +226,9 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem);          // [kStages]  tile operands ready
-    uint64_t* empty = full + kStages;                            // [kStages]  MMAs that read the stage are done
-    uint64_t* raw_full = empty + kStages;                        // [kRawStages]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);          // [kStages2]  tile operands ready
+    uint64_t* empty = full + kStages2;                           // [kStages2]  MMAs that read the stage are done
+    uint64_t* raw_full = empty + kStages2;                       // [kRawStages]
     uint64_t* raw_empty = raw_full + kRawStages;                 // [kRawStages]
     uint64_t* acc_full = raw_empty + kRawStages;                 // [2] accumulator finished
     uint64_t* acc_empty = acc_full + 2;                          // [2] accumulator drained
@@ -229,8 +237,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 5); mbar_init(&empty[s], 1); }
-        for (int s = 0; s < kRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 4); }
+        for (int s = 0; s < kStages2; ++s) { mbar_init(&full[s], 1 + kDeqWarpsPerSub * kSubTiles); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < kRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kDeqWarpsPerSub); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         *s_err = 0;
         mbar_fence_init();
@@ -246,7 +254,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
 
     const uint32_t total_tiles = p.n_tiles * p.m_tiles;
     const uint32_t nkb = p.kblocks + p.lora_kblocks;
-    const uint32_t xbytes = p.limbs * p.tt * 128;                // activation bytes per Q4 stage (32 KB)
+    const uint32_t xbytes = p.limbs * p.tt * 128;                // activation bytes per Q4 stage
+    // accumulator buffers: two sub-tiles of tt columns each; double-buffered when they fit twice in 512 columns
+    const uint32_t acc_cols = kSubTiles * p.tt;
+    const uint32_t nbuf = acc_cols * 2 <= 512 ? 2u : 1u;
 
     if (warp == 0) {
         // ---------------- TMA: activation tiles, dense LoRA tiles ----------------
@@ -254,42 +265,44 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
             uint32_t it = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int32_t n0 = (int32_t)((tile / p.m_tiles) * kTileN), m0 = (int32_t)((tile % p.m_tiles) * p.tt);
+                const int32_t n0 = (int32_t)((tile / p.m_tiles) * kCtaRows), m0 = (int32_t)((tile % p.m_tiles) * p.tt);
                 for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
-                    const uint32_t s = it % kStages;
-                    if (!mbar_wait(&empty[s], ((it / kStages) & 1u) ^ 1u)) { ok = false; break; }
-                    uint8_t* st = smem + kOffStages + s * kStageBytes;
+                    const uint32_t s = it % kStages2;
+                    if (!mbar_wait(&empty[s], ((it / kStages2) & 1u) ^ 1u)) { ok = false; break; }
+                    uint8_t* st = smem + kOffStages + s * kStage2Bytes;
+                    uint8_t* bt = st + kSubTiles * kTileABytes;
                     if (kb < p.kblocks) {
-#ifdef LQ4_EXP_NO_X
-                        if (kb != 0) { mbar_arrive(&full[s]); continue; }
-#endif
                         mbar_arrive_expect_tx(&full[s], xbytes);
                         // the converted activations hold the hi limb in columns [0, k), the lo limb in [k, 2k)
-                        tma_load_tile(st + kTileABytes, &tm_x, (int32_t)(kb * kBlockK), m0, &full[s]);
-                        if (p.limbs == 2)
-                            tma_load_tile(st + kTileABytes + p.tt * 128, &tm_x, (int32_t)(p.k + kb * kBlockK), m0, &full[s]);
+                        tma_load_tile(bt, &tm_x, (int32_t)(kb * kBlockK), m0, &full[s]);
+                        if (p.limbs == 2) tma_load_tile(bt + p.tt * 128, &tm_x, (int32_t)(p.k + kb * kBlockK), m0, &full[s]);
                     } else {
+                        // dense stage: both operands by TMA; the A box spans all 256 rows (two sub-tiles)
                         const uint32_t d = kb - p.kblocks, seg = d / p.seg_len, within = d - seg * p.seg_len;
-                        mbar_arrive_expect_tx(&full[s], kTileABytes + p.tt * 128);
+                        mbar_arrive_expect_tx(&full[s], kSubTiles * kTileABytes + p.tt * 128);
                         tma_load_tile(st, &tm_da, (int32_t)(p.seg_a_off[seg] + within * kBlockK), n0, &full[s]);
-                        tma_load_tile(st + kTileABytes, &tm_db, (int32_t)(p.seg_b_off[seg] + within * kBlockK), m0, &full[s]);
+                        tma_load_tile(bt, &tm_db, (int32_t)(p.seg_b_off[seg] + within * kBlockK), m0, &full[s]);
                     }
                 }
             }
             if (!ok) { atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
         }
-    } else if (warp == 10) {
-        // ---------------- TMA: packed Q4 rows, 4 blocks (two k blocks) per load ----------------
+    } else if (warp == kGemmWarps - 1) {
+        // ---------------- TMA: packed Q4 rows, per sub-tile 4 blocks (two k blocks) per load ----------------
         if (lane == 0) {
             uint32_t rit = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int32_t n0 = (int32_t)((tile / p.m_tiles) * kTileN);
-                for (uint32_t pr = 0; pr < p.kblocks / 2; ++pr, ++rit) {
-                    const uint32_t rs = rit % kRawStages;
-                    if (!mbar_wait(&raw_empty[rs], ((rit / kRawStages) & 1u) ^ 1u)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&raw_full[rs], kRawBytes);
-                    tma_load_tile(smem + kOffRaw + rs * kRawBytes, &tm_w, (int32_t)(pr * 20), n0, &raw_full[rs]);
+                const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+                const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
+                for (uint32_t pr = 0; pr < p.kblocks / 2 && ok; ++pr) {
+                    for (uint32_t sub = 0; sub < nsub; ++sub, ++rit) {
+                        const uint32_t rs = rit % kRawStages;
+                        if (!mbar_wait(&raw_empty[rs], ((rit / kRawStages) & 1u) ^ 1u)) { ok = false; break; }
+                        mbar_arrive_expect_tx(&raw_full[rs], kRawBytes);
+                        tma_load_tile(smem + kOffRaw + rs * kRawBytes, &tm_w, (int32_t)(pr * 20), (int32_t)(n0 + sub * kTileN),
+                                      &raw_full[rs]);
+                    }
                 }
             }
             if (!ok) { atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
@@ -301,23 +314,27 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-                const uint32_t buf = tcount & 1u;
-                if (!mbar_wait(&acc_empty[buf], ((tcount >> 1) & 1u) ^ 1u)) { ok = false; break; }
+                const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+                const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
+                const uint32_t buf = tcount % nbuf;
+                if (!mbar_wait(&acc_empty[buf], ((tcount / nbuf) & 1u) ^ 1u)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * 256;
+                const uint32_t d_tmem = tmem_base + buf * acc_cols;
                 for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
-                    const uint32_t s = it % kStages;
-                    if (!mbar_wait(&full[s], (it / kStages) & 1u)) { ok = false; break; }
+                    const uint32_t s = it % kStages2;
+                    if (!mbar_wait(&full[s], (it / kStages2) & 1u)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + kOffStages + s * kStageBytes);
-                    const uint32_t b_addr = a_addr + kTileABytes;
+                    const uint32_t a_addr = smem_u32(smem + kOffStages + s * kStage2Bytes);
+                    const uint32_t b_addr = a_addr + kSubTiles * kTileABytes;
                     const uint32_t nl = kb < p.kblocks ? p.limbs : 1u;
-                    for (uint32_t l = 0; l < nl; ++l) {
-                        const uint64_t da = make_smem_desc(a_addr);
-                        const uint64_t db = make_smem_desc(b_addr + l * p.tt * 128);
+                    for (uint32_t sub = 0; sub < nsub; ++sub) {
+                        const uint64_t da = make_smem_desc(a_addr + sub * kTileABytes);
+                        for (uint32_t l = 0; l < nl; ++l) {
+                            const uint64_t db = make_smem_desc(b_addr + l * p.tt * 128);
 #pragma unroll
-                        for (uint32_t k4 = 0; k4 < 4; ++k4)      // 16 k per MMA = 32 bytes = 2 descriptor units
-                            umma_f16(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | l | k4) != 0 ? 1u : 0u);
+                            for (uint32_t k4 = 0; k4 < 4; ++k4)      // 16 k per MMA = 32 bytes = 2 descriptor units
+                                umma_f16(d_tmem + sub * p.tt, da + 2 * k4, db + 2 * k4, idesc, (kb | l | k4) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit(&empty[s]);
                 }
@@ -326,68 +343,74 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
             }
             if (!ok) { atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
         }
-    } else if (warp >= 2 && warp <= 5) {
-        // ---------------- dequantizers: thread r owns weight row n0 + r ----------------
-        const uint32_t r = (uint32_t)(tid - 64);
-        uint32_t it = 0, rit = 0;
+    } else if (warp >= 2 && warp < 2 + 2 * kDeqWarpsPerSub) {
+        // ---- dequantizers: group `sub`; thread = weight row n0 + sub*128 + r, Q4 block `blk` of the k block ----
+        const uint32_t sub = (uint32_t)(warp - 2) / kDeqWarpsPerSub;
+        const uint32_t gt = (uint32_t)(tid - 64) - sub * (kDeqWarpsPerSub * 32);
+        const uint32_t r = gt & 127u, blk = gt >> 7;
+        uint32_t it = 0, rit = 0;      // rit counts raw entries of ALL groups, as the raw producer does
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+            const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
+            const bool active = sub < nsub;
             for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
-                const uint32_t s = it % kStages;
-                if (!mbar_wait(&empty[s], ((it / kStages) & 1u) ^ 1u)) { ok = false; break; }
-                if (kb < p.kblocks) {
-                    const uint32_t rs = rit % kRawStages;
-                    if ((kb & 1u) == 0 && !mbar_wait(&raw_full[rs], (rit / kRawStages) & 1u)) { ok = false; break; }
+                const uint32_t s = it % kStages2;
+                if (!mbar_wait(&empty[s], ((it / kStages2) & 1u) ^ 1u)) { ok = false; break; }
+                if (kb < p.kblocks && active) {
+                    const uint32_t my = rit + sub;                  // this group's entry of the current pair
+                    const uint32_t rs = my % kRawStages;
+                    if ((kb & 1u) == 0 && !mbar_wait(&raw_full[rs], (my / kRawStages) & 1u)) { ok = false; break; }
                     // rows past n were zero-filled by the TMA: scale 0, bias 0, codes 0 -> weights 0
-                    const uint2* src = reinterpret_cast<const uint2*>(smem + kOffRaw + rs * kRawBytes + r * 80 + (kb & 1u) * 40);
-                    uint32_t q[10];
+                    uint8_t* a_tile = smem + kOffStages + s * kStage2Bytes + sub * kTileABytes;
 #pragma unroll
-                    for (int i = 0; i < 5; ++i) { const uint2 v = src[i]; q[2 * i] = v.x; q[2 * i + 1] = v.y; }
-                    uint8_t* a_tile = smem + kOffStages + s * kStageBytes;
-#ifdef LQ4_EXP_NO_DEQ
-                    if (q[0] == 0x12345678u)
-#endif
+                    for (uint32_t b = blk; b < 2; b += kDeqWarpsPerSub / 4) {
+                        const uint32_t* src = reinterpret_cast<const uint32_t*>(smem + kOffRaw + rs * kRawBytes + r * 80 + (kb & 1u) * 40 + b * 20);
+                        uint32_t q[5];
 #pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        const uint32_t meta = q[5 * b];
-                        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)(meta & 0xffffu)));
-                        const __half2 b2 = __half2half2(__ushort_as_half((unsigned short)(meta >> 16)));
+                        for (int i = 0; i < 5; ++i) q[i] = src[i];
+                        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)(q[0] & 0xffffu)));
+                        const __half2 b2 = __half2half2(__ushort_as_half((unsigned short)(q[0] >> 16)));
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<uint4*>(a_tile + swz128(r, 4 * b + j)) = dequant_word_f16(q[5 * b + 1 + j], d2, b2);
+                            *reinterpret_cast<uint4*>(a_tile + swz128(r, 4 * b + j)) = dequant_word_f16(q[1 + j], d2, b2);
                     }
                     fence_async_smem();          // generic-proxy writes -> visible to the tensor core
                     if (kb & 1u) {
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&raw_empty[rs]);
-                        ++rit;
                     }
                 }
+                if (kb < p.kblocks && (kb & 1u)) rit += nsub;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&full[s]);
             }
         }
         if (!ok) { if (lane == 0) atomicOr(p.status, kDevErrBarrierTimeout); *s_err = 1; }
-    } else if (warp >= 6 && warp <= 9) {
+    } else if (warp >= 2 + 2 * kDeqWarpsPerSub && warp < kGemmWarps - 1) {
         // ---------------- epilogue: TMEM -> registers -> Y ----------------
         const uint32_t quarter = (uint32_t)warp & 3u;            // TMEM lanes this warp may read
         uint32_t tcount = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-            const uint32_t buf = tcount & 1u;
-            const uint32_t n = (tile / p.m_tiles) * kTileN + quarter * 32 + lane;
+            const uint32_t buf = tcount % nbuf;
+            const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+            const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
             const uint32_t m0 = (tile % p.m_tiles) * p.tt;
-            if (!mbar_wait(&acc_full[buf], (tcount >> 1) & 1u)) { ok = false; break; }
+            if (!mbar_wait(&acc_full[buf], (tcount / nbuf) & 1u)) { ok = false; break; }
             tc_fence_after();
-            for (uint32_t c0 = 0; c0 < p.tt; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + buf * 256 + c0, v);
-                tmem_ld_wait();
-                if (n < p.n) {
+            for (uint32_t sub = 0; sub < nsub; ++sub) {
+                const uint32_t n = n0 + sub * kTileN + quarter * 32 + lane;
+                for (uint32_t c0 = 0; c0 < p.tt; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((quarter * 32) << 16) + buf * acc_cols + sub * p.tt + c0, v);
+                    tmem_ld_wait();
+                    if (n < p.n) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const uint32_t m = m0 + c0 + j;
-                        if (c0 + j < p.tt && m < p.m) p.y[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
+                        for (int j = 0; j < 32; ++j) {
+                            const uint32_t m = m0 + c0 + j;
+                            if (c0 + j < p.tt && m < p.m) p.y[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -548,12 +571,12 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
             convert_rows_kernel<<<(unsigned)((a_oct + 255) / 256), 256, 0, s>>>(la, LQ4_DTYPE_F32, rank, k, al, 2ull * k, k);
             ++nl;
             CUtensorMap tm_al, tm_x32;
-            if (!make_f16_map(&tm_al, al, 2ull * k, rank, 2ull * k, kTileN)) return fail("tensor map (A)", cudaErrorInvalidValue);
+            if (!make_f16_map(&tm_al, al, 2ull * k, rank, 2ull * k, kCtaRows)) return fail("tensor map (A)", cudaErrorInvalidValue);
             if (!make_f16_map(&tm_x32, x16, (uint64_t)limbs * k, m, (uint64_t)limbs * k, 32)) return fail("tensor map (x32)", cudaErrorInvalidValue);
             GemmParams q{};
             q.status = status;
             q.w = w; q.y = t; q.ldy = rank; q.m = m; q.n = rank; q.k = k;
-            q.limbs = 1; q.tt = 32; q.n_tiles = (rank + kTileN - 1) / kTileN; q.m_tiles = (m + 31) / 32;
+            q.limbs = 1; q.tt = 32; q.n_tiles = (rank + kCtaRows - 1) / kCtaRows; q.m_tiles = (m + 31) / 32;
             q.kblocks = 0;
             q.seg_len = k / kBlockK;
             q.seg_a_off[0] = 0; q.seg_b_off[0] = 0;          // Ah . Xh
@@ -571,7 +594,7 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
         const unsigned bblocks = (unsigned)((bn + 255) / 256 < (uint64_t)sm_count * 16 ? (bn + 255) / 256 : (uint64_t)sm_count * 16);
         split_rows_kernel<<<bblocks, 256, 0, s>>>(lb, n, rank, rp, lscale, bl);
         nl += 2;
-        if (!make_f16_map(&tm_da, bl, 2ull * rp, n, 2ull * rp, kTileN)) return fail("tensor map (B)", cudaErrorInvalidValue);
+        if (!make_f16_map(&tm_da, bl, 2ull * rp, n, 2ull * rp, kCtaRows)) return fail("tensor map (B)", cudaErrorInvalidValue);
         if (!make_f16_map(&tm_db, tl, 2ull * rp, m, 2ull * rp, tt)) return fail("tensor map (T)", cudaErrorInvalidValue);
         p.seg_len = rp / kBlockK;
         p.seg_a_off[0] = 0;  p.seg_b_off[0] = 0;         // Bh . Th
@@ -584,7 +607,7 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
     // 5. the main product
     p.w = w; p.y = y; p.ldy = ldy; p.m = m; p.n = n; p.k = k;
     p.limbs = limbs; p.tt = tt;
-    p.n_tiles = (n + kTileN - 1) / kTileN;
+    p.n_tiles = (n + kCtaRows - 1) / kCtaRows;
     p.m_tiles = (m + tt - 1) / tt;
     p.kblocks = k / kBlockK;
     if ((e = launch_kernel(p, tm_x, tm_w, tm_da, tm_db, sm_count, s)) != cudaSuccess) return fail("GEMM launch", e);
