@@ -37,9 +37,9 @@ UNIT = "GB/s"
 LORA_RANK, LORA_ALPHA = 16, 32.0
 SHAPES = [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)]      # (k, n)
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu
-# capture summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per projection (decode kernel + its LoRA projection
+# kernel), averaged over the four shapes of a layer, from the ncu capture summarised in profiles/
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 33.89e6   # profiles/decode_kernel_large_layer_set.md: 33.33 MB + 0.56 MB (projection)
 
 
 def algorithmic_bytes(m, n, k, rank):
@@ -339,7 +339,7 @@ def run_ours(args):
     achieved = (per_step_bytes / world) * args.steps / (ms * 1e-3) / 1e9
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32 accumulate over int4 codes x f16-split f32 activations", "data": "synthetic",
+            "dtype": "int4 codes x int8-limb activations in exact s32, block scales and accumulation in f32", "data": "synthetic",
             "config": workload_config(args, world),
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / e2e_steps,
                     "h2d_bytes_per_step": int(args.layers * sum(m * k * 4 for k, _ in SHAPES)),
@@ -455,6 +455,33 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
     return out
 
 
+def run_only(args):
+    """Small single cases for profiler captures (no JSON line): a few launches of one kernel."""
+    import torch
+    from lattice_b200 import CudaQ4Backend, Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    be = CudaQ4Backend(0)
+    dev = torch.device("cuda", 0)
+    if args.only == "gemm-slice":          # M=2048, K=5120 on a 2176-row N-shard of the 17408 outputs, bf16, LoRA r=64
+        m, k, n, r, dt = 2048, 5120, 2176, 64, torch.bfloat16
+    elif args.only == "decode-up":         # M=1, 5120 -> 17408, LoRA r=16
+        m, k, n, r, dt = 1, 5120, 17408, 16, torch.float32
+    else:
+        raise SystemExit("unknown --only case")
+    w = torch.randn((n, k), device=dev) * 0.02
+    qw = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), n, k)
+    del w
+    a = torch.randn((r, k), device=dev) * 0.02
+    b = torch.randn((n, r), device=dev) * 0.02
+    x = torch.randn((m, k), device=dev).to(dt)
+    y = torch.empty((m, n), device=dev)
+    for _ in range(3):
+        be.dispatch_gemm_q4(x, 0, qw, y, 0, m, n, k, lora=LoraDesc(a.data_ptr(), b.data_ptr(), r, 2.0))
+    torch.cuda.synchronize()
+    be.check_device_status()
+    print("ok", args.only)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -465,12 +492,15 @@ def main():
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
+    ap.add_argument("--only", default=None, help="gemm-slice | decode-up: three launches of one case, for profiling")
     ap.add_argument("--no-aux", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.only:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
