@@ -39,7 +39,8 @@ SHAPES = [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)]      # (k, n
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per projection (decode kernel + its LoRA projection
 # kernel), averaged over the four shapes of a layer, from the ncu capture summarised in profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 33.89e6   # profiles/decode_kernel_large_layer_set.md: 33.33 MB + 0.56 MB (projection)
+# dram bytes per decode launch from the ncu captures under profiles/ (None: not captured)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"per-projection": 33.89e6, "grouped": None}
 
 
 def algorithmic_bytes(m, n, k, rank):
@@ -174,6 +175,8 @@ def workload_config(args, world):
     return {"workload": "configs[2] large-layer decode set: (5120->5120, 5120->1024, 5120->17408, 17408->5120) "
                         f"x {args.layers} layers, M={args.m}, Q4 weights ~N(0,0.02^2), LoRA r={LORA_RANK} alpha={LORA_ALPHA:g}",
             "m": args.m, "layers": args.layers, "lora_rank": LORA_RANK,
+            "launch": ("one lq4_linear_group call per set: the four independent projections share one persistent launch"
+                       if args.launch == "grouped" else "one lq4_linear call per projection"),
             "parallelism": f"N-sharded column-parallel x{world} + NCCL all-gather" if world > 1 else "single GPU",
             "l2": "inputs larger than L2: every launch streams distinct weights, "
                   f"{args.layers * 131.072:.0f} MB of Q4 payload per step per job"}
@@ -225,35 +228,49 @@ def run_ours(args):
         layers.append(projs)
     gen.manual_seed(99)
     xs = {k: torch.randn((m, k), generator=gen, device=dev) for k in (5120, 17408)}
-    y_local = {si: torch.empty((m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
-    y_full = {si: torch.empty((world * m, layers[0][si]["nl"]), device=dev) for si in range(len(SHAPES))}
+    # The outputs of one set sit side by side in one [m, sum(n_local)] buffer (each projection writes
+    # its column range, ldy = row pitch), so that a sharded set needs ONE all-gather.
+    nls = [layers[0][si]["nl"] for si in range(len(SHAPES))]
+    offs = [sum(nls[:si]) for si in range(len(SHAPES))]
+    y_cat = torch.empty((m, sum(nls)), device=dev)
+    y_local = {si: y_cat[:, offs[si]:offs[si] + nls[si]] for si in range(len(SHAPES))}
+    y_full = torch.empty((world * m, sum(nls)), device=dev)
     torch.cuda.synchronize()
     note("synthetic model built")
+    grouped = args.launch == "grouped"
+
+    def run_set(projs, x_of, grouped=grouped):
+        if grouped:
+            # one persistent launch for the set's four projections (plus one small launch for the
+            # four adapters' x.A^T)
+            be.linear_group([(x_of[p["k"]], p["qw"], p["lora"]) for p in projs], [y_local[si] for si in range(len(projs))])
+        else:
+            for si, p in enumerate(projs):
+                be.dispatch_gemm_q4(x_of[p["k"]], 0, p["qw"], y_local[si], 0, m, p["nl"], p["k"], lora=p["lora"],
+                                    ldy=y_cat.stride(0))
+        if world > 1:
+            dist.all_gather_into_tensor(y_full, y_cat)
 
     def step():
         for projs in layers:
-            for si, p in enumerate(projs):
-                be.dispatch_gemm_q4(xs[p["k"]], 0, p["qw"], y_local[si], 0, m, p["nl"], p["k"], lora=p["lora"])
-                if world > 1:
-                    dist.all_gather_into_tensor(y_full[si], y_local[si])
+            run_set(projs, xs)
 
     # pinned host buffers for the end-to-end variant
     hx = {k: torch.randn((m, k)).pin_memory() for k in (5120, 17408)}
-    hy = {si: torch.empty((world * m, layers[0][si]["nl"])).pin_memory() for si in range(len(SHAPES))}
+    hy = torch.empty((world * m, sum(nls))).pin_memory()
     dx = {k: torch.empty((m, k), device=dev) for k in (5120, 17408)}
 
     def e2e_step():
+        # per set: host activations in (pinned -> device), the public call, host result out, wait
         for projs in layers:
-            for si, p in enumerate(projs):
-                if world == 1:
-                    # the C ABI's host-buffer entry point: H2D of x, kernel, D2H of y, wait
-                    be.linear_host(hx[p["k"]].numpy(), p["qw"], hy[si].numpy().reshape(m, p["nl"]), lora=p["lora"])
-                else:
-                    dx[p["k"]].copy_(hx[p["k"]], non_blocking=True)
-                    be.dispatch_gemm_q4(dx[p["k"]], 0, p["qw"], y_local[si], 0, m, p["nl"], p["k"], lora=p["lora"])
-                    dist.all_gather_into_tensor(y_full[si], y_local[si])
-                    hy[si].copy_(y_full[si], non_blocking=True)
-                    torch.cuda.current_stream().synchronize()
+            for k in dx:
+                dx[k].copy_(hx[k], non_blocking=True)
+            run_set(projs, dx)
+            if world > 1:
+                hy.copy_(y_full, non_blocking=True)
+            else:
+                hy.copy_(y_cat, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
 
     # The device-timed leg replays a CUDA graph of one step (the launch-bound inner loop is captured
     # once; replay removes the per-call host cost).  --eager times plain calls instead.
@@ -331,9 +348,10 @@ def run_ours(args):
     value = per_step_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e_value = per_step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
     hbm_peak, tc_peak, tc_sust, which = measured_peaks()
-    n_lin = args.layers * len(SHAPES)
-    # the step's launches are all the decode kernel (one per projection at m <= 4), so the average
-    # launch duration is the event time over the launches, and algorithmic bytes per launch divide
+    n_lin = args.layers * (1 if grouped else len(SHAPES))
+    # the step's launches are the decode kernel (one per set when grouped, else one per projection)
+    # with the small adapter-projection kernel overlapped in front of each, so the average launch
+    # duration is the event time over the decode launches, and algorithmic bytes per launch divide
     # the same way; per GPU each rank streams 1/world of the bytes
     avg_launch_us = ms * 1e3 / (args.steps * n_lin)
     achieved = (per_step_bytes / world) * args.steps / (ms * 1e-3) / 1e9
@@ -345,15 +363,26 @@ def run_ours(args):
                     "h2d_bytes_per_step": int(args.layers * sum(m * k * 4 for k, _ in SHAPES)),
                     "d2h_bytes_per_step": int(args.layers * sum(m * n * 4 for _, n in SHAPES))},
             "gpu_launches": int(launches), "launch_mode": graph_info["mode"],
-            "roofline": {"bound": "hbm", "kernel": "decode_kernel<1> (one launch per projection; the LoRA projection kernel before it overlaps through PDL)",
+            "roofline": {"bound": "hbm", "kernel": ("decode_kernel<1, 8>: one persistent launch per set of four projections" if grouped
+                                                 else "decode_kernel<1, 1>: one launch per projection") +
+                                                "; the adapter projection kernel before it overlaps through PDL",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
                          "avg_launch_us": avg_launch_us, "algorithmic_bytes_per_launch": per_step_bytes / world / n_lin,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH[args.launch] if m == 1 and world == 1 else None},
             "clocks": clocks}
 
     if rank == 0 and world == 1 and not args.no_aux:
         line["aux"] = aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust)
+        # the same step with the other launch mode, timed the same way
+        def other_step():
+            for projs in layers:
+                run_set(projs, xs, not grouped)
+        ofn, ol = make_graphed(other_step)
+        oms, _ = timed(ofn, args.steps, args.warmup, ol)
+        ov = per_step_bytes * args.steps / (oms * 1e-3) / 1e9
+        line["aux"]["decode_set_" + ("per_projection" if grouped else "grouped") + "_launches"] = {
+            "GB/s": ov, "frac_hbm": ov / hbm_peak, "ms_per_step": oms / args.steps}
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(layers[0])
     if rank == 0:
@@ -466,6 +495,22 @@ def run_only(args):
         m, k, n, r, dt = 2048, 5120, 2176, 64, torch.bfloat16
     elif args.only == "decode-up":         # M=1, 5120 -> 17408, LoRA r=16
         m, k, n, r, dt = 1, 5120, 17408, 16, torch.float32
+    elif args.only == "decode-set":        # M=1, one grouped launch over the four large-layer shapes, LoRA r=16
+        probs, keep = [], []
+        for k, n in SHAPES:
+            w = torch.randn((n, k), device=dev) * 0.02
+            qw = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), n, k)
+            del w
+            a = torch.randn((LORA_RANK, k), device=dev) * 0.02
+            b = torch.randn((n, LORA_RANK), device=dev) * 0.02
+            keep += [a, b]
+            probs.append((torch.randn((1, k), device=dev), qw, LoraDesc(a.data_ptr(), b.data_ptr(), LORA_RANK, 2.0)))
+        for _ in range(3):
+            be.linear_group(probs)
+        torch.cuda.synchronize()
+        be.check_device_status()
+        print("ok", args.only)
+        return
     else:
         raise SystemExit("unknown --only case")
     w = torch.randn((n, k), device=dev) * 0.02
@@ -490,9 +535,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--launch", default="grouped", choices=["grouped", "per-projection"],
+                    help="grouped: one persistent launch per set of four projections (lq4_linear_group); "
+                         "per-projection: one lq4_linear call each")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
-    ap.add_argument("--only", default=None, help="gemm-slice | decode-up: three launches of one case, for profiling")
+    ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set: three launches of one case, for profiling")
     ap.add_argument("--no-aux", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

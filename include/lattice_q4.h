@@ -127,6 +127,19 @@ int32_t lq4_abi_version(void);
  * launch.  m == 0 or n == 0 is a no-op; k == 0 or k % 32 != 0 returns LQ4_ERR_K. */
 lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* args, void* stream);
 
+/* Several independent decode projections in ONE persistent launch.  `args[0..count)` are
+ * complete lq4_linear problems; none may read what another one writes.  When every problem has
+ * the same m <= 4, no rotation, k % 128 == 0, 16-byte aligned w and x, LoRA rank <= 128, and
+ * count <= 8, the work of all problems is split evenly over the SMs as one range (launch,
+ * activation prologue and tail are paid once, not once per projection) after one small launch
+ * that projects every adapter's t = A x.  Any other group is served problem by problem through
+ * lq4_linear, with identical results.  Replaces the reference's habit of encoding a decode
+ * step's projections back to back into one Metal command buffer
+ * (crates/inference/src/forward/metal_qwen35.rs:4458-4462, one encoder for all layers) and its
+ * merged-row GEMVs with per-range adapters (inner/layers/gdn.rs:69-105,293-300: one GEMV over
+ * qkv||z rows, then LoRA into sub-ranges): q/k/v, or gate/up, share x and go in one group. */
+lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t count, void* stream);
+
 /* Decode projection (m <= 4) for callers that cannot allocate device memory: an engine that
  * handed every byte to its own pool at start-up, or a decode loop that cannot afford the
  * device-wide synchronisation inside cudaMalloc/cudaFree.  No counterpart in the reference:

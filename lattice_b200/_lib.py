@@ -45,6 +45,7 @@ SIGNATURES = {
     "lq4_linear": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_void_p]),
     "lq4_linear_host": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_void_p]),
     "lq4_linear_decode_noalloc": (C.c_int32, [C.POINTER(LinearArgs), C.c_void_p]),
+    "lq4_linear_group": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_uint32, C.c_void_p]),
     "lq4_lora_apply": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32, C.c_uint32, C.c_void_p,
                                    C.c_uint32, C.c_uint64, C.POINTER(LoraDesc), C.c_void_p]),
     "lq4_dequant_f32": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),

@@ -329,6 +329,34 @@ class CudaQ4Backend:
         self.dispatch_gemm_q4(x.contiguous(), 0, qw, y, 0, m, qw.n, k, lora=lora, rot=rot, path=path)
         return y
 
+    def linear_group(self, problems, outs: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
+        """Several independent projections in one call (one persistent launch for decode shapes).
+
+        ``problems`` is a list of ``(x, qw)`` or ``(x, qw, lora)`` with ``x`` ``[m, k]`` on the device;
+        returns the list of ``[m, n]`` f32 outputs.  No output may alias another problem's input."""
+        n_prob = len(problems)
+        if n_prob == 0:
+            return []
+        arr = (LinearArgs * n_prob)()
+        keep = []
+        ys = []
+        for i, pr in enumerate(problems):
+            x, qw = pr[0], pr[1]
+            lora = pr[2] if len(pr) > 2 else None
+            m, k = x.shape
+            self._require_k("linear_group", k)
+            x = x.contiguous()
+            y = outs[i] if outs is not None else torch.empty((m, qw.n), dtype=torch.float32, device=x.device)
+            assert x.is_cuda and y.is_cuda and y.dtype == torch.float32
+            assert y.shape == (m, qw.n) and y.stride(1) == 1, "outputs are [m, n] with unit column stride"
+            keep.append((x, lora))
+            ys.append(y)
+            ldy = y.stride(0) if m > 1 or y.stride(0) >= qw.n else qw.n      # row pitch of a column slice
+            arr[i] = LinearArgs(x.data_ptr(), self._dtype_of(x), m, qw.n, k, qw.payload_ptr, y.data_ptr(), ldy,
+                                C.pointer(lora) if lora is not None else None, None, _lib.PATH_AUTO)
+        check(_lib.lib().lq4_linear_group(self._ctx, arr, n_prob, _stream()))
+        return ys
+
     def linear_host(self, x: np.ndarray, qw: Q4WeightBuf, y: np.ndarray, *, lora: Optional[LoraDesc] = None,
                     rot: Optional[RotDesc] = None) -> None:
         """End-to-end call with HOST activations and output (copies inside the call, waits for y)."""

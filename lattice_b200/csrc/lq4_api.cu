@@ -363,6 +363,76 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     return LQ4_OK;
 }
 
+lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t count, void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (count == 0) return LQ4_OK;
+    if (!args) return fail(LQ4_ERR_NULL, "args is NULL");
+    lq4_status st;
+    for (uint32_t i = 0; i < count; ++i)
+        if ((st = validate_linear(&args[i]))) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+
+    // One launch serves the whole group when every problem is a decode-kernel case of the same
+    // token count; anything else runs problem by problem with the same results.
+    bool one_launch = count >= 2 && count <= (uint32_t)kMaxGroup;
+    GemvParams ps[kMaxGroup];
+    size_t smem = 0;
+    if (one_launch) {
+        for (uint32_t i = 0; i < count && one_launch; ++i) {
+            const lq4_linear_args& a = args[i];
+            const uint32_t rank = a.lora ? a.lora->rank : 0;
+            one_launch = a.m >= 1 && a.m <= 4 && a.m == args[0].m && a.n > 0 && !a.rot && (a.k % 128 == 0) &&
+                         aligned(a.w, 16) && aligned(a.x, 16) && rank <= (uint32_t)kGemvMaxRank &&
+                         (a.path == LQ4_PATH_AUTO || a.path == LQ4_PATH_GEMV_MMA);
+            if (!one_launch) break;
+            GemvParams p{};
+            p.w = a.w; p.y = a.y; p.ldy = a.ldy ? a.ldy : a.n;
+            p.m = a.m; p.n = a.n; p.k = a.k;
+            p.kb = a.k / 32; p.kg = p.kb / kGemvGranuleBlocks;
+            p.tiles = (a.n + kGemvTileRows - 1) / kGemvTileRows;
+            p.nt = 1; p.gmax = 2 * a.m;
+            p.status = ctx->status;
+            p.tsync = ctx->tsync;
+            p.use_pdl = ctx->pdl;
+            p.sm_count = ctx->sm_count;
+            p.x = a.x; p.x_dtype = a.x_dtype;
+            if (a.lora) { p.la = a.lora->a; p.lb = a.lora->b; p.rank = rank; p.lscale = a.lora->scale; }
+            ps[i] = p;
+        }
+        if (one_launch) smem = decode_group_plan_smem(ps, count);
+        one_launch = one_launch && smem != 0;
+    }
+    if (!one_launch) {
+        for (uint32_t i = 0; i < count; ++i)
+            if ((st = lq4_linear(ctx, &args[i], stream))) return st;
+        return LQ4_OK;
+    }
+
+    const uint32_t m = args[0].m;
+    size_t t_floats = 0;
+    for (uint32_t i = 0; i < count; ++i) t_floats += ((size_t)m * ps[i].rank + 63) / 64 * 64;
+    if ((st = ensure(ctx, ctx->t, t_floats * sizeof(float) + 256, false, s))) return st;
+    float* tptr[kMaxGroup];
+    size_t toff = 0;
+    bool any_rank = false;
+    for (uint32_t i = 0; i < count; ++i) {
+        tptr[i] = (float*)ctx->t.p + toff;
+        toff += ((size_t)m * ps[i].rank + 63) / 64 * 64;
+        if (ps[i].rank) { ps[i].t_g = tptr[i]; any_rank = true; }
+    }
+    const uint64_t units = decode_group_units(ps, count);
+    const int grid = (int)(units < (uint64_t)ctx->sm_count ? units : (uint64_t)ctx->sm_count);
+    if ((st = ensure(ctx, ctx->partials, (size_t)grid * kGemvTileRows * 4 * 8, true, s))) return st;
+    for (uint32_t i = 0; i < count; ++i) ps[i].partials = (float*)ctx->partials.p;
+    if (any_rank) {
+        LQ4_CUDA(launch_lora_project_group(ps, count, tptr, m, ctx->pdl, s));
+        ctx->launches += 1;
+    }
+    LQ4_CUDA(launch_decode_group(ps, count, smem, grid, s));
+    ctx->launches += 1;
+    return LQ4_OK;
+}
+
 lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
     if (!a) return fail(LQ4_ERR_NULL, "args is NULL");

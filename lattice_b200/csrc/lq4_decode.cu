@@ -184,10 +184,22 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, ui
     named_bar_sync(kBarConsumers, kConsumerThreads);
 }
 
-template <int MT>
-__global__ void __launch_bounds__(kGemvThreads, 1)
-decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
-              const __grid_constant__ CUtensorMap tm_mid, const __grid_constant__ CUtensorMap tm_small) {
+// Arguments of one launch: NP problems (NP = 1 for a single projection).  The shared-memory
+// offsets, the stage count, the workspace pointers and the PDL flag are taken from p[0]; the
+// problems differ in weights, shapes, activations, output and adapter.
+template <int NP>
+struct DecodeArgs {
+    GemvParams p[NP];
+    CUtensorMap maps[NP][3];      // boxes of 20, 12 and 4 blocks x 128 rows
+    uint64_t ub[NP + 1];          // first work unit of each problem (units: 4 blocks x 128 rows)
+    uint32_t count;
+    uint32_t any_rank;            // some problem has a LoRA adapter
+};
+
+template <int MT, int NP>
+__global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_constant__ DecodeArgs<NP> ga) {
+    const GemvParams& p = ga.p[0];
+    const uint32_t count = NP == 1 ? 1u : ga.count;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint64_t* empty = full + kMaxStages;
@@ -218,11 +230,11 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
     if (p.use_pdl) pdl_launch_dependents();
 
     const uint64_t G = gridDim.x;
-    const uint64_t total = (uint64_t)p.tiles * p.kg;
+    const uint64_t total = NP == 1 ? (uint64_t)p.tiles * p.kg : ga.ub[count];
     // whole-tile mode hands out entire tiles (no partial sums); otherwise equal shares of granules
-    const uint64_t r0 = p.whole_tiles ? range_begin(blockIdx.x, p.tiles, G) * p.kg : range_begin(blockIdx.x, total, G);
-    const uint64_t r1 = p.whole_tiles ? range_begin(blockIdx.x + 1, p.tiles, G) * p.kg
-                                      : range_begin(blockIdx.x + 1, total, G);
+    const bool whole = NP == 1 && p.whole_tiles;
+    const uint64_t r0 = whole ? range_begin(blockIdx.x, p.tiles, G) * p.kg : range_begin(blockIdx.x, total, G);
+    const uint64_t r1 = whole ? range_begin(blockIdx.x + 1, p.tiles, G) * p.kg : range_begin(blockIdx.x + 1, total, G);
     uint32_t issued = 0;
 
     if (warp == 8) {
@@ -231,11 +243,16 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
             const uint64_t pol = l2_policy_evict_first();
             uint32_t it = 0;
             bool ok = true;
+            uint32_t pi = 0;
             for (uint64_t pos = r0; pos < r1 && ok;) {
-                const uint32_t tile = (uint32_t)(pos / p.kg);
-                const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * p.kg);
+                if (NP > 1)
+                    while (pi + 1 < count && pos >= ga.ub[pi + 1]) ++pi;
+                const GemvParams& q = ga.p[pi];
+                const uint64_t local = NP == 1 ? pos : pos - ga.ub[pi];
+                const uint32_t tile = (uint32_t)(local / q.kg);
+                const uint32_t g0 = (uint32_t)(local - (uint64_t)tile * q.kg);
                 const uint64_t left = r1 - pos;
-                const uint32_t g1 = (uint64_t)(p.kg - g0) < left ? p.kg : (uint32_t)(g0 + left);
+                const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
                 for (uint32_t gs = g0; gs < g1; ++it) {
                     const uint32_t ngr = stage_granules(g1 - gs);
                     const uint32_t s = it % NST;
@@ -243,7 +260,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                     uint8_t* st = smem + p.off_stage + (size_t)s * kSlotBytes;
                     mbar_arrive_expect_tx(&full[s], ngr * kSmallBytes);
                     // coordinates: x in 4-byte elements along the row, y = first row of the tile
-                    tma_load_2d(st, ngr == 5 ? &tm_big : (ngr == 3 ? &tm_mid : &tm_small), (int32_t)(gs * kGemvGranuleBlocks * 5),
+                    tma_load_2d(st, &ga.maps[pi][ngr == 5 ? 0 : (ngr == 3 ? 1 : 2)], (int32_t)(gs * kGemvGranuleBlocks * 5),
                                 (int32_t)(tile * kGemvTileRows), &full[s], pol);
                     gs += ngr;
                 }
@@ -263,13 +280,12 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
         // only t must be waited for, right before the first epilogue.  Without an adapter the previous
         // launch may be the producer of x, so the wait comes first.
         bool prior_done = false;
-        if (p.use_pdl && !p.rank) { pdl_wait_prior_grids(); prior_done = true; }
+        const bool any_rank = NP == 1 ? p.rank != 0 : ga.any_rank != 0;
+        if (p.use_pdl && !any_rank) { pdl_wait_prior_grids(); prior_done = true; }
         // launch generation: bumped once at the end of every launch, so a message written by an
         // earlier launch never carries the current tag
         const uint32_t tag = *reinterpret_cast<volatile const uint32_t*>(p.tsync) + 1u;
         LQ4_STAMP(1);
-        decode_prologue<MT>(p, smem, tid, r0, r1);
-        LQ4_STAMP(2);
 
         // A lane supplies B-operand registers only for the column pair (limb 0, limb 1) of its own
         // block; every other lane reads a block of zeros, so that its columns contribute nothing.
@@ -280,22 +296,37 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
 
         uint32_t it = 0;
         bool ok = true;
+        uint32_t pi = 0, cur = 0xffffffffu;
         for (uint64_t pos = r0; pos < r1 && ok;) {
-            const uint32_t tile = (uint32_t)(pos / p.kg);
-            const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * p.kg);
+            if (NP > 1)
+                while (pi + 1 < count && pos >= ga.ub[pi + 1]) ++pi;
+            const GemvParams& q = ga.p[pi];
+            const uint64_t ub0 = NP == 1 ? 0 : ga.ub[pi];
+            if (pi != cur) {
+                // first segment of a problem: convert the activation ranges this CTA needs from it
+                // (all consumer warps walk the same segments, so they meet here together)
+                if (cur != 0xffffffffu) named_bar_sync(kBarConsumers, kConsumerThreads);
+                const uint64_t ub1 = NP == 1 ? total : ga.ub[pi + 1];
+                decode_prologue<MT>(q, smem, tid, (r0 > ub0 ? r0 : ub0) - ub0, (r1 < ub1 ? r1 : ub1) - ub0);
+                cur = pi;
+                LQ4_STAMP(2);
+            }
+            const uint64_t local = pos - ub0;
+            const uint32_t tile = (uint32_t)(local / q.kg);
+            const uint32_t g0 = (uint32_t)(local - (uint64_t)tile * q.kg);
             const uint64_t left = r1 - pos;
-            const uint32_t g1 = (uint64_t)(p.kg - g0) < left ? p.kg : (uint32_t)(g0 + left);
+            const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
             pos += g1 - g0;
 
             float acc[MT][2];
 #pragma unroll
             for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = 0.0f;
-            if (p.rank && g0 == 0) {
+            if (q.rank && g0 == 0) {
                 // this CTA will finish the tile: pull the warp's 16 rows of LoRA B towards L2 now
                 const uint32_t rfirst = tile * kGemvTileRows + warp * 16;
-                const uint32_t rows = rfirst < p.n ? min(16u, p.n - rfirst) : 0u;
-                const char* bb = reinterpret_cast<const char*>(p.lb + (size_t)rfirst * p.rank);
-                for (uint32_t off = lane * 128; off < rows * p.rank * 4; off += 32 * 128)
+                const uint32_t rows = rfirst < q.n ? min(16u, q.n - rfirst) : 0u;
+                const char* bb = reinterpret_cast<const char*>(q.lb + (size_t)rfirst * q.rank);
+                for (uint32_t off = lane * 128; off < rows * q.rank * 4; off += 32 * 128)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(bb + off));
             }
 
@@ -373,7 +404,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                     v[mt][r] = s;
                 }
             }
-            const bool complete = (g0 == 0 && g1 == p.kg);
+            const bool complete = (g0 == 0 && g1 == q.kg);
             if (!complete && g0 != 0) {
                 // Contributor: this CTA's range starts inside the tile, so this is its first segment.
                 // Publish the partial sums and leave; the ticket add is a release, no reply is needed.
@@ -391,7 +422,7 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                 // Finisher: the CTA that owns the tile's first k part reaches it at the END of its own
                 // range, when the contributors (who met the tile at the START of theirs) are long done.
                 // The wait below is bounded and normally falls through at once.
-                const uint32_t c_last = owner_of((uint64_t)(tile + 1) * p.kg - 1, total, G);
+                const uint32_t c_last = owner_of(ub0 + (uint64_t)(tile + 1) * q.kg - 1, total, G);
                 // lanes poll different CTAs' messages (all 16 rows each), a fixed shuffle tree adds
                 // them: the sum does not depend on arrival order
                 float part[16 * MT];
@@ -432,19 +463,19 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
 
             // epilogue: LoRA term (the quad splits the rank), then quad thread t stores token t
             const uint32_t rowa = tile * kGemvTileRows + warp * 16 + g, rowb = rowa + 8;
-            if (p.rank) {
+            if (q.rank) {
                 if (!prior_done) { if (p.use_pdl) pdl_wait_prior_grids(); prior_done = true; }
                 float la[MT], lb2[MT];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) la[mt] = lb2[mt] = 0.0f;
-                const float* bra = p.lb + (size_t)(rowa < p.n ? rowa : 0) * p.rank;
-                const float* brb = p.lb + (size_t)(rowb < p.n ? rowb : 0) * p.rank;
+                const float* bra = q.lb + (size_t)(rowa < q.n ? rowa : 0) * q.rank;
+                const float* brb = q.lb + (size_t)(rowb < q.n ? rowb : 0) * q.rank;
 #pragma unroll 4
-                for (uint32_t j = t; j < p.rank; j += 4) {
+                for (uint32_t j = t; j < q.rank; j += 4) {
                     const float ba = __ldg(bra + j), bb = __ldg(brb + j);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const float tv = __ldcg(p.t_g + mt * p.rank + j);
+                        const float tv = __ldcg(q.t_g + mt * q.rank + j);
                         la[mt] = fmaf(ba, tv, la[mt]);
                         lb2[mt] = fmaf(bb, tv, lb2[mt]);
                     }
@@ -455,15 +486,15 @@ decode_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tm_big,
                     la[mt] += __shfl_xor_sync(kFull, la[mt], 2);
                     lb2[mt] += __shfl_xor_sync(kFull, lb2[mt], 1);
                     lb2[mt] += __shfl_xor_sync(kFull, lb2[mt], 2);
-                    v[mt][0] += p.lscale * la[mt];
-                    v[mt][1] += p.lscale * lb2[mt];
+                    v[mt][0] += q.lscale * la[mt];
+                    v[mt][1] += q.lscale * lb2[mt];
                 }
             }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                if (mt != t || (uint32_t)mt >= p.m) continue;
-                if (rowa < p.n) p.y[(size_t)mt * p.ldy + rowa] = v[mt][0];
-                if (rowb < p.n) p.y[(size_t)mt * p.ldy + rowb] = v[mt][1];
+                if (mt != t || (uint32_t)mt >= q.m) continue;
+                if (rowa < q.n) q.y[(size_t)mt * q.ldy + rowa] = v[mt][0];
+                if (rowb < q.n) q.y[(size_t)mt * q.ldy + rowb] = v[mt][1];
             }
         }
         if (!ok) {
@@ -529,10 +560,9 @@ bool make_weight_map(CUtensorMap* map, const uint8_t* w, uint32_t n, uint32_t kb
 
 inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
-template <int MT>
-cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtensorMap& mid, const CUtensorMap& small,
-                      size_t smem, int grid, cudaStream_t s) {
-    auto kern = decode_kernel<MT>;
+template <int MT, int NP>
+cudaError_t launch_mt(const DecodeArgs<NP>& ga, size_t smem, int grid, cudaStream_t s) {
+    auto kern = decode_kernel<MT, NP>;
     static bool attr_set = false;      // one opt-in to the full shared-memory carve-out per kernel
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - 1024);
@@ -546,14 +576,46 @@ cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtenso
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     int na = 0;
-    if (p.use_pdl) {
+    if (ga.p[0].use_pdl) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, kern, p, big, mid, small);
+    return cudaLaunchKernelEx(&cfg, kern, ga);
+}
+
+template <int NP>
+cudaError_t launch_args(const DecodeArgs<NP>& ga, size_t smem, int grid, cudaStream_t s) {
+    switch (ga.p[0].m) {
+        case 1: return launch_mt<1, NP>(ga, smem, grid, s);
+        case 2: return launch_mt<2, NP>(ga, smem, grid, s);
+        case 3: return launch_mt<3, NP>(ga, smem, grid, s);
+        case 4: return launch_mt<4, NP>(ga, smem, grid, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+// Encoding a tensor map costs about a microsecond of host time and weights are long-lived, so
+// the three maps of a payload are kept in a per-thread direct-mapped cache keyed by
+// (pointer, n, k).
+struct MapEntry { const uint8_t* w; uint32_t n, kb; CUtensorMap m[3]; };
+
+const MapEntry* maps_for(const uint8_t* w, uint32_t n, uint32_t kb) {
+    constexpr uint32_t kSlots = 512;
+    thread_local MapEntry* cache = nullptr;
+    if (!cache) cache = new MapEntry[kSlots]();
+    uint64_t h = reinterpret_cast<uintptr_t>(w) * 0x9E3779B97F4A7C15ull;
+    h ^= ((uint64_t)n << 32 | kb) * 0xC2B2AE3D27D4EB4Full;
+    MapEntry& e = cache[(h >> 40) % kSlots];
+    if (e.w == w && e.n == n && e.kb == kb) return &e;
+    e.w = nullptr;
+    if (!make_weight_map(&e.m[0], w, n, kb, 20) || !make_weight_map(&e.m[1], w, n, kb, 12) ||
+        !make_weight_map(&e.m[2], w, n, kb, 4))
+        return nullptr;
+    e.w = w; e.n = n; e.kb = kb;
+    return &e;
 }
 
 }  // namespace
@@ -562,14 +624,10 @@ cudaError_t launch_mt(const GemvParams& p, const CUtensorMap& big, const CUtenso
 // Runs right before the decode kernel.  With programmatic dependent launch it first waits for the
 // work before it (the producer of x) and only then lets the decode kernel start, which may
 // therefore read x at once and needs to wait for this grid only before it uses t.
-__global__ void __launch_bounds__(256) lora_project_kernel(const void* __restrict__ x, int x_dtype, uint32_t k,
-                                                           const float* __restrict__ la, uint32_t rank,
-                                                           float* __restrict__ t, int use_pdl, int vec4) {
-    if (use_pdl) {
-        pdl_wait_prior_grids();
-        pdl_launch_dependents();
-    }
-    const uint32_t pr = blockIdx.x, tok = pr / rank, j = pr - tok * rank;
+__device__ __forceinline__ void project_one(const void* __restrict__ x, int x_dtype, uint32_t k,
+                                            const float* __restrict__ la, uint32_t rank, float* __restrict__ t,
+                                            uint32_t pr, int vec4) {
+    const uint32_t tok = pr / rank, j = pr - tok * rank;
     const float* arow = la + (size_t)j * k;
     float s = 0.0f;
     if (vec4) {
@@ -590,6 +648,37 @@ __global__ void __launch_bounds__(256) lora_project_kernel(const void* __restric
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
     __syncthreads();
     if (threadIdx.x == 0) t[pr] = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+}
+
+__global__ void __launch_bounds__(256) lora_project_kernel(const void* __restrict__ x, int x_dtype, uint32_t k,
+                                                           const float* __restrict__ la, uint32_t rank,
+                                                           float* __restrict__ t, int use_pdl, int vec4) {
+    if (use_pdl) {
+        pdl_wait_prior_grids();
+        pdl_launch_dependents();
+    }
+    project_one(x, x_dtype, k, la, rank, t, blockIdx.x, vec4);
+}
+
+// The same for the problems of a grouped launch: CTA b serves problem i with start[i] <= b < start[i+1].
+struct ProjectGroupArgs {
+    const void* x[kMaxGroup];
+    const float* la[kMaxGroup];
+    float* t[kMaxGroup];
+    uint32_t k[kMaxGroup], rank[kMaxGroup], start[kMaxGroup + 1];
+    int32_t x_dtype[kMaxGroup], vec4[kMaxGroup];
+    uint32_t count;
+    int32_t use_pdl;
+};
+
+__global__ void __launch_bounds__(256) lora_project_group_kernel(const __grid_constant__ ProjectGroupArgs a) {
+    if (a.use_pdl) {
+        pdl_wait_prior_grids();
+        pdl_launch_dependents();
+    }
+    uint32_t pi = 0;
+    while (pi + 1 < a.count && blockIdx.x >= a.start[pi + 1]) ++pi;
+    project_one(a.x[pi], a.x_dtype[pi], a.k[pi], a.la[pi], a.rank[pi], a.t[pi], blockIdx.x - a.start[pi], a.vec4[pi]);
 }
 
 cudaError_t launch_lora_project_impl(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
@@ -619,6 +708,40 @@ cudaError_t launch_lora_project(const void* x, int x_dtype, uint32_t m, uint32_t
     return launch_lora_project_impl(x, x_dtype, m, k, la, rank, t, use_pdl, s);
 }
 
+
+cudaError_t launch_lora_project_group(const GemvParams* ps, uint32_t count, float* const* t, uint32_t m, int use_pdl,
+                                      cudaStream_t s) {
+    ProjectGroupArgs a{};
+    uint32_t n = 0;
+    a.start[0] = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemvParams& p = ps[i];
+        if (!p.rank) continue;
+        a.x[n] = p.x; a.la[n] = p.la; a.t[n] = t[i];
+        a.k[n] = p.k; a.rank[n] = p.rank; a.x_dtype[n] = p.x_dtype;
+        a.vec4[n] = p.x_dtype == LQ4_DTYPE_F32 && p.k % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(p.la) & 15) == 0;
+        a.start[n + 1] = a.start[n] + m * p.rank;
+        ++n;
+    }
+    if (n == 0) return cudaSuccess;
+    a.count = n;
+    a.use_pdl = use_pdl;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(a.start[n]);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (use_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, lora_project_group_kernel, a);
+}
 
 size_t decode_plan_smem(GemvParams& p) {
     if (p.m == 0 || p.m > 4 || p.kb == 0 || p.kb % kGemvGranuleBlocks != 0) return 0;
@@ -654,31 +777,79 @@ size_t decode_plan_smem(GemvParams& p) {
 uint64_t decode_units(const GemvParams& p) { return p.whole_tiles ? (uint64_t)p.tiles : (uint64_t)p.tiles * p.kg; }
 
 cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s) {
-    // Encoding a tensor map costs about a microsecond of host time; weights are long-lived, so the
-    // three maps of a payload are kept in a small per-thread cache keyed by (pointer, n, k).
-    struct Entry { const uint8_t* w; uint32_t n, kb; CUtensorMap big, mid, small; };
-    thread_local Entry cache[32];
-    thread_local uint32_t next = 0;
-    Entry* hit = nullptr;
-    for (Entry& e : cache)
-        if (e.w == p.w && e.n == p.n && e.kb == p.kb) { hit = &e; break; }
-    if (!hit) {
-        Entry& e = cache[next++ % 32];
-        if (!make_weight_map(&e.big, p.w, p.n, p.kb, 20) || !make_weight_map(&e.mid, p.w, p.n, p.kb, 12) ||
-            !make_weight_map(&e.small, p.w, p.n, p.kb, 4)) {
-            e.w = nullptr;
-            return cudaErrorInvalidValue;
+    const MapEntry* e = maps_for(p.w, p.n, p.kb);
+    if (!e) return cudaErrorInvalidValue;
+    DecodeArgs<1> ga{};
+    ga.p[0] = p;
+    for (int i = 0; i < 3; ++i) ga.maps[0][i] = e->m[i];
+    ga.ub[0] = 0;
+    ga.ub[1] = (uint64_t)p.tiles * p.kg;
+    ga.count = 1;
+    ga.any_rank = p.rank != 0;
+    return launch_args<1>(ga, smem, grid, s);
+}
+
+size_t decode_group_plan_smem(GemvParams* ps, uint32_t count) {
+    if (count == 0 || count > (uint32_t)kMaxGroup) return 0;
+    const uint32_t MT = ps[0].m;
+    if (MT == 0 || MT > 4) return 0;
+    uint32_t max_kb = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemvParams& p = ps[i];
+        if (p.m != MT || p.kb == 0 || p.kb % kGemvGranuleBlocks != 0 || p.signs) return 0;
+        max_kb = p.kb > max_kb ? p.kb : max_kb;
+    }
+    uint32_t off = 2 * kMaxStages * 8 + 128;      // mbarriers, then the block of zeros
+    const uint32_t off_xs = off;
+    off += align_up(max_kb * MT * 64, 128);
+    const uint32_t off_sx = off;
+    off += align_up(max_kb * MT * 8, 128);
+    const uint32_t budget = (uint32_t)kMaxSmem - 1024;
+    if (off + 2 * kSlotBytes > budget) return 0;
+    uint32_t nst = (budget - off) / kSlotBytes;
+    if (nst > 4) nst = 4;
+    for (uint32_t i = 0; i < count; ++i) {
+        GemvParams& p = ps[i];
+        p.off_t = p.off_xrot = 0;
+        p.off_xs = off_xs;
+        p.off_sx = off_sx;
+        p.off_stage = off;
+        p.stage_bytes = kSlotBytes;
+        p.off_stage_xs = p.off_stage_sx = 0;
+        p.nstages = nst;
+        p.kg = p.kb / kGemvGranuleBlocks;
+        p.whole_tiles = 0;
+    }
+    return (size_t)off + (size_t)nst * kSlotBytes;
+}
+
+uint64_t decode_group_units(const GemvParams* ps, uint32_t count) {
+    uint64_t total = 0;
+    for (uint32_t i = 0; i < count; ++i) total += (uint64_t)ps[i].tiles * ps[i].kg;
+    return total;
+}
+
+cudaError_t launch_decode_group(const GemvParams* ps, uint32_t count, size_t smem, int grid, cudaStream_t s) {
+    if (count == 0 || count > (uint32_t)kMaxGroup) return cudaErrorInvalidValue;
+    // the argument block is a few kilobytes: keep it off the stack of deep callers
+    thread_local DecodeArgs<kMaxGroup> ga;
+    ga.count = count;
+    ga.any_rank = 0;
+    ga.ub[0] = 0;
+    for (uint32_t i = 0; i < (uint32_t)kMaxGroup; ++i) {
+        const GemvParams& p = ps[i < count ? i : count - 1];
+        ga.p[i] = p;
+        if (i < count) {
+            const MapEntry* e = maps_for(p.w, p.n, p.kb);
+            if (!e) return cudaErrorInvalidValue;
+            for (int j = 0; j < 3; ++j) ga.maps[i][j] = e->m[j];
+            ga.ub[i + 1] = ga.ub[i] + (uint64_t)p.tiles * p.kg;
+            ga.any_rank |= p.rank != 0;
+        } else {
+            ga.ub[i + 1] = ga.ub[i];
         }
-        e.w = p.w; e.n = p.n; e.kb = p.kb;
-        hit = &e;
     }
-    switch (p.m) {
-        case 1: return launch_mt<1>(p, hit->big, hit->mid, hit->small, smem, grid, s);
-        case 2: return launch_mt<2>(p, hit->big, hit->mid, hit->small, smem, grid, s);
-        case 3: return launch_mt<3>(p, hit->big, hit->mid, hit->small, smem, grid, s);
-        case 4: return launch_mt<4>(p, hit->big, hit->mid, hit->small, smem, grid, s);
-        default: return cudaErrorInvalidValue;
-    }
+    return launch_args<kMaxGroup>(ga, smem, grid, s);
 }
 
 }  // namespace lq4

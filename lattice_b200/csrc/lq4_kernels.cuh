@@ -77,6 +77,17 @@ size_t decode_plan_smem(GemvParams& p);
 // Work units (tile, stage) of a planned launch; the grid is min(#SM, units).
 uint64_t decode_units(const GemvParams& p);
 cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s);
+// Several independent projections of the same token count in ONE persistent launch: the work
+// units of all problems form one stream-K range, so launch, prologue and tail are paid once.
+constexpr int kMaxGroup = 8;
+// Fills the shared-memory fields of every problem (sized for the longest k) and returns the
+// dynamic shared memory needed, or 0 if the group cannot run in one launch.
+size_t decode_group_plan_smem(GemvParams* ps, uint32_t count);
+uint64_t decode_group_units(const GemvParams* ps, uint32_t count);
+cudaError_t launch_decode_group(const GemvParams* ps, uint32_t count, size_t smem, int grid, cudaStream_t s);
+// t[i] = A_i x_i for every problem of the group that has an adapter, in one launch (none: no launch).
+cudaError_t launch_lora_project_group(const GemvParams* ps, uint32_t count, float* const* t, uint32_t m, int use_pdl,
+                                      cudaStream_t s);
 // t = A x for the decode kernel's LoRA epilogue; launched right before launch_decode.
 cudaError_t launch_lora_project(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
                                 float* t, int use_pdl, cudaStream_t s);

@@ -371,3 +371,80 @@ def test_config4_full_size_sampled_output_features(be):
     assert bool(torch.isfinite(y).all())
     y0 = be.linear(x, qw)
     assert float((y - y0).abs().max()) > 0.1
+
+
+# ---------------------------------------------------------------- grouped decode launch
+def _run_group(be, cases, bf16=False):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    keep, problems, qws = [], [], []
+    for case in cases:
+        qw = Q4WeightBuf.from_host_payload(case["payload"], case["n"], case["k"])
+        qws.append(qw)
+        x = dev(case["x"]).to(torch.bfloat16) if bf16 else dev(case["x"])
+        lora = None
+        if case["lora"] is not None:
+            a, b, s = case["lora"]
+            ad, bd = dev(a), dev(b)
+            keep += [ad, bd]
+            lora = LoraDesc(ad.data_ptr(), bd.data_ptr(), case["rank"], s)
+        problems.append((x, qw, lora))
+    outs = [torch.full((c["m"], c["n"]), float("nan"), dtype=torch.float32, device="cuda") for c in cases]
+    before = be.launch_count
+    be.linear_group(problems, outs)
+    launches = be.launch_count - before
+    be.check_device_status()
+    ys = [o.cpu().numpy() for o in outs]
+    for qw in qws:
+        qw.free()
+    return ys, launches
+
+
+@pytest.mark.parametrize("m", [1, 2, 4])
+def test_group_decode_set_matches_oracle(be, m):
+    # the four shapes of the large-layer decode set, scaled down 4x, each with its own adapter
+    shapes = [(1280, 1280), (1280, 256), (1280, 4352), (4352, 1280)]
+    cases = [make_case(3, m, k, n, 16, 32.0, extra=10 + i) for i, (k, n) in enumerate(shapes)]
+    ys, launches = _run_group(be, cases)
+    assert launches == 2          # one projection launch for all adapters, one decode launch
+    for y, c in zip(ys, cases):
+        assert not np.isnan(y).any()
+        assert tol_ratio(y, c["y_ref"]) <= 1.0
+
+
+def test_group_mixed_adapters_ragged_rows_eight_problems(be):
+    spec = [(1024, 300, 0), (2048, 129, 8), (128, 1000, 16), (1024, 128, 0), (3072, 77, 4), (1024, 2000, 0),
+            (512, 640, 128), (1024, 1, 2)]
+    cases = [make_case(2, 3, k, n, r, 2.0 * r, extra=30 + i) for i, (k, n, r) in enumerate(spec)]
+    ys, launches = _run_group(be, cases)
+    assert launches == 2
+    for y, c in zip(ys, cases):
+        assert not np.isnan(y).any()
+        assert tol_ratio(y, c["y_ref"]) <= 1.0
+
+
+def test_group_without_adapters_is_one_launch_and_repeatable(be):
+    cases = [make_case(1, 1, 1024, 3584, extra=50), make_case(1, 1, 1024, 512, extra=51)]
+    ys1, launches = _run_group(be, cases, bf16=False)
+    ys2, _ = _run_group(be, cases, bf16=False)
+    assert launches == 1
+    for y1, y2, c in zip(ys1, ys2, cases):
+        assert np.array_equal(y1.view(np.uint32), y2.view(np.uint32))     # fixed summation order
+        assert tol_ratio(y1, c["y_ref"]) <= 1.0
+
+
+def test_group_that_cannot_share_a_launch_runs_problem_by_problem(be):
+    # different token counts, an odd k and a rotated problem: served through the single-problem path
+    cases = [make_case(2, 1, 1024, 256, 16, 32.0, extra=60), make_case(2, 8, 1024, 256, 16, 32.0, extra=61),
+             make_case(2, 2, 96, 200, extra=62)]
+    ys, launches = _run_group(be, cases)
+    assert launches >= 3
+    for y, c in zip(ys, cases):
+        assert tol_ratio(y, c["y_ref"]) <= 1.0
+    # more problems than one launch takes
+    many = [make_case(1, 1, 256, 128, extra=70 + i) for i in range(9)]
+    ys, launches = _run_group(be, many)
+    assert launches == 9
+    for y, c in zip(ys, many):
+        assert tol_ratio(y, c["y_ref"]) <= 1.0
+    assert be.linear_group([]) == []
