@@ -374,15 +374,31 @@ def run_ours(args):
 
     if rank == 0 and world == 1 and not args.no_aux:
         line["aux"] = aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust)
-        # the same step with the other launch mode, timed the same way
-        def other_step():
-            for projs in layers:
-                run_set(projs, xs, not grouped)
-        ofn, ol = make_graphed(other_step)
-        oms, _ = timed(ofn, args.steps, args.warmup, ol)
-        ov = per_step_bytes * args.steps / (oms * 1e-3) / 1e9
-        line["aux"]["decode_set_" + ("per_projection" if grouped else "grouped") + "_launches"] = {
-            "GB/s": ov, "frac_hbm": ov / hbm_peak, "ms_per_step": oms / args.steps}
+        # the same decode set at other token counts and with the other launch mode, timed the same way
+        def time_sets(mm, grp):
+            xs_m = {k: torch.randn((mm, k), device=dev) for k in (5120, 17408)}
+            ycat_m = torch.empty((mm, sum(nls)), device=dev)
+            outs = [ycat_m[:, offs[si]:offs[si] + nls[si]] for si in range(len(SHAPES))]
+
+            def fn():
+                for projs in layers:
+                    if grp:
+                        be.linear_group([(xs_m[p["k"]], p["qw"], p["lora"]) for p in projs], outs)
+                    else:
+                        for si, p in enumerate(projs):
+                            be.dispatch_gemm_q4(xs_m[p["k"]], 0, p["qw"], outs[si], 0, mm, p["nl"], p["k"], lora=p["lora"],
+                                                ldy=ycat_m.stride(0))
+            gfn, gl = make_graphed(fn)
+            gms, _ = timed(gfn, min(args.steps, 20), 3, gl)
+            nsteps = min(args.steps, 20)
+            byts = args.layers * sum(algorithmic_bytes(mm, n, k, LORA_RANK) for k, n in SHAPES)
+            v = byts * nsteps / (gms * 1e-3) / 1e9
+            return {"GB/s": v, "frac_hbm": v / hbm_peak, "us_per_set": gms * 1e3 / nsteps / args.layers}
+        for mm in (1, 4, 16):
+            for grp in (True, False):
+                if mm == m and grp == grouped:
+                    continue
+                line["aux"][f"decode_set_M{mm}_" + ("grouped" if grp else "per_projection")] = time_sets(mm, grp)
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(layers[0])
     if rank == 0:
@@ -472,9 +488,6 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
         bench_linear("config1_M1_K1024_N3584_warm", 1, 1024, 3584, 0, 1, 512)
         bench_linear("config2_M1_lora16_cold", 1, 1024, 3584, 16, 128, 512)
         bench_linear("config2_M8_lora16_cold", 8, 1024, 3584, 16, 128, 512)
-        for mm in (4, 16):
-            for (k, n) in SHAPES:
-                bench_linear(f"config3_M{mm}_{k}to{n}_lora16", mm, k, n, 16, 4, 40)
         bench_linear("config5_quarot_M1_K4096_N11008", 1, 4096, 11008, 0, 8, 200, rot=True)
         bench_linear("config4_prefill_M2048_K5120_N17408_lora64_bf16", 2048, 5120, 17408, 64, 1, 5,
                      x_dtype=torch.bfloat16)
@@ -493,8 +506,8 @@ def run_only(args):
     dev = torch.device("cuda", 0)
     if args.only == "gemm-slice":          # M=2048, K=5120 on a 2176-row N-shard of the 17408 outputs, bf16, LoRA r=64
         m, k, n, r, dt = 2048, 5120, 2176, 64, torch.bfloat16
-    elif args.only == "decode-up":         # M=1, 5120 -> 17408, LoRA r=16
-        m, k, n, r, dt = 1, 5120, 17408, 16, torch.float32
+    elif args.only == "decode-up":         # M=--m (default 1), 5120 -> 17408, LoRA r=16
+        m, k, n, r, dt = args.m, 5120, 17408, 16, torch.float32
     elif args.only == "decode-set":        # M=1, one grouped launch over the four large-layer shapes, LoRA r=16
         probs, keep = [], []
         for k, n in SHAPES:

@@ -119,10 +119,9 @@ lq4_status validate_linear(const lq4_linear_args* a) {
     return LQ4_OK;
 }
 
-// One call of the decode kernel for at most 16 tokens.
-lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dtype, const float* signs,
-                        uint32_t m, float* y, uint64_t ldy, cudaStream_t s) {
-    GemvParams p{};
+void fill_params(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dtype, uint32_t m, float* y,
+                 uint64_t ldy, GemvParams& p) {
+    p = GemvParams{};
     p.w = a->w; p.y = y; p.ldy = ldy;
     p.m = m; p.n = a->n; p.k = a->k;
     p.kb = a->k / 32; p.kg = p.kb / kGemvGranuleBlocks;
@@ -130,22 +129,65 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
     p.nt = (2 * m + 7) / 8;
     p.gmax = p.nt == 1 ? 2 * m : 8;
     p.status = ctx->status;
+    p.tsync = ctx->tsync;          // launch generation and end-of-launch counter
+    p.use_pdl = ctx->pdl;
+    p.sm_count = ctx->sm_count;
+    p.x = x; p.x_dtype = x_dtype;
     if (a->lora) {
         p.la = a->lora->a; p.lb = a->lora->b; p.rank = a->lora->rank; p.lscale = a->lora->scale;
     }
-    const uint64_t total = (uint64_t)p.tiles * p.kg;
-    const int grid = (int)(total < (uint64_t)ctx->sm_count ? total : (uint64_t)ctx->sm_count);
-    lq4_status st;
-    if ((st = ensure(ctx, ctx->partials, (size_t)grid * 2 * kGemvTileRows * p.nt * 4 * sizeof(float), true, s))) return st;
-    if ((st = ensure(ctx, ctx->tickets, (size_t)p.tiles * 8 * sizeof(uint32_t), true, s))) return st;
-    p.partials = (float*)ctx->partials.p;
-    p.tickets = (uint32_t*)ctx->tickets.p;
+}
 
-    const bool resident = gemv_resident_fits(m, a->k, signs != nullptr);
-    if (resident) {
-        p.x = x; p.x_dtype = x_dtype; p.signs = signs;
-        p.tsync = ctx->tsync;      // launch generation and end-of-launch counter
-        p.use_pdl = ctx->pdl;
+// The dense decode kernel over 1..kMaxGroup problems of the same token count (<= 16): one
+// preparation launch (activation limbs, adapter projections), one persistent launch.
+lq4_status run_dense(lq4_ctx* ctx, GemvParams* ps, uint32_t count, cudaStream_t s) {
+    const uint32_t m = ps[0].m;
+    lq4_status st;
+    size_t rec_total = 0, t_floats = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        rec_total += (dense_record_bytes(m, ps[i].k) + 255) / 256 * 256;
+        t_floats += ((size_t)m * ps[i].rank + 63) / 64 * 64;
+    }
+    if ((st = ensure(ctx, ctx->xs, rec_total, false, s))) return st;
+    if ((st = ensure(ctx, ctx->t, t_floats * sizeof(float) + 256, false, s))) return st;
+    uint8_t* rec[kMaxGroup];
+    float* tptr[kMaxGroup];
+    size_t roff = 0, toff = 0;
+    uint64_t units = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        rec[i] = (uint8_t*)ctx->xs.p + roff;
+        tptr[i] = (float*)ctx->t.p + toff;
+        roff += (dense_record_bytes(m, ps[i].k) + 255) / 256 * 256;
+        toff += ((size_t)m * ps[i].rank + 63) / 64 * 64;
+        ps[i].xs_g = rec[i];
+        ps[i].t_g = ps[i].rank ? tptr[i] : nullptr;
+        units += (uint64_t)ps[i].tiles * ps[i].kg;
+    }
+    const size_t smem = dense_plan_smem(ps, count);
+    if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "dense decode plan does not fit");
+    const int grid = (int)(units < (uint64_t)ctx->sm_count ? units : (uint64_t)ctx->sm_count);
+    const size_t ng = (m + 3) / 4;
+    if ((st = ensure(ctx, ctx->partials, (size_t)grid * kGemvTileRows * ng * 4 * 8, true, s))) return st;
+    for (uint32_t i = 0; i < count; ++i) ps[i].partials = (float*)ctx->partials.p;
+    LQ4_CUDA(launch_dense_prep(ps, count, rec, tptr, ctx->pdl, s));
+    LQ4_CUDA(launch_dense(ps, count, smem, grid, s));
+    ctx->launches += 2;
+    return LQ4_OK;
+}
+
+// One projection of at most 16 tokens through the decode kernels: a single token whose row fits
+// in shared memory takes the resident kernel, everything else the dense one.
+lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dtype, const float* signs,
+                        uint32_t m, float* y, uint64_t ldy, cudaStream_t s) {
+    GemvParams p;
+    fill_params(ctx, a, x, x_dtype, m, y, ldy, p);
+    lq4_status st;
+    if (m == 1 && gemv_resident_fits(1, a->k, signs != nullptr)) {
+        p.signs = signs;
+        const uint64_t total = (uint64_t)p.tiles * p.kg;
+        const int grid = (int)(total < (uint64_t)ctx->sm_count ? total : (uint64_t)ctx->sm_count);
+        if ((st = ensure(ctx, ctx->partials, (size_t)grid * kGemvTileRows * 4 * 8, true, s))) return st;
+        p.partials = (float*)ctx->partials.p;
         if (p.rank) {
             // the projection t = A x runs as a small kernel right before; the decode kernel starts
             // streaming weights meanwhile and waits for t only before its first epilogue
@@ -154,7 +196,6 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
             ctx->launches += 1;
             p.t_g = (const float*)ctx->t.p;
         }
-        p.sm_count = ctx->sm_count;
         const size_t smem = gemv_plan_smem(p, true);
         if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "resident plan does not fit");
         const uint64_t units = decode_units(p);
@@ -163,25 +204,8 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
         ctx->launches += 1;
         return LQ4_OK;
     }
-    // staged variant: rotation (if any) was applied by the caller into the workspace
-    if ((st = ensure(ctx, ctx->xs, (size_t)p.kb * p.nt * p.gmax * 64, false, s))) return st;
-    if ((st = ensure(ctx, ctx->sx, (size_t)p.kb * p.nt * 16, false, s))) return st;
-    launch_prep_xs(x, x_dtype, m, a->k, p.nt, p.gmax, (uint8_t*)ctx->xs.p, (float*)ctx->sx.p, s);
-    ctx->launches += 1;
-    if (p.rank) {
-        if ((st = ensure(ctx, ctx->t, (size_t)m * p.rank * sizeof(float), false, s))) return st;
-        launch_lora_t(x, x_dtype, m, a->k, p.la, p.rank, (float*)ctx->t.p, s);
-        ctx->launches += 1;
-        p.t_g = (const float*)ctx->t.p;
-    }
-    p.xs_g = (const uint8_t*)ctx->xs.p;
-    p.sx_g = (const float*)ctx->sx.p;
-    p.use_pdl = 0;
-    const size_t smem = gemv_plan_smem(p, false);
-    if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "staged plan does not fit");
-    LQ4_CUDA(launch_gemv_mma(p, false, smem, grid, s));
-    ctx->launches += 1;
-    return LQ4_OK;
+    if (signs) return fail(LQ4_ERR_UNSUPPORTED, "rotation must be applied before the dense decode kernel");
+    return run_dense(ctx, &p, 1, s);
 }
 
 }  // namespace
@@ -302,7 +326,7 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     int path = a->path;
     if (path == LQ4_PATH_AUTO) {
         if (!fast_layout) path = LQ4_PATH_GEMV_GENERIC;
-        else if (a->m <= 4 && gemv_resident_fits(a->m, a->k, false)) path = LQ4_PATH_GEMV_MMA;   // decode kernel
+        else if (a->m <= (uint32_t)kGemvMaxM) path = LQ4_PATH_GEMV_MMA;                          // decode kernels
         else path = gemm_supported(a->m, a->n, a->k, rank) ? LQ4_PATH_GEMM_TC : LQ4_PATH_GEMV_MMA;
     }
     if (path != LQ4_PATH_GEMV_GENERIC && !fast_layout)
@@ -314,8 +338,8 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
 
     // The decode kernel rotates in its own prologue when the row fits; otherwise the
     // rotation runs as a kernel of its own into the workspace.
-    const bool in_kernel_rot = signs && path == LQ4_PATH_GEMV_MMA && a->m <= kGemvMaxM && rank == 0 &&
-                               gemv_resident_fits(a->m, a->k, true);
+    const bool in_kernel_rot = signs && path == LQ4_PATH_GEMV_MMA && a->m == 1 && rank == 0 &&
+                               gemv_resident_fits(1, a->k, true);
     if (signs && !in_kernel_rot) {
         if ((st = ensure(ctx, ctx->xrot, (size_t)a->m * a->k * 4, false, s))) return st;
         LQ4_CUDA(launch_hadamard_rows(x, x_dtype, signs, a->k, a->m, (float*)ctx->xrot.p, s));
@@ -376,39 +400,26 @@ lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t 
     // token count; anything else runs problem by problem with the same results.
     bool one_launch = count >= 2 && count <= (uint32_t)kMaxGroup;
     GemvParams ps[kMaxGroup];
+    const uint32_t m = args[0].m;
+    for (uint32_t i = 0; i < count && one_launch; ++i) {
+        const lq4_linear_args& a = args[i];
+        const uint32_t rank = a.lora ? a.lora->rank : 0;
+        one_launch = a.m >= 1 && a.m <= (uint32_t)kGemvMaxM && a.m == m && a.n > 0 && !a.rot && (a.k % 128 == 0) &&
+                     aligned(a.w, 16) && aligned(a.x, 16) && rank <= (uint32_t)kGemvMaxRank &&
+                     (a.path == LQ4_PATH_AUTO || a.path == LQ4_PATH_GEMV_MMA);
+        if (one_launch) fill_params(ctx, &a, a.x, a.x_dtype, a.m, a.y, a.ldy ? a.ldy : a.n, ps[i]);
+    }
     size_t smem = 0;
-    if (one_launch) {
-        for (uint32_t i = 0; i < count && one_launch; ++i) {
-            const lq4_linear_args& a = args[i];
-            const uint32_t rank = a.lora ? a.lora->rank : 0;
-            one_launch = a.m >= 1 && a.m <= 4 && a.m == args[0].m && a.n > 0 && !a.rot && (a.k % 128 == 0) &&
-                         aligned(a.w, 16) && aligned(a.x, 16) && rank <= (uint32_t)kGemvMaxRank &&
-                         (a.path == LQ4_PATH_AUTO || a.path == LQ4_PATH_GEMV_MMA);
-            if (!one_launch) break;
-            GemvParams p{};
-            p.w = a.w; p.y = a.y; p.ldy = a.ldy ? a.ldy : a.n;
-            p.m = a.m; p.n = a.n; p.k = a.k;
-            p.kb = a.k / 32; p.kg = p.kb / kGemvGranuleBlocks;
-            p.tiles = (a.n + kGemvTileRows - 1) / kGemvTileRows;
-            p.nt = 1; p.gmax = 2 * a.m;
-            p.status = ctx->status;
-            p.tsync = ctx->tsync;
-            p.use_pdl = ctx->pdl;
-            p.sm_count = ctx->sm_count;
-            p.x = a.x; p.x_dtype = a.x_dtype;
-            if (a.lora) { p.la = a.lora->a; p.lb = a.lora->b; p.rank = rank; p.lscale = a.lora->scale; }
-            ps[i] = p;
-        }
-        if (one_launch) smem = decode_group_plan_smem(ps, count);
-        one_launch = one_launch && smem != 0;
+    if (one_launch && m == 1) {
+        smem = decode_group_plan_smem(ps, count);      // 0: some row does not fit in shared memory
     }
     if (!one_launch) {
         for (uint32_t i = 0; i < count; ++i)
             if ((st = lq4_linear(ctx, &args[i], stream))) return st;
         return LQ4_OK;
     }
+    if (m > 1 || !smem) return run_dense(ctx, ps, count, s);
 
-    const uint32_t m = args[0].m;
     size_t t_floats = 0;
     for (uint32_t i = 0; i < count; ++i) t_floats += ((size_t)m * ps[i].rank + 63) / 64 * 64;
     if ((st = ensure(ctx, ctx->t, t_floats * sizeof(float) + 256, false, s))) return st;

@@ -23,55 +23,14 @@
 
 #include <mutex>
 
-#include "lq4_gemv_common.cuh"
+#include "lq4_decode_common.cuh"
 
 namespace lq4 {
 
 namespace {
 
 using namespace gemv;
-
-constexpr int kBigBlocks = 20;                                   // blocks per row in a big stage
-constexpr int kSmallBlocks = kGemvGranuleBlocks;                 // 4
-constexpr uint32_t kSlotBytes = kGemvTileRows * kBigBlocks * kBlockBytes;      // 51,200
-constexpr uint32_t kSmallBytes = kGemvTileRows * kSmallBlocks * kBlockBytes;   // 10,240
-constexpr int kMaxStages = 8;
-constexpr uint32_t kZeroOffset = 2 * kMaxStages * 8;   // 32 zero bytes after the mbarriers
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
-                                            uint64_t* bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
-        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
-        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
-        : "memory");
-}
-
-// Cross-CTA messages are 8-byte {value, tag} pairs written with one store: the tag arrives with
-// the value, so neither side needs a fence (a gpu-scope fence here would wait for the hundreds of
-// kilobytes of weight loads the SM has in flight).  The tag is the launch generation.
-__device__ __forceinline__ void msg_store(uint2* p, float v, uint32_t tag) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
-}
-__device__ __forceinline__ uint2 msg_load(const uint2* p) {
-    uint2 r;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
-    return r;
-}
-// u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
-__device__ __forceinline__ void imma_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-constexpr float kLimb1Ratio = 254.0f;    // limb 1 is in units of scale / 254
-
-__device__ __forceinline__ uint32_t pack_s8x4(float a, float b, float c, float d) {
-    return ((uint32_t)(int)a & 0xffu) | (((uint32_t)(int)b & 0xffu) << 8) | (((uint32_t)(int)c & 0xffu) << 16) |
-           (((uint32_t)(int)d & 0xffu) << 24);
-}
+using namespace dec;
 
 // Activations of one Q4 block (32 values, four threads with eight each) become two int8 limbs
 // with a common f32 scale s = max|x| / 127:  x ~= s * (l0 + l1 / 254), |l0|, |l1| <= 127, so the
@@ -108,10 +67,6 @@ __device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT
         make_uint2(pack_s8x4(l1[0], l1[2], l1[4], l1[6]), pack_s8x4(l1[1], l1[3], l1[5], l1[7]));
     if (j == 0) sx[(size_t)blk * MT + mp] = make_float2(s0, sum);
 }
-
-// Granules (4 blocks each) the next stage takes when `left` remain in the segment: 5, 3 or 1.
-// Row strides of 100, 60 and 20 words keep the consumer loads free of bank conflicts.
-__device__ __forceinline__ uint32_t stage_granules(uint32_t left) { return left >= 5 ? 5u : (left >= 3 ? 3u : 1u); }
 
 // Prologue of the 256 consumer threads: rotation, LoRA partial projection, activation limbs.
 template <int MT>
@@ -183,18 +138,6 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, ui
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
 }
-
-// Arguments of one launch: NP problems (NP = 1 for a single projection).  The shared-memory
-// offsets, the stage count, the workspace pointers and the PDL flag are taken from p[0]; the
-// problems differ in weights, shapes, activations, output and adapter.
-template <int NP>
-struct DecodeArgs {
-    GemvParams p[NP];
-    CUtensorMap maps[NP][3];      // boxes of 20, 12 and 4 blocks x 128 rows
-    uint64_t ub[NP + 1];          // first work unit of each problem (units: 4 blocks x 128 rows)
-    uint32_t count;
-    uint32_t any_rank;            // some problem has a LoRA adapter
-};
 
 template <int MT, int NP>
 __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_constant__ DecodeArgs<NP> ga) {
@@ -586,22 +529,28 @@ cudaError_t launch_mt(const DecodeArgs<NP>& ga, size_t smem, int grid, cudaStrea
     return cudaLaunchKernelEx(&cfg, kern, ga);
 }
 
-template <int NP>
-cudaError_t launch_args(const DecodeArgs<NP>& ga, size_t smem, int grid, cudaStream_t s) {
+// Single problems of up to four tokens (the library's own dispatch sends only one token here; the
+// allocation-free entry point uses all four); groups are one token per problem.
+cudaError_t launch_args(const DecodeArgs<1>& ga, size_t smem, int grid, cudaStream_t s) {
     switch (ga.p[0].m) {
-        case 1: return launch_mt<1, NP>(ga, smem, grid, s);
-        case 2: return launch_mt<2, NP>(ga, smem, grid, s);
-        case 3: return launch_mt<3, NP>(ga, smem, grid, s);
-        case 4: return launch_mt<4, NP>(ga, smem, grid, s);
+        case 1: return launch_mt<1, 1>(ga, smem, grid, s);
+        case 2: return launch_mt<2, 1>(ga, smem, grid, s);
+        case 3: return launch_mt<3, 1>(ga, smem, grid, s);
+        case 4: return launch_mt<4, 1>(ga, smem, grid, s);
         default: return cudaErrorInvalidValue;
     }
 }
+cudaError_t launch_args(const DecodeArgs<kMaxGroup>& ga, size_t smem, int grid, cudaStream_t s) {
+    if (ga.p[0].m != 1) return cudaErrorInvalidValue;
+    return launch_mt<1, kMaxGroup>(ga, smem, grid, s);
+}
 
+}  // namespace
+
+namespace dec {
 // Encoding a tensor map costs about a microsecond of host time and weights are long-lived, so
 // the three maps of a payload are kept in a per-thread direct-mapped cache keyed by
 // (pointer, n, k).
-struct MapEntry { const uint8_t* w; uint32_t n, kb; CUtensorMap m[3]; };
-
 const MapEntry* maps_for(const uint8_t* w, uint32_t n, uint32_t kb) {
     constexpr uint32_t kSlots = 512;
     thread_local MapEntry* cache = nullptr;
@@ -618,38 +567,12 @@ const MapEntry* maps_for(const uint8_t* w, uint32_t n, uint32_t kb) {
     return &e;
 }
 
-}  // namespace
+}  // namespace dec
 
 // t[tok][j] = sum_k A[j][k] * x[tok][k]: one CTA per (token, rank row), fixed reduction order.
 // Runs right before the decode kernel.  With programmatic dependent launch it first waits for the
 // work before it (the producer of x) and only then lets the decode kernel start, which may
 // therefore read x at once and needs to wait for this grid only before it uses t.
-__device__ __forceinline__ void project_one(const void* __restrict__ x, int x_dtype, uint32_t k,
-                                            const float* __restrict__ la, uint32_t rank, float* __restrict__ t,
-                                            uint32_t pr, int vec4) {
-    const uint32_t tok = pr / rank, j = pr - tok * rank;
-    const float* arow = la + (size_t)j * k;
-    float s = 0.0f;
-    if (vec4) {
-        const float4* a4 = reinterpret_cast<const float4*>(arow);
-        const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)tok * k);
-#pragma unroll 4
-        for (uint32_t i = threadIdx.x; i < k / 4; i += 256) {
-            const float4 a = __ldg(a4 + i), b = x4[i];
-            s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
-        }
-    } else {
-#pragma unroll 4
-        for (uint32_t i = threadIdx.x; i < k; i += 256) s = fmaf(__ldg(arow + i), load_act(x, x_dtype, (size_t)tok * k + i), s);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    __shared__ float part[8];
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
-    __syncthreads();
-    if (threadIdx.x == 0) t[pr] = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
-}
-
 __global__ void __launch_bounds__(256) lora_project_kernel(const void* __restrict__ x, int x_dtype, uint32_t k,
                                                            const float* __restrict__ la, uint32_t rank,
                                                            float* __restrict__ t, int use_pdl, int vec4) {
@@ -657,7 +580,7 @@ __global__ void __launch_bounds__(256) lora_project_kernel(const void* __restric
         pdl_wait_prior_grids();
         pdl_launch_dependents();
     }
-    project_one(x, x_dtype, k, la, rank, t, blockIdx.x, vec4);
+    dec::project_one(x, x_dtype, k, la, rank, t, blockIdx.x, vec4);
 }
 
 // The same for the problems of a grouped launch: CTA b serves problem i with start[i] <= b < start[i+1].
@@ -678,7 +601,7 @@ __global__ void __launch_bounds__(256) lora_project_group_kernel(const __grid_co
     }
     uint32_t pi = 0;
     while (pi + 1 < a.count && blockIdx.x >= a.start[pi + 1]) ++pi;
-    project_one(a.x[pi], a.x_dtype[pi], a.k[pi], a.la[pi], a.rank[pi], a.t[pi], blockIdx.x - a.start[pi], a.vec4[pi]);
+    dec::project_one(a.x[pi], a.x_dtype[pi], a.k[pi], a.la[pi], a.rank[pi], a.t[pi], blockIdx.x - a.start[pi], a.vec4[pi]);
 }
 
 cudaError_t launch_lora_project_impl(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
@@ -786,13 +709,13 @@ cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream
     ga.ub[1] = (uint64_t)p.tiles * p.kg;
     ga.count = 1;
     ga.any_rank = p.rank != 0;
-    return launch_args<1>(ga, smem, grid, s);
+    return launch_args(ga, smem, grid, s);
 }
 
 size_t decode_group_plan_smem(GemvParams* ps, uint32_t count) {
     if (count == 0 || count > (uint32_t)kMaxGroup) return 0;
     const uint32_t MT = ps[0].m;
-    if (MT == 0 || MT > 4) return 0;
+    if (MT != 1) return 0;
     uint32_t max_kb = 0;
     for (uint32_t i = 0; i < count; ++i) {
         const GemvParams& p = ps[i];
@@ -849,7 +772,7 @@ cudaError_t launch_decode_group(const GemvParams* ps, uint32_t count, size_t sme
             ga.ub[i + 1] = ga.ub[i];
         }
     }
-    return launch_args<kMaxGroup>(ga, smem, grid, s);
+    return launch_args(ga, smem, grid, s);
 }
 
 }  // namespace lq4

@@ -1,0 +1,108 @@
+// Pieces shared by the two decode kernels (lq4_decode.cu: one token, activations resident in
+// shared memory; lq4_dense.cu: 2..16 tokens, activation limbs staged beside the weights).
+#pragma once
+
+#include <cuda.h>
+
+#include "lq4_gemv_common.cuh"
+
+namespace lq4 {
+namespace dec {
+
+using namespace gemv;
+
+constexpr int kBigBlocks = 20;                                   // blocks per row in a big stage
+constexpr int kSmallBlocks = kGemvGranuleBlocks;                 // 4
+constexpr uint32_t kSlotBytes = kGemvTileRows * kBigBlocks * kBlockBytes;      // 51,200
+constexpr uint32_t kSmallBytes = kGemvTileRows * kSmallBlocks * kBlockBytes;   // 10,240
+constexpr int kMaxStages = 8;
+constexpr uint32_t kZeroOffset = 2 * kMaxStages * 8;   // 32 zero bytes after the mbarriers
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
+                                            uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
+// Cross-CTA messages are 8-byte {value, tag} pairs written with one store: the tag arrives with
+// the value, so neither side needs a fence (a gpu-scope fence here would wait for the hundreds of
+// kilobytes of weight loads the SM has in flight).  The tag is the launch generation.
+__device__ __forceinline__ void msg_store(uint2* p, float v, uint32_t tag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 msg_load(const uint2* p) {
+    uint2 r;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    return r;
+}
+// u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
+__device__ __forceinline__ void imma_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr float kLimb1Ratio = 254.0f;    // limb 1 is in units of scale / 254
+
+__device__ __forceinline__ uint32_t pack_s8x4(float a, float b, float c, float d) {
+    return ((uint32_t)(int)a & 0xffu) | (((uint32_t)(int)b & 0xffu) << 8) | (((uint32_t)(int)c & 0xffu) << 16) |
+           (((uint32_t)(int)d & 0xffu) << 24);
+}
+
+// Granules (4 blocks each) the next stage takes when `left` remain in the segment: 5, 3 or 1.
+// Row strides of 100, 60 and 20 words keep the consumer loads free of bank conflicts.
+__device__ __forceinline__ uint32_t stage_granules(uint32_t left) { return left >= 5 ? 5u : (left >= 3 ? 3u : 1u); }
+
+// Arguments of one launch: NP problems (NP = 1 for a single projection).  The shared-memory
+// offsets, the stage count, the workspace pointers and the PDL flag are taken from p[0]; the
+// problems differ in weights, shapes, activations, output and adapter.
+template <int NP>
+struct DecodeArgs {
+    GemvParams p[NP];
+    CUtensorMap maps[NP][3];      // boxes of 20, 12 and 4 blocks x 128 rows
+    uint64_t ub[NP + 1];          // first work unit of each problem (units: 4 blocks x 128 rows)
+    uint32_t count;
+    uint32_t any_rank;            // some problem has a LoRA adapter
+};
+
+
+// One CTA of 256 threads computes t[pr] = sum_k A[j][k] * x[tok][k] for pr = tok * rank + j, with a
+// fixed reduction order.
+__device__ __forceinline__ void project_one(const void* __restrict__ x, int x_dtype, uint32_t k,
+                                            const float* __restrict__ la, uint32_t rank, float* __restrict__ t,
+                                            uint32_t pr, int vec4) {
+    const uint32_t tok = pr / rank, j = pr - tok * rank;
+    const float* arow = la + (size_t)j * k;
+    float s = 0.0f;
+    if (vec4) {
+        const float4* a4 = reinterpret_cast<const float4*>(arow);
+        const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)tok * k);
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < k / 4; i += 256) {
+            const float4 a = __ldg(a4 + i), b = x4[i];
+            s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
+        }
+    } else {
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < k; i += 256) s = fmaf(__ldg(arow + i), load_act(x, x_dtype, (size_t)tok * k + i), s);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __shared__ float part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) t[pr] = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+}
+
+// Host side: the three tensor maps of a payload (boxes of 20, 12 and 4 blocks x 128 rows), from a
+// per-thread cache keyed by (pointer, n, k).  NULL if the driver entry point is missing or the
+// encode fails.
+struct MapEntry { const uint8_t* w; uint32_t n, kb; CUtensorMap m[3]; };
+const MapEntry* maps_for(const uint8_t* w, uint32_t n, uint32_t kb);
+
+}  // namespace dec
+}  // namespace lq4

@@ -92,6 +92,17 @@ cudaError_t launch_lora_project_group(const GemvParams* ps, uint32_t count, floa
 cudaError_t launch_lora_project(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
                                 float* t, int use_pdl, cudaStream_t s);
 
+// ---- lq4_dense.cu ---------------------------------------------------------------
+// Decode kernel for 2..16 tokens (any k): activation limbs are prepared per call into per-block
+// records (dense_record_bytes each problem) by launch_dense_prep, which also computes t = A x
+// for the problems with an adapter; launch_dense then serves 1..kMaxGroup problems of the same
+// token count in one persistent launch.  GemvParams::xs_g points at a problem's records.
+size_t dense_record_bytes(uint32_t m, uint32_t k);
+size_t dense_plan_smem(GemvParams* ps, uint32_t count);
+cudaError_t launch_dense_prep(const GemvParams* ps, uint32_t count, uint8_t* const* rec, float* const* t, int use_pdl,
+                              cudaStream_t s);
+cudaError_t launch_dense(const GemvParams* ps, uint32_t count, size_t smem, int grid, cudaStream_t s);
+
 // Fills the smem-dependent fields of `p` and returns the dynamic shared memory the
 // launch needs, or 0 if the shape does not fit the requested variant.
 size_t gemv_plan_smem(GemvParams& p, bool resident);

@@ -448,3 +448,40 @@ def test_group_that_cannot_share_a_launch_runs_problem_by_problem(be):
     for y, c in zip(ys, many):
         assert tol_ratio(y, c["y_ref"]) <= 1.0
     assert be.linear_group([]) == []
+
+
+# ---------------------------------------------------------------- dense decode kernel (2..16 tokens)
+@pytest.mark.parametrize("m,k,n,rank", [(2, 1024, 3584, 16), (5, 1024, 3584, 16), (12, 2048, 640, 0), (16, 1024, 3584, 64),
+                                        (13, 128, 130, 3), (16, 5120, 384, 16), (4, 17408, 256, 16), (16, 17408, 200, 128)])
+def test_dense_decode_tokens_and_long_rows(be, m, k, n, rank):
+    case = make_case(2, m, k, n, rank, 2.0 * rank, extra=200 + m)
+    y = run_case(be, case, path=_lib.PATH_GEMV_MMA)
+    assert not np.isnan(y).any()
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+    y2 = run_case(be, case)                     # automatic dispatch takes the same kernel for m <= 16
+    assert np.array_equal(y.view(np.uint32), y2.view(np.uint32))
+
+
+def test_dense_decode_bf16_activations_and_rotation(be):
+    case = make_case(2, 8, 1024, 512, 16, 32.0, bf16_x=True, extra=210)
+    y = run_case(be, case, bf16=True)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+    rot = make_case(5, 6, 1024, 300, quarot=True, extra=211)
+    y = run_case(be, rot)
+    assert tol_ratio(y, rot["y_ref"]) <= 1.0
+
+
+def test_dense_decode_more_than_sixteen_tokens_in_chunks(be):
+    case = make_case(2, 37, 256, 200, 8, 16.0, extra=212)
+    y = run_case(be, case, path=_lib.PATH_GEMV_MMA)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+def test_group_sixteen_tokens(be):
+    shapes = [(1280, 1280), (1280, 256), (1280, 4352), (4352, 1280)]
+    cases = [make_case(3, 16, k, n, 16, 32.0, extra=220 + i) for i, (k, n) in enumerate(shapes)]
+    ys, launches = _run_group(be, cases)
+    assert launches == 2
+    for y, c in zip(ys, cases):
+        assert not np.isnan(y).any()
+        assert tol_ratio(y, c["y_ref"]) <= 1.0
