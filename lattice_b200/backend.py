@@ -114,6 +114,18 @@ class _LoraAdapter:
     max_rank: int = 0
 
 
+class PreparedGroup:
+    """Argument block of one ``lq4_linear_group`` call, reusable while its tensors live."""
+
+    def __init__(self, backend: "CudaQ4Backend", arr, count: int, outs: List[torch.Tensor], keep):
+        self._be, self._arr, self._count, self.outs, self._keep = backend, arr, count, outs, keep
+        self._fn = _lib.lib().lq4_linear_group
+
+    def __call__(self) -> List[torch.Tensor]:
+        check(self._fn(self._be._ctx, self._arr, self._count, _stream()))
+        return self.outs
+
+
 class CudaQ4Backend:
     """One instance per device and owning thread, like the reference's GPU state."""
 
@@ -329,33 +341,38 @@ class CudaQ4Backend:
         self.dispatch_gemm_q4(x.contiguous(), 0, qw, y, 0, m, qw.n, k, lora=lora, rot=rot, path=path)
         return y
 
-    def linear_group(self, problems, outs: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
-        """Several independent projections in one call (one persistent launch for decode shapes).
+    def prepare_group(self, problems, outs: Optional[List[torch.Tensor]] = None) -> "PreparedGroup":
+        """Builds the argument block of a grouped call once; calling the result launches it.
 
-        ``problems`` is a list of ``(x, qw)`` or ``(x, qw, lora)`` with ``x`` ``[m, k]`` on the device;
-        returns the list of ``[m, n]`` f32 outputs.  No output may alias another problem's input."""
+        ``problems`` is a list of ``(x, qw)`` or ``(x, qw, lora)`` with ``x`` ``[m, k]`` on the device.  The
+        tensors are referenced, not copied: refill ``x`` in place between calls.  No output may alias
+        another problem's input."""
         n_prob = len(problems)
-        if n_prob == 0:
-            return []
-        arr = (LinearArgs * n_prob)()
-        keep = []
-        ys = []
+        arr = (LinearArgs * max(n_prob, 1))()
+        keep, ys = [], []
         for i, pr in enumerate(problems):
             x, qw = pr[0], pr[1]
             lora = pr[2] if len(pr) > 2 else None
             m, k = x.shape
             self._require_k("linear_group", k)
-            x = x.contiguous()
+            assert x.is_cuda and x.is_contiguous(), "activations are contiguous [m, k] device tensors"
             y = outs[i] if outs is not None else torch.empty((m, qw.n), dtype=torch.float32, device=x.device)
-            assert x.is_cuda and y.is_cuda and y.dtype == torch.float32
+            assert y.is_cuda and y.dtype == torch.float32
             assert y.shape == (m, qw.n) and y.stride(1) == 1, "outputs are [m, n] with unit column stride"
-            keep.append((x, lora))
+            keep.append((x, qw, lora))
             ys.append(y)
             ldy = y.stride(0) if m > 1 or y.stride(0) >= qw.n else qw.n      # row pitch of a column slice
             arr[i] = LinearArgs(x.data_ptr(), self._dtype_of(x), m, qw.n, k, qw.payload_ptr, y.data_ptr(), ldy,
                                 C.pointer(lora) if lora is not None else None, None, _lib.PATH_AUTO)
-        check(_lib.lib().lq4_linear_group(self._ctx, arr, n_prob, _stream()))
-        return ys
+        return PreparedGroup(self, arr, n_prob, ys, keep)
+
+    def linear_group(self, problems, outs: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
+        """Several independent projections in one call (one persistent launch for decode shapes);
+        returns the list of ``[m, n]`` f32 outputs."""
+        if len(problems) == 0:
+            return []
+        problems = [(pr[0].contiguous(),) + tuple(pr[1:]) for pr in problems]
+        return self.prepare_group(problems, outs)()
 
     def linear_host(self, x: np.ndarray, qw: Q4WeightBuf, y: np.ndarray, *, lora: Optional[LoraDesc] = None,
                     rot: Optional[RotDesc] = None) -> None:

@@ -48,8 +48,8 @@ struct lq4_ctx {
     int sm_count = 0;
     uint64_t launches = 0;
     int32_t* status = nullptr;    // device status word
-    uint32_t* tsync = nullptr;    // {arrived, finished} of the LoRA partial exchange
-    Buf xrot, xs, sx, t, tpart, partials, tickets, hx, hy, gemm;
+    uint32_t* tsync = nullptr;    // 64-bit launch counter of the decode kernels
+    Buf xrot, xs, t, tmsg, partials, hx, hy, gemm;   // xs: activation limb records of the dense decode kernel
     bool allow_grow = true;
     int pdl = 1;
 };
@@ -126,15 +126,15 @@ void fill_params(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dt
     p.m = m; p.n = a->n; p.k = a->k;
     p.kb = a->k / 32; p.kg = p.kb / kGemvGranuleBlocks;
     p.tiles = (a->n + kGemvTileRows - 1) / kGemvTileRows;
-    p.nt = (2 * m + 7) / 8;
-    p.gmax = p.nt == 1 ? 2 * m : 8;
     p.status = ctx->status;
     p.tsync = ctx->tsync;          // launch generation and end-of-launch counter
     p.use_pdl = ctx->pdl;
     p.sm_count = ctx->sm_count;
     p.x = x; p.x_dtype = x_dtype;
+    p.tsplit = 1;
     if (a->lora) {
         p.la = a->lora->a; p.lb = a->lora->b; p.rank = a->lora->rank; p.lscale = a->lora->scale;
+        p.tsplit = decode_tsplit(a->k);
     }
 }
 
@@ -189,18 +189,15 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
         if ((st = ensure(ctx, ctx->partials, (size_t)grid * kGemvTileRows * 4 * 8, true, s))) return st;
         p.partials = (float*)ctx->partials.p;
         if (p.rank) {
-            // the projection t = A x runs as a small kernel right before; the decode kernel starts
-            // streaming weights meanwhile and waits for t only before its first epilogue
-            if ((st = ensure(ctx, ctx->t, (size_t)m * p.rank * sizeof(float), false, s))) return st;
-            LQ4_CUDA(launch_lora_project(x, x_dtype, m, a->k, p.la, p.rank, (float*)ctx->t.p, p.use_pdl, s));
-            ctx->launches += 1;
-            p.t_g = (const float*)ctx->t.p;
+            // the kernel's producer warps compute t = A x themselves and pass it on as tagged messages
+            if ((st = ensure(ctx, ctx->tmsg, (size_t)m * p.rank * p.tsplit * sizeof(uint2), true, s))) return st;
+            p.tmsg = (uint2*)ctx->tmsg.p;
         }
-        const size_t smem = gemv_plan_smem(p, true);
+        const size_t smem = decode_plan_smem(p);
         if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "resident plan does not fit");
         const uint64_t units = decode_units(p);
         const int dgrid = (int)(units < (uint64_t)ctx->sm_count ? units : (uint64_t)ctx->sm_count);
-        LQ4_CUDA(launch_gemv_mma(p, true, smem, dgrid, s));
+        LQ4_CUDA(launch_decode(p, smem, dgrid, s));
         ctx->launches += 1;
         return LQ4_OK;
     }
@@ -266,8 +263,7 @@ void lq4_ctx_destroy(lq4_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
-    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->sx, &ctx->t, &ctx->tpart, &ctx->partials, &ctx->tickets, &ctx->hx,
-                   &ctx->hy, &ctx->gemm})
+    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm})
         if (b->p) cudaFree(b->p);
     if (ctx->status) cudaFree(ctx->status);
     delete ctx;
@@ -278,16 +274,14 @@ lq4_status lq4_ctx_reserve(lq4_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uin
     LQ4_CUDA(cudaSetDevice(ctx->device));
     cudaStream_t s = 0;
     const uint32_t mm = m < 16 ? m : 16;
-    const uint32_t nt = (2 * mm + 7) / 8, kb = k / 32;
     const size_t G = ctx->sm_count;
     lq4_status st;
+    // a group of eight problems of this shape still fits without growing
     if ((st = ensure(ctx, ctx->xrot, (size_t)m * k * 4, false, s))) return st;
-    if ((st = ensure(ctx, ctx->xs, (size_t)kb * nt * 8 * 64, false, s))) return st;
-    if ((st = ensure(ctx, ctx->sx, (size_t)kb * nt * 16, false, s))) return st;
-    if ((st = ensure(ctx, ctx->t, (size_t)m * rank * 4 + 256, false, s))) return st;
-    if ((st = ensure(ctx, ctx->tpart, G * 4 * (size_t)(rank ? rank : 1) * 8, true, s))) return st;
-    if ((st = ensure(ctx, ctx->partials, G * 2 * kGemvTileRows * nt * 4 * 4, true, s))) return st;
-    if ((st = ensure(ctx, ctx->tickets, ((size_t)n + 127) / 128 * 8 * 4, true, s))) return st;
+    if ((st = ensure(ctx, ctx->xs, (size_t)kMaxGroup * (dense_record_bytes(mm, k) + 256), false, s))) return st;
+    if ((st = ensure(ctx, ctx->t, (size_t)kMaxGroup * ((size_t)mm * rank + 64) * 4 + 256, false, s))) return st;
+    if ((st = ensure(ctx, ctx->tmsg, (size_t)kMaxGroup * (rank ? rank : 1) * 8 * sizeof(uint2), true, s))) return st;
+    if ((st = ensure(ctx, ctx->partials, G * kGemvTileRows * ((mm + 3) / 4) * 4 * 8, true, s))) return st;
     if ((st = ensure(ctx, ctx->hx, (size_t)m * k * 4, false, s))) return st;
     if ((st = ensure(ctx, ctx->hy, (size_t)m * n * 4, false, s))) return st;
     if (m > 16) {
@@ -420,25 +414,18 @@ lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t 
     }
     if (m > 1 || !smem) return run_dense(ctx, ps, count, s);
 
-    size_t t_floats = 0;
-    for (uint32_t i = 0; i < count; ++i) t_floats += ((size_t)m * ps[i].rank + 63) / 64 * 64;
-    if ((st = ensure(ctx, ctx->t, t_floats * sizeof(float) + 256, false, s))) return st;
-    float* tptr[kMaxGroup];
-    size_t toff = 0;
-    bool any_rank = false;
+    size_t items = 0;
+    for (uint32_t i = 0; i < count; ++i) items += (size_t)m * ps[i].rank * ps[i].tsplit;
+    if ((st = ensure(ctx, ctx->tmsg, items * sizeof(uint2), true, s))) return st;
+    items = 0;
     for (uint32_t i = 0; i < count; ++i) {
-        tptr[i] = (float*)ctx->t.p + toff;
-        toff += ((size_t)m * ps[i].rank + 63) / 64 * 64;
-        if (ps[i].rank) { ps[i].t_g = tptr[i]; any_rank = true; }
+        ps[i].tmsg = (uint2*)ctx->tmsg.p + items;
+        items += (size_t)m * ps[i].rank * ps[i].tsplit;
     }
     const uint64_t units = decode_group_units(ps, count);
     const int grid = (int)(units < (uint64_t)ctx->sm_count ? units : (uint64_t)ctx->sm_count);
     if ((st = ensure(ctx, ctx->partials, (size_t)grid * kGemvTileRows * 4 * 8, true, s))) return st;
     for (uint32_t i = 0; i < count; ++i) ps[i].partials = (float*)ctx->partials.p;
-    if (any_rank) {
-        LQ4_CUDA(launch_lora_project_group(ps, count, tptr, m, ctx->pdl, s));
-        ctx->launches += 1;
-    }
     LQ4_CUDA(launch_decode_group(ps, count, smem, grid, s));
     ctx->launches += 1;
     return LQ4_OK;

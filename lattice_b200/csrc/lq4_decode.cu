@@ -32,11 +32,8 @@ namespace {
 using namespace gemv;
 using namespace dec;
 
-// Activations of one Q4 block (32 values, four threads with eight each) become two int8 limbs
-// with a common f32 scale s = max|x| / 127:  x ~= s * (l0 + l1 / 254), |l0|, |l1| <= 127, so the
-// representation error is below max|x| / 64516.  The integer dot products with the 4-bit codes
-// are then exact.  Bytes are stored in the order the MMA B operand wants them: per nibble word
-// {k0,k2,k4,k6} then {k1,k3,k5,k7}.  `sx` receives {s, sum of the 32 activations}.
+// Limbs of eight activations (octet `o` of token slot `mp`) into the resident layout:
+// limbs [block][token][limb 0, limb 1][32 B], per-block info {scale, sum of the 32 activations}.
 __device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT, uint32_t mp, uint32_t o,
                                             bool active, const float (&v)[8]) {
     float amax = 0.0f;
@@ -48,24 +45,12 @@ __device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT
     sum += __shfl_xor_sync(kFull, sum, 1);
     sum += __shfl_xor_sync(kFull, sum, 2);
     if (!active) return;
-    const bool tiny = !(amax > 1e-30f);
-    const float s0 = tiny ? 1.0f : amax * (1.0f / 127.0f);
-    const float inv0 = tiny ? 0.0f : 127.0f / amax;
-    const float inv1 = inv0 * kLimb1Ratio;
-    float l0[8], l1[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        l0[i] = fminf(fmaxf(rintf(v[i] * inv0), -127.0f), 127.0f);
-        const float r = fmaf(-l0[i], s0, v[i]);
-        l1[i] = fminf(fmaxf(rintf(r * inv1), -127.0f), 127.0f);
-    }
+    const Limbs8 l = make_limbs8(v, amax);
     const uint32_t blk = o >> 2, j = o & 3;
     uint8_t* dst = xs + ((size_t)blk * MT + mp) * 64 + j * 8;
-    *reinterpret_cast<uint2*>(dst) =
-        make_uint2(pack_s8x4(l0[0], l0[2], l0[4], l0[6]), pack_s8x4(l0[1], l0[3], l0[5], l0[7]));
-    *reinterpret_cast<uint2*>(dst + 32) =
-        make_uint2(pack_s8x4(l1[0], l1[2], l1[4], l1[6]), pack_s8x4(l1[1], l1[3], l1[5], l1[7]));
-    if (j == 0) sx[(size_t)blk * MT + mp] = make_float2(s0, sum);
+    *reinterpret_cast<uint2*>(dst) = make_uint2(l.l0a, l.l0b);
+    *reinterpret_cast<uint2*>(dst + 32) = make_uint2(l.l1a, l.l1b);
+    if (j == 0) sx[(size_t)blk * MT + mp] = make_float2(l.scale, sum);
 }
 
 // Prologue of the 256 consumer threads: rotation, LoRA partial projection, activation limbs.
@@ -172,62 +157,105 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
     __syncthreads();
     if (p.use_pdl) pdl_launch_dependents();
 
-    const uint64_t G = gridDim.x;
-    const uint64_t total = NP == 1 ? (uint64_t)p.tiles * p.kg : ga.ub[count];
+    // this CTA's problem, and its share of that problem's work units among the problem's CTAs
+    uint32_t pi = 0;
+    if (NP > 1)
+        while (pi + 1 < count && blockIdx.x >= ga.cta_begin[pi + 1]) ++pi;
+    const GemvParams& q = ga.p[pi];
+    const uint32_t cta0 = NP == 1 ? 0u : ga.cta_begin[pi];
+    const uint64_t G = NP == 1 ? gridDim.x : ga.cta_begin[pi + 1] - cta0;
+    const uint32_t cl = blockIdx.x - cta0;
+    const uint64_t total = (uint64_t)q.tiles * q.kg;
     // whole-tile mode hands out entire tiles (no partial sums); otherwise equal shares of granules
     const bool whole = NP == 1 && p.whole_tiles;
-    const uint64_t r0 = whole ? range_begin(blockIdx.x, p.tiles, G) * p.kg : range_begin(blockIdx.x, total, G);
-    const uint64_t r1 = whole ? range_begin(blockIdx.x + 1, p.tiles, G) * p.kg : range_begin(blockIdx.x + 1, total, G);
+    const uint64_t r0 = whole ? range_begin(cl, q.tiles, G) * q.kg : range_begin(cl, total, G);
+    const uint64_t r1 = whole ? range_begin(cl + 1, q.tiles, G) * q.kg : range_begin(cl + 1, total, G);
     uint32_t issued = 0;
 
     if (warp == 8) {
         // ------------------------------ producer ------------------------------
-        if (lane == 0) {
-            const uint64_t pol = l2_policy_evict_first();
-            uint32_t it = 0;
-            bool ok = true;
-            uint32_t pi = 0;
-            for (uint64_t pos = r0; pos < r1 && ok;) {
+        // All 32 lanes walk the same loop; lane 0 issues the copies.  Once the ring is full for the
+        // first time (the consumers are still converting activations), the warp takes its share of
+        // the LoRA projections t = A x and publishes them as tagged messages.
+        const uint64_t pol = l2_policy_evict_first();
+        const bool any_rank = NP == 1 ? p.rank != 0 : ga.any_rank != 0;
+        bool projected = !any_rank;
+        auto project = [&]() {
+            projected = true;
+            if (p.use_pdl) pdl_wait_prior_grids();          // x may come from the launch before this one
+            const uint32_t tag = launch_tag(p.tsync);
+            // work item e = (problem, token, rank row, k piece); item e belongs to CTA e mod grid
+            const uint32_t nitems = NP == 1 ? p.m * p.rank * p.tsplit : ga.dot_start[count];
+            uint32_t pj = 0;
+            for (uint32_t e = blockIdx.x; e < nitems; e += gridDim.x) {
                 if (NP > 1)
-                    while (pi + 1 < count && pos >= ga.ub[pi + 1]) ++pi;
-                const GemvParams& q = ga.p[pi];
-                const uint64_t local = NP == 1 ? pos : pos - ga.ub[pi];
-                const uint32_t tile = (uint32_t)(local / q.kg);
-                const uint32_t g0 = (uint32_t)(local - (uint64_t)tile * q.kg);
-                const uint64_t left = r1 - pos;
-                const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
-                for (uint32_t gs = g0; gs < g1; ++it) {
-                    const uint32_t ngr = stage_granules(g1 - gs);
-                    const uint32_t s = it % NST;
-                    if (!mbar_wait(&empty[s], ((it / NST) & 1u) ^ 1u)) { ok = false; break; }
+                    while (pj + 1 < count && e >= ga.dot_start[pj + 1]) ++pj;
+                const GemvParams& qq = ga.p[pj];
+                const uint32_t local = NP == 1 ? e : e - ga.dot_start[pj];
+                const uint32_t dot = local / qq.tsplit, sp = local - dot * qq.tsplit;
+                const uint32_t tok = dot / qq.rank, j = dot - tok * qq.rank;
+                const uint32_t k4 = qq.k / 4;
+                const uint32_t chunk4 = ((k4 + qq.tsplit - 1) / qq.tsplit + 31u) & ~31u;
+                const uint32_t i0 = sp * chunk4, i1 = min(k4, i0 + chunk4);
+                const float* arow = qq.la + (size_t)j * qq.k;
+                float s = 0.0f;
+                const bool vec4 = qq.x_dtype == LQ4_DTYPE_F32 && ((reinterpret_cast<uintptr_t>(qq.x) | reinterpret_cast<uintptr_t>(qq.la)) & 15u) == 0;
+                if (vec4) {
+                    const float4* a4 = reinterpret_cast<const float4*>(arow);
+                    const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(qq.x) + (size_t)tok * qq.k);
+#pragma unroll 8
+                    for (uint32_t i = i0 + lane; i < i1; i += 32) {
+                        const float4 a = __ldg(a4 + i), b = x4[i];
+                        s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
+                    }
+                } else {
+#pragma unroll 8
+                    for (uint32_t i = i0 * 4 + lane; i < i1 * 4; i += 32)
+                        s = fmaf(__ldg(arow + i), load_act(qq.x, qq.x_dtype, (size_t)tok * qq.k + i), s);
+                }
+#pragma unroll
+                for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
+                if (lane == 0) msg_store(qq.tmsg + local, s, tag);
+            }
+        };
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint64_t pos = r0; pos < r1 && ok;) {
+            const uint32_t tile = (uint32_t)(pos / q.kg);
+            const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
+            const uint64_t left = r1 - pos;
+            const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
+            for (uint32_t gs = g0; gs < g1; ++it) {
+                if (it == NST && !projected) project();
+                const uint32_t ngr = stage_granules(g1 - gs);
+                const uint32_t s = it % NST;
+                bool got = true;
+                if (lane == 0) got = mbar_wait(&empty[s], ((it / NST) & 1u) ^ 1u);
+                if (!__shfl_sync(kFull, got, 0)) { ok = false; break; }
+                if (lane == 0) {
                     uint8_t* st = smem + p.off_stage + (size_t)s * kSlotBytes;
                     mbar_arrive_expect_tx(&full[s], ngr * kSmallBytes);
                     // coordinates: x in 4-byte elements along the row, y = first row of the tile
                     tma_load_2d(st, &ga.maps[pi][ngr == 5 ? 0 : (ngr == 3 ? 1 : 2)], (int32_t)(gs * kGemvGranuleBlocks * 5),
                                 (int32_t)(tile * kGemvTileRows), &full[s], pol);
-                    gs += ngr;
                 }
-                pos += g1 - g0;
+                gs += ngr;
             }
-            issued = it;
-            if (!ok) {
-                atomicOr(p.status, kDevErrBarrierTimeout);
-                s_err = 1;
-            }
+            pos += g1 - g0;
+        }
+        if (!projected) project();
+        issued = it;
+        if (!ok && lane == 0) {
+            atomicOr(p.status, kDevErrBarrierTimeout);
+            s_err = 1;
         }
     } else {
         // ------------------------------ consumers ------------------------------
         const int g = lane >> 2, t = lane & 3;
-        // With a LoRA adapter the launch before this one is the small projection kernel (t = A x),
-        // which itself waited for everything earlier before it let this grid start: x is final, and
-        // only t must be waited for, right before the first epilogue.  Without an adapter the previous
-        // launch may be the producer of x, so the wait comes first.
-        bool prior_done = false;
-        const bool any_rank = NP == 1 ? p.rank != 0 : ga.any_rank != 0;
-        if (p.use_pdl && !any_rank) { pdl_wait_prior_grids(); prior_done = true; }
-        // launch generation: bumped once at the end of every launch, so a message written by an
-        // earlier launch never carries the current tag
-        const uint32_t tag = *reinterpret_cast<volatile const uint32_t*>(p.tsync) + 1u;
+        // x may come from the launch before this one
+        if (p.use_pdl) pdl_wait_prior_grids();
+        // a message written by an earlier launch never carries this launch's tag
+        const uint32_t tag = launch_tag(p.tsync);
         LQ4_STAMP(1);
 
         // A lane supplies B-operand registers only for the column pair (limb 0, limb 1) of its own
@@ -239,24 +267,45 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
 
         uint32_t it = 0;
         bool ok = true;
-        uint32_t pi = 0, cur = 0xffffffffu;
-        for (uint64_t pos = r0; pos < r1 && ok;) {
-            if (NP > 1)
-                while (pi + 1 < count && pos >= ga.ub[pi + 1]) ++pi;
-            const GemvParams& q = ga.p[pi];
-            const uint64_t ub0 = NP == 1 ? 0 : ga.ub[pi];
-            if (pi != cur) {
-                // first segment of a problem: convert the activation ranges this CTA needs from it
-                // (all consumer warps walk the same segments, so they meet here together)
-                if (cur != 0xffffffffu) named_bar_sync(kBarConsumers, kConsumerThreads);
-                const uint64_t ub1 = NP == 1 ? total : ga.ub[pi + 1];
-                decode_prologue<MT>(q, smem, tid, (r0 > ub0 ? r0 : ub0) - ub0, (r1 < ub1 ? r1 : ub1) - ub0);
-                cur = pi;
-                LQ4_STAMP(2);
+        bool t_loaded = false;
+        float* t_sm = reinterpret_cast<float*>(smem + p.off_t);
+        // Gathers t = A x from the producer warps' messages (written in the first microseconds of the
+        // launch) into shared memory, adding the k pieces of every dot product in order.  All eight
+        // consumer warps call it at the same point of their (identical) walk.  Bounded wait.
+        auto gather_t = [&]() {
+            bool good = true;
+            for (uint32_t idx = tid; idx < q.m * q.rank; idx += kConsumerThreads) {
+                const uint2* src = q.tmsg + (size_t)idx * q.tsplit;
+                float sum = 0.0f;
+                for (uint32_t s0 = 0; s0 < q.tsplit; s0 += 8) {
+                    uint2 msg[8];
+                    const long long t0 = wait_clock();
+                    for (;;) {
+                        bool all = true;
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            if (s0 + u >= q.tsplit) continue;
+                            msg[u] = msg_load(src + s0 + u);
+                            all = all && (msg[u].y == tag);
+                        }
+                        if (all) break;
+                        if (wait_expired(t0)) { good = false; break; }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (s0 + u < q.tsplit) sum += __uint_as_float(msg[u].x);
+                }
+                t_sm[idx] = sum;
             }
-            const uint64_t local = pos - ub0;
-            const uint32_t tile = (uint32_t)(local / q.kg);
-            const uint32_t g0 = (uint32_t)(local - (uint64_t)tile * q.kg);
+            if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
+            named_bar_sync(kBarConsumers, kConsumerThreads);
+            t_loaded = true;
+        };
+        decode_prologue<MT>(q, smem, tid, r0, r1);
+        LQ4_STAMP(2);
+        for (uint64_t pos = r0; pos < r1 && ok;) {
+            const uint32_t tile = (uint32_t)(pos / q.kg);
+            const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
             const uint64_t left = r1 - pos;
             const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
             pos += g1 - g0;
@@ -279,6 +328,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 const uint32_t s = it % NST;
                 if (!mbar_wait(&full[s], (it / NST) & 1u)) { ok = false; break; }
                 if (it == 0) LQ4_STAMP(3);
+                // by now the projections are published; fetching them here keeps the round trip off
+                // the end of the tile (the ring keeps the memory pipe busy meanwhile)
+                if (it == 6 && q.rank && !t_loaded) gather_t();
                 const uint8_t* st = smem + p.off_stage + (size_t)s * kSlotBytes;
                 const uint8_t* row0 = st + (warp * 16 + g) * rs + t * kBlockBytes;
                 const uint8_t* row1 = row0 + 8 * rs;
@@ -348,6 +400,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 }
             }
             const bool complete = (g0 == 0 && g1 == q.kg);
+            const uint32_t rowa = tile * kGemvTileRows + warp * 16 + g, rowb = rowa + 8;
+            const float* bra = q.lb + (size_t)(rowa < q.n ? rowa : 0) * q.rank;
+            const float* brb = q.lb + (size_t)(rowb < q.n ? rowb : 0) * q.rank;
+            // first 16 rank columns of B (four per quad lane), requested before the fix-up wait so that
+            // the two round trips overlap
+            float ba0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bb0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (q.rank && (complete || g0 == 0)) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t j = t + 4 * u;
+                    if (j < q.rank) { ba0[u] = __ldg(bra + j); bb0[u] = __ldg(brb + j); }
+                }
+            }
             if (!complete && g0 != 0) {
                 // Contributor: this CTA's range starts inside the tile, so this is its first segment.
                 // Publish the partial sums and leave; the ticket add is a release, no reply is needed.
@@ -365,7 +430,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 // Finisher: the CTA that owns the tile's first k part reaches it at the END of its own
                 // range, when the contributors (who met the tile at the START of theirs) are long done.
                 // The wait below is bounded and normally falls through at once.
-                const uint32_t c_last = owner_of(ub0 + (uint64_t)(tile + 1) * q.kg - 1, total, G);
+                const uint32_t c_last = cta0 + owner_of((uint64_t)(tile + 1) * q.kg - 1, total, G);
                 // lanes poll different CTAs' messages (all 16 rows each), a fixed shuffle tree adds
                 // them: the sum does not depend on arrival order
                 float part[16 * MT];
@@ -405,20 +470,27 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
             }
 
             // epilogue: LoRA term (the quad splits the rank), then quad thread t stores token t
-            const uint32_t rowa = tile * kGemvTileRows + warp * 16 + g, rowb = rowa + 8;
             if (q.rank) {
-                if (!prior_done) { if (p.use_pdl) pdl_wait_prior_grids(); prior_done = true; }
+                if (!t_loaded) gather_t();
                 float la[MT], lb2[MT];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) la[mt] = lb2[mt] = 0.0f;
-                const float* bra = q.lb + (size_t)(rowa < q.n ? rowa : 0) * q.rank;
-                const float* brb = q.lb + (size_t)(rowb < q.n ? rowb : 0) * q.rank;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t j = t + 4 * u;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const float tv = j < q.rank ? t_sm[mt * q.rank + j] : 0.0f;
+                        la[mt] = fmaf(ba0[u], tv, la[mt]);
+                        lb2[mt] = fmaf(bb0[u], tv, lb2[mt]);
+                    }
+                }
 #pragma unroll 4
-                for (uint32_t j = t; j < q.rank; j += 4) {
+                for (uint32_t j = t + 16; j < q.rank; j += 4) {
                     const float ba = __ldg(bra + j), bb = __ldg(brb + j);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const float tv = __ldcg(q.t_g + mt * q.rank + j);
+                        const float tv = t_sm[mt * q.rank + j];
                         la[mt] = fmaf(ba, tv, la[mt]);
                         lb2[mt] = fmaf(bb, tv, lb2[mt]);
                     }
@@ -450,20 +522,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
     // memory: wait (bounded) for the stages that were issued before leaving.
     __syncthreads();
 #ifdef LQ4_TIMELINE
-    if (tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+    if (tid == 0) {
         stamp(5);
-        unsigned long long* out = reinterpret_cast<unsigned long long*>(p.y + p.n) + (blockIdx.x ? 8 : 0);   // experiment builds only: y needs 128 spare bytes
-        for (int i = 0; i < 6; ++i) out[i] = s_tl[i];
+        // experiment builds only: y of problem 0 needs 4 KB of spare bytes after its n outputs
+        unsigned long long* out = reinterpret_cast<unsigned long long*>(p.y + p.n);
+        if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)
+            for (int i = 0; i < 6; ++i) out[(blockIdx.x ? 8 : 0) + i] = s_tl[i];
+        out[16 + 2 * blockIdx.x] = s_tl[0];
+        out[17 + 2 * blockIdx.x] = s_tl[5];
     }
 #endif
-    if (tid == 0) {
-        // the last CTA to get here (all of them have read the generation by now) advances it
-        const uint32_t old = atomicAdd(p.tsync + 1, 1u);
-        if (old == (uint32_t)G - 1) {
-            p.tsync[1] = 0;
-            p.tsync[0] = p.tsync[0] + 1u;
-        }
-    }
+    if (tid == 0) launch_done(p.tsync, blockIdx.x, gridDim.x);
     if (s_err && warp == 8 && lane == 0) {
         const uint32_t first = issued > NST ? issued - NST : 0;
         for (uint32_t j = first; j < issued; ++j) mbar_wait(&full[j % NST], (j / NST) & 1u);
@@ -548,6 +617,28 @@ cudaError_t launch_args(const DecodeArgs<kMaxGroup>& ga, size_t smem, int grid, 
 }  // namespace
 
 namespace dec {
+void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* cta_begin) {
+    constexpr uint64_t kTileCharge = 8;          // fix-up and epilogue of a tile, in work units
+    uint64_t cost[kMaxGroup], units[kMaxGroup];
+    uint32_t n[kMaxGroup];
+    for (uint32_t i = 0; i < count; ++i) {
+        units[i] = (uint64_t)ps[i].tiles * ps[i].kg;
+        cost[i] = (uint64_t)ps[i].tiles * (ps[i].kg + kTileCharge);
+        n[i] = 1;
+    }
+    for (uint32_t left = grid > count ? grid - count : 0; left > 0; --left) {
+        // the next CTA goes to the problem whose CTAs carry the most
+        uint32_t best = count;
+        for (uint32_t i = 0; i < count; ++i) {
+            if (n[i] >= units[i]) continue;
+            if (best == count || cost[i] * n[best] > cost[best] * n[i]) best = i;
+        }
+        if (best == count) break;
+        ++n[best];
+    }
+    cta_begin[0] = 0;
+    for (uint32_t i = 0; i < count; ++i) cta_begin[i + 1] = cta_begin[i] + n[i];
+}
 // Encoding a tensor map costs about a microsecond of host time and weights are long-lived, so
 // the three maps of a payload are kept in a per-thread direct-mapped cache keyed by
 // (pointer, n, k).
@@ -569,108 +660,11 @@ const MapEntry* maps_for(const uint8_t* w, uint32_t n, uint32_t kb) {
 
 }  // namespace dec
 
-// t[tok][j] = sum_k A[j][k] * x[tok][k]: one CTA per (token, rank row), fixed reduction order.
-// Runs right before the decode kernel.  With programmatic dependent launch it first waits for the
-// work before it (the producer of x) and only then lets the decode kernel start, which may
-// therefore read x at once and needs to wait for this grid only before it uses t.
-__global__ void __launch_bounds__(256) lora_project_kernel(const void* __restrict__ x, int x_dtype, uint32_t k,
-                                                           const float* __restrict__ la, uint32_t rank,
-                                                           float* __restrict__ t, int use_pdl, int vec4) {
-    if (use_pdl) {
-        pdl_wait_prior_grids();
-        pdl_launch_dependents();
-    }
-    dec::project_one(x, x_dtype, k, la, rank, t, blockIdx.x, vec4);
-}
-
-// The same for the problems of a grouped launch: CTA b serves problem i with start[i] <= b < start[i+1].
-struct ProjectGroupArgs {
-    const void* x[kMaxGroup];
-    const float* la[kMaxGroup];
-    float* t[kMaxGroup];
-    uint32_t k[kMaxGroup], rank[kMaxGroup], start[kMaxGroup + 1];
-    int32_t x_dtype[kMaxGroup], vec4[kMaxGroup];
-    uint32_t count;
-    int32_t use_pdl;
-};
-
-__global__ void __launch_bounds__(256) lora_project_group_kernel(const __grid_constant__ ProjectGroupArgs a) {
-    if (a.use_pdl) {
-        pdl_wait_prior_grids();
-        pdl_launch_dependents();
-    }
-    uint32_t pi = 0;
-    while (pi + 1 < a.count && blockIdx.x >= a.start[pi + 1]) ++pi;
-    dec::project_one(a.x[pi], a.x_dtype[pi], a.k[pi], a.la[pi], a.rank[pi], a.t[pi], blockIdx.x - a.start[pi], a.vec4[pi]);
-}
-
-cudaError_t launch_lora_project_impl(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
-                                     float* t, int use_pdl, cudaStream_t s) {
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(m * rank);
-    cfg.blockDim = dim3(256);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    int na = 0;
-    if (use_pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    const int vec4 = x_dtype == LQ4_DTYPE_F32 && k % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
-                     (reinterpret_cast<uintptr_t>(la) & 15) == 0;
-    return cudaLaunchKernelEx(&cfg, lora_project_kernel, x, x_dtype, k, la, rank, t, use_pdl, vec4);
-}
-
-
-cudaError_t launch_lora_project(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
-                                float* t, int use_pdl, cudaStream_t s) {
-    return launch_lora_project_impl(x, x_dtype, m, k, la, rank, t, use_pdl, s);
-}
-
-
-cudaError_t launch_lora_project_group(const GemvParams* ps, uint32_t count, float* const* t, uint32_t m, int use_pdl,
-                                      cudaStream_t s) {
-    ProjectGroupArgs a{};
-    uint32_t n = 0;
-    a.start[0] = 0;
-    for (uint32_t i = 0; i < count; ++i) {
-        const GemvParams& p = ps[i];
-        if (!p.rank) continue;
-        a.x[n] = p.x; a.la[n] = p.la; a.t[n] = t[i];
-        a.k[n] = p.k; a.rank[n] = p.rank; a.x_dtype[n] = p.x_dtype;
-        a.vec4[n] = p.x_dtype == LQ4_DTYPE_F32 && p.k % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
-                    (reinterpret_cast<uintptr_t>(p.la) & 15) == 0;
-        a.start[n + 1] = a.start[n] + m * p.rank;
-        ++n;
-    }
-    if (n == 0) return cudaSuccess;
-    a.count = n;
-    a.use_pdl = use_pdl;
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(a.start[n]);
-    cfg.blockDim = dim3(256);
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    int na = 0;
-    if (use_pdl) {
-        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[na].val.programmaticStreamSerializationAllowed = 1;
-        ++na;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, lora_project_group_kernel, a);
-}
-
 size_t decode_plan_smem(GemvParams& p) {
     if (p.m == 0 || p.m > 4 || p.kb == 0 || p.kb % kGemvGranuleBlocks != 0) return 0;
     const uint32_t MT = p.m;
     uint32_t off = 2 * kMaxStages * 8 + 128;      // mbarriers, then the block of zeros
-    p.off_t = off;
+    p.off_t = off;                                // t = A x of the problem being finished
     off += align_up(p.m * p.rank * 4, 128);
     p.off_xrot = 0;
     if (p.signs) {
@@ -682,8 +676,6 @@ size_t decode_plan_smem(GemvParams& p) {
     p.off_sx = off;
     off += align_up(p.kb * MT * 8, 128);
     p.off_stage = off;
-    p.stage_bytes = kSlotBytes;
-    p.off_stage_xs = p.off_stage_sx = 0;
     const uint32_t budget = (uint32_t)kMaxSmem - 1024;    // static shared memory and driver reserve
     if (off + 2 * kSlotBytes > budget) return 0;
     uint32_t nst = (budget - off) / kSlotBytes;
@@ -705,8 +697,10 @@ cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream
     DecodeArgs<1> ga{};
     ga.p[0] = p;
     for (int i = 0; i < 3; ++i) ga.maps[0][i] = e->m[i];
-    ga.ub[0] = 0;
-    ga.ub[1] = (uint64_t)p.tiles * p.kg;
+    ga.cta_begin[0] = 0;
+    ga.cta_begin[1] = (uint32_t)grid;
+    ga.dot_start[0] = 0;
+    ga.dot_start[1] = p.m * p.rank * p.tsplit;
     ga.count = 1;
     ga.any_rank = p.rank != 0;
     return launch_args(ga, smem, grid, s);
@@ -723,6 +717,10 @@ size_t decode_group_plan_smem(GemvParams* ps, uint32_t count) {
         max_kb = p.kb > max_kb ? p.kb : max_kb;
     }
     uint32_t off = 2 * kMaxStages * 8 + 128;      // mbarriers, then the block of zeros
+    uint32_t max_t = 0;
+    for (uint32_t i = 0; i < count; ++i) max_t = ps[i].m * ps[i].rank > max_t ? ps[i].m * ps[i].rank : max_t;
+    const uint32_t off_t = off;
+    off += align_up(max_t * 4, 128);
     const uint32_t off_xs = off;
     off += align_up(max_kb * MT * 64, 128);
     const uint32_t off_sx = off;
@@ -733,12 +731,11 @@ size_t decode_group_plan_smem(GemvParams* ps, uint32_t count) {
     if (nst > 4) nst = 4;
     for (uint32_t i = 0; i < count; ++i) {
         GemvParams& p = ps[i];
-        p.off_t = p.off_xrot = 0;
+        p.off_xrot = 0;
+        p.off_t = off_t;
         p.off_xs = off_xs;
         p.off_sx = off_sx;
         p.off_stage = off;
-        p.stage_bytes = kSlotBytes;
-        p.off_stage_xs = p.off_stage_sx = 0;
         p.nstages = nst;
         p.kg = p.kb / kGemvGranuleBlocks;
         p.whole_tiles = 0;
@@ -758,7 +755,9 @@ cudaError_t launch_decode_group(const GemvParams* ps, uint32_t count, size_t sme
     thread_local DecodeArgs<kMaxGroup> ga;
     ga.count = count;
     ga.any_rank = 0;
-    ga.ub[0] = 0;
+    split_ctas(ps, count, (uint32_t)grid, ga.cta_begin);
+    for (uint32_t i = count; i < (uint32_t)kMaxGroup; ++i) ga.cta_begin[i + 1] = ga.cta_begin[count];
+    ga.dot_start[0] = 0;
     for (uint32_t i = 0; i < (uint32_t)kMaxGroup; ++i) {
         const GemvParams& p = ps[i < count ? i : count - 1];
         ga.p[i] = p;
@@ -766,10 +765,10 @@ cudaError_t launch_decode_group(const GemvParams* ps, uint32_t count, size_t sme
             const MapEntry* e = maps_for(p.w, p.n, p.kb);
             if (!e) return cudaErrorInvalidValue;
             for (int j = 0; j < 3; ++j) ga.maps[i][j] = e->m[j];
-            ga.ub[i + 1] = ga.ub[i] + (uint64_t)p.tiles * p.kg;
+            ga.dot_start[i + 1] = ga.dot_start[i] + p.m * p.rank * p.tsplit;
             ga.any_rank |= p.rank != 0;
         } else {
-            ga.ub[i + 1] = ga.ub[i];
+            ga.dot_start[i + 1] = ga.dot_start[i];
         }
     }
     return launch_args(ga, smem, grid, s);

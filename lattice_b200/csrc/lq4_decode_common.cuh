@@ -38,6 +38,21 @@ __device__ __forceinline__ uint2 msg_load(const uint2* p) {
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
     return r;
 }
+// Launch tags.  Every launch adds exactly 256 to a 64-bit counter: CTA c adds its share of 256
+// virtual arrivals with a fire-and-forget reduction when it is done.  (counter >> 8) + 1, read after
+// the previous launch has completed and before the reading CTA has added its own share, is
+// therefore the same in every CTA of a launch and new in every launch, and no CTA has to wait for
+// an atomic's return value on its way out.
+__device__ __forceinline__ uint32_t launch_tag(const uint32_t* counter) {
+    unsigned long long c;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(c) : "l"(counter) : "memory");
+    return (uint32_t)(c >> 8) + 1u;
+}
+__device__ __forceinline__ void launch_done(uint32_t* counter, uint32_t cta, uint32_t grid) {
+    const unsigned long long share = 256u / grid + (cta < 256u % grid ? 1u : 0u);
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(share) : "memory");
+}
+
 // u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
 __device__ __forceinline__ void imma_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -48,9 +63,40 @@ __device__ __forceinline__ void imma_16832(int (&d)[4], const uint32_t (&a)[4], 
 
 constexpr float kLimb1Ratio = 254.0f;    // limb 1 is in units of scale / 254
 
-__device__ __forceinline__ uint32_t pack_s8x4(float a, float b, float c, float d) {
-    return ((uint32_t)(int)a & 0xffu) | (((uint32_t)(int)b & 0xffu) << 8) | (((uint32_t)(int)c & 0xffu) << 16) |
-           (((uint32_t)(int)d & 0xffu) << 24);
+// Eight activations of one Q4 block (a quad of threads holds its 32) -> two int8 limbs with the
+// block's common scale s = max|x| / 127:  x ~= s * (l0 + l1 / 254), |l0|, |l1| <= 127, so the
+// representation error is below max|x| / 64516 and integer dot products with the 4-bit codes are
+// exact.  `amax` is the block's max |x| (already reduced over the quad).  Rounding uses the
+// 1.5 * 2^23 trick: after the add, the low byte of the float's bit pattern is the two's-complement
+// integer, so no float-to-int conversions are needed.  Output words hold the limbs of
+// {v0, v2, v4, v6} (a) and {v1, v3, v5, v7} (b): the order of the MMA's k slots.
+struct Limbs8 { uint32_t l0a, l0b, l1a, l1b; float scale; };
+
+__device__ __forceinline__ uint32_t low_bytes4(float a, float b, float c, float d) {
+    const uint32_t lo = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x0040);
+    const uint32_t hi = __byte_perm(__float_as_uint(c), __float_as_uint(d), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
+__device__ __forceinline__ Limbs8 make_limbs8(const float (&v)[8], float amax) {
+    constexpr float kMagic = 12582912.0f;              // 1.5 * 2^23
+    const bool tiny = !(amax > 1e-30f);
+    Limbs8 r;
+    r.scale = tiny ? 1.0f : amax * (1.0f / 127.0f);
+    const float inv0 = tiny ? 0.0f : 127.0f / amax;
+    const float inv1 = inv0 * kLimb1Ratio;
+    float f0[8], f1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        f0[i] = fmaf(v[i], inv0, kMagic);                               // |v * inv0| <= 127
+        const float res = fmaf(-(f0[i] - kMagic), r.scale, v[i]);       // what limb 0 leaves over
+        f1[i] = fminf(fmaxf(res * inv1, -127.0f), 127.0f) + kMagic;
+    }
+    r.l0a = low_bytes4(f0[0], f0[2], f0[4], f0[6]);
+    r.l0b = low_bytes4(f0[1], f0[3], f0[5], f0[7]);
+    r.l1a = low_bytes4(f1[0], f1[2], f1[4], f1[6]);
+    r.l1b = low_bytes4(f1[1], f1[3], f1[5], f1[7]);
+    return r;
 }
 
 // Granules (4 blocks each) the next stage takes when `left` remain in the segment: 5, 3 or 1.
@@ -64,7 +110,8 @@ template <int NP>
 struct DecodeArgs {
     GemvParams p[NP];
     CUtensorMap maps[NP][3];      // boxes of 20, 12 and 4 blocks x 128 rows
-    uint64_t ub[NP + 1];          // first work unit of each problem (units: 4 blocks x 128 rows)
+    uint32_t cta_begin[NP + 1];   // CTAs [cta_begin[i], cta_begin[i+1]) work on problem i and on nothing else
+    uint32_t dot_start[NP + 1];   // resident kernel: first LoRA projection dot (token, rank row) of each problem
     uint32_t count;
     uint32_t any_rank;            // some problem has a LoRA adapter
 };
@@ -97,6 +144,12 @@ __device__ __forceinline__ void project_one(const void* __restrict__ x, int x_dt
     __syncthreads();
     if (threadIdx.x == 0) t[pr] = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
 }
+
+// Host side: hands each problem a contiguous share of the grid's CTAs, proportional to its cost
+// (work units of 4 blocks x 128 rows, plus a fixed charge per tile for the fix-up and epilogue), so
+// that no CTA has to switch problems.  Needs grid >= count; a problem never gets more CTAs than
+// it has units.
+void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* cta_begin);
 
 // Host side: the three tensor maps of a payload (boxes of 20, 12 and 4 blocks x 128 rows), from a
 // per-thread cache keyed by (pointer, n, k).  NULL if the driver entry point is missing or the

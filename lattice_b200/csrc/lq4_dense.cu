@@ -76,24 +76,14 @@ __global__ void __launch_bounds__(256) dense_prep_kernel(const __grid_constant__
     sum += __shfl_xor_sync(kFull, sum, 1);
     sum += __shfl_xor_sync(kFull, sum, 2);
     if (!in_range) return;
-    const bool tiny = !(amax > 1e-30f);
-    const float s0 = tiny ? 1.0f : amax * (1.0f / 127.0f);
-    const float inv0 = tiny ? 0.0f : 127.0f / amax;
-    const float inv1 = inv0 * kLimb1Ratio;
-    float l0[8], l1[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        l0[i] = fminf(fmaxf(rintf(v[i] * inv0), -127.0f), 127.0f);
-        const float r = fmaf(-l0[i], s0, v[i]);
-        l1[i] = fminf(fmaxf(rintf(r * inv1), -127.0f), 127.0f);
-    }
+    const Limbs8 l = make_limbs8(v, amax);
     uint8_t* rec = a.rec[pi] + (size_t)blk * rec_bytes(a.ng);
     uint8_t* grp = rec + (slot >> 2) * 256 + (slot & 3) * 32 + t * 4;      // column g = 2 * (slot & 3): 16 B per column
-    *reinterpret_cast<uint32_t*>(grp) = pack_s8x4(l0[0], l0[2], l0[4], l0[6]);
-    *reinterpret_cast<uint32_t*>(grp + 128) = pack_s8x4(l0[1], l0[3], l0[5], l0[7]);
-    *reinterpret_cast<uint32_t*>(grp + 16) = pack_s8x4(l1[0], l1[2], l1[4], l1[6]);
-    *reinterpret_cast<uint32_t*>(grp + 16 + 128) = pack_s8x4(l1[1], l1[3], l1[5], l1[7]);
-    if (t == 0) *reinterpret_cast<float2*>(rec + a.ng * 256 + slot * 8) = make_float2(s0, sum);
+    *reinterpret_cast<uint32_t*>(grp) = l.l0a;
+    *reinterpret_cast<uint32_t*>(grp + 128) = l.l0b;
+    *reinterpret_cast<uint32_t*>(grp + 16) = l.l1a;
+    *reinterpret_cast<uint32_t*>(grp + 16 + 128) = l.l1b;
+    if (t == 0) *reinterpret_cast<float2*>(rec + a.ng * 256 + slot * 8) = make_float2(l.scale, sum);
 }
 
 template <int NG>
@@ -136,16 +126,23 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
     // first records; the consumers wait for it before they touch anything.
     if (p.use_pdl) pdl_launch_dependents();
 
-    const uint64_t G = gridDim.x;
-    const uint64_t total = NP == 1 ? (uint64_t)p.tiles * p.kg : ga.ub[count];
-    const uint64_t r0 = range_begin(blockIdx.x, total, G), r1 = range_begin(blockIdx.x + 1, total, G);
+    // this CTA's problem, and its share of that problem's work units among the problem's CTAs
+    uint32_t pi = 0;
+    if (NP > 1)
+        while (pi + 1 < count && blockIdx.x >= ga.cta_begin[pi + 1]) ++pi;
+    const GemvParams& q = ga.p[pi];
+    const uint32_t cta0 = NP == 1 ? 0u : ga.cta_begin[pi];
+    const uint64_t G = NP == 1 ? gridDim.x : ga.cta_begin[pi + 1] - cta0;
+    const uint32_t cl = blockIdx.x - cta0;
+    const uint64_t total = (uint64_t)q.tiles * q.kg;
+    const uint64_t r0 = range_begin(cl, total, G), r1 = range_begin(cl + 1, total, G);
     uint32_t issued = 0;
 
     if (warp == 8) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
             const uint64_t pol = l2_policy_evict_first();
-            uint32_t it = 0, pi = 0;
+            uint32_t it = 0;
             bool ok = true;
             // The first weight stage is requested before the previous launch is known to be done; its
             // records follow as soon as it is (and go out before the later weight stages, which would
@@ -160,12 +157,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
                 npend = 0;
             };
             for (uint64_t pos = r0; pos < r1 && ok;) {
-                if (NP > 1)
-                    while (pi + 1 < count && pos >= ga.ub[pi + 1]) ++pi;
-                const GemvParams& q = ga.p[pi];
-                const uint64_t local = NP == 1 ? pos : pos - ga.ub[pi];
-                const uint32_t tile = (uint32_t)(local / q.kg);
-                const uint32_t g0 = (uint32_t)(local - (uint64_t)tile * q.kg);
+                const uint32_t tile = (uint32_t)(pos / q.kg);
+                const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
                 const uint64_t left = r1 - pos;
                 const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
                 for (uint32_t gs = g0; gs < g1; ++it) {
@@ -200,17 +193,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
         const int g = lane >> 2, t = lane & 3;
         if (p.use_pdl) pdl_wait_prior_grids();
         DSTAMP(1);
-        const uint32_t tag = *reinterpret_cast<volatile const uint32_t*>(p.tsync) + 1u;
-        uint32_t it = 0, pi = 0;
+        const uint32_t tag = launch_tag(p.tsync);
+        uint32_t it = 0;
         bool ok = true;
         for (uint64_t pos = r0; pos < r1 && ok;) {
-            if (NP > 1)
-                while (pi + 1 < count && pos >= ga.ub[pi + 1]) ++pi;
-            const GemvParams& q = ga.p[pi];
-            const uint64_t ub0 = NP == 1 ? 0 : ga.ub[pi];
-            const uint64_t local = pos - ub0;
-            const uint32_t tile = (uint32_t)(local / q.kg);
-            const uint32_t g0 = (uint32_t)(local - (uint64_t)tile * q.kg);
+            const uint32_t tile = (uint32_t)(pos / q.kg);
+            const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
             const uint64_t left = r1 - pos;
             const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
             pos += g1 - g0;
@@ -293,7 +281,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
             if (!complete) {
                 // Finisher: owns the tile's first k part and meets it at the END of its range, when the
                 // contributors (who met it at the START of theirs) are normally done.  Bounded wait.
-                const uint32_t c_last = owner_of(ub0 + (uint64_t)(tile + 1) * q.kg - 1, total, G);
+                const uint32_t c_last = cta0 + owner_of((uint64_t)(tile + 1) * q.kg - 1, total, G);
                 constexpr int CB = NG == 1 ? 8 : 4;     // contributors polled together
                 bool good = true;
                 for (uint32_t c0 = blockIdx.x + 1; c0 <= c_last && good; c0 += CB) {
@@ -419,14 +407,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
         for (int i = 0; i < 8; ++i) out[i] = s_tl[i];
     }
 #endif
-    if (tid == 0) {
-        // the last CTA to get here (all of them have read the generation by now) advances it
-        const uint32_t old = atomicAdd(p.tsync + 1, 1u);
-        if (old == (uint32_t)G - 1) {
-            p.tsync[1] = 0;
-            p.tsync[0] = p.tsync[0] + 1u;
-        }
-    }
+    if (tid == 0) launch_done(p.tsync, blockIdx.x, gridDim.x);
     // After a failed wait some copies may still be in flight towards this CTA's shared memory:
     // wait (bounded) for the stages that were issued before leaving.
     if (s_err && warp == 8 && lane == 0) {
@@ -494,7 +475,6 @@ size_t dense_plan_smem(GemvParams* ps, uint32_t count) {
     for (uint32_t i = 0; i < count; ++i) {
         GemvParams& p = ps[i];
         p.off_stage = off;
-        p.stage_bytes = slot;
         p.nstages = nst;
         p.kg = p.kb / kGemvGranuleBlocks;
         p.whole_tiles = 0;
@@ -550,8 +530,9 @@ cudaError_t launch_dense(const GemvParams* ps, uint32_t count, size_t smem, int 
         DecodeArgs<1> ga{};
         ga.p[0] = p;
         for (int j = 0; j < 3; ++j) ga.maps[0][j] = e->m[j];
-        ga.ub[0] = 0;
-        ga.ub[1] = (uint64_t)p.tiles * p.kg;
+        ga.cta_begin[0] = 0;
+        ga.cta_begin[1] = (uint32_t)grid;
+        ga.dot_start[0] = ga.dot_start[1] = 0;
         ga.count = 1;
         ga.any_rank = p.rank != 0;
         return launch_args<1>(ga, smem, grid, s);
@@ -559,7 +540,9 @@ cudaError_t launch_dense(const GemvParams* ps, uint32_t count, size_t smem, int 
     thread_local DecodeArgs<kMaxGroup> ga;
     ga.count = count;
     ga.any_rank = 0;
-    ga.ub[0] = 0;
+    split_ctas(ps, count, (uint32_t)grid, ga.cta_begin);
+    for (uint32_t i = count; i < (uint32_t)kMaxGroup; ++i) ga.cta_begin[i + 1] = ga.cta_begin[count];
+    for (uint32_t i = 0; i <= (uint32_t)kMaxGroup; ++i) ga.dot_start[i] = 0;
     for (uint32_t i = 0; i < (uint32_t)kMaxGroup; ++i) {
         const GemvParams& p = ps[i < count ? i : count - 1];
         ga.p[i] = p;
@@ -567,10 +550,7 @@ cudaError_t launch_dense(const GemvParams* ps, uint32_t count, size_t smem, int 
             const MapEntry* e = maps_for(p.w, p.n, p.kb);
             if (!e) return cudaErrorInvalidValue;
             for (int j = 0; j < 3; ++j) ga.maps[i][j] = e->m[j];
-            ga.ub[i + 1] = ga.ub[i] + (uint64_t)p.tiles * p.kg;
             ga.any_rank |= p.rank != 0;
-        } else {
-            ga.ub[i + 1] = ga.ub[i];
         }
     }
     return launch_args<kMaxGroup>(ga, smem, grid, s);

@@ -561,8 +561,9 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
     if (rank) {
         float* t = reinterpret_cast<float*>(base + ws.t);
         if (m <= 32) {
-            // few tokens: one CTA per (token, rank row) dot product is quicker than a GEMM with one or two tiles
-            if ((e = launch_lora_project(x, x_dtype, m, k, la, rank, t, 0, s)) != cudaSuccess) return fail("projection launch", e);
+            // few tokens: one warp per (token, rank row) dot product is quicker than a GEMM with one or two tiles
+            launch_lora_t(x, x_dtype, m, k, la, rank, t, s);
+            if ((e = cudaGetLastError()) != cudaSuccess) return fail("projection launch", e);
             ++nl;
         } else {
             // 2. A -> [Ah | Al] in the activations' column order; 3. T = X A^T on the tensor cores (f32)

@@ -18,18 +18,15 @@ cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs,
                                  float* out, cudaStream_t s);
 void launch_rot_signs(uint64_t seed, uint32_t dim, float* signs, cudaStream_t s);
 
-// ---- lq4_gemv.cu ----------------------------------------------------------------
-// Geometry of the decode kernel.
+// ---- decode kernels: geometry and parameters ------------------------------------------
 constexpr int kGemvTileRows = 128;        // output rows per tile: 8 consumer warps x 16
-constexpr int kGemvStageBlocks = 16;      // Q4 blocks (of one row) per pipeline stage
 constexpr int kGemvGranuleBlocks = 4;     // stream-K split granularity along k (16-byte aligned pieces)
-constexpr int kGemvRowStride = kGemvStageBlocks * kBlockBytes + 16;   // 336 B: rows 4 banks apart (x odd)
-constexpr int kGemvStageWBytes = kGemvTileRows * kGemvRowStride;      // 43008
 constexpr int kGemvThreads = 288;         // 8 consumer warps + 1 producer warp
-constexpr int kGemvMaxM = 16;
+constexpr int kGemvMaxM = 16;             // tokens per decode launch
 constexpr int kGemvMaxRank = 128;
 constexpr int kMaxSmem = 232448;          // 227 KB opt-in limit per CTA
 
+// One projection as the decode kernels see it.
 struct GemvParams {
     const uint8_t* w;
     float* y;
@@ -38,36 +35,28 @@ struct GemvParams {
     uint32_t kb;            // k / 32
     uint32_t kg;            // granules per row = kb / 4
     uint32_t tiles;         // ceil(n / 128)
-    uint32_t nt;            // n-tiles of 8 columns: ceil(2m / 8)
-    uint32_t gmax;          // fragment columns stored per n-tile (2, 4, 6 or 8)
     uint32_t nstages;
-    // resident-activation variant: raw activations, converted in the CTA prologue
-    const void* x;
+    const void* x;          // activations [m, k]
     int32_t x_dtype;
-    const float* signs;     // non-NULL: rotate in the prologue (k a power of two)
-    // staged-activation variant: fragments and block sums prepared by prep_xs
-    const uint8_t* xs_g;
-    const float* sx_g;
-    const float* t_g;       // staged variant: finished t[m][rank]
-    // LoRA
+    const float* signs;     // resident kernel only; non-NULL: rotate in the prologue (k a power of two)
+    const uint8_t* xs_g;    // dense kernel: activation limb records prepared by launch_dense_prep
+    // LoRA: t = A x
+    const float* t_g;       // dense kernel: [m][rank], finished by the launch before it
+    uint2* tmsg;            // resident kernel: [m][rank][tsplit] {partial dot, tag} messages written by the kernel itself
+    uint32_t tsplit;        // resident kernel: pieces each projection dot product is cut into along k
     const float* la;
     const float* lb;
     uint32_t rank;
     float lscale;
-    float* tpart;           // resident variant: [grid][m*rank] partial projections
-    uint32_t* tsync;        // resident variant: {arrived, finished}
-    // stream-K fix-up
-    float* partials;        // [grid][2][128 * nt * 4]
-    uint32_t* tickets;      // [tiles * 8]
+    // cross-CTA state
+    uint32_t* tsync;        // 64-bit launch counter (8-byte aligned), see launch_tag()
+    float* partials;        // [grid][128 rows][tokens] 8-byte {partial sum, tag} messages
     int32_t* status;
     // shared-memory offsets (bytes from the dynamic smem base)
-    uint32_t off_t, off_stage, stage_bytes, off_stage_xs, off_stage_sx, off_xs, off_sx, off_xrot;
+    uint32_t off_stage, off_xs, off_sx, off_xrot, off_t;
     uint32_t use_pdl;
-    // resident decode kernel (lq4_decode.cu)
-    uint32_t stage_blocks;  // Q4 blocks of one row per pipeline stage: 20, 12 or 4
-    uint32_t spt;           // stages per tile = ceil(kb / stage_blocks)
     int32_t sm_count;       // SMs of the device (0: assume 148)
-    uint32_t whole_tiles;   // 1: every CTA gets entire tiles, no cross-CTA partial sums
+    uint32_t whole_tiles;   // resident kernel: every CTA gets entire tiles, no cross-CTA partial sums
 };
 
 // ---- lq4_decode.cu ---------------------------------------------------------------
@@ -77,6 +66,11 @@ size_t decode_plan_smem(GemvParams& p);
 // Work units (tile, stage) of a planned launch; the grid is min(#SM, units).
 uint64_t decode_units(const GemvParams& p);
 cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s);
+// Pieces the resident kernel cuts each LoRA projection dot product into along k (one warp each).
+inline uint32_t decode_tsplit(uint32_t k) {
+    const uint32_t s = (k / 4 + 767) / 768;
+    return s < 1 ? 1 : (s > 8 ? 8 : s);
+}
 // Several independent projections of the same token count in ONE persistent launch: the work
 // units of all problems form one stream-K range, so launch, prologue and tail are paid once.
 constexpr int kMaxGroup = 8;
@@ -85,12 +79,6 @@ constexpr int kMaxGroup = 8;
 size_t decode_group_plan_smem(GemvParams* ps, uint32_t count);
 uint64_t decode_group_units(const GemvParams* ps, uint32_t count);
 cudaError_t launch_decode_group(const GemvParams* ps, uint32_t count, size_t smem, int grid, cudaStream_t s);
-// t[i] = A_i x_i for every problem of the group that has an adapter, in one launch (none: no launch).
-cudaError_t launch_lora_project_group(const GemvParams* ps, uint32_t count, float* const* t, uint32_t m, int use_pdl,
-                                      cudaStream_t s);
-// t = A x for the decode kernel's LoRA epilogue; launched right before launch_decode.
-cudaError_t launch_lora_project(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank,
-                                float* t, int use_pdl, cudaStream_t s);
 
 // ---- lq4_dense.cu ---------------------------------------------------------------
 // Decode kernel for 2..16 tokens (any k): activation limbs are prepared per call into per-block
@@ -103,15 +91,10 @@ cudaError_t launch_dense_prep(const GemvParams* ps, uint32_t count, uint8_t* con
                               cudaStream_t s);
 cudaError_t launch_dense(const GemvParams* ps, uint32_t count, size_t smem, int grid, cudaStream_t s);
 
-// Fills the smem-dependent fields of `p` and returns the dynamic shared memory the
-// launch needs, or 0 if the shape does not fit the requested variant.
-size_t gemv_plan_smem(GemvParams& p, bool resident);
+// True if `m` (<= 4) activation rows of length k fit the resident decode kernel's shared memory.
 bool gemv_resident_fits(uint32_t m, uint32_t k, bool rot);
-cudaError_t launch_gemv_mma(const GemvParams& p, bool resident, size_t smem, int grid, cudaStream_t s);
 
-// Activation preparation for the staged variant and for the generic kernel.
-void launch_prep_xs(const void* x, int x_dtype, uint32_t m, uint32_t k, uint32_t nt, uint32_t gmax, uint8_t* xs_g,
-                    float* sx_g, cudaStream_t s);
+// Fallbacks for shapes the TMA-based kernels do not take (lq4_gemv.cu).
 void launch_lora_t(const void* x, int x_dtype, uint32_t m, uint32_t k, const float* la, uint32_t rank, float* t,
                    cudaStream_t s);
 void launch_gemv_generic(const void* x, int x_dtype, const uint8_t* w, float* y, uint64_t ldy, uint32_t m,

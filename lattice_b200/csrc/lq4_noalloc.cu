@@ -23,7 +23,7 @@ constexpr uint32_t kNaMaxN = 32768;         // output rows per call
 constexpr uint32_t kNaMaxRank = 64;         // LoRA rank
 constexpr size_t kNaCtrlBytes = 256 + (size_t)(kNaMaxN / kGemvTileRows) * 8 * 4;                  // status, counters, tickets
 constexpr size_t kNaPartialBytes = (size_t)kNaMaxGrid * 2 * kGemvTileRows * 4 * sizeof(float);    // 655,360
-constexpr size_t kNaTpartBytes = 4096;                                                           // t = A x: up to 4 x 64 floats
+constexpr size_t kNaTpartBytes = 4 * 64 * 8 * 8;                                                  // t = A x messages: 4 tokens x rank 64 x 8 k pieces x 8 B
 constexpr size_t kNaScratchBytes = ((kNaCtrlBytes + 255) / 256) * 256 + kNaPartialBytes + kNaTpartBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
@@ -98,34 +98,28 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
     p.m = a->m; p.n = a->n; p.k = a->k;
     p.kb = a->k / 32; p.kg = p.kb / kGemvGranuleBlocks;
     p.tiles = (a->n + kGemvTileRows - 1) / kGemvTileRows;
-    p.nt = 1; p.gmax = 2 * a->m;
     p.x = a->x; p.x_dtype = a->x_dtype; p.signs = signs;
-    if (a->lora) { p.la = a->lora->a; p.lb = a->lora->b; p.rank = rank; p.lscale = a->lora->scale; }
+    p.tsplit = 1;
+    if (a->lora) { p.la = a->lora->a; p.lb = a->lora->b; p.rank = rank; p.lscale = a->lora->scale; p.tsplit = decode_tsplit(a->k); }
     p.sm_count = sms < (int)kNaMaxGrid ? sms : (int)kNaMaxGrid;
 
-    // carve the array: [status | counters | tickets] [partials] [LoRA partials]
+    // carve the array: [status | counters] [partial-sum messages] [t = A x]
     p.status = reinterpret_cast<int32_t*>(base);
     p.tsync = reinterpret_cast<uint32_t*>(base + 64);
-    p.tickets = reinterpret_cast<uint32_t*>(base + 256);
     unsigned char* q = base + ((kNaCtrlBytes + 255) / 256) * 256;
     p.partials = reinterpret_cast<float*>(q);
-    float* t_scratch = reinterpret_cast<float*>(q + kNaPartialBytes);     // t = A x, m * rank floats
+    p.tmsg = reinterpret_cast<uint2*>(q + kNaPartialBytes);               // t = A x messages
     p.use_pdl = 0;
     // The array keeps whatever the previous call left, on purpose: every cross-CTA message in it is
     // tagged with the launch generation stored in the array, which each launch advances, so stale
     // messages are never mistaken for new ones; only the status word has to start at zero.
     e = cudaMemsetAsync(base, 0, 4, s);
     if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
-    const size_t smem = gemv_plan_smem(p, true);
+    const size_t smem = decode_plan_smem(p);
     if (!smem) return fail(LQ4_ERR_NOSPACE, "shared-memory plan does not fit");
-    if (p.rank) {
-        e = launch_lora_project(a->x, a->x_dtype, a->m, a->k, p.la, p.rank, t_scratch, 0, s);
-        if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
-        p.t_g = t_scratch;
-    }
     const uint64_t units = decode_units(p);
     const uint64_t grid = units < (uint64_t)p.sm_count ? units : (uint64_t)p.sm_count;
-    e = launch_gemv_mma(p, true, smem, (int)grid, s);
+    e = launch_decode(p, smem, (int)grid, s);
     if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
     return LQ4_OK;
 }
