@@ -177,7 +177,9 @@ def workload_config(args, world):
             "m": args.m, "layers": args.layers, "lora_rank": LORA_RANK,
             "launch": ("one lq4_linear_group call per set: the four independent projections share one persistent launch"
                        if args.launch == "grouped" else "one lq4_linear call per projection"),
-            "parallelism": f"N-sharded column-parallel x{world} + NCCL all-gather" if world > 1 else "single GPU",
+            "parallelism": (f"N-sharded column-parallel x{world}, " +
+                            ("all-gather fused into the decode kernel's epilogue (peer stores over NVLink + arrival counters)"
+                             if args.gather == "peer" else "one NCCL all-gather per set")) if world > 1 else "single GPU",
             "l2": "inputs larger than L2: every launch streams distinct weights, "
                   f"{args.layers * 131.072:.0f} MB of Q4 payload per step per job"}
 
@@ -223,18 +225,33 @@ def run_ours(args):
             a = torch.randn((LORA_RANK, k), generator=gen, device=dev) * 0.02
             gen.manual_seed(7000003 * li + 307 * si + 13 * rank + 5)
             b = torch.randn((nl, LORA_RANK), generator=gen, device=dev) * 0.02
-            projs.append(dict(k=k, n=n, nl=nl, qw=Q4WeightBuf.from_device_payload(payload, nl, k), a=a, b=b,
+            projs.append(dict(k=k, n=n, nl=nl, n0=n0, qw=Q4WeightBuf.from_device_payload(payload, nl, k), a=a, b=b,
                               lora=LoraDesc(a.data_ptr(), b.data_ptr(), LORA_RANK, scale)))
         layers.append(projs)
     gen.manual_seed(99)
     xs = {k: torch.randn((m, k), generator=gen, device=dev) for k in (5120, 17408)}
-    # The outputs of one set sit side by side in one [m, sum(n_local)] buffer (each projection writes
-    # its column range, ldy = row pitch), so that a sharded set needs ONE all-gather.
+    # The outputs of one set sit side by side in one buffer, each projection writing its column range
+    # (ldy = row pitch).  One GPU: [m, sum(n)].  Several GPUs: the same [m, sum(n)] buffer exists on
+    # every rank as a peer buffer, a rank computes the columns of its N-shards and the decode kernels'
+    # epilogue writes them into every rank's copy (--gather peer); or, the plain way, the local slices
+    # are exchanged with ONE NCCL all-gather per set (--gather nccl).
+    from lattice_b200.sharded import PeerGather
+    peer_mode = world > 1 and args.gather == "peer"
     nls = [layers[0][si]["nl"] for si in range(len(SHAPES))]
     offs = [sum(nls[:si]) for si in range(len(SHAPES))]
-    y_cat = torch.empty((m, sum(nls)), device=dev)
-    y_local = {si: y_cat[:, offs[si]:offs[si] + nls[si]] for si in range(len(SHAPES))}
-    y_full = torch.empty((world * m, sum(nls)), device=dev)
+    full_n = [n for _, n in SHAPES]
+    full_offs = [sum(full_n[:si]) for si in range(len(SHAPES))]
+    pg = PeerGather(m, sum(full_n), device=local_rank) if peer_mode else None
+    gdesc = pg.desc if peer_mode else None
+    if peer_mode:
+        y_cat = pg.full
+        y_local = {si: y_cat[:, full_offs[si] + layers[0][si]["n0"]:full_offs[si] + layers[0][si]["n0"] + nls[si]]
+                   for si in range(len(SHAPES))}
+        y_full = y_cat
+    else:
+        y_cat = torch.empty((m, sum(nls)), device=dev)
+        y_local = {si: y_cat[:, offs[si]:offs[si] + nls[si]] for si in range(len(SHAPES))}
+        y_full = torch.empty((world * m, sum(nls)), device=dev)
     torch.cuda.synchronize()
     note("synthetic model built")
     grouped = args.launch == "grouped"
@@ -243,27 +260,50 @@ def run_ours(args):
 
     def run_set(projs, x_of, grouped=grouped):
         if grouped:
-            # one persistent launch for the set's four projections (plus one small launch for the
-            # four adapters' x.A^T); the argument block is built once per (set, input buffers)
+            # one persistent launch for the set's four projections; the argument block is built once
+            # per (set, input buffers)
             key = (id(projs), id(x_of))
             if key not in prepared:
                 prepared[key] = be.prepare_group([(x_of[p["k"]], p["qw"], p["lora"]) for p in projs],
-                                                 [y_local[si] for si in range(len(projs))])
+                                                 [y_local[si] for si in range(len(projs))], gather=gdesc,
+                                                 wait_gather=gdesc)
             prepared[key]()
         else:
             for si, p in enumerate(projs):
                 be.dispatch_gemm_q4(x_of[p["k"]], 0, p["qw"], y_local[si], 0, m, p["nl"], p["k"], lora=p["lora"],
-                                    ldy=y_cat.stride(0))
-        if world > 1:
+                                    ldy=y_cat.stride(0), gather=gdesc, wait_gather=gdesc if si == 0 else None)
+        if world > 1 and not peer_mode:
             dist.all_gather_into_tensor(y_full, y_cat)
+        # peer mode: every set's kernel waits itself for the arrivals of the sets before it (as a layer
+        # that consumes gathered activations does); the last set of a step is waited for in step()
+
+    if peer_mode:
+        # check the fused gather once against NCCL: every rank must hold every rank's columns
+        run_set(layers[0], xs)
+        be.gather_wait(gdesc)
+        torch.cuda.synchronize()
+        dist.barrier()
+        for si, p in enumerate(layers[0]):
+            mine = y_local[si].contiguous()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            if len({shard_plan(p["n"], p["k"], world, r)[1] - shard_plan(p["n"], p["k"], world, r)[0] for r in range(world)}) == 1:
+                dist.all_gather(parts, mine)
+                want = torch.cat(parts, dim=1)
+                got = y_cat[:, full_offs[si]:full_offs[si] + p["n"]]
+                if not torch.equal(want, got):
+                    raise SystemExit(f"fused all-gather mismatch on rank {rank}, projection {si}")
+        dist.barrier()
+        note("fused all-gather checked against NCCL")
 
     def step():
         for projs in layers:
             run_set(projs, xs)
+        if peer_mode:
+            be.gather_wait(gdesc)                  # stream-ordered: the last set's peer columns have arrived
 
     # pinned host buffers for the end-to-end variant
     hx = {k: torch.randn((m, k)).pin_memory() for k in (5120, 17408)}
-    hy = torch.empty((world * m, sum(nls))).pin_memory()
+    hy = torch.empty(tuple(y_full.shape)).pin_memory()
     dx = {k: torch.empty((m, k), device=dev) for k in (5120, 17408)}
 
     def e2e_step():
@@ -272,6 +312,8 @@ def run_ours(args):
             for k in dx:
                 dx[k].copy_(hx[k], non_blocking=True)
             run_set(projs, dx)
+            if peer_mode:
+                be.gather_wait(gdesc)
             if world > 1:
                 hy.copy_(y_full, non_blocking=True)
             else:
@@ -283,9 +325,9 @@ def run_ours(args):
     graph_info = {"mode": "eager"}
 
     def make_graphed(fn):
-        if args.eager or world > 1:
+        if args.eager or (world > 1 and not peer_mode):
             # with NCCL collectives inside the step, capture is left out: a captured all-gather did
-            # not complete on this pool, so multi-GPU steps are timed as plain calls
+            # not complete on this pool, so such steps are timed as plain calls
             if world > 1:
                 graph_info["mode"] = "eager (multi-GPU step with NCCL all-gather)"
             return fn, None
@@ -410,6 +452,9 @@ def run_ours(args):
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        if pg is not None:
+            prepared.clear()
+            pg.close()
         dist.barrier()
         dist.destroy_process_group()
 
@@ -557,6 +602,9 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "per-projection"],
                     help="grouped: one persistent launch per set of four projections (lq4_linear_group); "
                          "per-projection: one lq4_linear call each")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="several GPUs: peer = all-gather fused into the kernel epilogue (stores into every "
+                         "rank's buffer over NVLink); nccl = one NCCL all-gather per set")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set: three launches of one case, for profiling")

@@ -87,6 +87,19 @@ typedef struct {
     uint32_t dim;
 } lq4_rot_desc;
 
+/* Column-parallel all-gather fused into the decode kernels' epilogue: every GPU of the group
+ * computes its own rows of W (an N-shard) and writes the results straight into the output
+ * buffer of EVERY GPU over NVLink, then signals each peer's arrival counter.  `bases[r]` is
+ * rank r's peer buffer (lq4_peer_buf_*) as mapped in this process, bases[rank] this GPU's own;
+ * all buffers have the same layout and `y` of the call must point into the own buffer's payload
+ * (lq4_peer_buf_payload): the same byte offset is written in every peer.  No counterpart in the
+ * reference (single GPU); the NCCL all-gather it replaces is the plain way to do the same. */
+#define LQ4_MAX_PEERS 8
+typedef struct {
+    uint32_t world, rank;
+    void* bases[LQ4_MAX_PEERS];
+} lq4_gather_desc;
+
 typedef struct {
     const void* x;        /* [m, k] row-major activations, f32 or bf16 */
     int32_t x_dtype;      /* LQ4_DTYPE_* */
@@ -100,6 +113,11 @@ typedef struct {
     const lq4_lora_desc* lora;   /* NULL = no adapter for this projection */
     const lq4_rot_desc* rot;     /* NULL = no online rotation */
     int32_t path;         /* LQ4_PATH_* */
+    const lq4_gather_desc* gather;   /* NULL = results stay on this GPU; else m <= 16 decode shapes only */
+    const lq4_gather_desc* wait_gather;   /* non-NULL: x holds gathered results (it lives in the own peer buffer):
+                                             before x is read, wait (bounded) until every peer's results of all
+                                             gathered launches this rank has issued so far have arrived; the
+                                             same wait as lq4_gather_wait, without a launch of its own */
 } lq4_linear_args;
 
 /* ---- context ----------------------------------------------------------- */
@@ -139,6 +157,28 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* args, void* stream);
  * merged-row GEMVs with per-range adapters (inner/layers/gdn.rs:69-105,293-300: one GEMV over
  * qkv||z rows, then LoRA into sub-ranges): q/k/v, or gate/up, share x and go in one group. */
 lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t count, void* stream);
+
+/* ---- peer buffers for the fused all-gather ------------------------------------ */
+typedef struct lq4_peer_buf lq4_peer_buf;
+#define LQ4_PEER_HANDLE_BYTES 64
+/* Allocates (cudaMalloc, zero-filled) a buffer other processes on the same node can map:
+ * 256 control bytes (arrival counter, launch sequence, CTA counter) followed by `payload_bytes` of output. */
+lq4_status lq4_peer_buf_create(uint64_t payload_bytes, lq4_peer_buf** out);
+void lq4_peer_buf_free(lq4_peer_buf* b);
+/* The buffer's base (what goes into lq4_gather_desc::bases for the owner) and its payload. */
+void* lq4_peer_buf_base(const lq4_peer_buf* b);
+void* lq4_peer_buf_payload(const lq4_peer_buf* b);
+/* 64 opaque bytes to hand to the other ranks (any transport), and the call that maps a peer's
+ * buffer from them; the returned base goes into lq4_gather_desc::bases[peer]. */
+lq4_status lq4_peer_buf_export(const lq4_peer_buf* b, uint8_t* handle_out);
+lq4_status lq4_peer_buf_open(const uint8_t* handle, void** base_out);
+lq4_status lq4_peer_buf_close(void* base);
+/* Stream-ordered wait (bounded: about two seconds, then LQ4_ERR_DEVICE through lq4_ctx_check) until
+ * every peer's results of all gathered launches issued so far on this rank have arrived here.
+ * Ranks must issue the same sequence of gathered launches.  A buffer may be overwritten by the
+ * peers' NEXT gathered launch as soon as they get there: alternate two buffers, or synchronise the
+ * ranks, before reading results late. */
+lq4_status lq4_gather_wait(lq4_ctx* ctx, const lq4_gather_desc* gather, void* stream);
 
 /* Decode projection (m <= 4) for callers that cannot allocate device memory: an engine that
  * handed every byte to its own pool at start-up, or a decode loop that cannot afford the

@@ -26,10 +26,19 @@ class RotDesc(C.Structure):
     _fields_ = [("signs", C.c_void_p), ("dim", C.c_uint32)]
 
 
+MAX_PEERS = 8
+PEER_HANDLE_BYTES = 64
+
+
+class GatherDesc(C.Structure):
+    _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("bases", C.c_void_p * MAX_PEERS)]
+
+
 class LinearArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("m", C.c_uint32), ("n", C.c_uint32),
                 ("k", C.c_uint32), ("w", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_uint64),
-                ("lora", C.POINTER(LoraDesc)), ("rot", C.POINTER(RotDesc)), ("path", C.c_int32)]
+                ("lora", C.POINTER(LoraDesc)), ("rot", C.POINTER(RotDesc)), ("path", C.c_int32),
+                ("gather", C.POINTER(GatherDesc)), ("wait_gather", C.POINTER(GatherDesc))]
 
 
 # name -> (restype, argtypes); every symbol the header declares
@@ -46,6 +55,14 @@ SIGNATURES = {
     "lq4_linear_host": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_void_p]),
     "lq4_linear_decode_noalloc": (C.c_int32, [C.POINTER(LinearArgs), C.c_void_p]),
     "lq4_linear_group": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_uint32, C.c_void_p]),
+    "lq4_peer_buf_create": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p)]),
+    "lq4_peer_buf_free": (None, [C.c_void_p]),
+    "lq4_peer_buf_base": (C.c_void_p, [C.c_void_p]),
+    "lq4_peer_buf_payload": (C.c_void_p, [C.c_void_p]),
+    "lq4_peer_buf_export": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "lq4_peer_buf_open": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "lq4_peer_buf_close": (C.c_int32, [C.c_void_p]),
+    "lq4_gather_wait": (C.c_int32, [C.c_void_p, C.POINTER(GatherDesc), C.c_void_p]),
     "lq4_lora_apply": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32, C.c_uint32, C.c_void_p,
                                    C.c_uint32, C.c_uint64, C.POINTER(LoraDesc), C.c_void_p]),
     "lq4_dequant_f32": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),

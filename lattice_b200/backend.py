@@ -26,7 +26,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import LinearArgs, LoraDesc, Lq4Error, RotDesc, check
+from ._lib import GatherDesc, LinearArgs, LoraDesc, Lq4Error, RotDesc, check
 
 
 def _stream() -> int:
@@ -170,10 +170,13 @@ class CudaQ4Backend:
     # ---- the seam -----------------------------------------------------------
     def _linear(self, x_ptr: int, x_dtype: int, w_ptr: int, y_ptr: int, m: int, n: int, k: int, ldy: int = 0,
                 lora: Optional[LoraDesc] = None, rot: Optional[RotDesc] = None, path: int = _lib.PATH_AUTO,
-                host: bool = False) -> None:
+                host: bool = False, gather: Optional[GatherDesc] = None,
+                wait_gather: Optional[GatherDesc] = None) -> None:
         args = LinearArgs(x_ptr, x_dtype, m, n, k, w_ptr, y_ptr, ldy,
                           C.pointer(lora) if lora is not None else None,
-                          C.pointer(rot) if rot is not None else None, path)
+                          C.pointer(rot) if rot is not None else None, path,
+                          C.pointer(gather) if gather is not None else None,
+                          C.pointer(wait_gather) if wait_gather is not None else None)
         fn = _lib.lib().lq4_linear_host if host else _lib.lib().lq4_linear
         check(fn(self._ctx, C.byref(args), _stream()))
 
@@ -194,14 +197,15 @@ class CudaQ4Backend:
     def dispatch_gemm_q4_at(self, x: torch.Tensor, x_offset: int, qw: Q4WeightBuf, qw_extra_offset: int,
                             y: torch.Tensor, y_offset: int, m: int, n: int, k: int, *,
                             lora: Optional[LoraDesc] = None, rot: Optional[RotDesc] = None,
-                            ldy: int = 0, path: int = _lib.PATH_AUTO) -> None:
+                            ldy: int = 0, path: int = _lib.PATH_AUTO, gather: Optional[GatherDesc] = None,
+                            wait_gather: Optional[GatherDesc] = None) -> None:
         """``y[m, n] = x[m, k] . Wq4[n, k]^T`` (overwrites y); ``qw_extra_offset`` bytes into the payload."""
         if m == 0 or n == 0:
             return
         self._require_k("dispatch_gemm_q4_at", k)
         assert x.is_cuda and y.is_cuda and y.dtype == torch.float32
         self._linear(x.data_ptr() + x_offset, self._dtype_of(x), qw.payload_ptr + qw_extra_offset,
-                     y.data_ptr() + y_offset, m, n, k, ldy, lora, rot, path)
+                     y.data_ptr() + y_offset, m, n, k, ldy, lora, rot, path, gather=gather, wait_gather=wait_gather)
 
     def dispatch_gemm_q4(self, x: torch.Tensor, x_offset: int, qw: Q4WeightBuf, y: torch.Tensor, y_offset: int,
                          m: int, n: int, k: int, **kw) -> None:
@@ -341,7 +345,8 @@ class CudaQ4Backend:
         self.dispatch_gemm_q4(x.contiguous(), 0, qw, y, 0, m, qw.n, k, lora=lora, rot=rot, path=path)
         return y
 
-    def prepare_group(self, problems, outs: Optional[List[torch.Tensor]] = None) -> "PreparedGroup":
+    def prepare_group(self, problems, outs: Optional[List[torch.Tensor]] = None,
+                      gather: Optional[GatherDesc] = None, wait_gather: Optional[GatherDesc] = None) -> "PreparedGroup":
         """Builds the argument block of a grouped call once; calling the result launches it.
 
         ``problems`` is a list of ``(x, qw)`` or ``(x, qw, lora)`` with ``x`` ``[m, k]`` on the device.  The
@@ -363,16 +368,24 @@ class CudaQ4Backend:
             ys.append(y)
             ldy = y.stride(0) if m > 1 or y.stride(0) >= qw.n else qw.n      # row pitch of a column slice
             arr[i] = LinearArgs(x.data_ptr(), self._dtype_of(x), m, qw.n, k, qw.payload_ptr, y.data_ptr(), ldy,
-                                C.pointer(lora) if lora is not None else None, None, _lib.PATH_AUTO)
+                                C.pointer(lora) if lora is not None else None, None, _lib.PATH_AUTO,
+                                C.pointer(gather) if gather is not None else None,
+                                C.pointer(wait_gather) if wait_gather is not None else None)
+        keep += [gather, wait_gather]
         return PreparedGroup(self, arr, n_prob, ys, keep)
 
-    def linear_group(self, problems, outs: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
+    def gather_wait(self, gather: GatherDesc) -> None:
+        """Stream-ordered wait until every peer's results of the gathered launches issued so far are here."""
+        check(_lib.lib().lq4_gather_wait(self._ctx, C.byref(gather), _stream()))
+
+    def linear_group(self, problems, outs: Optional[List[torch.Tensor]] = None,
+                     gather: Optional[GatherDesc] = None, wait_gather: Optional[GatherDesc] = None) -> List[torch.Tensor]:
         """Several independent projections in one call (one persistent launch for decode shapes);
         returns the list of ``[m, n]`` f32 outputs."""
         if len(problems) == 0:
             return []
         problems = [(pr[0].contiguous(),) + tuple(pr[1:]) for pr in problems]
-        return self.prepare_group(problems, outs)()
+        return self.prepare_group(problems, outs, gather, wait_gather)()
 
     def linear_host(self, x: np.ndarray, qw: Q4WeightBuf, y: np.ndarray, *, lora: Optional[LoraDesc] = None,
                     rot: Optional[RotDesc] = None) -> None:

@@ -116,6 +116,20 @@ lq4_status validate_linear(const lq4_linear_args* a) {
         if (!is_pow2(a->k) || a->k > 16384) return fail(LQ4_ERR_ROT, "rotation needs k a power of two <= 16384");
     }
     if (a->path < LQ4_PATH_AUTO || a->path > LQ4_PATH_GEMM_TC) return fail(LQ4_ERR_UNSUPPORTED, "unknown path");
+    if (a->wait_gather) {
+        const lq4_gather_desc* g = a->wait_gather;
+        if (g->world < 1 || g->world > LQ4_MAX_PEERS || g->rank >= g->world || !g->bases[g->rank])
+            return fail(LQ4_ERR_SHAPE, "wait_gather: world must be 1..8, rank < world, own base non-NULL");
+    }
+    if (a->gather) {
+        const lq4_gather_desc* g = a->gather;
+        if (g->world < 1 || g->world > LQ4_MAX_PEERS || g->rank >= g->world)
+            return fail(LQ4_ERR_SHAPE, "gather: world must be 1..8 and rank < world");
+        for (uint32_t r = 0; r < g->world; ++r)
+            if (!g->bases[r] || !aligned(g->bases[r], 256)) return fail(LQ4_ERR_NULL, "gather: a peer buffer base is NULL or misaligned");
+        if (reinterpret_cast<const char*>(a->y) < static_cast<const char*>(g->bases[g->rank]) + 256)
+            return fail(LQ4_ERR_SHAPE, "gather: y must point into the payload of this rank's own peer buffer");
+    }
     return LQ4_OK;
 }
 
@@ -131,6 +145,20 @@ void fill_params(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dt
     p.use_pdl = ctx->pdl;
     p.sm_count = ctx->sm_count;
     p.x = x; p.x_dtype = x_dtype;
+    if (a->gather && a->gather->world > 1) {
+        const lq4_gather_desc* g = a->gather;
+        p.world = g->world;
+        p.grank = g->rank;
+        for (uint32_t r = 0; r < g->world; ++r) {
+            p.peer_off[r] = static_cast<const char*>(g->bases[r]) - static_cast<const char*>(g->bases[g->rank]);
+            p.peer_arrive[r] = static_cast<unsigned long long*>(g->bases[r]);
+        }
+        p.gseq = static_cast<unsigned long long*>(g->bases[g->rank]) + 1;
+    }
+    if (a->wait_gather && a->wait_gather->world > 1) {
+        p.wait_arrive = static_cast<const unsigned long long*>(a->wait_gather->bases[a->wait_gather->rank]);
+        p.wait_world = a->wait_gather->world;
+    }
     p.tsplit = 1;
     if (a->lora) {
         p.la = a->lora->a; p.lb = a->lora->b; p.rank = a->lora->rank; p.lscale = a->lora->scale;
@@ -209,7 +237,7 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
 
 extern "C" {
 
-int32_t lq4_abi_version(void) { return 1; }
+int32_t lq4_abi_version(void) { return 2; }
 
 const char* lq4_last_error(void) { return g_last_error.c_str(); }
 
@@ -325,15 +353,23 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     }
     if (path != LQ4_PATH_GEMV_GENERIC && !fast_layout)
         return fail(LQ4_ERR_ALIGN, "fast paths need k % 128 == 0, 16-byte aligned w and x, rank <= 128");
+    if (a->gather && a->gather->world > 1 && (path != LQ4_PATH_GEMV_MMA || a->m > (uint32_t)kGemvMaxM))
+        return fail(LQ4_ERR_UNSUPPORTED, "the fused all-gather is built into the decode kernels only (m <= 16, fast layout)");
 
     const void* x = a->x;
     int x_dtype = a->x_dtype;
     const float* signs = a->rot ? a->rot->signs : nullptr;
+    // the decode kernels wait for gathered inputs themselves; every other first reader of x
+    // (rotation kernel, tensor-core path, generic kernel) gets the stand-alone wait in front
+    bool wait_in_kernel = path == LQ4_PATH_GEMV_MMA && a->m <= (uint32_t)kGemvMaxM;
 
     // The decode kernel rotates in its own prologue when the row fits; otherwise the
     // rotation runs as a kernel of its own into the workspace.
     const bool in_kernel_rot = signs && path == LQ4_PATH_GEMV_MMA && a->m == 1 && rank == 0 &&
                                gemv_resident_fits(1, a->k, true);
+    if (signs && !in_kernel_rot) wait_in_kernel = false;
+    if (a->wait_gather && a->wait_gather->world > 1 && !wait_in_kernel)
+        if ((st = lq4_gather_wait(ctx, a->wait_gather, stream))) return st;
     if (signs && !in_kernel_rot) {
         if ((st = ensure(ctx, ctx->xrot, (size_t)a->m * a->k * 4, false, s))) return st;
         LQ4_CUDA(launch_hadamard_rows(x, x_dtype, signs, a->k, a->m, (float*)ctx->xrot.p, s));
@@ -401,6 +437,8 @@ lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t 
         one_launch = a.m >= 1 && a.m <= (uint32_t)kGemvMaxM && a.m == m && a.n > 0 && !a.rot && (a.k % 128 == 0) &&
                      aligned(a.w, 16) && aligned(a.x, 16) && rank <= (uint32_t)kGemvMaxRank &&
                      (a.path == LQ4_PATH_AUTO || a.path == LQ4_PATH_GEMV_MMA);
+        one_launch = one_launch && a.gather == args[0].gather &&      // one arrival signal, one wait per launch
+                     a.wait_gather == args[0].wait_gather;
         if (one_launch) fill_params(ctx, &a, a.x, a.x_dtype, a.m, a.y, a.ldy ? a.ldy : a.n, ps[i]);
     }
     size_t smem = 0;
@@ -431,9 +469,114 @@ lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t 
     return LQ4_OK;
 }
 
+// ---- peer buffers and the wait of the fused all-gather ------------------------------------
+struct lq4_peer_buf {
+    void* base = nullptr;
+    uint64_t payload_bytes = 0;
+};
+
+namespace {
+// One thread.  With programmatic dependent launch it first lets the launch after it start (a decode
+// kernel begins streaming weights at once and waits for this grid before it reads activations),
+// then waits for the gathered launch before it, whose sequence count it needs.
+__global__ void gather_wait_kernel(const unsigned long long* arrive, const unsigned long long* gseq, uint32_t world,
+                                   int32_t* status, int use_pdl) {
+    if (use_pdl) {
+        pdl_launch_dependents();
+        pdl_wait_prior_grids();
+    }
+    unsigned long long seq;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(seq) : "l"(gseq) : "memory");
+    const unsigned long long need = (seq >> 8) * 256ull * (world - 1);
+    const long long t0 = wait_clock();
+    for (;;) {
+        unsigned long long v;
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(arrive) : "memory");
+        if (v >= need) break;
+        if (wait_expired(t0)) { atomicOr(status, kDevErrGridWaitTimeout); break; }
+    }
+}
+}  // namespace
+
+lq4_status lq4_peer_buf_create(uint64_t payload_bytes, lq4_peer_buf** out) {
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    *out = nullptr;
+    if (payload_bytes == 0) return fail(LQ4_ERR_SHAPE, "payload_bytes is 0");
+    lq4_peer_buf* b = new lq4_peer_buf();
+    const size_t bytes = 256 + (size_t)((payload_bytes + 255) / 256 * 256);
+    cudaError_t e = cudaMalloc(&b->base, bytes);
+    if (e == cudaSuccess) e = cudaMemset(b->base, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        if (b->base) cudaFree(b->base);
+        delete b;
+        return cuda_fail(e, "peer buffer allocation");
+    }
+    b->payload_bytes = payload_bytes;
+    *out = b;
+    return LQ4_OK;
+}
+
+void lq4_peer_buf_free(lq4_peer_buf* b) {
+    if (!b) return;
+    if (b->base) cudaFree(b->base);
+    delete b;
+}
+
+void* lq4_peer_buf_base(const lq4_peer_buf* b) { return b ? b->base : nullptr; }
+void* lq4_peer_buf_payload(const lq4_peer_buf* b) { return b ? static_cast<char*>(b->base) + 256 : nullptr; }
+
+lq4_status lq4_peer_buf_export(const lq4_peer_buf* b, uint8_t* handle_out) {
+    if (!b || !handle_out) return fail(LQ4_ERR_NULL, "buffer or handle_out is NULL");
+    static_assert(sizeof(cudaIpcMemHandle_t) == LQ4_PEER_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    LQ4_CUDA(cudaIpcGetMemHandle(&h, b->base));
+    memcpy(handle_out, &h, sizeof(h));
+    return LQ4_OK;
+}
+
+lq4_status lq4_peer_buf_open(const uint8_t* handle, void** base_out) {
+    if (!handle || !base_out) return fail(LQ4_ERR_NULL, "handle or base_out is NULL");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    LQ4_CUDA(cudaIpcOpenMemHandle(base_out, h, cudaIpcMemLazyEnablePeerAccess));
+    return LQ4_OK;
+}
+
+lq4_status lq4_peer_buf_close(void* base) {
+    if (!base) return LQ4_OK;
+    LQ4_CUDA(cudaIpcCloseMemHandle(base));
+    return LQ4_OK;
+}
+
+lq4_status lq4_gather_wait(lq4_ctx* ctx, const lq4_gather_desc* g, void* stream) {
+    if (!ctx || !g) return fail(LQ4_ERR_NULL, "ctx or gather is NULL");
+    if (g->world < 1 || g->world > LQ4_MAX_PEERS || g->rank >= g->world || !g->bases[g->rank])
+        return fail(LQ4_ERR_SHAPE, "gather: world must be 1..8, rank < world, own base non-NULL");
+    if (g->world == 1) return LQ4_OK;
+    const unsigned long long* own = static_cast<const unsigned long long*>(g->bases[g->rank]);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(1);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (ctx->pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    LQ4_CUDA(cudaLaunchKernelEx(&cfg, gather_wait_kernel, own, own + 1, g->world, ctx->status, ctx->pdl));
+    ctx->launches += 1;
+    return LQ4_OK;
+}
+
 lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
     if (!a) return fail(LQ4_ERR_NULL, "args is NULL");
+    if (a->gather || a->wait_gather) return fail(LQ4_ERR_UNSUPPORTED, "lq4_linear_host takes host buffers: no fused all-gather");
     if (a->m == 0 || a->n == 0) return LQ4_OK;
     if (!a->x || !a->y) return fail(LQ4_ERR_NULL, "x and y must be non-NULL");
     if (a->k == 0 || a->k % 32 != 0) return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32");

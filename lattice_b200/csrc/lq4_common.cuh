@@ -86,6 +86,23 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
 __device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- arrivals of a fused all-gather ----------------------------------------------------
+// Waits (bounded) until every peer's results of all gathered launches this rank has issued so far
+// have arrived: each such launch of a peer adds 256 to `arrive[0]`, each of this rank's own adds
+// 256 to `arrive[1]`.  Called by whole warps after the previous launch is known to be complete.
+// Returns false on timeout.
+__device__ __forceinline__ bool wait_gather_arrivals(const unsigned long long* arrive, uint32_t world) {
+    unsigned long long seq, v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(seq) : "l"(arrive + 1) : "memory");
+    const unsigned long long need = (seq >> 8) * 256ull * (world - 1);
+    const long long t0 = wait_clock();
+    for (;;) {
+        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(arrive) : "memory");
+        if (v >= need) return true;
+        if (wait_expired(t0)) return false;
+    }
+}
+
 // ---- named barriers (subsets of a CTA) ----------------------------------------------
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -183,6 +183,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
         auto project = [&]() {
             projected = true;
             if (p.use_pdl) pdl_wait_prior_grids();          // x may come from the launch before this one
+            if (p.wait_world > 1 && !wait_gather_arrivals(p.wait_arrive, p.wait_world) && lane == 0)
+                atomicOr(p.status, kDevErrGridWaitTimeout);
             const uint32_t tag = launch_tag(p.tsync);
             // work item e = (problem, token, rank row, k piece); item e belongs to CTA e mod grid
             const uint32_t nitems = NP == 1 ? p.m * p.rank * p.tsplit : ga.dot_start[count];
@@ -252,8 +254,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
     } else {
         // ------------------------------ consumers ------------------------------
         const int g = lane >> 2, t = lane & 3;
-        // x may come from the launch before this one
+        // x may come from the launch before this one, or from the peers of a fused all-gather
         if (p.use_pdl) pdl_wait_prior_grids();
+        if (p.wait_world > 1 && !wait_gather_arrivals(p.wait_arrive, p.wait_world) && lane == 0)
+            atomicOr(p.status, kDevErrGridWaitTimeout);
         // a message written by an earlier launch never carries this launch's tag
         const uint32_t tag = launch_tag(p.tsync);
         LQ4_STAMP(1);
@@ -508,8 +512,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 if (mt != t || (uint32_t)mt >= q.m) continue;
-                if (rowa < q.n) q.y[(size_t)mt * q.ldy + rowa] = v[mt][0];
-                if (rowb < q.n) q.y[(size_t)mt * q.ldy + rowb] = v[mt][1];
+                if (rowa < q.n) store_out(q, (size_t)mt * q.ldy + rowa, v[mt][0]);
+                if (rowb < q.n) store_out(q, (size_t)mt * q.ldy + rowb, v[mt][1]);
             }
         }
         if (!ok) {
@@ -532,7 +536,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
         out[17 + 2 * blockIdx.x] = s_tl[5];
     }
 #endif
-    if (tid == 0) launch_done(p.tsync, blockIdx.x, gridDim.x);
+    if (tid == 0) {
+        gather_done(p, blockIdx.x, gridDim.x);
+        launch_done(p.tsync, blockIdx.x, gridDim.x);
+    }
     if (s_err && warp == 8 && lane == 0) {
         const uint32_t first = issued > NST ? issued - NST : 0;
         for (uint32_t j = first; j < issued; ++j) mbar_wait(&full[j % NST], (j / NST) & 1u);

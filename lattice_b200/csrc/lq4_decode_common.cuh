@@ -53,6 +53,34 @@ __device__ __forceinline__ void launch_done(uint32_t* counter, uint32_t cta, uin
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(share) : "memory");
 }
 
+// Output store; with a fused all-gather the value also goes to the same place in every peer.
+__device__ __forceinline__ void store_out(const GemvParams& q, size_t idx, float v) {
+    q.y[idx] = v;
+    if (q.world > 1) {
+        char* own = reinterpret_cast<char*>(q.y + idx);
+        for (uint32_t r = 0; r < q.world; ++r)
+            if (r != q.grank) *reinterpret_cast<float*>(own + q.peer_off[r]) = v;
+    }
+}
+// One thread per CTA, after the CTA's last output store (and a CTA barrier).  The CTAs of a launch
+// count themselves on a counter in this GPU's own memory (each adds its share of 256); the one
+// that completes the 256 tells every peer, with a single remote reduction each, that the launch's
+// results have arrived, and advances this rank's sequence counter.  Remote reductions to one
+// address are slow, hence one per launch and peer rather than one per CTA.
+__device__ __forceinline__ void gather_done(const GemvParams& q, uint32_t cta, uint32_t grid) {
+    if (q.world <= 1) return;
+    const unsigned long long share = 256u / grid + (cta < 256u % grid ? 1u : 0u);
+    __threadfence_system();                  // this CTA's stores into the peers are performed
+    if (share == 0) return;
+    const unsigned long long old = atomicAdd(q.gseq + 1, share);
+    if (((old + share) & 255ull) != 0) return;
+    __threadfence_system();
+    for (uint32_t r = 0; r < q.world; ++r)
+        if (r != q.grank)
+            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(q.peer_arrive[r]), "l"(256ull) : "memory");
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(q.gseq), "l"(256ull) : "memory");
+}
+
 // u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
 __device__ __forceinline__ void imma_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(

@@ -41,6 +41,9 @@ struct PrepArgs {
     int32_t x_dtype[kMaxGroup], vec4[kMaxGroup];
     uint32_t count, m, ng;
     int32_t use_pdl;
+    const unsigned long long* wait_arrive;   // x holds gathered results: wait for the peers first (wait_world > 1)
+    uint32_t wait_world;
+    int32_t* status;
 };
 
 // Limb records for every (block, token slot) and t = A x for every adapter, in one launch.
@@ -49,6 +52,8 @@ __global__ void __launch_bounds__(256) dense_prep_kernel(const __grid_constant__
         pdl_wait_prior_grids();
         pdl_launch_dependents();
     }
+    if (a.wait_world > 1 && !wait_gather_arrivals(a.wait_arrive, a.wait_world) && threadIdx.x == 0)
+        atomicOr(a.status, kDevErrGridWaitTimeout);
     const uint32_t nlimb = a.limb_start[a.count];
     if (blockIdx.x >= nlimb) {
         const uint32_t b = blockIdx.x - nlimb;
@@ -387,8 +392,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
             for (int ng = 0; ng < NG; ++ng) {
                 const uint32_t tok = ng * 4 + t;
                 if (tok >= q.m) continue;
-                if (rowa < q.n) q.y[(size_t)tok * q.ldy + rowa] = acc[ng][0];
-                if (rowb < q.n) q.y[(size_t)tok * q.ldy + rowb] = acc[ng][1];
+                if (rowa < q.n) store_out(q, (size_t)tok * q.ldy + rowa, acc[ng][0]);
+                if (rowb < q.n) store_out(q, (size_t)tok * q.ldy + rowb, acc[ng][1]);
             }
             DSTAMP(5);
         }
@@ -407,7 +412,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
         for (int i = 0; i < 8; ++i) out[i] = s_tl[i];
     }
 #endif
-    if (tid == 0) launch_done(p.tsync, blockIdx.x, gridDim.x);
+    if (tid == 0) {
+        gather_done(p, blockIdx.x, gridDim.x);
+        launch_done(p.tsync, blockIdx.x, gridDim.x);
+    }
     // After a failed wait some copies may still be in flight towards this CTA's shared memory:
     // wait (bounded) for the stages that were issued before leaving.
     if (s_err && warp == 8 && lane == 0) {
@@ -490,6 +498,9 @@ cudaError_t launch_dense_prep(const GemvParams* ps, uint32_t count, uint8_t* con
     a.m = ps[0].m;
     a.ng = (ps[0].m + 3) / 4;
     a.use_pdl = use_pdl;
+    a.wait_arrive = ps[0].wait_arrive;
+    a.wait_world = ps[0].wait_world;
+    a.status = ps[0].status;
     a.limb_start[0] = a.proj_start[0] = 0;
     for (uint32_t i = 0; i < count; ++i) {
         const GemvParams& p = ps[i];

@@ -55,6 +55,14 @@ struct GemvParams {
     // shared-memory offsets (bytes from the dynamic smem base)
     uint32_t off_stage, off_xs, off_sx, off_xrot, off_t;
     uint32_t use_pdl;
+    // fused all-gather (world > 1): results are also written into every peer's buffer
+    uint32_t world, grank;
+    int64_t peer_off[LQ4_MAX_PEERS];                  // bytes from an element of y to the same element in peer r
+    unsigned long long* peer_arrive[LQ4_MAX_PEERS];   // peer r's arrival counter
+    unsigned long long* gseq;                         // this rank's count of gathered launches (x 256); gseq[1] counts the CTAs of the running launch
+    // x depends on gathered results: wait for the peers' arrivals before reading it (wait_world > 1)
+    const unsigned long long* wait_arrive;            // own arrival counter; own sequence counter follows it
+    uint32_t wait_world;
     int32_t sm_count;       // SMs of the device (0: assume 148)
     uint32_t whole_tiles;   // resident kernel: every CTA gets entire tiles, no cross-CTA partial sums
 };

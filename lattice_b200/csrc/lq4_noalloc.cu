@@ -43,6 +43,7 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
         return s;
     };
     if (!a) return fail(LQ4_ERR_NULL, "args is NULL");
+    if (a->gather || a->wait_gather) return fail(LQ4_ERR_UNSUPPORTED, "lq4_linear_decode_noalloc has no fused all-gather");
     if (a->m == 0 || a->n == 0) return LQ4_OK;
     if (a->k == 0 || a->k % 32 != 0) return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32");
     if (!a->x || !a->w || !a->y) return fail(LQ4_ERR_NULL, "x, w and y must be non-NULL");

@@ -59,3 +59,68 @@ class ShardedLinear:
         parts = [torch.empty((m, s), dtype=y_local.dtype, device=y_local.device) for s in self.sizes]
         dist.all_gather(parts, y_local.contiguous(), group=self.group)
         return torch.cat(parts, dim=1)
+
+
+class _DeviceArray:
+    """Exposes a raw device address range to torch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, shape: Tuple[int, ...], owner):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": "<f4", "data": (ptr, False), "version": 2}
+        self._owner = owner
+
+
+class PeerGather:
+    """Output buffers for the all-gather that is fused into the decode kernels' epilogue.
+
+    Every rank allocates one peer buffer (``lq4_peer_buf_create``), the 64-byte handles travel over the
+    process group, and each rank maps the others' buffers.  ``full`` is this rank's ``[m, n_total]`` f32
+    output as a torch tensor: a projection writes its column range of it (``out=full[:, c0:c1]``) with
+    ``gather=self.desc`` and the kernel stores the same values into every peer's ``full``.  After
+    ``backend.gather_wait(self.desc)`` the columns written by the peers are complete here as well.
+    """
+
+    def __init__(self, m: int, n_total: int, group: Optional[dist.ProcessGroup] = None, device: Optional[int] = None):
+        L = _lib.lib()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > _lib.MAX_PEERS:
+            raise ValueError(f"at most {_lib.MAX_PEERS} ranks")
+        if device is not None:
+            torch.cuda.set_device(device)
+        self.m, self.n_total = m, n_total
+        h = C.c_void_p()
+        _lib.check(L.lq4_peer_buf_create(m * n_total * 4, C.byref(h)))
+        self._buf = h.value
+        self._opened: List[int] = []
+        own_base = L.lq4_peer_buf_base(self._buf)
+        handle = (C.c_uint8 * _lib.PEER_HANDLE_BYTES)()
+        _lib.check(L.lq4_peer_buf_export(self._buf, handle))
+        bases = [0] * self.world
+        bases[self.rank] = own_base
+        if self.world > 1:
+            handles: List[Optional[bytes]] = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                raw = (C.c_uint8 * _lib.PEER_HANDLE_BYTES).from_buffer_copy(handles[r])
+                p = C.c_void_p()
+                _lib.check(L.lq4_peer_buf_open(raw, C.byref(p)))
+                self._opened.append(p.value)
+                bases[r] = p.value
+        self.desc = _lib.GatherDesc(self.world, self.rank, (C.c_void_p * _lib.MAX_PEERS)(*bases))
+        self.full = torch.as_tensor(_DeviceArray(L.lq4_peer_buf_payload(self._buf), (m, n_total), self), device="cuda")
+
+    def close(self) -> None:
+        L = _lib.lib()
+        if dist.is_initialized() and self.world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)       # nobody unmaps while a peer may still write
+        for p in self._opened:
+            L.lq4_peer_buf_close(p)
+        self._opened = []
+        if self._buf:
+            self.full = None
+            L.lq4_peer_buf_free(self._buf)
+            self._buf = None

@@ -487,3 +487,78 @@ def test_group_sixteen_tokens(be):
     for y, c in zip(ys, cases):
         assert not np.isnan(y).any()
         assert tol_ratio(y, c["y_ref"]) <= 1.0
+
+
+# ---------------------------------------------------------------- all-gather fused into the epilogue
+def _peer_pair():
+    """Two peer buffers on this GPU standing in for two ranks' output buffers."""
+    L = _lib.lib()
+    bufs = []
+    for _ in range(2):
+        h = C.c_void_p()
+        _lib.check(L.lq4_peer_buf_create(16 * 8192 * 4, C.byref(h)))
+        bufs.append(h.value)
+    bases = [L.lq4_peer_buf_base(b) for b in bufs]
+    return bufs, bases
+
+
+def _as_tensor(ptr, shape):
+    from lattice_b200.sharded import _DeviceArray
+    return torch.as_tensor(_DeviceArray(ptr, shape, None), device="cuda")
+
+
+@pytest.mark.parametrize("m", [1, 4])
+def test_fused_all_gather_writes_every_peer_and_signals(be, m):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import GatherDesc, LoraDesc
+    L = _lib.lib()
+    bufs, bases = _peer_pair()
+    try:
+        n_total, k = 1024 + 384, 1024
+        cases = [make_case(2, m, k, 1024, 16, 32.0, extra=300), make_case(2, m, k, 384, 16, 32.0, extra=301)]
+        full = [_as_tensor(L.lq4_peer_buf_payload(b), (m, n_total)) for b in bufs]
+        for f in full:
+            f.fill_(float("nan"))
+        ctrl = [_as_tensor(bs, (64,)).view(torch.int64) for bs in bases]
+        # "rank 0" computes columns [0, 1024), "rank 1" columns [1024, 1408); each writes both buffers
+        col0 = [0, 1024]
+        keep = []
+        for r, case in enumerate(cases):
+            desc = GatherDesc(2, r, (C.c_void_p * _lib.MAX_PEERS)(*bases))
+            qw = Q4WeightBuf.from_host_payload(case["payload"], case["n"], case["k"])
+            a, b, s = case["lora"]
+            ad, bd = dev(a), dev(b)
+            lora = LoraDesc(ad.data_ptr(), bd.data_ptr(), 16, s)
+            keep += [qw, ad, bd, desc]
+            out = full[r][:, col0[r]:col0[r] + case["n"]]
+            be.linear_group([(dev(case["x"]), qw, lora), (dev(case["x"]), qw, lora)], [out, out], gather=desc) \
+                if r == 0 else be.dispatch_gemm_q4(dev(case["x"]), 0, qw, out, 0, m, case["n"], k, lora=lora,
+                                                   ldy=n_total, gather=desc)
+        # both "ranks" have launched once: each one's wait finds the other's 256 arrivals
+        for desc in (keep[3], keep[7]):
+            be.gather_wait(desc)
+        be.check_device_status()
+        want = np.concatenate([c["y_ref"] for c in cases], axis=1)
+        for f in full:
+            got = f.cpu().numpy()
+            assert not np.isnan(got).any()
+            assert tol_ratio(got, want) <= 1.0
+        assert np.array_equal(full[0].cpu().numpy().view(np.uint32), full[1].cpu().numpy().view(np.uint32))
+        # each gathered launch adds exactly 256 to the peer's arrival counter and to its own sequence counter
+        assert [int(c[0]) for c in ctrl] == [256, 256] and [int(c[1]) for c in ctrl] == [256, 256]
+        assert [int(c[2]) for c in ctrl] == [256, 256]      # the CTAs of each launch counted themselves
+        # a launch whose input depends on gathered results waits inside the kernel: all arrivals are
+        # there already, so it goes straight through and computes the same values
+        y2 = torch.full((m, cases[1]["n"]), float("nan"), device="cuda")
+        be.dispatch_gemm_q4(dev(cases[1]["x"]), 0, keep[4], y2, 0, m, cases[1]["n"], k, lora=LoraDesc(keep[5].data_ptr(), keep[6].data_ptr(), 16, cases[1]["lora"][2]),
+                            wait_gather=keep[7])
+        be.check_device_status()
+        assert tol_ratio(y2.cpu().numpy(), cases[1]["y_ref"]) <= 1.0
+        # the fused gather is a decode-kernel feature: the tensor-core path refuses it
+        big = torch.zeros((64, k), device="cuda")
+        with pytest.raises(_lib.Lq4Error):
+            be.dispatch_gemm_q4(big, 0, keep[0], full[0][:1, :1024].expand(64, 1024), 0, 64, 1024, k, gather=keep[3])
+    finally:
+        torch.cuda.synchronize()
+        for b in bufs:
+            L.lq4_peer_buf_free(b)
