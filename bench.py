@@ -236,7 +236,8 @@ def run_ours(args):
     # epilogue writes them into every rank's copy (--gather peer); or, the plain way, the local slices
     # are exchanged with ONE NCCL all-gather per set (--gather nccl).
     from lattice_b200.sharded import PeerGather
-    peer_mode = world > 1 and args.gather == "peer"
+    peer_mode = world > 1 and args.gather in ("peer", "peer-nowait")
+    peer_wait = args.gather == "peer"
     nls = [layers[0][si]["nl"] for si in range(len(SHAPES))]
     offs = [sum(nls[:si]) for si in range(len(SHAPES))]
     full_n = [n for _, n in SHAPES]
@@ -266,13 +267,13 @@ def run_ours(args):
             if key not in prepared:
                 prepared[key] = be.prepare_group([(x_of[p["k"]], p["qw"], p["lora"]) for p in projs],
                                                  [y_local[si] for si in range(len(projs))], gather=gdesc,
-                                                 wait_gather=gdesc)
+                                                 wait_gather=gdesc if peer_wait else None)
             prepared[key]()
         else:
             for si, p in enumerate(projs):
                 be.dispatch_gemm_q4(x_of[p["k"]], 0, p["qw"], y_local[si], 0, m, p["nl"], p["k"], lora=p["lora"],
-                                    ldy=y_cat.stride(0), gather=gdesc, wait_gather=gdesc if si == 0 else None)
-        if world > 1 and not peer_mode:
+                                    ldy=y_cat.stride(0), gather=gdesc, wait_gather=gdesc if si == 0 and peer_wait else None)
+        if world > 1 and args.gather == "nccl":
             dist.all_gather_into_tensor(y_full, y_cat)
         # peer mode: every set's kernel waits itself for the arrivals of the sets before it (as a layer
         # that consumes gathered activations does); the last set of a step is waited for in step()
@@ -298,7 +299,7 @@ def run_ours(args):
     def step():
         for projs in layers:
             run_set(projs, xs)
-        if peer_mode:
+        if peer_mode and peer_wait:
             be.gather_wait(gdesc)                  # stream-ordered: the last set's peer columns have arrived
 
     # pinned host buffers for the end-to-end variant
@@ -325,7 +326,7 @@ def run_ours(args):
     graph_info = {"mode": "eager"}
 
     def make_graphed(fn):
-        if args.eager or (world > 1 and not peer_mode):
+        if args.eager or (world > 1 and args.gather == "nccl"):
             # with NCCL collectives inside the step, capture is left out: a captured all-gather did
             # not complete on this pool, so such steps are timed as plain calls
             if world > 1:
@@ -602,9 +603,10 @@ def main():
     ap.add_argument("--launch", default="grouped", choices=["grouped", "per-projection"],
                     help="grouped: one persistent launch per set of four projections (lq4_linear_group); "
                          "per-projection: one lq4_linear call each")
-    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "peer-nowait", "none"],
                     help="several GPUs: peer = all-gather fused into the kernel epilogue (stores into every "
-                         "rank's buffer over NVLink); nccl = one NCCL all-gather per set")
+                         "rank's buffer over NVLink); nccl = one NCCL all-gather per set; peer-nowait and none are "
+                         "diagnostics (no waiting for the peers / no exchange at all): their values are not results")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set: three launches of one case, for profiling")

@@ -473,6 +473,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 }
             }
 
+            LQ4_STAMP(6);
             // epilogue: LoRA term (the quad splits the rank), then quad thread t stores token t
             if (q.rank) {
                 if (!t_loaded) gather_t();
@@ -515,6 +516,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 if (rowa < q.n) store_out(q, (size_t)mt * q.ldy + rowa, v[mt][0]);
                 if (rowb < q.n) store_out(q, (size_t)mt * q.ldy + rowb, v[mt][1]);
             }
+            LQ4_STAMP(7);
         }
         if (!ok) {
             if (lane == 0) atomicOr(p.status, kDevErrBarrierTimeout);
@@ -528,12 +530,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
 #ifdef LQ4_TIMELINE
     if (tid == 0) {
         stamp(5);
-        // experiment builds only: y of problem 0 needs 4 KB of spare bytes after its n outputs
+        // experiment builds only: y of problem 0 needs 10 KB of spare bytes after its n outputs
         unsigned long long* out = reinterpret_cast<unsigned long long*>(p.y + p.n);
         if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)
             for (int i = 0; i < 6; ++i) out[(blockIdx.x ? 8 : 0) + i] = s_tl[i];
-        out[16 + 2 * blockIdx.x] = s_tl[0];
-        out[17 + 2 * blockIdx.x] = s_tl[5];
+        for (int i = 0; i < 8; ++i) out[16 + 8 * blockIdx.x + i] = s_tl[i];
     }
 #endif
     if (tid == 0) {

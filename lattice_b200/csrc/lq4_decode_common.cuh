@@ -29,13 +29,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
 
 // Cross-CTA messages are 8-byte {value, tag} pairs written with one store: the tag arrives with
 // the value, so neither side needs a fence (a gpu-scope fence here would wait for the hundreds of
-// kilobytes of weight loads the SM has in flight).  The tag is the launch generation.
+// kilobytes of weight loads the SM has in flight).  The tag identifies the launch.  Both sides
+// use relaxed gpu-scope accesses, which are served by L2: a polling load must never be answered
+// from a stale L1 line.
 __device__ __forceinline__ void msg_store(uint2* p, float v, uint32_t tag) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
 }
 __device__ __forceinline__ uint2 msg_load(const uint2* p) {
     uint2 r;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
     return r;
 }
 // Launch tags.  Every launch adds exactly 256 to a 64-bit counter: CTA c adds its share of 256
@@ -70,7 +72,10 @@ __device__ __forceinline__ void store_out(const GemvParams& q, size_t idx, float
 __device__ __forceinline__ void gather_done(const GemvParams& q, uint32_t cta, uint32_t grid) {
     if (q.world <= 1) return;
     const unsigned long long share = 256u / grid + (cta < 256u % grid ? 1u : 0u);
-    __threadfence_system();                  // this CTA's stores into the peers are performed
+    // Release chain: this CTA's stores (after the CTA barrier) -> gpu-scope fence + add on the local
+    // counter -> observed by the launch's last CTA -> its system-scope fence + remote reduction ->
+    // the peer's system-scope acquire of the arrival counter.
+    __threadfence();
     if (share == 0) return;
     const unsigned long long old = atomicAdd(q.gseq + 1, share);
     if (((old + share) & 255ull) != 0) return;
