@@ -1,24 +1,33 @@
-// Resident decode kernel (m <= 4): y[m, n] = x[m, k] * Wq4[n, k]^T (+ LoRA) (+ rotation of x).
+// Resident decode kernel: y[m, n] = x[m, k] * Wq4[n, k]^T (+ LoRA) (+ rotation of x) for one token
+// (up to four through the allocation-free entry point), and for groups of such projections in
+// one launch.
 //
 // HBM-bound: the packed weights are read once, everything else is small.
 //  * One persistent CTA per SM.  A producer warp streams weight tiles with TMA
 //    (cp.async.bulk.tensor.2d, one instruction per stage) into a shared-memory ring;
-//    completion is counted on mbarriers.  A "big" stage is 128 rows x 20 blocks (51,200 B),
-//    a "small" one 128 rows x 4 blocks; rows stay densely packed, and 100- and 20-word row
-//    strides keep every consumer load free of bank conflicts.
+//    completion is counted on mbarriers.  A stage is 128 rows x 20, 12 or 4 blocks (51,200 B at
+//    most); rows stay densely packed, and the 100-, 60- and 20-word row strides keep every
+//    consumer load free of bank conflicts.
 //  * Eight consumer warps own 16 rows each.  Within a group of four Q4 blocks, the four
-//    threads of an MMA quad take one block each: the 16 k-slots of every warp MMA then hold
-//    four k-values of four different blocks, and the B operand is zero outside the column
-//    pair (hi limb, lo limb) that belongs to the thread's block.  After eight MMAs each
-//    thread holds the full 32-element dot products of its own block for two rows, so the
-//    per-block scale/bias step (f16 -> f32 conversions, three FMAs per row) is done once per
-//    four blocks per thread instead of once per block by every thread.
-//  * The activation row(s) are converted once per CTA into f16 hi/lo limbs kept in shared
-//    memory (optionally after the randomized Hadamard rotation, also done in shared memory).
-//  * Work is split stream-K style in units of 4 blocks x 128 rows; tiles shared by several
-//    CTAs are finished by the last arriver, which adds the partials in CTA order.
-//  * LoRA: each CTA projects its own k slice onto A, the partials are exchanged through
-//    global memory (bounded wait) and s * B * t is added in the tile epilogue.
+//    threads of an MMA quad take one block each: the 32 k-slots of a u8 x s8 warp MMA (m16n8k32)
+//    hold eight codes of each of the four blocks, and the B operand is zero outside the column
+//    pair (limb 0, limb 1) that belongs to the thread's block.  After four MMAs each thread holds
+//    the exact integer dot products of its own block for two rows, so the per-block scale/bias
+//    step is done once per four blocks per thread.
+//  * The activation row is converted once per CTA into two int8 limbs with a per-block f32 scale
+//    kept in shared memory (optionally after the randomized Hadamard rotation, also done in the
+//    CTA); only the k range(s) the CTA touches are converted.
+//  * Work is split stream-K style in units of 4 blocks x 128 rows (or in whole tiles when that
+//    keeps the SMs busy).  The CTA that owns a tile's first k part finishes the tile: the others
+//    publish their partial sums as 8-byte {value, launch tag} messages and the finisher adds them
+//    in CTA order (bounded wait).  No fences, no atomics with a returned value on the way.
+//  * In a grouped launch every problem gets a contiguous share of the CTAs in proportion to its
+//    cost; a CTA works on one problem only.
+//  * LoRA: once the ring is full for the first time, the producer warps compute the projection
+//    t = A x (work items of one dot-product piece each, spread over all CTAs) and publish it as
+//    tagged messages; finishers gather t into shared memory and add s * B * t in the epilogue.
+//  * With a fused all-gather the epilogue also stores into every peer GPU's output buffer and
+//    the launch's last CTA signals the peers' arrival counters.
 #include <cuda.h>
 
 #include <mutex>
@@ -53,6 +62,67 @@ __device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT
     if (j == 0) sx[(size_t)blk * MT + mp] = make_float2(l.scale, sum);
 }
 
+// Randomized Hadamard transform of one activation row of K = 256 * R elements by the 256 consumer
+// threads: x'[i] = (1 / sqrt(K)) * sum_j H[i][j] * signs[j] * x[j].  The log2(K) butterfly levels
+// are independent of one another, so they are taken in the order that needs the least traffic:
+// thread (warp w, lane l) first holds elements l + 32 w + 256 r and does the levels of the r bits
+// in registers and those of the lane bits with shuffles; one trip through shared memory regroups
+// the row so that the three warp bits sit in registers for the last three levels.
+template <int R>
+__device__ __forceinline__ void fwht_row_fast(const void* x, int x_dtype, const float* signs, float* xrot, uint32_t x_off,
+                                              int ctid) {
+    const uint32_t lane = ctid & 31, w = ctid >> 5, K = 256u * R;
+    float v[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const uint32_t i = lane + 32 * w + 256 * r;
+        v[r] = load_act(x, x_dtype, (size_t)x_off + i) * signs[i];
+    }
+#pragma unroll
+    for (int h = 1; h < R; h <<= 1) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (r & h) continue;
+            const float a = v[r], b = v[r + h];
+            v[r] = a + b;
+            v[r + h] = a - b;
+        }
+    }
+#pragma unroll
+    for (int mask = 1; mask < 32; mask <<= 1) {
+        const bool upper = (lane & mask) != 0;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float o = __shfl_xor_sync(kFull, v[r], mask);
+            v[r] = upper ? o - v[r] : v[r] + o;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) xrot[lane + 32 * w + 256 * r] = v[r];
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+    // regroup: register q + 8 s holds element lane + 32 q + 256 (w + 8 s)
+#pragma unroll
+    for (int s = 0; s < R / 8; ++s)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q + 8 * s] = xrot[lane + 32 * q + 256 * (w + 8 * s)];
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (r & h) continue;
+            const float a = v[r], b = v[r + h];
+            v[r] = a + b;
+            v[r + h] = a - b;
+        }
+    }
+    const float sc = 1.0f / sqrtf((float)K);
+#pragma unroll
+    for (int s = 0; s < R / 8; ++s)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) xrot[lane + 32 * q + 256 * (w + 8 * s)] = v[q + 8 * s] * sc;
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+
 // Prologue of the 256 consumer threads: rotation, LoRA partial projection, activation limbs.
 template <int MT>
 __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, uint64_t r0, uint64_t r1) {
@@ -61,23 +131,36 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, ui
     const bool rot = p.signs != nullptr;
 
     if (rot) {
-        for (uint32_t i = ctid; i < M * K; i += kConsumerThreads)
-            xrot[i] = __fmul_rn(load_act(p.x, p.x_dtype, i), p.signs[i % K]);
-        named_bar_sync(kBarConsumers, kConsumerThreads);
-        const uint32_t half = K / 2;
-        for (uint32_t h = 1; h < K; h <<= 1) {
-            for (uint32_t bi = ctid; bi < M * half; bi += kConsumerThreads) {
-                const uint32_t row = bi / half, bb = bi - row * half;
-                const uint32_t j = row * K + (bb / h) * 2 * h + (bb % h);
-                const float a = xrot[j], b = xrot[j + h];
-                xrot[j] = __fadd_rn(a, b);
-                xrot[j + h] = __fsub_rn(a, b);
+        const uint32_t R = K / kConsumerThreads;          // elements per thread in the fast transform
+        if (R == 8 || R == 16 || R == 32 || R == 64) {
+            for (uint32_t row = 0; row < M; ++row) {
+                switch (R) {
+                    case 8: fwht_row_fast<8>(p.x, p.x_dtype, p.signs, xrot + (size_t)row * K, row * K, ctid); break;
+                    case 16: fwht_row_fast<16>(p.x, p.x_dtype, p.signs, xrot + (size_t)row * K, row * K, ctid); break;
+                    case 32: fwht_row_fast<32>(p.x, p.x_dtype, p.signs, xrot + (size_t)row * K, row * K, ctid); break;
+                    default: fwht_row_fast<64>(p.x, p.x_dtype, p.signs, xrot + (size_t)row * K, row * K, ctid); break;
+                }
             }
+        } else {
+            // short rows: one butterfly level per pass over shared memory
+            for (uint32_t i = ctid; i < M * K; i += kConsumerThreads)
+                xrot[i] = __fmul_rn(load_act(p.x, p.x_dtype, i), p.signs[i % K]);
+            named_bar_sync(kBarConsumers, kConsumerThreads);
+            const uint32_t half = K / 2;
+            for (uint32_t h = 1; h < K; h <<= 1) {
+                for (uint32_t bi = ctid; bi < M * half; bi += kConsumerThreads) {
+                    const uint32_t row = bi / half, bb = bi - row * half;
+                    const uint32_t j = row * K + (bb / h) * 2 * h + (bb % h);
+                    const float a = xrot[j], b = xrot[j + h];
+                    xrot[j] = __fadd_rn(a, b);
+                    xrot[j + h] = __fsub_rn(a, b);
+                }
+                named_bar_sync(kBarConsumers, kConsumerThreads);
+            }
+            const float sc = __fdiv_rn(1.0f, __fsqrt_rn((float)K));
+            for (uint32_t i = ctid; i < M * K; i += kConsumerThreads) xrot[i] = __fmul_rn(xrot[i], sc);
             named_bar_sync(kBarConsumers, kConsumerThreads);
         }
-        const float sc = __fdiv_rn(1.0f, __fsqrt_rn((float)K));
-        for (uint32_t i = ctid; i < M * K; i += kConsumerThreads) xrot[i] = __fmul_rn(xrot[i], sc);
-        named_bar_sync(kBarConsumers, kConsumerThreads);
     }
 
     // limbs: [block][token][limb 0, limb 1][32 B]; per-block info {scale, sum}: [block][token]
@@ -136,14 +219,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t NST = p.nstages;
-#ifdef LQ4_TIMELINE
-    __shared__ unsigned long long s_tl[8];
-    auto stamp = [&](int i) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); s_tl[i] = t; };
-    if (tid == 0) stamp(0);
-#define LQ4_STAMP(i) do { if (tid == 0) stamp(i); } while (0)
-#else
-#define LQ4_STAMP(i) do {} while (0)
-#endif
     if (tid == 0) {
         for (uint32_t s = 0; s < NST; ++s) {
             mbar_init(&full[s], 1);
@@ -260,7 +335,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
             atomicOr(p.status, kDevErrGridWaitTimeout);
         // a message written by an earlier launch never carries this launch's tag
         const uint32_t tag = launch_tag(p.tsync);
-        LQ4_STAMP(1);
 
         // A lane supplies B-operand registers only for the column pair (limb 0, limb 1) of its own
         // block; every other lane reads a block of zeros, so that its columns contribute nothing.
@@ -306,7 +380,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
             t_loaded = true;
         };
         decode_prologue<MT>(q, smem, tid, r0, r1);
-        LQ4_STAMP(2);
         for (uint64_t pos = r0; pos < r1 && ok;) {
             const uint32_t tile = (uint32_t)(pos / q.kg);
             const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
@@ -331,7 +404,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
                 const uint32_t s = it % NST;
                 if (!mbar_wait(&full[s], (it / NST) & 1u)) { ok = false; break; }
-                if (it == 0) LQ4_STAMP(3);
                 // by now the projections are published; fetching them here keeps the round trip off
                 // the end of the tile (the ring keeps the memory pipe busy meanwhile)
                 if (it == 6 && q.rank && !t_loaded) gather_t();
@@ -389,7 +461,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 gs += ngr;
             }
             if (!ok) break;
-            LQ4_STAMP(4);
 
             // each thread of a quad covered blocks = t (mod 4): add the four
             float v[MT][2];
@@ -473,7 +544,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 }
             }
 
-            LQ4_STAMP(6);
             // epilogue: LoRA term (the quad splits the rank), then quad thread t stores token t
             if (q.rank) {
                 if (!t_loaded) gather_t();
@@ -516,7 +586,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 if (rowa < q.n) store_out(q, (size_t)mt * q.ldy + rowa, v[mt][0]);
                 if (rowb < q.n) store_out(q, (size_t)mt * q.ldy + rowb, v[mt][1]);
             }
-            LQ4_STAMP(7);
         }
         if (!ok) {
             if (lane == 0) atomicOr(p.status, kDevErrBarrierTimeout);
@@ -527,16 +596,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
     // After a failed wait some TMA loads may still be in flight towards this CTA's shared
     // memory: wait (bounded) for the stages that were issued before leaving.
     __syncthreads();
-#ifdef LQ4_TIMELINE
-    if (tid == 0) {
-        stamp(5);
-        // experiment builds only: y of problem 0 needs 10 KB of spare bytes after its n outputs
-        unsigned long long* out = reinterpret_cast<unsigned long long*>(p.y + p.n);
-        if (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)
-            for (int i = 0; i < 6; ++i) out[(blockIdx.x ? 8 : 0) + i] = s_tl[i];
-        for (int i = 0; i < 8; ++i) out[16 + 8 * blockIdx.x + i] = s_tl[i];
-    }
-#endif
     if (tid == 0) {
         gather_done(p, blockIdx.x, gridDim.x);
         launch_done(p.tsync, blockIdx.x, gridDim.x);

@@ -107,16 +107,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
     const uint32_t count = NP == 1 ? 1u : ga.count;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t NST = p.nstages;
-#ifdef LQ4_TIMELINE
-    __shared__ unsigned long long s_tl[16];
-    auto stamp = [&](int i) { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); s_tl[i] = t; };
-    if (tid == 0) { for (int i = 0; i < 16; ++i) s_tl[i] = 0; stamp(0); }
-#define DSTAMP(i) do { if (tid == 0) stamp(i); } while (0)
-#define DSTAMP_ONCE(i) do { if (tid == 0 && s_tl[i] == 0) stamp(i); } while (0)
-#else
-#define DSTAMP(i) do {} while (0)
-#define DSTAMP_ONCE(i) do {} while (0)
-#endif
     if (tid == 0) {
         for (uint32_t s = 0; s < NST; ++s) {
             mbar_init(&full[s], 1);
@@ -197,7 +187,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
         // ------------------------------ consumers ------------------------------
         const int g = lane >> 2, t = lane & 3;
         if (p.use_pdl) pdl_wait_prior_grids();
-        DSTAMP(1);
         const uint32_t tag = launch_tag(p.tsync);
         uint32_t it = 0;
         bool ok = true;
@@ -225,7 +214,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
                 const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
                 const uint32_t s = it % NST;
                 if (!mbar_wait(&full[s], (it / NST) & 1u)) { ok = false; break; }
-                DSTAMP_ONCE(2);
                 const uint8_t* st = smem + p.off_stage + (size_t)s * kSlot;
                 const uint8_t* row0 = st + (warp * 16 + g) * rs;
                 const uint8_t* row1 = row0 + 8 * rs;
@@ -266,8 +254,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
                 gs += ngr;
             }
             if (!ok) break;
-            DSTAMP_ONCE(3);
-            DSTAMP(7);
 
             // thread (g, t) holds rows g and g+8 of the warp's 16 for tokens 4 ng + t
             const bool complete = (g0 == 0 && g1 == q.kg);
@@ -328,7 +314,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
                 if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
             }
 
-            DSTAMP(4);
             // epilogue: LoRA term for the thread's two rows and NG tokens, then the stores
             const uint32_t rowa = tile * kGemvTileRows + warp * 16 + g, rowb = rowa + 8;
             if (q.rank) {
@@ -395,7 +380,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
                 if (rowa < q.n) store_out(q, (size_t)tok * q.ldy + rowa, acc[ng][0]);
                 if (rowb < q.n) store_out(q, (size_t)tok * q.ldy + rowb, acc[ng][1]);
             }
-            DSTAMP(5);
         }
         if (!ok) {
             if (lane == 0) atomicOr(p.status, kDevErrBarrierTimeout);
@@ -404,14 +388,6 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
     }
 
     __syncthreads();
-#ifdef LQ4_TIMELINE
-    if (tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
-        stamp(6);
-        // experiment builds only: y (token 0 row) needs 128 spare bytes after its n outputs
-        unsigned long long* out = reinterpret_cast<unsigned long long*>(p.y + p.n) + (blockIdx.x ? 8 : 0);
-        for (int i = 0; i < 8; ++i) out[i] = s_tl[i];
-    }
-#endif
     if (tid == 0) {
         gather_done(p, blockIdx.x, gridDim.x);
         launch_done(p.tsync, blockIdx.x, gridDim.x);

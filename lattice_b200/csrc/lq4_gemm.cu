@@ -5,14 +5,18 @@
 // are weight rows and the columns are tokens: the epilogue then stores 32 consecutive output
 // features per warp instruction (coalesced along n).
 //
-//   CTA tile      128 weight rows x TT tokens (TT = 256 with f16-exact activations, 128 when the
-//                 activations are carried as two f16 limbs), K loop in blocks of 64
+//   CTA tile      256 weight rows (two 128-row sub-tiles, one TMEM accumulator each) x TT tokens
+//                 (TT = 256 with f16-exact activations, 128 when the activations are carried as two
+//                 f16 limbs); both sub-tiles multiply the same activation tile, which is therefore
+//                 loaded once per 256 weight rows; K loop in blocks of 64, three 64 KB stages
 //   warp 0        TMA producer: activation tiles (and the dense LoRA tiles) -> shared memory
 //   warp 1        TMEM allocation, then one elected lane issues tcgen05.mma / tcgen05.commit
-//   warps 2..5    dequantizers: read 2 Q4 blocks per weight row from global memory, convert
-//                 in registers (magic-number int4 -> f16, one HFMA2 per pair for q*d+b) and
-//                 write the 128 x 64 f16 tile in the 128-byte-swizzled K-major layout the MMA reads
-//   warps 6..9    epilogue: tcgen05.ld the finished accumulator, store f32 to Y
+//   warps 2..5    dequantizers of sub-tile 0, warps 6..9 of sub-tile 1: read the raw Q4 blocks of
+//                 their rows from a small shared-memory ring, convert in registers (magic-number
+//                 int4 -> f16, one HFMA2 per pair for q*d+b) and write the 128 x 64 f16 tile in the
+//                 128-byte-swizzled K-major layout the MMA reads
+//   warps 10..13  epilogue: tcgen05.ld the finished accumulators, store f32 to Y
+//   warp 14       TMA producer of the raw Q4 ring (128 rows x 4 blocks per stage)
 //
 // Operands are f16 with f32 accumulation.  Dequantized weights are rounded once to f16; the
 // activations are exact in f16 when they come as bf16, and are split into hi + lo f16 limbs

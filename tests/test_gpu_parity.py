@@ -562,3 +562,12 @@ def test_fused_all_gather_writes_every_peer_and_signals(be, m):
         torch.cuda.synchronize()
         for b in bufs:
             L.lq4_peer_buf_free(b)
+
+
+@pytest.mark.parametrize("k", [256, 2048, 4096, 8192, 16384])
+def test_rotation_in_the_decode_prologue_all_row_lengths(be, k):
+    # k < 2048 takes the level-by-level transform, longer rows the register/shuffle one
+    case = make_case(5, 1, k, 384, quarot=True, extra=400 + k // 256)
+    y = run_case(be, case, path=_lib.PATH_GEMV_MMA)
+    assert not np.isnan(y).any()
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
