@@ -39,8 +39,9 @@ SHAPES = [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)]      # (k, n
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per projection (decode kernel + its LoRA projection
 # kernel), averaged over the four shapes of a layer, from the ncu capture summarised in profiles/
-# dram bytes per decode launch from the ncu captures under profiles/ (None: not captured)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"per-projection": 33.89e6, "grouped": None}
+# dram bytes per decode launch from the ncu launch list in profiles/decode_kernel_large_layer_set.md
+# (None: not captured for the current kernel)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"per-projection": None, "grouped": 138.64e6}
 
 
 def algorithmic_bytes(m, n, k, rank):
