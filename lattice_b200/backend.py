@@ -219,8 +219,41 @@ class CudaQ4Backend:
         self.dispatch_gemm_q4(x, 0, qw, y, 0, m, n, k, **kw)
 
     # ---- LoRA ------------------------------------------------------------------
-    def load_lora_adapter(self, layers: List[LoraLayerData], scale: float, quarot_seed: Optional[int] = None) -> None:
-        """Copies the adapter to the device after the reference's load-time checks."""
+    # Which side of a projection the residual-stream rotation was absorbed on
+    # (crates/inference/src/quant/quarot/plan.rs:935-941, tests at :1483-1514).
+    QUAROT_INPUT_SIDE = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", "in_proj_qkv", "in_proj_z",
+                         "in_proj_b", "in_proj_a")
+    QUAROT_OUTPUT_SIDE = ("o_proj", "down_proj", "out_proj")
+
+    def _rotate_adapter_layer(self, layer: LoraLayerData, seed: int, hidden_dim: int):
+        """Rotation correction of one adapter projection for a QuaRot base, on the device
+        (crates/inference/src/quant/quarot/lora.rs:32-58,150-216): input side ``A <- A R^T`` (R applied to
+        every row of A), output side ``B <- R B`` (R applied to every column of B).  Modules outside the
+        plan are refused, as in the reference."""
+        a = np.ascontiguousarray(layer.a, dtype=np.float32).reshape(layer.rank, layer.d_in)
+        b = np.ascontiguousarray(layer.b, dtype=np.float32).reshape(layer.d_out, layer.rank)
+        if layer.module in self.QUAROT_INPUT_SIDE:
+            if layer.d_in != hidden_dim:
+                raise Lq4Error(_lib.ERR_SHAPE, f"rotate_adapter_for_quarot: layer {layer.layer_idx} module "
+                                               f"'{layer.module}' has d_in={layer.d_in} but hidden_dim={hidden_dim}")
+            signs = self.rot_signs(seed, hidden_dim)
+            a = self.hadamard_rows(torch.from_numpy(a).cuda(), signs).cpu().numpy()
+        elif layer.module in self.QUAROT_OUTPUT_SIDE:
+            if layer.d_out != hidden_dim:
+                raise Lq4Error(_lib.ERR_SHAPE, f"rotate_adapter_for_quarot: layer {layer.layer_idx} module "
+                                               f"'{layer.module}' has d_out={layer.d_out} but hidden_dim={hidden_dim}")
+            signs = self.rot_signs(seed, hidden_dim)
+            bt = torch.from_numpy(np.ascontiguousarray(b.T)).cuda()          # columns of B as rows
+            b = np.ascontiguousarray(self.hadamard_rows(bt, signs).cpu().numpy().T)
+        else:
+            raise Lq4Error(_lib.ERR_LORA, f"rotate_adapter_for_quarot: layer {layer.layer_idx} targets module "
+                                          f"'{layer.module}' which is not in the rotation plan")
+        return a, b
+
+    def load_lora_adapter(self, layers: List[LoraLayerData], scale: float, quarot_seed: Optional[int] = None,
+                          quarot_hidden_dim: Optional[int] = None) -> None:
+        """Copies the adapter to the device after the reference's load-time checks.  With ``quarot_seed`` (and
+        the hidden dimension the base was rotated in) the factors are first corrected for the rotated base."""
         if self.lora is not None:
             raise Lq4Error(_lib.ERR_LORA, "LoRA adapter already loaded; call unload_lora_adapter first")
         if len(layers) == 0:
@@ -228,8 +261,8 @@ class CudaQ4Backend:
         if not math.isfinite(scale):
             raise Lq4Error(_lib.ERR_LORA, f"load_lora_adapter: scale must be finite, got {scale}")
         if quarot_seed is not None:
-            raise Lq4Error(_lib.ERR_UNSUPPORTED, "adapter rotation for a QuaRot base is not built yet: "
-                                                 "rotate A/B before loading")
+            if quarot_hidden_dim is None or quarot_hidden_dim <= 0 or quarot_hidden_dim & (quarot_hidden_dim - 1):
+                raise Lq4Error(_lib.ERR_ROT, "quarot_hidden_dim must be a power of two")
         projections: List[Dict[str, _LoraProjection]] = [dict() for _ in range(self.num_hidden_layers)]
         max_rank = 0
         try:
@@ -254,8 +287,15 @@ class CudaQ4Backend:
                 if layer.module in projections[layer.layer_idx]:
                     raise Lq4Error(_lib.ERR_LORA, f"load_lora_adapter: duplicate projection for layer "
                                                   f"{layer.layer_idx} module '{layer.module}'")
-                a = np.ascontiguousarray(layer.a, dtype=np.float32).reshape(-1)
-                b = np.ascontiguousarray(layer.b, dtype=np.float32).reshape(-1)
+                if quarot_seed is not None:
+                    if np.asarray(layer.a).size != layer.rank * layer.d_in or np.asarray(layer.b).size != layer.d_out * layer.rank:
+                        raise Lq4Error(_lib.ERR_SHAPE, f"load_lora_adapter: layer {layer.layer_idx} module "
+                                                       f"'{layer.module}' factor sizes do not match its shape")
+                    a, b = self._rotate_adapter_layer(layer, quarot_seed, quarot_hidden_dim)
+                    a, b = a.reshape(-1), b.reshape(-1)
+                else:
+                    a = np.ascontiguousarray(layer.a, dtype=np.float32).reshape(-1)
+                    b = np.ascontiguousarray(layer.b, dtype=np.float32).reshape(-1)
                 h = C.c_void_p()
                 # A/B length, overflow and u32 checks happen in the library
                 check(_lib.lib().lq4_lora_upload(a.ctypes.data_as(C.c_void_p), a.size, b.ctypes.data_as(C.c_void_p),

@@ -571,3 +571,55 @@ def test_rotation_in_the_decode_prologue_all_row_lengths(be, k):
     y = run_case(be, case, path=_lib.PATH_GEMV_MMA)
     assert not np.isnan(y).any()
     assert tol_ratio(y, case["y_ref"]) <= 1.0
+
+
+def test_adapter_rotation_for_a_quarot_base_at_load_time():
+    """Input side A <- A R^T, output side B <- R B, unknown modules refused
+    (crates/inference/src/quant/quarot/lora.rs:150-216 and its tests)."""
+    from lattice_b200 import CudaQ4Backend, LoraLayerData
+    hidden, inter, rank, seed = 256, 512, 4, 0xC0FFEE
+    rng = np.random.default_rng(5)
+    a_q = rng.standard_normal((rank, hidden), dtype=np.float32) * 0.1
+    b_q = rng.standard_normal((inter, rank), dtype=np.float32) * 0.1
+    a_o = rng.standard_normal((rank, inter), dtype=np.float32) * 0.1
+    b_o = rng.standard_normal((hidden, rank), dtype=np.float32) * 0.1
+    be2 = CudaQ4Backend(0, num_hidden_layers=1)
+    try:
+        be2.load_lora_adapter([LoraLayerData(0, "gate_proj", a_q, b_q, rank, hidden, inter),
+                               LoraLayerData(0, "down_proj", a_o, b_o, rank, inter, hidden)], scale=2.0,
+                              quarot_seed=seed, quarot_hidden_dim=hidden)
+        signs = oracle.signs_from_seed(seed, hidden)
+        h = rng.standard_normal((1, hidden), dtype=np.float32)
+        # input side: the delta on the rotated activation R h equals the oracle's with its rotated A,
+        # and equals the unrotated delta on h (B A R^T R h = B A h)
+        rh = oracle.rh_apply(signs, h.reshape(-1)).reshape(1, hidden)
+        y = torch.zeros((1, inter), device="cuda")
+        be2.dispatch_lora_if_active(dev(rh), 0, y, 0, 0, "gate_proj")
+        a_rot = oracle.absorb_rotation(a_q, rank, hidden, signs, "input")
+        want = np.zeros(inter, np.float32)
+        assert oracle.apply_lora(a_rot, b_q, rank, hidden, inter, 2.0, rh, want)
+        assert np.max(np.abs(y.cpu().numpy().reshape(-1) - want)) <= 1e-5 * max(1.0, float(np.max(np.abs(want))))
+        plain = np.zeros(inter, np.float32)
+        assert oracle.apply_lora(a_q, b_q, rank, hidden, inter, 2.0, h, plain)
+        assert np.max(np.abs(want - plain)) <= 1e-4
+        # output side: the delta comes out in the rotated basis, R (B A x)
+        xi = rng.standard_normal((1, inter), dtype=np.float32)
+        y2 = torch.zeros((1, hidden), device="cuda")
+        be2.dispatch_lora_if_active(dev(xi), 0, y2, 0, 0, "down_proj")
+        b_rot = oracle.absorb_rotation(b_o, hidden, rank, signs, "output")
+        want2 = np.zeros(hidden, np.float32)
+        assert oracle.apply_lora(a_o, b_rot, rank, inter, hidden, 2.0, xi, want2)
+        assert np.max(np.abs(y2.cpu().numpy().reshape(-1) - want2)) <= 1e-5 * max(1.0, float(np.max(np.abs(want2))))
+        plain2 = np.zeros(hidden, np.float32)
+        assert oracle.apply_lora(a_o, b_o, rank, inter, hidden, 2.0, xi, plain2)
+        assert np.max(np.abs(want2 - oracle.rh_apply(signs, plain2))) <= 1e-4
+        be2.unload_lora_adapter()
+        with pytest.raises(_lib.Lq4Error):       # not in the rotation plan
+            be2.load_lora_adapter([LoraLayerData(0, "conv1d", a_q, b_q, rank, hidden, inter)], 2.0,
+                                  quarot_seed=seed, quarot_hidden_dim=hidden)
+        with pytest.raises(_lib.Lq4Error):       # input-side module whose d_in is not the hidden dimension
+            be2.load_lora_adapter([LoraLayerData(0, "q_proj", a_o, b_o, rank, inter, hidden)], 2.0,
+                                  quarot_seed=seed, quarot_hidden_dim=hidden)
+        assert not be2.has_lora_adapter()
+    finally:
+        be2.close()
