@@ -399,10 +399,10 @@ def run_ours(args):
     e2e_value = per_step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
     hbm_peak, tc_peak, tc_sust, which = measured_peaks()
     n_lin = args.layers * (1 if grouped else len(SHAPES))
-    # the step's launches are the decode kernel (one per set when grouped, else one per projection)
-    # with the small adapter-projection kernel overlapped in front of each, so the average launch
-    # duration is the event time over the decode launches, and algorithmic bytes per launch divide
-    # the same way; per GPU each rank streams 1/world of the bytes
+    # the step's launches are the decode kernel, one per set when grouped, else one per projection (at
+    # M = 1 nothing else runs; at M > 1 a small preparation kernel is chained in front of each), so the
+    # average launch duration is the event time over the decode launches, and algorithmic bytes per
+    # launch divide the same way; per GPU each rank streams 1/world of the bytes
     avg_launch_us = ms * 1e3 / (args.steps * n_lin)
     achieved = (per_step_bytes / world) * args.steps / (ms * 1e-3) / 1e9
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -415,7 +415,9 @@ def run_ours(args):
             "gpu_launches": int(launches), "launch_mode": graph_info["mode"],
             "roofline": {"bound": "hbm", "kernel": ("decode_kernel<1, 8>: one persistent launch per set of four projections" if grouped
                                                  else "decode_kernel<1, 1>: one launch per projection") +
-                                                "; the adapter projection kernel before it overlaps through PDL",
+                                                ", LoRA projection inside the same launch" if m == 1 else
+                                                "dense_kernel + dense_prep_kernel (activation limbs, LoRA projection) per " +
+                                                ("set" if grouped else "projection"),
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
                          "avg_launch_us": avg_launch_us, "algorithmic_bytes_per_launch": per_step_bytes / world / n_lin,

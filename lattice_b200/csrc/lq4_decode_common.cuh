@@ -28,10 +28,9 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
 }
 
 // Cross-CTA messages are 8-byte {value, tag} pairs written with one store: the tag arrives with
-// the value, so neither side needs a fence (a gpu-scope fence here would wait for the hundreds of
-// kilobytes of weight loads the SM has in flight).  The tag identifies the launch.  Both sides
-// use relaxed gpu-scope accesses, which are served by L2: a polling load must never be answered
-// from a stale L1 line.
+// the value, so neither side needs a fence (a gpu-scope fence in mid-stream would wait for the
+// hundreds of kilobytes of weight loads the SM has in flight).  The tag identifies the launch.
+// Both sides use relaxed gpu-scope accesses, which are served by L2.
 __device__ __forceinline__ void msg_store(uint2* p, float v, uint32_t tag) {
     asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
 }
@@ -84,6 +83,7 @@ __device__ __forceinline__ void gather_done(const GemvParams& q, uint32_t cta, u
         if (r != q.grank)
             asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(q.peer_arrive[r]), "l"(256ull) : "memory");
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(q.gseq), "l"(256ull) : "memory");
+    __threadfence_system();                  // this CTA is about to go quiet: push the signals out now
 }
 
 // u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
