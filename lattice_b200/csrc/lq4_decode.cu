@@ -506,42 +506,48 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 // range, when the contributors (who met the tile at the START of theirs) are long done.
                 // The wait below is bounded and normally falls through at once.
                 const uint32_t c_last = cta0 + owner_of((uint64_t)(tile + 1) * q.kg - 1, total, G);
-                // lanes poll different CTAs' messages (all 16 rows each), a fixed shuffle tree adds
-                // them: the sum does not depend on arrival order
-                float part[16 * MT];
-#pragma unroll
-                for (int i = 0; i < 16 * MT; ++i) part[i] = 0.0f;
+                // Every thread fetches the messages of its own two rows from each contributor (the four
+                // threads of a quad read the same words); the loop is warp-uniform, so the warp never
+                // splits, and contributors are added in CTA order: the sum does not depend on arrival order.
+                constexpr int CB = 4;                          // contributors polled together
                 bool good = true;
-                for (uint32_t c = blockIdx.x + 1 + lane; c <= c_last; c += 32) {
-                    const uint2* src = reinterpret_cast<const uint2*>(p.partials) + ((size_t)c * kGemvTileRows + warp * 16) * MT;
-                    // all loads of a sweep are in flight together; sweep again only while a tag is missing
-                    uint2 msg[16 * MT];
+                for (uint32_t c0 = blockIdx.x + 1; c0 <= c_last && good; c0 += CB) {
+                    uint2 msg[CB][2 * MT];
                     const long long t0 = wait_clock();
-                    bool all = false;
-                    while (!all) {
+                    for (;;) {
+                        bool all = true;
 #pragma unroll
-                        for (int i = 0; i < 16 * MT; ++i) msg[i] = msg_load(src + i);
-                        all = true;
+                        for (int cb = 0; cb < CB; ++cb) {
+                            if (c0 + cb > c_last) continue;
+                            const uint2* src = reinterpret_cast<const uint2*>(p.partials) +
+                                               ((size_t)(c0 + cb) * kGemvTileRows + warp * 16) * MT;
 #pragma unroll
-                        for (int i = 0; i < 16 * MT; ++i) all = all && (msg[i].y == tag);
-                        if (!all && wait_expired(t0)) { good = false; break; }
+                            for (int mt = 0; mt < MT; ++mt) {
+                                msg[cb][2 * mt] = msg_load(src + g * MT + mt);
+                                msg[cb][2 * mt + 1] = msg_load(src + (g + 8) * MT + mt);
+                            }
+                        }
+                        // all loads of a sweep are in flight together; the tags are looked at afterwards
+#pragma unroll
+                        for (int cb = 0; cb < CB; ++cb) {
+                            if (c0 + cb > c_last) continue;
+#pragma unroll
+                            for (int i = 0; i < 2 * MT; ++i) all = all && msg[cb][i].y == tag;
+                        }
+                        if (__all_sync(kFull, all)) break;
+                        if (__any_sync(kFull, wait_expired(t0))) { good = false; break; }
                     }
 #pragma unroll
-                    for (int i = 0; i < 16 * MT; ++i) part[i] += __uint_as_float(msg[i].x);
-                }
-                if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
+                    for (int cb = 0; cb < CB; ++cb) {
+                        if (c0 + cb > c_last) continue;
 #pragma unroll
-                for (int i = 0; i < 16 * MT; ++i) {
-#pragma unroll
-                    for (int o = 16; o; o >>= 1) part[i] += __shfl_xor_sync(kFull, part[i], o);
-                }
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-                    for (int r = 0; r < 8; ++r) {        // select without dynamic register indexing
-                        if (r == g) { v[mt][0] += part[r * MT + mt]; v[mt][1] += part[(r + 8) * MT + mt]; }
+                        for (int mt = 0; mt < MT; ++mt) {
+                            v[mt][0] += __uint_as_float(msg[cb][2 * mt].x);
+                            v[mt][1] += __uint_as_float(msg[cb][2 * mt + 1].x);
+                        }
                     }
                 }
+                if (!good && lane == 0) atomicOr(p.status, kDevErrGridWaitTimeout);
             }
 
             // epilogue: LoRA term (the quad splits the rank), then quad thread t stores token t

@@ -297,8 +297,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
 #pragma unroll
                             for (int i = 0; i < 2 * NG; ++i) all = all && (msg[cb][i].y == tag);
                         }
-                        if (all) break;
-                        if (wait_expired(t0)) { good = false; break; }
+                        if (__all_sync(kFull, all)) break;                 // warp-uniform: the warp never splits
+                        if (__any_sync(kFull, wait_expired(t0))) { good = false; break; }
                     }
                     // contributors are added in CTA order: the sum does not depend on arrival order
 #pragma unroll
@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
                         }
                     }
                 }
-                if (!good) atomicOr(p.status, kDevErrGridWaitTimeout);
+                if (!good && lane == 0) atomicOr(p.status, kDevErrGridWaitTimeout);
             }
 
             // epilogue: LoRA term for the thread's two rows and NG tokens, then the stores
