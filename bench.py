@@ -544,7 +544,7 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
         bench_linear("config2_M1_lora16_cold", 1, 1024, 3584, 16, 128, 512)
         bench_linear("config2_M8_lora16_cold", 8, 1024, 3584, 16, 128, 512)
         bench_linear("config5_quarot_M1_K4096_N11008", 1, 4096, 11008, 0, 8, 200, rot=True)
-        bench_linear("config4_prefill_M2048_K5120_N17408_lora64_bf16", 2048, 5120, 17408, 64, 1, 5,
+        bench_linear("config4_prefill_M2048_K5120_N17408_lora64_bf16", 2048, 5120, 17408, 64, 1, 10,
                      x_dtype=torch.bfloat16)
         bench_linear("config5_quarot_M512_K4096_N11008", 512, 4096, 11008, 0, 1, 5, rot=True)
     except Exception as e:                                   # an aux failure must not hide the headline

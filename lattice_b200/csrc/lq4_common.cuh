@@ -89,8 +89,8 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // ---- arrivals of a fused all-gather ----------------------------------------------------
 // Waits (bounded) until every peer's results of all gathered launches this rank has issued so far
 // have arrived: each such launch of a peer adds 256 to `arrive[0]`, each of this rank's own adds
-// 256 to `arrive[1]`.  Called by whole warps after the previous launch is known to be complete.
-// Returns false on timeout.
+// 256 to `arrive[1]`.  Called by ONE thread of a warp or CTA after the previous launch is known to be
+// complete; the others follow through a warp or CTA barrier.  Returns false on timeout.
 __device__ __forceinline__ bool wait_gather_arrivals(const unsigned long long* arrive, uint32_t world) {
     unsigned long long seq, v;
     asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(seq) : "l"(arrive + 1) : "memory");

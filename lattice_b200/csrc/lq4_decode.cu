@@ -258,8 +258,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
         auto project = [&]() {
             projected = true;
             if (p.use_pdl) pdl_wait_prior_grids();          // x may come from the launch before this one
-            if (p.wait_world > 1 && !wait_gather_arrivals(p.wait_arrive, p.wait_world) && lane == 0)
-                atomicOr(p.status, kDevErrGridWaitTimeout);
+            if (p.wait_world > 1) {       // one lane polls the arrival counter, the warp follows
+                if (lane == 0 && !wait_gather_arrivals(p.wait_arrive, p.wait_world)) atomicOr(p.status, kDevErrGridWaitTimeout);
+                __syncwarp();
+            }
             const uint32_t tag = launch_tag(p.tsync);
             // work item e = (problem, token, rank row, k piece); item e belongs to CTA e mod grid
             const uint32_t nitems = NP == 1 ? p.m * p.rank * p.tsplit : ga.dot_start[count];
@@ -331,8 +333,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
         const int g = lane >> 2, t = lane & 3;
         // x may come from the launch before this one, or from the peers of a fused all-gather
         if (p.use_pdl) pdl_wait_prior_grids();
-        if (p.wait_world > 1 && !wait_gather_arrivals(p.wait_arrive, p.wait_world) && lane == 0)
-            atomicOr(p.status, kDevErrGridWaitTimeout);
+        if (p.wait_world > 1) {           // one thread polls the arrival counter, the consumers follow
+            if (tid == 0 && !wait_gather_arrivals(p.wait_arrive, p.wait_world)) atomicOr(p.status, kDevErrGridWaitTimeout);
+            named_bar_sync(kBarConsumers, kConsumerThreads);
+        }
         // a message written by an earlier launch never carries this launch's tag
         const uint32_t tag = launch_tag(p.tsync);
 

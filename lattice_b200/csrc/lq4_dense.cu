@@ -52,8 +52,10 @@ __global__ void __launch_bounds__(256) dense_prep_kernel(const __grid_constant__
         pdl_wait_prior_grids();
         pdl_launch_dependents();
     }
-    if (a.wait_world > 1 && !wait_gather_arrivals(a.wait_arrive, a.wait_world) && threadIdx.x == 0)
-        atomicOr(a.status, kDevErrGridWaitTimeout);
+    if (a.wait_world > 1) {               // one thread polls the arrival counter, the CTA follows
+        if (threadIdx.x == 0 && !wait_gather_arrivals(a.wait_arrive, a.wait_world)) atomicOr(a.status, kDevErrGridWaitTimeout);
+        __syncthreads();
+    }
     const uint32_t nlimb = a.limb_start[a.count];
     if (blockIdx.x >= nlimb) {
         const uint32_t b = blockIdx.x - nlimb;
