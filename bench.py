@@ -305,22 +305,46 @@ def run_ours(args):
 
     # pinned host buffers for the end-to-end variant
     hx = {k: torch.randn((m, k)).pin_memory() for k in (5120, 17408)}
-    hy = torch.empty(tuple(y_full.shape)).pin_memory()
+    hy = torch.empty((args.layers,) + tuple(y_full.shape)).pin_memory()      # one result per set
     dx = {k: torch.empty((m, k), device=dev) for k in (5120, 17408)}
 
-    def e2e_step():
-        # per set: host activations in (pinned -> device), the public call, host result out, wait
-        for projs in layers:
+    def e2e_body():
+        # per set: host activations in (pinned -> device), the public call, host result out
+        for li, projs in enumerate(layers):
             for k in dx:
                 dx[k].copy_(hx[k], non_blocking=True)
             run_set(projs, dx)
-            if peer_mode:
+            if peer_mode and peer_wait:
                 be.gather_wait(gdesc)
-            if world > 1:
-                hy.copy_(y_full, non_blocking=True)
-            else:
-                hy.copy_(y_cat, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            hy[li].copy_(y_full if world > 1 else y_cat, non_blocking=True)
+
+    # The copies and kernels of one step are captured in a CUDA graph too when the step holds no NCCL
+    # call; a step is then one graph launch and one wait for the results on the host.
+    e2e_info = {"mode": "plain calls, one wait per step"}
+    e2e_graph = None
+    if not args.eager and not (world > 1 and args.gather == "nccl"):
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                e2e_body()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            e2e_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(e2e_graph, stream=side):
+                e2e_body()
+            e2e_info["mode"] = "cuda-graph replay of the step's copies and kernels, one wait per step"
+        except Exception as e:
+            e2e_graph = None
+            e2e_info["mode"] = "plain calls, one wait per step (graph capture failed: %r)" % (e,)
+            torch.cuda.synchronize()
+
+    def e2e_step():
+        if e2e_graph is not None:
+            e2e_graph.replay()
+        else:
+            e2e_body()
+        torch.cuda.current_stream().synchronize()        # the host reads the step's results
 
     # The device-timed leg replays a CUDA graph of one step (the launch-bound inner loop is captured
     # once; replay removes the per-call host cost).  --eager times plain calls instead.
@@ -410,7 +434,8 @@ def run_ours(args):
             "dtype": "int4 codes x int8-limb activations in exact s32, block scales and accumulation in f32", "data": "synthetic",
             "config": workload_config(args, world),
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / e2e_steps,
-                    "h2d_bytes_per_step": int(args.layers * sum(m * k * 4 for k, _ in SHAPES)),
+                    "mode": e2e_info["mode"],
+                    "h2d_bytes_per_step": int(args.layers * sum(m * k * 4 for k in (5120, 17408))),
                     "d2h_bytes_per_step": int(args.layers * sum(m * n * 4 for _, n in SHAPES))},
             "gpu_launches": int(launches), "launch_mode": graph_info["mode"],
             "roofline": {"bound": "hbm", "kernel": ("decode_kernel<1, 8>: one persistent launch per set of four projections" if grouped
