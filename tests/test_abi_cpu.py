@@ -122,3 +122,26 @@ def test_entry_points_reject_null_and_bad_shapes_without_a_device(L):
     assert L.lq4_quantize_f32(None, 32, 0, None, None, None) == _lib.ERR_NULL
     assert L.lq4_status_string(_lib.ERR_K).startswith(b"k must")
     assert L.lq4_ctx_launch_count(None) == 0
+
+
+def test_group_gather_and_peer_buffer_entry_points_validate_without_a_device(L):
+    assert L.lq4_abi_version() >= 2
+    assert L.lq4_linear_group(None, None, 0, None) == _lib.ERR_NULL
+    args = (_lib.LinearArgs * 2)()
+    # a context is needed before anything else is looked at; NULL is refused
+    assert L.lq4_linear_group(None, args, 2, None) == _lib.ERR_NULL
+    assert L.lq4_gather_wait(None, None, None) == _lib.ERR_NULL
+    h = C.c_void_p()
+    assert L.lq4_peer_buf_create(0, C.byref(h)) == _lib.ERR_SHAPE and h.value is None
+    assert L.lq4_peer_buf_create(16, None) == _lib.ERR_NULL
+    buf = (C.c_uint8 * _lib.PEER_HANDLE_BYTES)()
+    assert L.lq4_peer_buf_export(None, buf) == _lib.ERR_NULL
+    assert L.lq4_peer_buf_open(None, C.byref(h)) == _lib.ERR_NULL
+    assert L.lq4_peer_buf_open(buf, None) == _lib.ERR_NULL
+    assert L.lq4_peer_buf_close(None) == _lib.OK
+    assert L.lq4_peer_buf_base(None) is None and L.lq4_peer_buf_payload(None) is None
+    L.lq4_peer_buf_free(None)
+    # the argument block carries the two gather descriptors after `path` (ABI version 2)
+    names = [f[0] for f in _lib.LinearArgs._fields_]
+    assert names[-3:] == ["path", "gather", "wait_gather"]
+    assert C.sizeof(_lib.GatherDesc) == 8 + 8 * _lib.MAX_PEERS

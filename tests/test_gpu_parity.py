@@ -507,7 +507,7 @@ def _as_tensor(ptr, shape):
     return torch.as_tensor(_DeviceArray(ptr, shape, None), device="cuda")
 
 
-@pytest.mark.parametrize("m", [1, 4])
+@pytest.mark.parametrize("m", [1, 4, 16])
 def test_fused_all_gather_writes_every_peer_and_signals(be, m):
     from lattice_b200 import Q4WeightBuf
     from lattice_b200._lib import GatherDesc, LoraDesc
@@ -554,6 +554,15 @@ def test_fused_all_gather_writes_every_peer_and_signals(be, m):
                             wait_gather=keep[7])
         be.check_device_status()
         assert tol_ratio(y2.cpu().numpy(), cases[1]["y_ref"]) <= 1.0
+        # a prefill-sized consumer of gathered activations gets the stand-alone wait in front of its kernels
+        big_case = make_case(2, 64, k, 256, extra=302)
+        qwb = Q4WeightBuf.from_host_payload(big_case["payload"], 256, k)
+        yb = torch.full((64, 256), float("nan"), device="cuda")
+        before = be.launch_count
+        be.dispatch_gemm_q4(dev(big_case["x"]), 0, qwb, yb, 0, 64, 256, k, wait_gather=keep[7])
+        be.check_device_status()
+        assert be.launch_count - before >= 2          # the wait kernel and the GEMM's kernels
+        assert tol_ratio(yb.cpu().numpy(), big_case["y_ref"]) <= 1.0
         # the fused gather is a decode-kernel feature: the tensor-core path refuses it
         big = torch.zeros((64, k), device="cuda")
         with pytest.raises(_lib.Lq4Error):
