@@ -78,12 +78,13 @@ __device__ __forceinline__ void gather_done(const GemvParams& q, uint32_t cta, u
     if (share == 0) return;
     const unsigned long long old = atomicAdd(q.gseq + 1, share);
     if (((old + share) & 255ull) != 0) return;
+    // one system-scope release fence for the whole launch, then relaxed signals (a release on every
+    // remote reduction would repeat the fence once per peer)
     __threadfence_system();
     for (uint32_t r = 0; r < q.world; ++r)
         if (r != q.grank)
-            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(q.peer_arrive[r]), "l"(256ull) : "memory");
+            asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(q.peer_arrive[r]), "l"(256ull) : "memory");
     asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(q.gseq), "l"(256ull) : "memory");
-    __threadfence_system();                  // this CTA is about to go quiet: push the signals out now
 }
 
 // u8 x s8 -> s32 warp MMA: D(16x8) += A(16x32, u8, row) * B(32x8, s8, col).
