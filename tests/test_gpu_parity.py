@@ -632,3 +632,25 @@ def test_adapter_rotation_for_a_quarot_base_at_load_time():
         assert not be2.has_lora_adapter()
     finally:
         be2.close()
+
+
+def test_resident_decode_bf16_activations_with_adapter_long_row(be):
+    # one token, bf16 activations: the in-kernel adapter projection takes its element-wise path, and a
+    # 17408-long row is cut into six k pieces per dot product
+    for k, n, rank in [(1024, 384, 16), (17408, 256, 8)]:
+        case = make_case(3, 1, k, n, rank=rank, alpha=2.0 * rank, bf16_x=True, extra=500 + rank)
+        y = run_case(be, case, bf16=True)
+        assert tol_ratio(y, case["y_ref"]) <= 1.0
+    # unaligned adapter factors (4-byte aligned only) also take the element-wise path
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    case = make_case(3, 1, 1024, 384, rank=16, alpha=32.0, extra=520)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], case["n"], case["k"])
+    a, b, s = case["lora"]
+    abuf = torch.zeros(a.size + 1, device="cuda")
+    abuf[1:] = dev(a).reshape(-1)
+    bd = dev(b)
+    y = be.linear(dev(case["x"]), qw, lora=LoraDesc(abuf.data_ptr() + 4, bd.data_ptr(), 16, s))
+    be.check_device_status()
+    assert tol_ratio(y.cpu().numpy(), case["y_ref"]) <= 1.0
+    qw.free()
