@@ -540,7 +540,29 @@ def cpu_baseline(gpu_layer):
         dt = time.perf_counter() - t0
         if dt > 12.0 or reps >= 200:
             break
-    return {"value": set_bytes * reps / dt / 1e9, "unit": UNIT, "cores": 1, "kind": "port",
+    # second formulation: the decode shader's fused arithmetic straight from the Q4 payload (dequantization
+    # inside the timed region), one thread, followed by the same apply_lora
+    fused = None
+    try:
+        payloads = [p["qw"]._keep.cpu().numpy() for p in gpu_layer]
+
+        def fused_set():
+            for (x, wd, a, b, sc), pl, (k, n) in zip(layer, payloads, [(p["k"], p["nl"]) for p in gpu_layer]):
+                y = oracle.gemv_q4_decode_form(x[0], pl, n, k)
+                oracle.apply_lora(a, b, LORA_RANK, k, n, sc, x[0], y)
+        fused_set()
+        r2, t2 = 0, time.perf_counter()
+        while True:
+            fused_set()
+            r2 += 1
+            d2 = time.perf_counter() - t2
+            if d2 > 6.0 or r2 >= 100:
+                break
+        fused = {"value": set_bytes * r2 / d2 / 1e9, "unit": UNIT, "cores": 1, "ms_per_token_set": d2 / r2 * 1e3,
+                 "what": "decode-shader arithmetic on the packed Q4 payload (dequantization timed), 1 thread"}
+    except Exception as e:                          # the second formulation must not hide the first
+        fused = {"error": repr(e)}
+    return {"value": set_bytes * reps / dt / 1e9, "unit": UNIT, "cores": 1, "kind": "port", "fused_dequant_variant": fused,
             "sample": f"{reps} repeats of one token-set (4 projections of layer 0, M=1, LoRA r=16), single thread as "
                       f"the reference's matmul_bt is; kernel {oracle.matmul_bt_kernel(1, 5120, 5120)}; "
                       f"f32 weights pre-dequantized at load (untimed)", "ms_per_token_set": dt / reps * 1e3}
