@@ -184,14 +184,14 @@ lq4_status lq4_gather_wait(lq4_ctx* ctx, const lq4_gather_desc* gather, void* st
  * handed every byte to its own pool at start-up, or a decode loop that cannot afford the
  * device-wide synchronisation inside cudaMalloc/cudaFree.  No counterpart in the reference:
  * this entry point exists only in this library.  It takes no context; the kernel's scratch
- * (stream-K partial sums and tickets, the LoRA partial exchange) lives in a fixed 1 MB
+ * (stream-K partial-sum messages, the launch counter, the LoRA projection messages) lives in a fixed 1 MB
  * array inside the loaded module, held by every GPU that loads the library until exit.
  * Limits, rejected with LQ4_ERR_NOSPACE: m <= 4, n <= 32768, LoRA rank <= 64, and m * k small
  * enough for the activation rows to sit in shared memory (m * k <= 56000); k % 128 == 0
  * and 16-byte aligned w and x are required (LQ4_ERR_ALIGN).  It calls no cudaMalloc, cudaFree
  * or other allocating routine.  The first call on a device resolves the array's address; make
  * that call before any stream capture.  All calls on a device share the array, which keeps the
- * last call's contents (messages in it carry a launch generation, so nothing stale is reused): calls that
+ * last call's contents (messages in it carry a per-launch tag, so nothing stale is reused): calls that
  * overlap on the GPU race, so order them on one stream.  `args->path` is ignored. */
 lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* args, void* stream);
 

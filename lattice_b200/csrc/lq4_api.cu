@@ -141,7 +141,7 @@ void fill_params(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dt
     p.kb = a->k / 32; p.kg = p.kb / kGemvGranuleBlocks;
     p.tiles = (a->n + kGemvTileRows - 1) / kGemvTileRows;
     p.status = ctx->status;
-    p.tsync = ctx->tsync;          // launch generation and end-of-launch counter
+    p.tsync = ctx->tsync;          // 64-bit launch counter the message tags come from
     p.use_pdl = ctx->pdl;
     p.sm_count = ctx->sm_count;
     p.x = x; p.x_dtype = x_dtype;

@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
             }
             if (!complete && g0 != 0) {
                 // Contributor: this CTA's range starts inside the tile, so this is its first segment.
-                // Publish the partial sums and leave; the ticket add is a release, no reply is needed.
+                // Publish the partial sums as tagged messages and go on; no reply is needed.
                 uint2* dst = reinterpret_cast<uint2*>(p.partials) + ((size_t)blockIdx.x * kGemvTileRows + warp * 16) * MT;
                 if (t == 0) {
 #pragma unroll

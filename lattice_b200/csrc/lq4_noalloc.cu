@@ -4,8 +4,8 @@
 // later cudaMalloc fails or eats into another tenant's share), and a latency-critical decode
 // loop in which the device-wide synchronisation hidden inside cudaMalloc/cudaFree would
 // stall every stream.  Neither can create an lq4_ctx, whose workspace lives in cudaMalloc'd
-// buffers.  Here the kernel's scratch (stream-K partial sums and tickets, the LoRA partial
-// exchange, the status word) sits in a fixed array that is part of the loaded module instead.
+// buffers.  Here the kernel's scratch (stream-K partial-sum messages, the launch counter, the LoRA
+// projection messages, the status word) sits in a fixed array that is part of the loaded module instead.
 #include <cmath>
 #include <mutex>
 
@@ -21,7 +21,7 @@ constexpr uint32_t kNaMaxGrid = 160;        // CTAs (one per SM; B200 has 148)
 constexpr uint32_t kNaMaxM = 4;             // tokens per call
 constexpr uint32_t kNaMaxN = 32768;         // output rows per call
 constexpr uint32_t kNaMaxRank = 64;         // LoRA rank
-constexpr size_t kNaCtrlBytes = 256 + (size_t)(kNaMaxN / kGemvTileRows) * 8 * 4;                  // status, counters, tickets
+constexpr size_t kNaCtrlBytes = 256 + (size_t)(kNaMaxN / kGemvTileRows) * 8 * 4;                  // status word, launch counter
 constexpr size_t kNaPartialBytes = (size_t)kNaMaxGrid * 2 * kGemvTileRows * 4 * sizeof(float);    // 655,360
 constexpr size_t kNaTpartBytes = 4 * 64 * 8 * 8;                                                  // t = A x messages: 4 tokens x rank 64 x 8 k pieces x 8 B
 constexpr size_t kNaScratchBytes = ((kNaCtrlBytes + 255) / 256) * 256 + kNaPartialBytes + kNaTpartBytes;
@@ -112,7 +112,7 @@ extern "C" lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* a, void* 
     p.tmsg = reinterpret_cast<uint2*>(q + kNaPartialBytes);               // t = A x messages
     p.use_pdl = 0;
     // The array keeps whatever the previous call left, on purpose: every cross-CTA message in it is
-    // tagged with the launch generation stored in the array, which each launch advances, so stale
+    // tagged from the launch counter stored in the array, which each launch advances, so stale
     // messages are never mistaken for new ones; only the status word has to start at zero.
     e = cudaMemsetAsync(base, 0, 4, s);
     if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, cudaGetErrorString(e));
