@@ -654,3 +654,38 @@ def test_resident_decode_bf16_activations_with_adapter_long_row(be):
     be.check_device_status()
     assert tol_ratio(y.cpu().numpy(), case["y_ref"]) <= 1.0
     qw.free()
+
+
+def test_checkpoint_directory_through_its_manifest(be, tmp_path):
+    """quantize_index.json (QuaRot flavour) -> uploaded weights by tensor name -> a projection that matches the oracle."""
+    import json
+    from lattice_b200 import manifest as mf
+    cases = {"model.layers.0.mlp.gate_proj.weight": make_case(2, 1, 256, 384, extra=600),
+             "model.layers.0.mlp.up_proj.weight": make_case(2, 1, 256, 128, extra=601)}
+    entries = []
+    for i, (name, c) in enumerate(cases.items()):
+        fname = f"t{i}.q4"
+        (tmp_path / fname).write_bytes(oracle.q4_file_bytes([c["n"], c["k"]], c["n"] * c["k"], c["payload"]))
+        entries.append({"name": name, "file": fname, "quantized": True, "shape": [c["n"], c["k"]], "numel": c["n"] * c["k"]})
+    entries.append({"name": "model.norm.weight", "file": "norm.f16", "quantized": False, "shape": [256], "numel": 256})
+    (tmp_path / mf.MANIFEST_NAME).write_text(json.dumps({"quarot_seed": 7, "tensors": entries}))
+    assert mf.load_manifest(str(tmp_path)).quarot_seed == 7
+    weights = mf.load_q4_directory(str(tmp_path))
+    try:
+        assert set(weights) == set(cases)            # the f16 tensor is skipped
+        for name, c in cases.items():
+            y = be.linear(dev(c["x"]), weights[name])
+            assert tol_ratio(y.cpu().numpy(), c["y_ref"]) <= 1.0
+    finally:
+        for qw in weights.values():
+            qw.free()
+    # a shape in the manifest that contradicts the file is refused by the library's loader
+    entries[0]["shape"] = [c["n"], c["k"] * 2]
+    (tmp_path / mf.MANIFEST_NAME).write_text(json.dumps(entries))
+    with pytest.raises(_lib.Lq4Error):
+        mf.load_q4_directory(str(tmp_path))
+    entries[0]["shape"] = None
+    entries[0]["file"] = "../escape.q4"
+    (tmp_path / mf.MANIFEST_NAME).write_text(json.dumps(entries))
+    with pytest.raises(mf.ManifestError):
+        mf.load_q4_directory(str(tmp_path))
