@@ -48,9 +48,11 @@ struct PrepArgs {
 
 // Limb records for every (block, token slot) and t = A x for every adapter, in one launch.
 __global__ void __launch_bounds__(256) dense_prep_kernel(const __grid_constant__ PrepArgs a) {
+    // The decode kernel behind this one may start at once: it only streams weights until it has
+    // waited for this grid, which in turn waits here for whatever produced x.
     if (a.use_pdl) {
-        pdl_wait_prior_grids();
         pdl_launch_dependents();
+        pdl_wait_prior_grids();
     }
     if (a.wait_world > 1) {               // one thread polls the arrival counter, the CTA follows
         if (threadIdx.x == 0 && !wait_gather_arrivals(a.wait_arrive, a.wait_world)) atomicOr(a.status, kDevErrGridWaitTimeout);
