@@ -22,7 +22,12 @@
 // activations are exact in f16 when they come as bf16, and are split into hi + lo f16 limbs
 // (two MMAs on the same weight tile) when they come as f32.
 // LoRA enters as extra K blocks: D += (s*B)[n, :] . T[m, :] with T = X A^T computed beforehand
-// (f32) and both factors carried as hi/lo f16 pairs.
+// (f32) and both factors carried as hi/lo f16 pairs.  T itself comes from the same kernel in its
+// all-dense mode with the roles swapped: the tokens are the 256-row operand (every row of the box
+// is real work; a rank-64 adapter would fill a quarter of it), A is the narrow one, and the k range
+// is cut into pieces, one output tile each, so that about one wave of CTAs shares a product that
+// would otherwise be a long serial loop on m / 256 of them.  The pieces (of T^T) are summed in
+// index order by the kernel that splits T into limbs.
 //
 // Within each group of 8 consecutive k the stored order is (k0,k4,k1,k5,k2,k6,k3,k7): that is
 // the order in which the nibble extraction yields pairs, and the activation tiles are written
@@ -178,6 +183,37 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict
     }
 }
 
+// The same split for T = X A^T as the k-split projection leaves it: `pieces` partial sums of the TRANSPOSE,
+// part[s][j][row] (rows of `ld` floats, pieces `piece_stride` floats apart).  Sums the pieces in index order
+// and writes dst[row][j] = hi, dst[row][cp + j] = lo.  Block = 32 rows x 32 columns through shared memory,
+// so that both the reads (along `row`) and the writes (along `j`) are contiguous.
+__global__ void __launch_bounds__(256) sum_split_transposed_kernel(const float* __restrict__ part, uint32_t pieces,
+                                                                   uint64_t piece_stride, uint64_t ld, uint32_t rows,
+                                                                   uint32_t cols, uint32_t cp, __half* __restrict__ dst) {
+    __shared__ float tile[32][33];
+    const uint32_t row0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t j = j0 + ty + 8 * i, row = row0 + tx;
+        float acc = 0.0f;
+        if (j < cols && row < rows)
+            for (uint32_t s = 0; s < pieces; ++s) acc += part[s * piece_stride + (uint64_t)j * ld + row];
+        tile[ty + 8 * i][tx] = acc;
+    }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t i = 0; i < 4; ++i) {
+        const uint32_t row = row0 + ty + 8 * i, j = j0 + tx;
+        if (row < rows && j < cp) {
+            __half h, l;
+            split_f16(tile[tx][ty + 8 * i], h, l);
+            dst[(uint64_t)row * 2 * cp + j] = h;
+            dst[(uint64_t)row * 2 * cp + cp + j] = l;
+        }
+    }
+}
+
 struct GemmParams {
     const uint8_t* w;
     float* y;
@@ -191,6 +227,8 @@ struct GemmParams {
     uint32_t seg_len;        // dense blocks per segment
     uint32_t seg_a_off[4];   // column offset of each dense segment in the A-operand matrix
     uint32_t seg_b_off[4];   // ... and in the B-operand matrix
+    uint32_t ksplit;         // all-dense products only: the k range is cut into ksplit pieces, one output tile each;
+    uint64_t split_stride;   // piece s adds s * seg_len blocks to every segment offset and writes y + s * split_stride
     int32_t* status;
 };
 
@@ -256,7 +294,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr;
 
-    const uint32_t total_tiles = p.n_tiles * p.m_tiles;
+    const uint32_t tps = p.n_tiles * p.m_tiles;                  // tiles per k piece
+    const uint32_t total_tiles = tps * p.ksplit;
     const uint32_t nkb = p.kblocks + p.lora_kblocks;
     const uint32_t xbytes = p.limbs * p.tt * 128;                // activation bytes per Q4 stage
     // accumulator buffers: two sub-tiles of tt columns each; double-buffered when they fit twice in 512 columns
@@ -269,7 +308,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
             uint32_t it = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int32_t n0 = (int32_t)((tile / p.m_tiles) * kCtaRows), m0 = (int32_t)((tile % p.m_tiles) * p.tt);
+                const int32_t n0 = (int32_t)(((tile % tps) / p.m_tiles) * kCtaRows), m0 = (int32_t)((tile % p.m_tiles) * p.tt);
                 for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
                     const uint32_t s = it % kStages2;
                     if (!mbar_wait(&empty[s], ((it / kStages2) & 1u) ^ 1u)) { ok = false; break; }
@@ -282,7 +321,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
                         if (p.limbs == 2) tma_load_tile(bt + p.tt * 128, &tm_x, (int32_t)(p.k + kb * kBlockK), m0, &full[s]);
                     } else {
                         // dense stage: both operands by TMA; the A box spans all 256 rows (two sub-tiles)
-                        const uint32_t d = kb - p.kblocks, seg = d / p.seg_len, within = d - seg * p.seg_len;
+                        const uint32_t d = kb - p.kblocks, seg = d / p.seg_len;
+                        const uint32_t within = d - seg * p.seg_len + (tile / tps) * p.seg_len;
                         mbar_arrive_expect_tx(&full[s], kSubTiles * kTileABytes + p.tt * 128);
                         tma_load_tile(st, &tm_da, (int32_t)(p.seg_a_off[seg] + within * kBlockK), n0, &full[s]);
                         tma_load_tile(bt, &tm_db, (int32_t)(p.seg_b_off[seg] + within * kBlockK), m0, &full[s]);
@@ -297,7 +337,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
             uint32_t rit = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+                const uint32_t n0 = ((tile % tps) / p.m_tiles) * kCtaRows;
                 const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
                 for (uint32_t pr = 0; pr < p.kblocks / 2 && ok; ++pr) {
                     for (uint32_t sub = 0; sub < nsub; ++sub, ++rit) {
@@ -318,7 +358,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
-                const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+                const uint32_t n0 = ((tile % tps) / p.m_tiles) * kCtaRows;
                 const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
                 const uint32_t buf = tcount % nbuf;
                 if (!mbar_wait(&acc_empty[buf], ((tcount / nbuf) & 1u) ^ 1u)) { ok = false; break; }
@@ -355,7 +395,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
         uint32_t it = 0, rit = 0;      // rit counts raw entries of ALL groups, as the raw producer does
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+            const uint32_t n0 = ((tile % tps) / p.m_tiles) * kCtaRows;
             const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
             const bool active = sub < nsub;
             for (uint32_t kb = 0; kb < nkb; ++kb, ++it) {
@@ -398,9 +438,10 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
             const uint32_t buf = tcount % nbuf;
-            const uint32_t n0 = (tile / p.m_tiles) * kCtaRows;
+            const uint32_t n0 = ((tile % tps) / p.m_tiles) * kCtaRows;
             const uint32_t nsub = n0 + kTileN < p.n ? 2u : 1u;
             const uint32_t m0 = (tile % p.m_tiles) * p.tt;
+            float* yout = p.y + (tile / tps) * p.split_stride;
             if (!mbar_wait(&acc_full[buf], (tcount / nbuf) & 1u)) { ok = false; break; }
             tc_fence_after();
             for (uint32_t sub = 0; sub < nsub; ++sub) {
@@ -413,7 +454,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const uint32_t m = m0 + c0 + j;
-                            if (c0 + j < p.tt && m < p.m) p.y[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
+                            if (c0 + j < p.tt && m < p.m) yout[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
                         }
                     }
                 }
@@ -489,13 +530,23 @@ struct GemmWorkspace {
     size_t x16, al, t, tl, bl, total;
 };
 
+// Pieces the k range of the projection T = X A^T is cut into: the largest divisor of k / 64 that is at most
+// 16 and keeps (256-token tiles) x pieces within about one wave of CTAs.
+uint32_t projection_pieces(uint32_t m, uint32_t k) {
+    const uint32_t tiles = (m + kCtaRows - 1) / kCtaRows, kb = k / kBlockK;
+    uint32_t best = 1;
+    for (uint32_t s = 2; s <= 16 && s <= kb; ++s)
+        if (kb % s == 0 && tiles * s <= 160) best = s;
+    return best;
+}
+
 GemmWorkspace plan_workspace(uint32_t m, uint32_t n, uint32_t k, uint32_t rank, uint32_t limbs) {
     GemmWorkspace ws{};
     const uint32_t rp = round_up(rank, kBlockK);
     size_t off = 0;
     ws.x16 = off; off += up256((size_t)m * limbs * k * 2);
     ws.al = off;  off += up256((size_t)rank * 2 * k * 2);
-    ws.t = off;   off += up256((size_t)m * rank * 4);
+    ws.t = off;   off += up256((size_t)projection_pieces(m, k) * rank * round_up(m, 4) * 4);
     ws.tl = off;  off += up256((size_t)m * 2 * rp * 2);
     ws.bl = off;  off += up256((size_t)n * 2 * rp * 2);
     ws.total = off;
@@ -511,7 +562,7 @@ cudaError_t launch_kernel(const GemmParams& p, const CUtensorMap& tx, const CUte
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const uint32_t tiles = p.n_tiles * p.m_tiles;
+    const uint32_t tiles = p.n_tiles * p.m_tiles * p.ksplit;
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
     gemm_tc_kernel<<<grid, kGemmWarps * 32, smem, s>>>(p, tx, tw, tda, tdb);
     return cudaGetLastError();
@@ -564,6 +615,8 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
     p.status = status;
     if (rank) {
         float* t = reinterpret_cast<float*>(base + ws.t);
+        uint32_t pieces = 0;                        // 0: t holds T itself, [m][rank]
+        const uint64_t mld = round_up(m, 4);        // row length of T^T (16-byte rows)
         if (m <= 32) {
             // few tokens: one warp per (token, rank row) dot product is quicker than a GEMM with one or two tiles
             launch_lora_t(x, x_dtype, m, k, la, rank, t, s);
@@ -575,26 +628,34 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
             const uint64_t a_oct = (uint64_t)rank * k / 8;
             convert_rows_kernel<<<(unsigned)((a_oct + 255) / 256), 256, 0, s>>>(la, LQ4_DTYPE_F32, rank, k, al, 2ull * k, k);
             ++nl;
-            CUtensorMap tm_al, tm_x32;
-            if (!make_f16_map(&tm_al, al, 2ull * k, rank, 2ull * k, kCtaRows)) return fail("tensor map (A)", cudaErrorInvalidValue);
-            if (!make_f16_map(&tm_x32, x16, (uint64_t)limbs * k, m, (uint64_t)limbs * k, 32)) return fail("tensor map (x32)", cudaErrorInvalidValue);
+            // X is the 256-row operand (every row of the box is a token), A the narrow one; the k range is
+            // cut into pieces so that about one wave of CTAs shares the work.  Output: pieces of T^T.
+            CUtensorMap tm_al, tm_xw;
+            const uint32_t ta = round_up(rank, 32);
+            if (!make_f16_map(&tm_al, al, 2ull * k, rank, 2ull * k, ta)) return fail("tensor map (A)", cudaErrorInvalidValue);
+            if (!make_f16_map(&tm_xw, x16, (uint64_t)limbs * k, m, (uint64_t)limbs * k, kCtaRows)) return fail("tensor map (x rows)", cudaErrorInvalidValue);
+            pieces = projection_pieces(m, k);
             GemmParams q{};
             q.status = status;
-            q.w = w; q.y = t; q.ldy = rank; q.m = m; q.n = rank; q.k = k;
-            q.limbs = 1; q.tt = 32; q.n_tiles = (rank + kCtaRows - 1) / kCtaRows; q.m_tiles = (m + 31) / 32;
+            q.w = w; q.y = t; q.ldy = mld; q.m = rank; q.n = m; q.k = k;
+            q.limbs = 1; q.tt = ta; q.n_tiles = (m + kCtaRows - 1) / kCtaRows; q.m_tiles = 1;
             q.kblocks = 0;
-            q.seg_len = k / kBlockK;
-            q.seg_a_off[0] = 0; q.seg_b_off[0] = 0;          // Ah . Xh
-            q.seg_a_off[1] = k; q.seg_b_off[1] = 0;          // Al . Xh
-            q.seg_a_off[2] = 0; q.seg_b_off[2] = k;          // Ah . Xl (two-limb activations only)
+            q.ksplit = pieces; q.split_stride = (uint64_t)rank * mld;
+            q.seg_len = k / kBlockK / pieces;
+            q.seg_a_off[0] = 0; q.seg_b_off[0] = 0;          // Xh . Ah
+            q.seg_a_off[1] = 0; q.seg_b_off[1] = k;          // Xh . Al
+            q.seg_a_off[2] = k; q.seg_b_off[2] = 0;          // Xl . Ah (two-limb activations only)
             q.lora_kblocks = (limbs == 2 ? 3u : 2u) * q.seg_len;
-            if ((e = launch_kernel(q, tm_x32, tm_w, tm_al, tm_x32, sm_count, s)) != cudaSuccess) return fail("projection GEMM launch", e);
+            if ((e = launch_kernel(q, tm_xw, tm_w, tm_xw, tm_al, sm_count, s)) != cudaSuccess) return fail("projection GEMM launch", e);
             ++nl;
         }
         // 4. hi/lo limbs of T and of s * B
         __half* tl = reinterpret_cast<__half*>(base + ws.tl);
         __half* bl = reinterpret_cast<__half*>(base + ws.bl);
-        split_rows_kernel<<<(unsigned)(((uint64_t)m * rp + 255) / 256), 256, 0, s>>>(t, m, rank, rp, 1.0f, tl);
+        if (pieces)
+            sum_split_transposed_kernel<<<dim3((m + 31) / 32, rp / 32), 256, 0, s>>>(t, pieces, (uint64_t)rank * mld, mld, m, rank, rp, tl);
+        else
+            split_rows_kernel<<<(unsigned)(((uint64_t)m * rp + 255) / 256), 256, 0, s>>>(t, m, rank, rp, 1.0f, tl);
         const uint64_t bn = (uint64_t)n * rp;
         const unsigned bblocks = (unsigned)((bn + 255) / 256 < (uint64_t)sm_count * 16 ? (bn + 255) / 256 : (uint64_t)sm_count * 16);
         split_rows_kernel<<<bblocks, 256, 0, s>>>(lb, n, rank, rp, lscale, bl);
@@ -615,6 +676,7 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
     p.n_tiles = (n + kCtaRows - 1) / kCtaRows;
     p.m_tiles = (m + tt - 1) / tt;
     p.kblocks = k / kBlockK;
+    p.ksplit = 1;
     if ((e = launch_kernel(p, tm_x, tm_w, tm_da, tm_db, sm_count, s)) != cudaSuccess) return fail("GEMM launch", e);
     ++nl;
     if (launches) *launches = nl;
