@@ -185,32 +185,37 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float* __restrict
 
 // The same split for T = X A^T as the k-split projection leaves it: `pieces` partial sums of the TRANSPOSE,
 // part[s][j][row] (rows of `ld` floats, pieces `piece_stride` floats apart).  Sums the pieces in index order
-// and writes dst[row][j] = hi, dst[row][cp + j] = lo.  Block = 32 rows x 32 columns through shared memory,
-// so that both the reads (along `row`) and the writes (along `j`) are contiguous.
+// and writes dst[row][j] = hi, dst[row][cp + j] = lo.  Block = 32 rows x 8 columns through shared memory:
+// the reads run along `row` (128 bytes per warp and piece), the writes are 16-byte runs along `j`.
 __global__ void __launch_bounds__(256) sum_split_transposed_kernel(const float* __restrict__ part, uint32_t pieces,
                                                                    uint64_t piece_stride, uint64_t ld, uint32_t rows,
                                                                    uint32_t cols, uint32_t cp, __half* __restrict__ dst) {
-    __shared__ float tile[32][33];
-    const uint32_t row0 = blockIdx.x * 32, j0 = blockIdx.y * 32;
-    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
-#pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-        const uint32_t j = j0 + ty + 8 * i, row = row0 + tx;
+    __shared__ float tile[8][33];
+    const uint32_t row0 = blockIdx.x * 32, j0 = blockIdx.y * 8;
+    {
+        const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+        const uint32_t j = j0 + ty, row = row0 + tx;
         float acc = 0.0f;
-        if (j < cols && row < rows)
-            for (uint32_t s = 0; s < pieces; ++s) acc += part[s * piece_stride + (uint64_t)j * ld + row];
-        tile[ty + 8 * i][tx] = acc;
+        if (j < cols && row < rows) {
+            const float* src = part + (uint64_t)j * ld + row;
+            uint32_t s = 0;
+            for (; s + 4 <= pieces; s += 4) {
+                const float v0 = src[(s + 0) * piece_stride], v1 = src[(s + 1) * piece_stride];
+                const float v2 = src[(s + 2) * piece_stride], v3 = src[(s + 3) * piece_stride];
+                acc = (((acc + v0) + v1) + v2) + v3;
+            }
+            for (; s < pieces; ++s) acc += src[s * piece_stride];
+        }
+        tile[ty][tx] = acc;
     }
     __syncthreads();
-#pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) {
-        const uint32_t row = row0 + ty + 8 * i, j = j0 + tx;
-        if (row < rows && j < cp) {
-            __half h, l;
-            split_f16(tile[tx][ty + 8 * i], h, l);
-            dst[(uint64_t)row * 2 * cp + j] = h;
-            dst[(uint64_t)row * 2 * cp + cp + j] = l;
-        }
+    const uint32_t r = threadIdx.x >> 3, jj = threadIdx.x & 7u;
+    const uint32_t row = row0 + r, j = j0 + jj;
+    if (row < rows && j < cp) {
+        __half h, l;
+        split_f16(tile[jj][r], h, l);
+        dst[(uint64_t)row * 2 * cp + j] = h;
+        dst[(uint64_t)row * 2 * cp + cp + j] = l;
     }
 }
 
@@ -653,7 +658,7 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
         __half* tl = reinterpret_cast<__half*>(base + ws.tl);
         __half* bl = reinterpret_cast<__half*>(base + ws.bl);
         if (pieces)
-            sum_split_transposed_kernel<<<dim3((m + 31) / 32, rp / 32), 256, 0, s>>>(t, pieces, (uint64_t)rank * mld, mld, m, rank, rp, tl);
+            sum_split_transposed_kernel<<<dim3((m + 31) / 32, rp / 8), 256, 0, s>>>(t, pieces, (uint64_t)rank * mld, mld, m, rank, rp, tl);
         else
             split_rows_kernel<<<(unsigned)(((uint64_t)m * rp + 255) / 256), 256, 0, s>>>(t, m, rank, rp, 1.0f, tl);
         const uint64_t bn = (uint64_t)n * rp;
