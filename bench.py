@@ -638,6 +638,61 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
             out[name]["frac_bf16_burst"] = flops / us / 1e6 / tc_peak
             out[name]["frac_bf16_sustained"] = flops / us / 1e6 / tc_sust
 
+    def bench_lm_head(name, vocab, k, top_k, reps):
+        """One token's vocabulary projection + exact top-k (the reference's two-stage lm_head path); the
+        794 MB of Q4 rows are larger than L2, so one weight copy is a cold read every call."""
+        parts = []
+        for c0 in range(0, vocab, 31040):
+            gen.manual_seed(977 + c0)
+            w = torch.randn((min(31040, vocab - c0), k), generator=gen, device=dev) * 0.02
+            parts.append(be.quantize(w.reshape(-1)))
+            del w
+        payload = torch.cat(parts)
+        del parts
+        qw = Q4WeightBuf.from_device_payload(payload, vocab, k)
+        x = torch.randn((1, k), generator=gen, device=dev)
+        y = torch.empty((1, vocab), device=dev)
+        res = {}
+        mode = "cuda-graph replay"
+        for what in ("projection", "projection+topk", "topk"):
+            def call():
+                if what == "projection":
+                    be.dispatch_gemm_q4(x, 0, qw, y, 0, 1, vocab, k)
+                elif what == "topk":
+                    be.logits_topk(y[0], top_k)
+                else:
+                    be.lm_head_topk(x, qw, top_k)
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(reps):
+                        call()
+                g.replay()
+                torch.cuda.synchronize()
+                e0.record()
+                g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+            except Exception:
+                torch.cuda.synchronize()
+                mode = "plain calls"
+                e0.record()
+                for _ in range(reps):
+                    call()
+                e1.record()
+                torch.cuda.synchronize()
+            res[what] = e0.elapsed_time(e1) * 1e3 / reps
+        byts = vocab * (k // 32) * 20 + k * 4 + vocab * 4
+        us = res["projection+topk"]
+        out[name] = {"us_per_call": us, "us_projection_only": res["projection"], "us_topk_only": res["topk"],
+                     "GB/s": byts / us / 1e3, "frac_hbm": byts / us / 1e3 / hbm_peak, "top_k": top_k, "timing": mode}
+
     try:
         bench_linear("config1_M1_K1024_N3584_cold", 1, 1024, 3584, 0, 128, 512)
         bench_linear("config1_M1_K1024_N3584_warm", 1, 1024, 3584, 0, 1, 512)
@@ -647,6 +702,7 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
         bench_linear("config4_prefill_M2048_K5120_N17408_lora64_bf16", 2048, 5120, 17408, 64, 1, 10,
                      x_dtype=torch.bfloat16)
         bench_linear("config5_quarot_M512_K4096_N11008", 512, 4096, 11008, 0, 1, 5, rot=True)
+        bench_lm_head("lm_head_topk50_vocab248320_K5120", 248320, 5120, 50, 20)
     except Exception as e:                                   # an aux failure must not hide the headline
         out["error"] = repr(e)
     return out
@@ -678,6 +734,23 @@ def run_only(args):
         torch.cuda.synchronize()
         be.check_device_status()
         print("ok", args.only)
+        return
+    elif args.only == "lm-head":           # M=1, vocabulary projection 5120 -> 248320 + exact top-50
+        vocab, k = 248320, 5120
+        parts = []
+        for c0 in range(0, vocab, 31040):
+            w = torch.randn((31040, k), device=dev) * 0.02
+            parts.append(be.quantize(w.reshape(-1)))
+            del w
+        payload = torch.cat(parts)
+        del parts
+        qw = Q4WeightBuf.from_device_payload(payload, vocab, k)
+        x = torch.randn((1, k), device=dev)
+        for _ in range(3):
+            vals, ids = be.lm_head_topk(x, qw, 50)
+        torch.cuda.synchronize()
+        be.check_device_status()
+        print("ok", args.only, ids[:4].tolist())
         return
     else:
         raise SystemExit("unknown --only case")
@@ -712,7 +785,7 @@ def main():
                          "diagnostics (no waiting for the peers / no exchange at all): their values are not results")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
-    ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set: three launches of one case, for profiling")
+    ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set | lm-head: three launches of one case, for profiling")
     ap.add_argument("--no-aux", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -201,6 +201,33 @@ lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* args, void* stream);
  * the model's lifetime (crates/inference/src/forward/metal_qwen35.rs:599-702). */
 lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* args_with_host_x_y, void* stream);
 
+/* ---- lm_head: vocabulary projection + exact top-k ----------------------------------------- */
+
+#define LQ4_MAX_TOP_K 256u       /* MAX_TOP_K of the reference's selection kernels (shaders/qwen35.metal:1686) */
+
+/* One selected token: TopKCandidate (crates/inference/src/forward/shaders/qwen35.metal:1688-1695).
+ * Unused tail entries (top_k > number of non-NaN logits) hold the sentinel (-inf, UINT32_MAX). */
+typedef struct {
+    float logit;
+    uint32_t token_id;
+} lq4_topk_candidate;
+
+/* out[0 .. top_k) = the top_k entries of logits[0 .. n) in the order of topk_better
+ * (shaders/qwen35.metal:1697-1703): higher logit first, ties to the lower token id; NaN logits never rank.
+ * Replaces logits_topk first pass + logits_topk_merge_pass (shaders/qwen35.metal:1730-1770); exact for any
+ * distribution.  logits and out are device pointers.  top_k outside 1..LQ4_MAX_TOP_K: LQ4_ERR_SHAPE. */
+lq4_status lq4_logits_topk(lq4_ctx* ctx, const float* logits, uint32_t n, uint32_t top_k,
+                           lq4_topk_candidate* out, void* stream);
+
+/* The reference's two-stage lm_head path, lm_head_block_topk_q4 + merge (shaders/qwen35.metal:1931-1979,
+ * dispatched from forward/metal_qwen35/inner/dispatch.rs:1346-1436): logits = lq4_linear(args) for one
+ * token (args->m must be 1, else LQ4_ERR_SHAPE), then lq4_logits_topk over the n = vocabulary rows.
+ * args->y may be NULL: the logit row then lives only in the context's workspace (the sampler never sees
+ * it, as in the reference); non-NULL y receives the full row as well.  The fused all-gather fields must
+ * be NULL (LQ4_ERR_UNSUPPORTED). */
+lq4_status lq4_lm_head_topk(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t top_k,
+                            lq4_topk_candidate* out, void* stream);
+
 /* Standalone y[m, d_out] += scale * B (A x): the two-dispatch form of
  * dispatch_lora_if_active, for fused outputs where two adapters write two
  * column ranges of one y (gate||up, qkv||z). */

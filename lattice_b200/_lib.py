@@ -28,6 +28,7 @@ class RotDesc(C.Structure):
 
 MAX_PEERS = 8
 PEER_HANDLE_BYTES = 64
+MAX_TOP_K = 256
 
 
 class GatherDesc(C.Structure):
@@ -63,6 +64,8 @@ SIGNATURES = {
     "lq4_peer_buf_open": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "lq4_peer_buf_close": (C.c_int32, [C.c_void_p]),
     "lq4_gather_wait": (C.c_int32, [C.c_void_p, C.POINTER(GatherDesc), C.c_void_p]),
+    "lq4_logits_topk": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
+    "lq4_lm_head_topk": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_uint32, C.c_void_p, C.c_void_p]),
     "lq4_lora_apply": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32, C.c_uint32, C.c_void_p,
                                    C.c_uint32, C.c_uint64, C.POINTER(LoraDesc), C.c_void_p]),
     "lq4_dequant_f32": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),

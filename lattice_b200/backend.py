@@ -385,6 +385,42 @@ class CudaQ4Backend:
         self.dispatch_gemm_q4(x.contiguous(), 0, qw, y, 0, m, qw.n, k, lora=lora, rot=rot, path=path)
         return y
 
+    # ---- lm_head: vocabulary projection + exact top-k --------------------------------------
+    @staticmethod
+    def _split_candidates(cand: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``cand`` is ``[top_k, 2]`` int32 holding (logit bits, token id) pairs."""
+        return cand[:, 0].view(torch.float32), cand[:, 1]        # strided views: no copy kernels
+
+    def logits_topk(self, logits: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Top ``top_k`` of a device logit row in the reference's candidate order (higher logit first, ties to
+        the lower token id, NaN never ranks).  Returns ``(logits[top_k] f32, token_ids[top_k] int32)``; token
+        ids of unused slots are -1 (0xFFFFFFFF) with logit -inf."""
+        if logits.dtype != torch.float32 or logits.dim() != 1:
+            raise TypeError("logits must be a 1-D float32 device tensor")
+        logits = logits.contiguous()
+        cand = torch.empty((max(top_k, 1), 2), dtype=torch.int32, device=logits.device)
+        check(_lib.lib().lq4_logits_topk(self._ctx, logits.data_ptr(), logits.numel(), top_k, cand.data_ptr(), _stream()))
+        return self._split_candidates(cand)
+
+    def lm_head_topk(self, x: torch.Tensor, qw: Q4WeightBuf, top_k: int, *, lora: Optional[LoraDesc] = None,
+                     rot: Optional[RotDesc] = None, logits_out: Optional[torch.Tensor] = None
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
+        """One token's vocabulary projection followed by the exact top-k (the reference's two-stage lm_head
+        path).  ``x`` is ``[1, k]`` or ``[k]``; ``logits_out`` (``[n]`` f32), when given, also receives the
+        full logit row, otherwise it stays in the context's workspace."""
+        x = x.reshape(1, -1).contiguous()
+        k = x.shape[1]
+        self._require_k("lm_head_topk", k)
+        if k != qw.k:
+            raise ValueError(f"x has {k} columns, the weights have {qw.k}")
+        cand = torch.empty((max(top_k, 1), 2), dtype=torch.int32, device=x.device)
+        args = LinearArgs(x.data_ptr(), self._dtype_of(x), 1, qw.n, k, qw.payload_ptr,
+                          logits_out.data_ptr() if logits_out is not None else None, 0,
+                          C.pointer(lora) if lora is not None else None,
+                          C.pointer(rot) if rot is not None else None, _lib.PATH_AUTO, None, None)
+        check(_lib.lib().lq4_lm_head_topk(self._ctx, C.byref(args), top_k, cand.data_ptr(), _stream()))
+        return self._split_candidates(cand)
+
     def prepare_group(self, problems, outs: Optional[List[torch.Tensor]] = None,
                       gather: Optional[GatherDesc] = None, wait_gather: Optional[GatherDesc] = None) -> "PreparedGroup":
         """Builds the argument block of a grouped call once; calling the result launches it.

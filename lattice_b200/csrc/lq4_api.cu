@@ -49,7 +49,7 @@ struct lq4_ctx {
     uint64_t launches = 0;
     int32_t* status = nullptr;    // device status word
     uint32_t* tsync = nullptr;    // 64-bit launch counter of the decode kernels
-    Buf xrot, xs, t, tmsg, partials, hx, hy, gemm;   // xs: activation limb records of the dense decode kernel
+    Buf xrot, xs, t, tmsg, partials, hx, hy, gemm, logits, topk;   // xs: activation limb records of the dense decode kernel
     bool allow_grow = true;
     int pdl = 1;
 };
@@ -291,7 +291,7 @@ void lq4_ctx_destroy(lq4_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
-    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm})
+    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk})
         if (b->p) cudaFree(b->p);
     if (ctx->status) cudaFree(ctx->status);
     delete ctx;
@@ -601,6 +601,42 @@ lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* a, void* stream)
     }
     LQ4_CUDA(cudaStreamSynchronize(s));
     return LQ4_OK;
+}
+
+lq4_status lq4_logits_topk(lq4_ctx* ctx, const float* logits, uint32_t n, uint32_t top_k, lq4_topk_candidate* out,
+                           void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (top_k == 0 || top_k > LQ4_MAX_TOP_K) return fail(LQ4_ERR_SHAPE, "top_k must be in 1..256");
+    if (!logits || !out) return fail(LQ4_ERR_NULL, "logits and out must be non-NULL");
+    if (n == 0) return fail(LQ4_ERR_SHAPE, "n must be non-zero");
+    cudaStream_t s = (cudaStream_t)stream;
+    lq4_status st;
+    if ((st = ensure(ctx, ctx->topk, topk_scratch_bytes(n, top_k), false, s))) return st;
+    int nl = 0;
+    LQ4_CUDA(launch_topk(logits, n, top_k, ctx->topk.p, out, s, &nl));
+    ctx->launches += nl;
+    return LQ4_OK;
+}
+
+lq4_status lq4_lm_head_topk(lq4_ctx* ctx, const lq4_linear_args* a, uint32_t top_k, lq4_topk_candidate* out,
+                            void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (!a) return fail(LQ4_ERR_NULL, "args is NULL");
+    if (top_k == 0 || top_k > LQ4_MAX_TOP_K) return fail(LQ4_ERR_SHAPE, "top_k must be in 1..256");
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    if (a->m != 1) return fail(LQ4_ERR_SHAPE, "lq4_lm_head_topk takes one token (m == 1)");
+    if (a->n == 0) return fail(LQ4_ERR_SHAPE, "n must be non-zero");
+    if (a->gather || a->wait_gather) return fail(LQ4_ERR_UNSUPPORTED, "lq4_lm_head_topk has no fused all-gather");
+    cudaStream_t s = (cudaStream_t)stream;
+    lq4_linear_args b = *a;
+    lq4_status st;
+    if (!b.y) {
+        if ((st = ensure(ctx, ctx->logits, (size_t)a->n * 4, false, s))) return st;
+        b.y = (float*)ctx->logits.p;
+        b.ldy = 0;
+    }
+    if ((st = lq4_linear(ctx, &b, stream))) return st;
+    return lq4_logits_topk(ctx, b.y, a->n, top_k, out, stream);
 }
 
 lq4_status lq4_lora_apply(lq4_ctx* ctx, const void* x, int32_t x_dtype, uint32_t m, uint32_t k, float* y, uint32_t n,

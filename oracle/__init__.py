@@ -90,6 +90,8 @@ def lib() -> C.CDLL:
         L.orc_q4_linear.argtypes = [vp, vp, vp, vp, sz, sz, sz, vp, vp, sz, C.c_float, vp]
         L.orc_gemv_q4_decode_form.restype = None
         L.orc_gemv_q4_decode_form.argtypes = [vp, vp, vp, sz, sz]
+        L.orc_topk.argtypes = [vp, sz, sz, vp, vp]
+        L.orc_topk.restype = None
         _lib = L
     return _lib
 
@@ -313,3 +315,13 @@ def gemv_q4_decode_form(x, payload, n: int, k: int) -> np.ndarray:
     y = np.zeros(n, np.float32)
     lib().orc_gemv_q4_decode_form(_p(x), _p(p), _p(y), n, k)
     return y
+
+
+def topk(logits, k: int):
+    """(logits[k], token_ids[k]) of the k best entries in the reference's candidate order (higher logit
+    first, ties to the lower id, NaN never ranks); unused slots hold (-inf, 0xFFFFFFFF)."""
+    v = _c(logits, np.float32).reshape(-1)
+    out_l = np.zeros(k, np.float32)
+    out_i = np.zeros(k, np.uint32)
+    lib().orc_topk(_p(v), v.size, k, _p(out_l), _p(out_i))
+    return out_l, out_i

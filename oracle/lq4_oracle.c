@@ -803,4 +803,36 @@ void orc_gemv_q4_decode_form(const float* x, const uint8_t* payload, float* y, s
     }
 }
 
+/* Exact top-k of a logit row in the reference's candidate order:
+ * topk_better (crates/inference/src/forward/shaders/qwen35.metal:1697-1703) ranks the higher logit
+ * first and breaks ties towards the lower token id; a NaN logit becomes the sentinel
+ * (-inf, UINT32_MAX) before it competes (qwen35.metal:1916, :1967), so it never displaces a real
+ * token.  Slots past the number of candidates keep the sentinel, as the padded bitonic sort of
+ * the merge pass leaves them (qwen35.metal:1746-1768). */
+static int orc_topk_better(float al, uint32_t ai, float bl, uint32_t bi) {
+    if (al != al) return 0;
+    if (bl != bl) return 1;
+    if (al != bl) return al > bl;
+    return ai < bi;
+}
+
+void orc_topk(const float* logits, size_t n, size_t k, float* out_logit, uint32_t* out_id) {
+    for (size_t j = 0; j < k; ++j) { out_logit[j] = -INFINITY; out_id[j] = UINT32_MAX; }
+    if (k == 0) return;
+    for (size_t i = 0; i < n; ++i) {
+        float v = logits[i];
+        uint32_t id = (uint32_t)i;
+        if (v != v) { v = -INFINITY; id = UINT32_MAX; }
+        if (!orc_topk_better(v, id, out_logit[k - 1], out_id[k - 1])) continue;
+        size_t j = k - 1;
+        while (j > 0 && orc_topk_better(v, id, out_logit[j - 1], out_id[j - 1])) {
+            out_logit[j] = out_logit[j - 1];
+            out_id[j] = out_id[j - 1];
+            --j;
+        }
+        out_logit[j] = v;
+        out_id[j] = id;
+    }
+}
+
 int orc_abi_version(void) { return 1; }

@@ -145,3 +145,12 @@ def test_group_gather_and_peer_buffer_entry_points_validate_without_a_device(L):
     names = [f[0] for f in _lib.LinearArgs._fields_]
     assert names[-3:] == ["path", "gather", "wait_gather"]
     assert C.sizeof(_lib.GatherDesc) == 8 + 8 * _lib.MAX_PEERS
+
+
+def test_topk_entry_points_validate_without_a_device(L):
+    out = (C.c_uint64 * 4)()
+    logits = (C.c_float * 4)()
+    assert L.lq4_logits_topk(None, logits, 4, 2, out, None) == _lib.ERR_NULL
+    args = _lib.LinearArgs()
+    assert L.lq4_lm_head_topk(None, C.byref(args), 2, out, None) == _lib.ERR_NULL
+    assert _lib.MAX_TOP_K == 256

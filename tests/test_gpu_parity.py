@@ -689,3 +689,105 @@ def test_checkpoint_directory_through_its_manifest(be, tmp_path):
     (tmp_path / mf.MANIFEST_NAME).write_text(json.dumps(entries))
     with pytest.raises(mf.ManifestError):
         mf.load_q4_directory(str(tmp_path))
+
+
+# ---------------------------------------------------------------- lm_head: projection + exact top-k
+def _topk_ids(t):
+    return t.cpu().numpy().view(np.uint32)
+
+
+@pytest.mark.parametrize("n", [1, 37, 1024, 1025, 5000, 248320])
+@pytest.mark.parametrize("k", [1, 8, 50, 256])
+def test_logits_topk_is_exact_index_work(be, n, k):
+    # coarse values: most of the order is decided by the tie rule, and the result must be identical
+    rng = np.random.default_rng(n * 1000 + k)
+    logits = rng.integers(-300, 300, n).astype(np.float32) * np.float32(0.125)
+    if n > 40:
+        logits[rng.integers(0, n, 20)] = np.nan
+        logits[rng.integers(0, n, 5)] = -np.inf
+        logits[rng.integers(0, n, 3)] = np.inf
+    vals, ids = be.logits_topk(dev(logits), k)
+    rv, ri = oracle.topk(logits, k)
+    assert np.array_equal(_topk_ids(ids), ri)
+    assert np.array_equal(vals.cpu().numpy(), rv)
+    be.check_device_status()
+
+
+def test_logits_topk_all_winners_in_one_block(be):
+    # the reference's adversarial case (metal_qwen35.rs:24967-25040): every global winner sits in one
+    # 1024-row block; a block-local argmax or a truncated local list would drop some of them
+    n, k = 20000, 64
+    rng = np.random.default_rng(7)
+    logits = rng.standard_normal(n).astype(np.float32)
+    block = 5
+    winners = block * 1024 + rng.permutation(1024)[:k]
+    logits[winners] = 50.0 + rng.standard_normal(k).astype(np.float32)
+    vals, ids = be.logits_topk(dev(logits), k)
+    rv, ri = oracle.topk(logits, k)
+    assert set(ri.tolist()) == set(winners.tolist())
+    assert np.array_equal(_topk_ids(ids), ri) and np.array_equal(vals.cpu().numpy(), rv)
+
+
+def test_logits_topk_rejects_bad_requests(be):
+    from lattice_b200._lib import Lq4Error
+    t = dev(np.zeros(16, np.float32))
+    for k in (0, 257):
+        with pytest.raises(Lq4Error) as e:
+            be.logits_topk(t, k)
+        assert e.value.status == _lib.ERR_SHAPE
+
+
+def _assert_topk_agrees(ref_logits, ids, vals, k):
+    """The reference's acceptance rule for GPU-vs-CPU lm_head top-k (topk_set_agreement_or_boundary_tie,
+    metal_qwen35.rs:37488-37570): the sets are equal, or every differing token lies within epsilon of the
+    boundary logit.  On top of it: each returned logit is that row's logit within the output tolerance,
+    and the list is sorted in candidate order."""
+    ids = ids.astype(np.int64)
+    assert len(set(ids.tolist())) == k and ids.min() >= 0 and ids.max() < ref_logits.size
+    rms = float(np.sqrt(np.mean(ref_logits.astype(np.float64) ** 2)))
+    eps = 2e-3 * (float(np.max(np.abs(ref_logits))) + rms)
+    assert np.all(np.abs(vals - ref_logits[ids]) <= 1e-3 * (np.abs(ref_logits[ids]) + rms))
+    assert np.all((vals[:-1] > vals[1:]) | ((vals[:-1] == vals[1:]) & (ids[:-1] < ids[1:])))
+    rv, ri = oracle.topk(ref_logits, k)
+    diff = set(ri.tolist()) ^ set(ids.tolist())
+    assert all(abs(float(ref_logits[t]) - float(rv[-1])) <= eps for t in diff), sorted(diff)
+
+
+@pytest.mark.parametrize("n,k_dim,top_k,rank", [(4096 + 37, 1024, 8, 0), (4096 + 37, 1024, 50, 16), (32000, 2048, 64, 0)])
+def test_lm_head_topk_agrees_with_full_logits(be, n, k_dim, top_k, rank):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    case = make_case(3, 1, k_dim, n, rank=rank, alpha=2.0 * rank)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], n, k_dim)
+    lora, keep = None, []
+    if rank:
+        a, b, s = case["lora"]
+        keep = [dev(a), dev(b)]
+        lora = LoraDesc(keep[0].data_ptr(), keep[1].data_ptr(), rank, s)
+    x = dev(case["x"])
+    full = torch.full((n,), float("nan"), dtype=torch.float32, device="cuda")
+    vals, ids = be.lm_head_topk(x, qw, top_k, lora=lora, logits_out=full)
+    vals2, ids2 = be.lm_head_topk(x, qw, top_k, lora=lora)          # logit row kept in the workspace only
+    be.check_device_status()
+    ref = case["y_ref"].reshape(-1)
+    _assert_topk_agrees(ref, _topk_ids(ids), vals.cpu().numpy(), top_k)
+    assert np.array_equal(_topk_ids(ids), _topk_ids(ids2)) and np.array_equal(vals.cpu().numpy(), vals2.cpu().numpy())
+    # the selection itself is exact on the logits the projection produced
+    rv, ri = oracle.topk(full.cpu().numpy(), top_k)
+    assert np.array_equal(_topk_ids(ids), ri) and np.array_equal(vals.cpu().numpy(), rv)
+    assert tol_ratio(full.cpu().numpy().reshape(1, -1), case["y_ref"]) <= 1.0
+    qw.free()
+
+
+def test_lm_head_topk_takes_one_token(be):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LinearArgs, Lq4Error, check
+    case = make_case(1, 2, 256, 128)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], 128, 256)
+    x = dev(case["x"])
+    cand = torch.empty((4, 2), dtype=torch.int32, device="cuda")
+    args = LinearArgs(x.data_ptr(), _lib.DTYPE_F32, 2, 128, 256, qw.payload_ptr, None, 0, None, None, _lib.PATH_AUTO, None, None)
+    with pytest.raises(Lq4Error) as e:
+        check(_lib.lib().lq4_lm_head_topk(be._ctx, C.byref(args), 4, cand.data_ptr(), None))
+    assert e.value.status == _lib.ERR_SHAPE
+    qw.free()

@@ -315,3 +315,36 @@ def test_composed_linear_matches_plain_numpy():
     assert np.max(np.abs(y1 - (x[0].astype(np.float64) @ wd.T))) < 1e-5
     with pytest.raises(oracle.OracleError):
         oracle.q4_linear(x[:, :100], p, m, n, 100)
+
+
+def _reference_cpu_topk_ids(logits, k):
+    """cpu_topk_token_ids of the reference's own tests (crates/inference/src/forward/metal_qwen35.rs:24943-24952):
+    a stable sort of the ids by descending logit, truncated to k."""
+    order = np.argsort(-logits.astype(np.float64), kind="stable")
+    return order[:k].astype(np.uint32)
+
+
+def test_topk_order_matches_the_reference_cpu_selection():
+    rng = np.random.default_rng(171)
+    # coarse values: many exact ties, so that the tie rule (lower id first) decides most of the order
+    logits = rng.integers(-40, 40, 5000).astype(np.float32) * np.float32(0.25)
+    for k in (1, 8, 16, 40, 50, 64, 256):
+        vals, ids = oracle.topk(logits, k)
+        assert np.array_equal(ids, _reference_cpu_topk_ids(logits, k))
+        assert np.array_equal(vals, logits[ids])
+    # continuous values
+    logits = rng.standard_normal(3000).astype(np.float32)
+    vals, ids = oracle.topk(logits, 50)
+    assert np.array_equal(ids, _reference_cpu_topk_ids(logits, 50))
+
+
+def test_topk_nan_and_short_rows_keep_the_sentinel():
+    logits = np.array([1.0, np.nan, 5.0, -np.inf, 5.0, np.nan, 0.0, -0.0], np.float32)
+    vals, ids = oracle.topk(logits, 4)
+    assert ids.tolist() == [2, 4, 0, 6] and vals.tolist() == [5.0, 5.0, 1.0, 0.0]
+    vals, ids = oracle.topk(logits, 10)
+    # a real -inf logit ranks before the sentinel; the two NaN rows never appear
+    assert ids.tolist() == [2, 4, 0, 6, 7, 3] + [0xFFFFFFFF] * 4
+    assert np.all(np.isneginf(vals[5:]))
+    vals, ids = oracle.topk(np.full(7, np.nan, np.float32), 3)
+    assert ids.tolist() == [0xFFFFFFFF] * 3 and np.all(np.isneginf(vals))
