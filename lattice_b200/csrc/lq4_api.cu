@@ -49,7 +49,7 @@ struct lq4_ctx {
     uint64_t launches = 0;
     int32_t* status = nullptr;    // device status word
     uint32_t* tsync = nullptr;    // 64-bit launch counter of the decode kernels
-    Buf xrot, xs, t, tmsg, partials, hx, hy, gemm, logits, topk;   // xs: activation limb records of the dense decode kernel
+    Buf xrot, xs, t, tmsg, partials, hx, hy, gemm, logits, topk, topk_ctr;   // xs: activation limb records of the dense decode kernel
     bool allow_grow = true;
     int pdl = 1;
 };
@@ -291,7 +291,7 @@ void lq4_ctx_destroy(lq4_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
-    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk})
+    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk, &ctx->topk_ctr})
         if (b->p) cudaFree(b->p);
     if (ctx->status) cudaFree(ctx->status);
     delete ctx;
@@ -609,11 +609,13 @@ lq4_status lq4_logits_topk(lq4_ctx* ctx, const float* logits, uint32_t n, uint32
     if (top_k == 0 || top_k > LQ4_MAX_TOP_K) return fail(LQ4_ERR_SHAPE, "top_k must be in 1..256");
     if (!logits || !out) return fail(LQ4_ERR_NULL, "logits and out must be non-NULL");
     if (n == 0) return fail(LQ4_ERR_SHAPE, "n must be non-zero");
+    if (n > 0x7fffffffu) return fail(LQ4_ERR_OVERFLOW, "n does not fit");
     cudaStream_t s = (cudaStream_t)stream;
     lq4_status st;
-    if ((st = ensure(ctx, ctx->topk, topk_scratch_bytes(n, top_k), false, s))) return st;
+    if ((st = ensure(ctx, ctx->topk, topk_list_bytes(n, top_k), false, s))) return st;
+    if ((st = ensure(ctx, ctx->topk_ctr, topk_counter_bytes(n), true, s))) return st;      // zero once; launches keep it zero
     int nl = 0;
-    LQ4_CUDA(launch_topk(logits, n, top_k, ctx->topk.p, out, s, &nl));
+    LQ4_CUDA(launch_topk(logits, n, top_k, ctx->topk.p, (uint32_t*)ctx->topk_ctr.p, out, ctx->pdl, s, &nl));
     ctx->launches += nl;
     return LQ4_OK;
 }

@@ -109,9 +109,11 @@ void launch_gemv_generic(const void* x, int x_dtype, const uint8_t* w, float* y,
                          uint32_t n, uint32_t k, const float* t, const float* lb, uint32_t rank, float lscale,
                          int accumulate_only, cudaStream_t s);
 
-// Exact top-k of a logit row (lq4_topk.cu).  `scratch` holds topk_scratch_bytes(n, k) bytes.
-size_t topk_scratch_bytes(uint32_t n, uint32_t k);
-cudaError_t launch_topk(const float* logits, uint32_t n, uint32_t k, void* scratch, lq4_topk_candidate* out,
-                        cudaStream_t s, int* launches);
+// Exact top-k of a logit row (lq4_topk.cu), one launch.  `lists` holds topk_list_bytes(n, k) bytes; `counters`
+// holds topk_counter_bytes(n) bytes that are zero before their first use (every launch leaves them zero).
+size_t topk_list_bytes(uint32_t n, uint32_t k);
+size_t topk_counter_bytes(uint32_t n);
+cudaError_t launch_topk(const float* logits, uint32_t n, uint32_t k, void* lists, uint32_t* counters,
+                        lq4_topk_candidate* out, int use_pdl, cudaStream_t s, int* launches);
 
 }  // namespace lq4
