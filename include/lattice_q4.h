@@ -81,7 +81,13 @@ typedef struct {
 
 /* Online randomized Hadamard rotation x' = H (D x) applied to every activation
  * row before the matmul; `signs` holds k entries of +1/-1 (f32, device)
- * (crates/inference/src/quant/quarot/hadamard.rs:176-209). */
+ * (crates/inference/src/quant/quarot/hadamard.rs:176-209).
+ * dim == k: one rotation over the whole row (k a power of two).  dim < k: the block-diagonal
+ * rotation BlockHadamard (hadamard.rs:285-484) with block size `dim` (a power of two that divides k,
+ * k / dim <= 4096), the R4 rotation in front of down_proj on axes that are not powers of two
+ * (3584 = 28 x 128, 17408 = 68 x 256); block i uses signs[i * dim, (i + 1) * dim). */
+#define LQ4_MAX_ROT_LEN (1u << 24)   /* MAX_BLOCK_HADAMARD_LEN, hadamard.rs:318 */
+#define LQ4_MAX_ROT_BLOCKS 4096u     /* MAX_BLOCK_HADAMARD_BLOCKS, hadamard.rs:345 */
 typedef struct {
     const float* signs;
     uint32_t dim;
@@ -251,6 +257,16 @@ lq4_status lq4_quantize_f32(const float* data, uint64_t len, int32_t mode, uint8
  * f32 in and out, bit-identical to RandomizedHadamard::apply
  * (crates/inference/src/quant/quarot/hadamard.rs:197-209). */
 lq4_status lq4_hadamard_rows(const float* x, float* out, uint32_t rows, const lq4_rot_desc* rot, void* stream);
+
+/* BlockHadamard::apply (hadamard.rs:444-462) on `rows` vectors of length n: block size rot->dim, signs
+ * of n entries; bit-identical to the reference.  The constructor's refusals (n == 0, n > 1 << 24, block
+ * not a power of two or not dividing n, more than 4096 blocks) return LQ4_ERR_ROT. */
+lq4_status lq4_block_hadamard_rows(const float* x, float* out, uint32_t rows, uint32_t n,
+                                   const lq4_rot_desc* rot, void* stream);
+
+/* Fills `signs` (n entries) as BlockHadamard::new(seed, n, block) does: block i draws
+ * signs_from_seed(derive_block_seed(seed, i), block) (hadamard.rs:153-155, 401-414). */
+lq4_status lq4_block_rot_signs_from_seed(uint64_t seed, uint32_t n, uint32_t block, float* signs, void* stream);
 
 /* Fills `signs` with the +1/-1 diagonal of RandomizedHadamard::new(seed, dim)
  * (crates/inference/src/quant/quarot/hadamard.rs:114-139). */

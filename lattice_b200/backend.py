@@ -365,10 +365,27 @@ class CudaQ4Backend:
         check(_lib.lib().lq4_rot_signs_from_seed(seed & (2 ** 64 - 1), dim, s.data_ptr(), _stream()))
         return s
 
+    def block_rot_signs(self, seed: int, n: int, block: int) -> torch.Tensor:
+        """The flat sign buffer of ``BlockHadamard::new(seed, n, block)`` (hadamard.rs:358-414)."""
+        s = torch.empty(max(n, 1), dtype=torch.float32, device=f"cuda:{self.device}")
+        check(_lib.lib().lq4_block_rot_signs_from_seed(seed & (2 ** 64 - 1), n, block, s.data_ptr(), _stream()))
+        return s[:n]
+
     @staticmethod
-    def rot_desc(signs: torch.Tensor) -> RotDesc:
+    def rot_desc(signs: torch.Tensor, block: Optional[int] = None) -> RotDesc:
+        """``block=None``: one rotation over ``len(signs)`` entries; else the block-diagonal rotation with that
+        block size (``signs`` still holds one entry per activation column)."""
         assert signs.is_cuda and signs.dtype == torch.float32
-        return RotDesc(signs.data_ptr(), signs.numel())
+        return RotDesc(signs.data_ptr(), signs.numel() if block is None else block)
+
+    def block_hadamard_rows(self, x: torch.Tensor, signs: torch.Tensor, block: int) -> torch.Tensor:
+        """``BlockHadamard::apply`` on every row of ``x`` (``[rows, n]``, ``n = len(signs)``)."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+        out = torch.empty_like(x)
+        rot = self.rot_desc(signs, block)
+        n = signs.numel()
+        check(_lib.lib().lq4_block_hadamard_rows(x.data_ptr(), out.data_ptr(), x.numel() // max(n, 1), n, C.byref(rot), _stream()))
+        return out
 
     def hadamard_rows(self, x: torch.Tensor, signs: torch.Tensor) -> torch.Tensor:
         assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()

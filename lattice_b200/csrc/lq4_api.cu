@@ -112,8 +112,11 @@ lq4_status validate_linear(const lq4_linear_args* a) {
     }
     if (a->rot) {
         if (!a->rot->signs) return fail(LQ4_ERR_ROT, "rotation signs pointer is NULL");
-        if (a->rot->dim != a->k) return fail(LQ4_ERR_ROT, "rotation dim must equal k");
-        if (!is_pow2(a->k) || a->k > 16384) return fail(LQ4_ERR_ROT, "rotation needs k a power of two <= 16384");
+        // dim == k: one randomized Hadamard over the row; dim < k: block-diagonal (one per `dim` entries)
+        const uint32_t dim = a->rot->dim;
+        if (!is_pow2(dim) || dim > 16384) return fail(LQ4_ERR_ROT, "rotation needs a power-of-two dim <= 16384");
+        if (dim > a->k || a->k % dim != 0) return fail(LQ4_ERR_ROT, "rotation dim must equal k or divide it");
+        if (a->k / dim > LQ4_MAX_ROT_BLOCKS) return fail(LQ4_ERR_ROT, "more than 4096 rotation blocks");
     }
     if (a->path < LQ4_PATH_AUTO || a->path > LQ4_PATH_GEMM_TC) return fail(LQ4_ERR_UNSUPPORTED, "unknown path");
     if (a->wait_gather) {
@@ -365,14 +368,15 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
 
     // The decode kernel rotates in its own prologue when the row fits; otherwise the
     // rotation runs as a kernel of its own into the workspace.
-    const bool in_kernel_rot = signs && path == LQ4_PATH_GEMV_MMA && a->m == 1 && rank == 0 &&
+    const bool in_kernel_rot = signs && a->rot->dim == a->k && path == LQ4_PATH_GEMV_MMA && a->m == 1 && rank == 0 &&
                                gemv_resident_fits(1, a->k, true);
     if (signs && !in_kernel_rot) wait_in_kernel = false;
     if (a->wait_gather && a->wait_gather->world > 1 && !wait_in_kernel)
         if ((st = lq4_gather_wait(ctx, a->wait_gather, stream))) return st;
     if (signs && !in_kernel_rot) {
         if ((st = ensure(ctx, ctx->xrot, (size_t)a->m * a->k * 4, false, s))) return st;
-        LQ4_CUDA(launch_hadamard_rows(x, x_dtype, signs, a->k, a->m, (float*)ctx->xrot.p, s));
+        const uint32_t blocks = a->k / a->rot->dim;          // 1: full rotation; more: block-diagonal
+        LQ4_CUDA(launch_hadamard_rows(x, x_dtype, signs, a->rot->dim, a->m * blocks, (float*)ctx->xrot.p, s, blocks));
         ctx->launches += 1;
         x = ctx->xrot.p;
         x_dtype = LQ4_DTYPE_F32;
@@ -693,6 +697,38 @@ lq4_status lq4_hadamard_rows(const float* x, float* out, uint32_t rows, const lq
     if (!x || !out || !rot || !rot->signs) return fail(LQ4_ERR_NULL, "x, out and rot->signs must be non-NULL");
     if (!is_pow2(rot->dim) || rot->dim > 16384) return fail(LQ4_ERR_ROT, "rotation needs a power-of-two dim <= 16384");
     LQ4_CUDA(launch_hadamard_rows(x, LQ4_DTYPE_F32, rot->signs, rot->dim, rows, out, (cudaStream_t)stream));
+    return LQ4_OK;
+}
+
+static lq4_status check_block_rotation(uint32_t n, uint32_t block) {
+    // BlockHadamard::new, crates/inference/src/quant/quarot/hadamard.rs:358-400
+    if (n == 0 || n > LQ4_MAX_ROT_LEN) return fail(LQ4_ERR_ROT, "block rotation needs 0 < n <= 1 << 24");
+    if (!is_pow2(block)) return fail(LQ4_ERR_ROT, "block rotation needs a power-of-two block size");
+    if (n % block != 0) return fail(LQ4_ERR_ROT, "block size does not divide n");
+    if (n / block > LQ4_MAX_ROT_BLOCKS) return fail(LQ4_ERR_ROT, "more than 4096 rotation blocks");
+    return LQ4_OK;
+}
+
+lq4_status lq4_block_hadamard_rows(const float* x, float* out, uint32_t rows, uint32_t n, const lq4_rot_desc* rot,
+                                   void* stream) {
+    if (!x || !out || !rot || !rot->signs) return fail(LQ4_ERR_NULL, "x, out and rot->signs must be non-NULL");
+    lq4_status st;
+    if ((st = check_block_rotation(n, rot->dim))) return st;
+    if (rot->dim > 16384) return fail(LQ4_ERR_ROT, "block size above 16384");
+    if (rows == 0) return LQ4_OK;
+    const uint64_t launch_rows = (uint64_t)rows * (n / rot->dim);
+    if (launch_rows > 0x7fffffffull) return fail(LQ4_ERR_OVERFLOW, "rows * blocks does not fit");
+    LQ4_CUDA(launch_hadamard_rows(x, LQ4_DTYPE_F32, rot->signs, rot->dim, (uint32_t)launch_rows, out, (cudaStream_t)stream,
+                                  n / rot->dim));
+    return LQ4_OK;
+}
+
+lq4_status lq4_block_rot_signs_from_seed(uint64_t seed, uint32_t n, uint32_t block, float* signs, void* stream) {
+    lq4_status st;
+    if ((st = check_block_rotation(n, block))) return st;
+    if (!signs) return fail(LQ4_ERR_NULL, "signs is NULL");
+    launch_block_rot_signs(seed, n, block, signs, (cudaStream_t)stream);
+    LQ4_CUDA(cudaGetLastError());
     return LQ4_OK;
 }
 

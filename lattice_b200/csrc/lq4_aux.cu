@@ -127,11 +127,14 @@ void launch_quantize(const float* data, uint64_t len, int symmetric, uint8_t* pa
 // subtract of two values of the previous stage, so running the butterflies of
 // one stage in parallel reproduces the sequential result bit for bit.
 // ---------------------------------------------------------------------------
+// A block-diagonal rotation is the same kernel over rows of one block each: row r of the launch is block
+// r % sign_rows of its vector and takes that block's signs (sign_rows = 1: one diagonal for every row).
 __global__ void __launch_bounds__(512) hadamard_rows_kernel(const void* __restrict__ x, int x_dtype,
                                                             const float* __restrict__ signs, uint32_t dim,
-                                                            float* __restrict__ out) {
+                                                            uint32_t sign_rows, float* __restrict__ out) {
     extern __shared__ float row[];
     const size_t base = (size_t)blockIdx.x * dim;
+    signs += (size_t)(blockIdx.x % sign_rows) * dim;
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x)
         row[i] = __fmul_rn(load_act(x, x_dtype, base + i), signs[i]);
     __syncthreads();
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(512) hadamard_rows_kernel(const void* __restri
 }
 
 cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs, uint32_t dim, uint32_t rows,
-                                 float* out, cudaStream_t s) {
+                                 float* out, cudaStream_t s, uint32_t sign_rows) {
     const size_t smem = (size_t)dim * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(hadamard_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -157,7 +160,7 @@ cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs,
         if (e != cudaSuccess) return e;
     }
     if (rows == 0) return cudaSuccess;
-    hadamard_rows_kernel<<<rows, 512, smem, s>>>(x, x_dtype, signs, dim, out);
+    hadamard_rows_kernel<<<rows, dim >= 1024 ? 512 : (dim >= 128 ? dim / 2 : 64), smem, s>>>(x, x_dtype, signs, dim, sign_rows ? sign_rows : 1, out);
     return cudaGetLastError();
 }
 
@@ -171,6 +174,26 @@ __global__ void rot_signs_kernel(uint64_t seed, uint32_t dim, float* __restrict_
     z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
     z ^= z >> 31;
     signs[i] = (z & 1ull) ? -1.0f : 1.0f;
+}
+
+// Block i of a block-diagonal rotation draws its signs from the stream seeded with
+// mix(seed + i * gamma) (derive_block_seed of the reference).
+__global__ void block_rot_signs_kernel(uint64_t seed, uint32_t n, uint32_t block, float* __restrict__ signs) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t gamma = 0x9E3779B97F4A7C15ull;
+    auto mix = [](uint64_t z) {
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        return z ^ (z >> 31);
+    };
+    const uint64_t bseed = mix(seed + gamma * (uint64_t)(i / block));
+    signs[i] = (mix(bseed + gamma * (uint64_t)(i % block + 2)) & 1ull) ? -1.0f : 1.0f;
+}
+
+void launch_block_rot_signs(uint64_t seed, uint32_t n, uint32_t block, float* signs, cudaStream_t s) {
+    if (n == 0) return;
+    block_rot_signs_kernel<<<(n + 255) / 256, 256, 0, s>>>(seed, n, block, signs);
 }
 
 void launch_rot_signs(uint64_t seed, uint32_t dim, float* signs, cudaStream_t s) {

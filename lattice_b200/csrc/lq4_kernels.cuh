@@ -15,7 +15,8 @@ void launch_dequant(const uint8_t* payload, uint64_t n_blocks, float* out, int s
 void launch_quantize(const float* data, uint64_t len, int symmetric, uint8_t* payload, int32_t* status,
                      int sm_count, cudaStream_t s);
 cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs, uint32_t dim, uint32_t rows,
-                                 float* out, cudaStream_t s);
+                                 float* out, cudaStream_t s, uint32_t sign_rows = 1);
+void launch_block_rot_signs(uint64_t seed, uint32_t n, uint32_t block, float* signs, cudaStream_t s);
 void launch_rot_signs(uint64_t seed, uint32_t dim, float* signs, cudaStream_t s);
 
 // ---- decode kernels: geometry and parameters ------------------------------------------

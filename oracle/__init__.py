@@ -91,6 +91,9 @@ def lib() -> C.CDLL:
         L.orc_gemv_q4_decode_form.restype = None
         L.orc_gemv_q4_decode_form.argtypes = [vp, vp, vp, sz, sz]
         L.orc_topk.argtypes = [vp, sz, sz, vp, vp]
+        L.orc_block_hadamard_check.argtypes = [sz, sz]
+        L.orc_block_hadamard_signs.argtypes = [u64, sz, sz, vp]
+        L.orc_block_hadamard_apply_f32.argtypes = [vp, sz, sz, vp, C.c_int]
         L.orc_topk.restype = None
         _lib = L
     return _lib
@@ -325,3 +328,21 @@ def topk(logits, k: int):
     out_i = np.zeros(k, np.uint32)
     lib().orc_topk(_p(v), v.size, k, _p(out_l), _p(out_i))
     return out_l, out_i
+
+
+def block_hadamard_signs(seed: int, n: int, block: int) -> np.ndarray:
+    """The flat sign buffer of BlockHadamard::new(seed, n, block); raises where the constructor refuses."""
+    _check(lib().orc_block_hadamard_check(n, block), "block_hadamard_check")
+    out = np.zeros(n, np.float32)
+    _check(lib().orc_block_hadamard_signs(seed, n, block, _p(out)), "block_hadamard_signs")
+    return out
+
+
+def block_hadamard_apply(signs, data, block: int, inverse: bool = False) -> np.ndarray:
+    """BlockHadamard::apply / apply_inverse on one vector of len(signs) f32 values."""
+    s = _c(signs, np.float32).reshape(-1)
+    d = np.array(data, dtype=np.float32, copy=True).reshape(-1)
+    if d.size != s.size:
+        raise OracleError(ERR_SHAPE, "block_hadamard_apply")
+    _check(lib().orc_block_hadamard_apply_f32(_p(s), s.size, block, _p(d), 1 if inverse else 0), "block_hadamard_apply")
+    return d

@@ -673,6 +673,41 @@ int orc_rh_apply_inverse_f64(const float* signs, size_t n, double* d) {
     return ORC_OK;
 }
 
+/* BlockHadamard (crates/inference/src/quant/quarot/hadamard.rs:285-484): a block-diagonal rotation
+ * of a length-n vector, every block of `block` entries with its own sign diagonal and the
+ * orthonormal Walsh-Hadamard of that size.  The constructor's checks (hadamard.rs:358-400): n != 0,
+ * n <= 1 << 24, block a power of two that divides n, n / block <= 4096.  Block i's signs are
+ * signs_from_seed(derive_block_seed(seed, i), block), stored back to back (hadamard.rs:401-414). */
+#define ORC_MAX_BLOCK_HADAMARD_LEN ((size_t)1 << 24)
+#define ORC_MAX_BLOCK_HADAMARD_BLOCKS 4096
+
+int orc_block_hadamard_check(size_t n, size_t block) {
+    if (n == 0 || n > ORC_MAX_BLOCK_HADAMARD_LEN) return ORC_ERR_SHAPE;
+    if (!is_pow2(block)) return ORC_ERR_POW2;
+    if (n % block != 0) return ORC_ERR_SHAPE;
+    if (n / block > ORC_MAX_BLOCK_HADAMARD_BLOCKS) return ORC_ERR_SHAPE;
+    return ORC_OK;
+}
+
+int orc_block_hadamard_signs(uint64_t seed, size_t n, size_t block, float* out) {
+    int rc = orc_block_hadamard_check(n, block);
+    if (rc) return rc;
+    for (size_t i = 0; i < n / block; ++i) orc_signs_from_seed(orc_derive_block_seed(seed, i), block, out + i * block);
+    return ORC_OK;
+}
+
+/* apply (hadamard.rs:444-462): per block D then H; apply_inverse (hadamard.rs:465-482): H then D. */
+int orc_block_hadamard_apply_f32(const float* signs, size_t n, size_t block, float* d, int inverse) {
+    int rc = orc_block_hadamard_check(n, block);
+    if (rc) return rc;
+    for (size_t b0 = 0; b0 < n; b0 += block) {
+        rc = inverse ? orc_rh_apply_inverse_f32(signs + b0, block, d + b0) : orc_rh_apply_f32(signs + b0, block, d + b0);
+        if (rc) return rc;
+    }
+    return ORC_OK;
+}
+
+
 /* ------------------------------------------------------------------------
  * Rotation absorption.  crates/inference/src/quant/quarot/rotation.rs:82-195.
  * input side:  W <- W R^T  == apply R to every ROW   (rotation dim = cols)

@@ -154,3 +154,14 @@ def test_topk_entry_points_validate_without_a_device(L):
     args = _lib.LinearArgs()
     assert L.lq4_lm_head_topk(None, C.byref(args), 2, out, None) == _lib.ERR_NULL
     assert _lib.MAX_TOP_K == 256
+
+
+def test_block_rotation_entry_points_refuse_what_the_reference_constructor_refuses(L):
+    # BlockHadamard::new, quant/quarot/hadamard.rs:358-400: checked before anything touches a device
+    buf = (C.c_float * 4)()
+    for n, b in ((0, 64), ((1 << 24) + 64, 64), (100, 64), (96, 48), (64, 0), (1 << 24, 1)):
+        assert L.lq4_block_rot_signs_from_seed(1, n, b, buf, None) == _lib.ERR_ROT, (n, b)
+    assert L.lq4_block_rot_signs_from_seed(1, 128, 64, None, None) == _lib.ERR_NULL
+    rot = _lib.RotDesc(C.cast(buf, C.c_void_p).value, 48)
+    assert L.lq4_block_hadamard_rows(buf, buf, 1, 96, C.byref(rot), None) == _lib.ERR_ROT
+    assert L.lq4_block_hadamard_rows(None, buf, 1, 96, C.byref(rot), None) == _lib.ERR_NULL

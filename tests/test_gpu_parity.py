@@ -791,3 +791,61 @@ def test_lm_head_topk_takes_one_token(be):
         check(_lib.lib().lq4_lm_head_topk(be._ctx, C.byref(args), 4, cand.data_ptr(), None))
     assert e.value.status == _lib.ERR_SHAPE
     qw.free()
+
+
+# ---------------------------------------------------------------- block-diagonal rotation (R4 in front of down_proj)
+@pytest.mark.parametrize("n,block", [(3584, 128), (17408, 256), (17408, 128), (4096, 4096), (96, 32)])
+def test_block_rotation_signs_and_rows_bit_exact(be, n, block):
+    seed = 0x5EED0000 + n + block
+    signs = be.block_rot_signs(seed, n, block)
+    ref_signs = oracle.block_hadamard_signs(seed, n, block)
+    assert np.array_equal(signs.cpu().numpy(), ref_signs)
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal((3, n)).astype(np.float32)
+    y = be.block_hadamard_rows(dev(x), signs, block).cpu().numpy()
+    for r in range(3):
+        ref = oracle.block_hadamard_apply(ref_signs, x[r], block)
+        assert np.array_equal(y[r].view(np.uint32), ref.view(np.uint32))
+    be.check_device_status()
+
+
+@pytest.mark.parametrize("m,k,n,block,rank,bf16", [(1, 3584, 1024, 128, 0, False), (1, 17408, 2560, 256, 16, False),
+                                                   (4, 3584, 1024, 128, 16, False), (40, 3584, 512, 128, 0, True)])
+def test_projection_with_block_rotation_in_front(be, m, k, n, block, rank, bf16):
+    # the R4 recipe: down_proj rows were rotated block by block offline; the activations get the same rotation online
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    case = make_case(5, m, k, n, rank=rank, alpha=2.0 * rank, bf16_x=bf16)
+    signs_h = oracle.block_hadamard_signs(0xB10C, k, block)
+    xr = np.stack([oracle.block_hadamard_apply(signs_h, case["x"][i], block) for i in range(m)])
+    y_ref = oracle.q4_linear(xr, None, m, n, k, lora=None, w_f32=case["w_deq"])
+    if rank:
+        a, b, s = case["lora"]
+        # the adapter sees the rotated activations too (one x for both products, as in the fused call)
+        y_ref = oracle.q4_linear(xr, None, m, n, k, lora=case["lora"], w_f32=case["w_deq"])
+    qw = Q4WeightBuf.from_host_payload(case["payload"], n, k)
+    signs = dev(signs_h)
+    lora, keep = None, []
+    if rank:
+        keep = [dev(a), dev(b)]
+        lora = LoraDesc(keep[0].data_ptr(), keep[1].data_ptr(), rank, s)
+    x = dev(case["x"]).to(torch.bfloat16) if bf16 else dev(case["x"])
+    y = be.linear(x, qw, lora=lora, rot=be.rot_desc(signs, block))
+    be.check_device_status()
+    assert tol_ratio(y.cpu().numpy(), y_ref) <= 1.0
+    qw.free()
+
+
+def test_rotation_descriptor_must_divide_k(be):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import Lq4Error
+    case = make_case(1, 1, 384, 64)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], 64, 384)
+    signs = dev(np.ones(384, np.float32))
+    for block in (256, 48, 512):
+        with pytest.raises(Lq4Error) as e:
+            be.linear(dev(case["x"]), qw, rot=be.rot_desc(signs, block))
+        assert e.value.status == _lib.ERR_ROT
+    y = be.linear(dev(case["x"]), qw, rot=be.rot_desc(signs, 128))       # all-plus signs, block 128: accepted
+    be.check_device_status()
+    qw.free()

@@ -348,3 +348,37 @@ def test_topk_nan_and_short_rows_keep_the_sentinel():
     assert np.all(np.isneginf(vals[5:]))
     vals, ids = oracle.topk(np.full(7, np.nan, np.float32), 3)
     assert ids.tolist() == [0xFFFFFFFF] * 3 and np.all(np.isneginf(vals))
+
+
+# ---- BlockHadamard: the reference's own properties (quant/quarot/hadamard.rs tests, :502-1040) ----
+def test_block_hadamard_signs_match_per_block_randomized_hadamard():
+    seed, n, b = 0xC0FFEE, 3584, 128
+    s = oracle.block_hadamard_signs(seed, n, b)
+    for i in (0, 1, 13, 27):
+        assert np.array_equal(s[i * b:(i + 1) * b], oracle.signs_from_seed(oracle.derive_block_seed(seed, i), b))
+    # adjacent blocks' sign streams are not one-position-shifted copies (the defect derive_block_seed removes)
+    assert not np.array_equal(s[1:b], s[b:2 * b - 1])
+    assert set(np.unique(s).tolist()) == {-1.0, 1.0}
+
+
+def test_block_hadamard_round_trip_norm_and_partition():
+    rng = np.random.default_rng(4)
+    for n, b in ((3584, 128), (17408, 256), (64, 64), (96, 32)):
+        s = oracle.block_hadamard_signs(7, n, b)
+        x = rng.standard_normal(n).astype(np.float32)
+        y = oracle.block_hadamard_apply(s, x, b)
+        assert abs(np.linalg.norm(y) / np.linalg.norm(x) - 1.0) < 1e-5
+        assert np.max(np.abs(oracle.block_hadamard_apply(s, y, b, inverse=True) - x)) < 1e-5
+        # every block is RandomizedHadamard::apply of its own slice, nothing crosses a block boundary
+        i = (n // b) // 2
+        assert np.array_equal(y[i * b:(i + 1) * b], oracle.rh_apply(s[i * b:(i + 1) * b], x[i * b:(i + 1) * b]))
+        x2 = x.copy()
+        x2[:b] += 1.0
+        assert np.array_equal(oracle.block_hadamard_apply(s, x2, b)[b:], y[b:])
+
+
+def test_block_hadamard_refuses_what_the_constructor_refuses():
+    for n, b in ((0, 64), ((1 << 24) + 64, 64), (100, 64), (96, 48), (64, 0), (1 << 24, 1), (4097 * 2, 2)):
+        with pytest.raises(oracle.OracleError):
+            oracle.block_hadamard_signs(1, n, b)
+    oracle.block_hadamard_signs(1, 4096 * 2, 2)          # exactly 4096 blocks is accepted
