@@ -264,6 +264,16 @@ lq4_status lq4_hadamard_rows(const float* x, float* out, uint32_t rows, const lq
 lq4_status lq4_block_hadamard_rows(const float* x, float* out, uint32_t rows, uint32_t n,
                                    const lq4_rot_desc* rot, void* stream);
 
+/* QuaRot's online "Hadamard heads" rotation H_num_heads (x) I_head_dim on `rows` activations of
+ * num_heads * head_dim entries each: for every within-head channel the num_heads values across the heads
+ * are rotated by one RandomizedHadamard of dimension num_heads (`signs`: num_heads entries, device), the
+ * R3 rotation of the gated attention output in front of o_proj
+ * (apply_cross_head_rotation, crates/inference/src/quant/quarot/r3_reference.rs:246-264;
+ * OnlineRotationSpec::r3_full_attention, quant/quarot/plan.rs).  Bit-identical to that loop.  num_heads a
+ * power of two <= 128, else LQ4_ERR_ROT.  x and out must not overlap. */
+lq4_status lq4_cross_head_hadamard_rows(const float* x, float* out, uint32_t rows, uint32_t num_heads,
+                                        uint32_t head_dim, const float* signs, void* stream);
+
 /* Fills `signs` (n entries) as BlockHadamard::new(seed, n, block) does: block i draws
  * signs_from_seed(derive_block_seed(seed, i), block) (hadamard.rs:153-155, 401-414). */
 lq4_status lq4_block_rot_signs_from_seed(uint64_t seed, uint32_t n, uint32_t block, float* signs, void* stream);

@@ -73,6 +73,7 @@ SIGNATURES = {
     "lq4_hadamard_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(RotDesc), C.c_void_p]),
     "lq4_rot_signs_from_seed": (C.c_int32, [C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p]),
     "lq4_block_hadamard_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(RotDesc), C.c_void_p]),
+    "lq4_cross_head_hadamard_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "lq4_block_rot_signs_from_seed": (C.c_int32, [C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "lq4_weights_upload": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_void_p)]),
     "lq4_weights_load_q4_file": (C.c_int32, [C.c_char_p, C.POINTER(C.c_uint64), C.c_uint32, C.POINTER(C.c_void_p)]),

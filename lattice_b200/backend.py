@@ -394,6 +394,16 @@ class CudaQ4Backend:
         check(_lib.lib().lq4_hadamard_rows(x.data_ptr(), out.data_ptr(), x.numel() // signs.numel(), C.byref(rot), _stream()))
         return out
 
+    def cross_head_hadamard_rows(self, x: torch.Tensor, signs: torch.Tensor, head_dim: int) -> torch.Tensor:
+        """The R3 "Hadamard heads" rotation of every row of ``x`` (``[rows, num_heads * head_dim]``,
+        ``num_heads = len(signs)``): mixes across heads at each within-head channel."""
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+        nh = signs.numel()
+        out = torch.empty_like(x)
+        check(_lib.lib().lq4_cross_head_hadamard_rows(x.data_ptr(), out.data_ptr(), x.numel() // max(nh * head_dim, 1),
+                                                      nh, head_dim, signs.data_ptr(), _stream()))
+        return out
+
     def linear(self, x: torch.Tensor, qw: Q4WeightBuf, *, lora: Optional[LoraDesc] = None,
                rot: Optional[RotDesc] = None, path: int = _lib.PATH_AUTO, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Convenience wrapper: ``x`` is ``[m, k]`` on the device, returns ``[m, n]`` f32."""

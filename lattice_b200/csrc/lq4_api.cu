@@ -723,6 +723,17 @@ lq4_status lq4_block_hadamard_rows(const float* x, float* out, uint32_t rows, ui
     return LQ4_OK;
 }
 
+lq4_status lq4_cross_head_hadamard_rows(const float* x, float* out, uint32_t rows, uint32_t num_heads,
+                                        uint32_t head_dim, const float* signs, void* stream) {
+    if (!x || !out || !signs) return fail(LQ4_ERR_NULL, "x, out and signs must be non-NULL");
+    if (!is_pow2(num_heads) || num_heads > 128) return fail(LQ4_ERR_ROT, "num_heads must be a power of two <= 128");
+    if (head_dim == 0) return fail(LQ4_ERR_ROT, "head_dim must be non-zero");
+    if ((uint64_t)num_heads * head_dim > LQ4_MAX_ROT_LEN) return fail(LQ4_ERR_ROT, "num_heads * head_dim above 1 << 24");
+    if ((uint64_t)rows * head_dim > 0x7fffffffull * 128) return fail(LQ4_ERR_OVERFLOW, "rows * head_dim does not fit");
+    LQ4_CUDA(launch_cross_head_rows(x, signs, num_heads, head_dim, rows, out, (cudaStream_t)stream));
+    return LQ4_OK;
+}
+
 lq4_status lq4_block_rot_signs_from_seed(uint64_t seed, uint32_t n, uint32_t block, float* signs, void* stream) {
     lq4_status st;
     if ((st = check_block_rotation(n, block))) return st;

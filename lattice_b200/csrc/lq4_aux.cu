@@ -164,6 +164,49 @@ cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs,
     return cudaGetLastError();
 }
 
+// The cross-head rotation H_NH (x) I_head_dim of an activation [NH * head_dim] ("Hadamard heads", the R3
+// rotation in front of o_proj): one thread per (row, within-head channel) gathers the NH values of its
+// channel across the heads, applies signs and the butterflies in the sequential order (bit-identical to
+// the scalar loop), scales and scatters.  Neighbouring threads take neighbouring channels: coalesced.
+template <int NH>
+__global__ void __launch_bounds__(128) cross_head_rows_kernel(const float* __restrict__ x, const float* __restrict__ signs,
+                                                              uint32_t head_dim, uint64_t total, float* __restrict__ out) {
+    const uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const uint64_t row = idx / head_dim, base = row * NH * head_dim + (idx - row * head_dim);
+    float v[NH];
+#pragma unroll
+    for (int h = 0; h < NH; ++h) v[h] = __fmul_rn(x[base + (uint64_t)h * head_dim], signs[h]);
+#pragma unroll
+    for (int hh = 1; hh < NH; hh <<= 1)
+#pragma unroll
+        for (int i = 0; i < NH; i += 2 * hh)
+#pragma unroll
+            for (int j = i; j < i + hh; ++j) {
+                const float p = v[j], q = v[j + hh];
+                v[j] = __fadd_rn(p, q);
+                v[j + hh] = __fsub_rn(p, q);
+            }
+    const float sc = __fdiv_rn(1.0f, __fsqrt_rn((float)NH));
+#pragma unroll
+    for (int h = 0; h < NH; ++h) out[base + (uint64_t)h * head_dim] = __fmul_rn(v[h], sc);
+}
+
+cudaError_t launch_cross_head_rows(const float* x, const float* signs, uint32_t num_heads, uint32_t head_dim,
+                                   uint32_t rows, float* out, cudaStream_t s) {
+    const uint64_t total = (uint64_t)rows * head_dim;
+    if (total == 0) return cudaSuccess;
+    const unsigned grid = (unsigned)((total + 127) / 128);
+    switch (num_heads) {
+#define LQ4_CH_CASE(NH) case NH: cross_head_rows_kernel<NH><<<grid, 128, 0, s>>>(x, signs, head_dim, total, out); break;
+        LQ4_CH_CASE(1) LQ4_CH_CASE(2) LQ4_CH_CASE(4) LQ4_CH_CASE(8) LQ4_CH_CASE(16) LQ4_CH_CASE(32) LQ4_CH_CASE(64)
+        LQ4_CH_CASE(128)
+#undef LQ4_CH_CASE
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
 // splitmix64 sign stream: state_i = seed + (i + 2) * gamma, sign = +1 when the mixed low bit is 0.
 __global__ void rot_signs_kernel(uint64_t seed, uint32_t dim, float* __restrict__ signs) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -16,6 +16,8 @@ void launch_quantize(const float* data, uint64_t len, int symmetric, uint8_t* pa
                      int sm_count, cudaStream_t s);
 cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs, uint32_t dim, uint32_t rows,
                                  float* out, cudaStream_t s, uint32_t sign_rows = 1);
+cudaError_t launch_cross_head_rows(const float* x, const float* signs, uint32_t num_heads, uint32_t head_dim,
+                                   uint32_t rows, float* out, cudaStream_t s);
 void launch_block_rot_signs(uint64_t seed, uint32_t n, uint32_t block, float* signs, cudaStream_t s);
 void launch_rot_signs(uint64_t seed, uint32_t dim, float* signs, cudaStream_t s);
 

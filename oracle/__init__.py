@@ -92,6 +92,7 @@ def lib() -> C.CDLL:
         L.orc_gemv_q4_decode_form.argtypes = [vp, vp, vp, sz, sz]
         L.orc_topk.argtypes = [vp, sz, sz, vp, vp]
         L.orc_block_hadamard_check.argtypes = [sz, sz]
+        L.orc_cross_head_rotation_f32.argtypes = [vp, sz, sz, vp]
         L.orc_block_hadamard_signs.argtypes = [u64, sz, sz, vp]
         L.orc_block_hadamard_apply_f32.argtypes = [vp, sz, sz, vp, C.c_int]
         L.orc_topk.restype = None
@@ -345,4 +346,14 @@ def block_hadamard_apply(signs, data, block: int, inverse: bool = False) -> np.n
     if d.size != s.size:
         raise OracleError(ERR_SHAPE, "block_hadamard_apply")
     _check(lib().orc_block_hadamard_apply_f32(_p(s), s.size, block, _p(d), 1 if inverse else 0), "block_hadamard_apply")
+    return d
+
+
+def cross_head_rotation(signs, data, head_dim: int) -> np.ndarray:
+    """The R3 "Hadamard heads" rotation of one [num_heads * head_dim] activation; num_heads = len(signs)."""
+    s = _c(signs, np.float32).reshape(-1)
+    d = np.array(data, dtype=np.float32, copy=True).reshape(-1)
+    if d.size != s.size * head_dim:
+        raise OracleError(ERR_SHAPE, "cross_head_rotation")
+    _check(lib().orc_cross_head_rotation_f32(_p(s), s.size, head_dim, _p(d)), "cross_head_rotation")
     return d

@@ -838,6 +838,25 @@ void orc_gemv_q4_decode_form(const float* x, const uint8_t* payload, float* y, s
     }
 }
 
+/* QuaRot's online "Hadamard heads" factor H_num_heads (x) I_head_dim on a [num_heads * head_dim] activation
+ * (apply_cross_head_rotation, crates/inference/src/quant/quarot/r3_reference.rs:246-264; the R3 descriptor
+ * is OnlineRotationSpec::r3_full_attention, quant/quarot/plan.rs): for every within-head channel d the
+ * num_heads values data[h * head_dim + d] are gathered, rotated by ONE RandomizedHadamard of dimension
+ * num_heads (signs, then the orthonormal transform) and scattered back. */
+int orc_cross_head_rotation_f32(const float* signs, size_t num_heads, size_t head_dim, float* data) {
+    if (!is_pow2(num_heads)) return ORC_ERR_POW2;
+    float* channel = (float*)malloc(num_heads * sizeof(float));
+    if (!channel) return ORC_ERR_SHAPE;
+    int rc = ORC_OK;
+    for (size_t d = 0; d < head_dim && rc == ORC_OK; ++d) {
+        for (size_t h = 0; h < num_heads; ++h) channel[h] = data[h * head_dim + d];
+        rc = orc_rh_apply_f32(signs, num_heads, channel);
+        for (size_t h = 0; h < num_heads; ++h) data[h * head_dim + d] = channel[h];
+    }
+    free(channel);
+    return rc;
+}
+
 /* Exact top-k of a logit row in the reference's candidate order:
  * topk_better (crates/inference/src/forward/shaders/qwen35.metal:1697-1703) ranks the higher logit
  * first and breaks ties towards the lower token id; a NaN logit becomes the sentinel

@@ -849,3 +849,21 @@ def test_rotation_descriptor_must_divide_k(be):
     y = be.linear(dev(case["x"]), qw, rot=be.rot_desc(signs, 128))       # all-plus signs, block 128: accepted
     be.check_device_status()
     qw.free()
+
+
+@pytest.mark.parametrize("nh,dh", [(8, 256), (16, 128), (32, 128), (2, 64), (128, 8), (1, 32)])
+def test_cross_head_rotation_bit_exact(be, nh, dh):
+    # R3 in front of o_proj: H_nh (x) I_dh on the gated attention output
+    signs_h = oracle.signs_from_seed(0x703 + nh, nh)
+    rng = np.random.default_rng(nh * dh)
+    x = rng.standard_normal((5, nh * dh)).astype(np.float32)
+    y = be.cross_head_hadamard_rows(dev(x), dev(signs_h), dh).cpu().numpy()
+    for r in range(5):
+        ref = oracle.cross_head_rotation(signs_h, x[r], dh)
+        assert np.array_equal(y[r].view(np.uint32), ref.view(np.uint32))
+    be.check_device_status()
+    from lattice_b200._lib import Lq4Error
+    if nh == 8:
+        with pytest.raises(Lq4Error) as e:
+            be.cross_head_hadamard_rows(dev(np.zeros((1, 6 * 4), np.float32)), dev(np.ones(6, np.float32)), 4)
+        assert e.value.status == _lib.ERR_ROT

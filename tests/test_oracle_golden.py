@@ -382,3 +382,26 @@ def test_block_hadamard_refuses_what_the_constructor_refuses():
         with pytest.raises(oracle.OracleError):
             oracle.block_hadamard_signs(1, n, b)
     oracle.block_hadamard_signs(1, 4096 * 2, 2)          # exactly 4096 blocks is accepted
+
+
+def test_cross_head_rotation_is_the_kronecker_factor_and_cancels_through_o_proj():
+    # r3_reference.rs:521-640: the rotation equals (H_nh D) (x) I_head_dim, and an o_proj whose rows were
+    # rotated the same way (input-side absorption) reproduces the dense product
+    nh, dh, hidden = 8, 16, 12
+    rng = np.random.default_rng(3)
+    signs = oracle.signs_from_seed(0x703, nh)
+    x = rng.standard_normal(nh * dh).astype(np.float32)
+    y = oracle.cross_head_rotation(signs, x, dh)
+    hmat = np.array([[1.0]])
+    while hmat.shape[0] < nh:
+        hmat = np.block([[hmat, hmat], [hmat, -hmat]])
+    r = (hmat / np.sqrt(nh)) @ np.diag(signs.astype(np.float64))
+    full = np.kron(r, np.eye(dh))
+    assert np.max(np.abs(full @ x.astype(np.float64) - y)) < 1e-5
+    # a block rotation over contiguous head_dim blocks is a different transform
+    assert np.max(np.abs(oracle.block_hadamard_apply(oracle.block_hadamard_signs(0x703, nh * dh, dh), x, dh) - y)) > 1e-2
+    w = rng.standard_normal((hidden, nh * dh)).astype(np.float32)
+    w_rot = np.stack([oracle.cross_head_rotation(signs, w[i], dh) for i in range(hidden)])
+    assert np.max(np.abs(w_rot.astype(np.float64) @ y - w.astype(np.float64) @ x)) < 1e-4
+    with pytest.raises(oracle.OracleError):
+        oracle.cross_head_rotation(np.ones(6, np.float32), np.zeros(6 * 4, np.float32), 4)
