@@ -693,7 +693,64 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
         out[name] = {"us_per_call": us, "us_projection_only": res["projection"], "us_topk_only": res["topk"],
                      "GB/s": byts / us / 1e3, "frac_hbm": byts / us / 1e3 / hbm_peak, "top_k": top_k, "timing": mode}
 
+    def bench_mlp(name, hidden, inter, rank, copies, reps):
+        """One token's dense FFN (gate||up -> silu*up -> down) through lq4_mlp_block, against the same
+        three steps as separate calls (grouped gate/up launch, gating pass in torch, down call)."""
+        sets = []
+        for c in range(copies):
+            gen.manual_seed(4242 + c)
+            w = torch.randn((2 * inter, hidden), generator=gen, device=dev) * 0.02
+            qgu = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), 2 * inter, hidden)
+            del w
+            w = torch.randn((hidden, inter), generator=gen, device=dev) * 0.02
+            qd = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), hidden, inter)
+            del w
+            sets.append((qgu, qd))
+        keep, descs = [], []
+        for k_in, n_out in ((hidden, inter), (hidden, inter), (inter, hidden)):
+            a = torch.randn((rank, k_in), generator=gen, device=dev) * 0.02
+            b = torch.randn((n_out, rank), generator=gen, device=dev) * 0.02
+            keep += [a, b]
+            descs.append(LoraDesc(a.data_ptr(), b.data_ptr(), rank, 2.0))
+        x = torch.randn((1, hidden), generator=gen, device=dev)
+        y = torch.empty((1, hidden), device=dev)
+        gu = torch.empty((1, 2 * inter), device=dev)
+        hbuf = torch.empty((1, inter), device=dev)
+        res = {}
+        for what in ("block", "separate"):
+            def call(i):
+                qgu, qd = sets[i % copies]
+                if what == "block":
+                    be.mlp_block(x, qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2], gate_up=gu, out=y)
+                else:
+                    be.dispatch_gemm_q4_at(x, 0, qgu, 0, gu, 0, 1, inter, hidden, lora=descs[0])
+                    be.dispatch_gemm_q4_at(x, 0, qgu, inter * (hidden // 32) * 20, gu, inter * 4, 1, inter, hidden, lora=descs[1])
+                    torch.mul(torch.nn.functional.silu(gu[:, :inter]), gu[:, inter:], out=hbuf)
+                    be.dispatch_gemm_q4(hbuf, 0, qd, y, 0, 1, hidden, inter, lora=descs[2])
+            for i in range(3):
+                call(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for i in range(reps):
+                    call(i)
+            g.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            res[what] = e0.elapsed_time(e1) * 1e3 / reps
+        byts = 3 * inter * (hidden // 32) * 20 + 4 * rank * 3 * (hidden + inter)
+        us = res["block"]
+        out[name] = {"us_per_block": us, "us_separate_calls": res["separate"], "GB/s": byts / us / 1e3,
+                     "frac_hbm": byts / us / 1e3 / hbm_peak, "weight_copies": copies, "timing": "cuda-graph replay"}
+
     try:
+        bench_mlp("mlp_block_M1_hidden5120_inter17408_lora16", 5120, 17408, 16, 2, 40)
         bench_linear("config1_M1_K1024_N3584_cold", 1, 1024, 3584, 0, 128, 512)
         bench_linear("config1_M1_K1024_N3584_warm", 1, 1024, 3584, 0, 1, 512)
         bench_linear("config2_M1_lora16_cold", 1, 1024, 3584, 16, 128, 512)

@@ -207,6 +207,33 @@ lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* args, void* stream);
  * the model's lifetime (crates/inference/src/forward/metal_qwen35.rs:599-702). */
 lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* args_with_host_x_y, void* stream);
 
+/* ---- dense MLP block: gate||up -> silu(gate) * up -> down -------------------------------- */
+
+/* The FFN half of encode_mlp_block for dense layers
+ * (crates/inference/src/forward/metal_qwen35/inner/layers/mod.rs:93-148): one matmul over the merged
+ * gate_up_proj rows (N = 2 * inter) with the gate_proj / up_proj adapters on the two halves of its output,
+ * silu_mul_fused (shaders/qwen35.metal:712-722), then down_proj with its adapter. */
+typedef struct {
+    const void* x;                 /* [m, hidden] activations (the normed hidden state) */
+    int32_t x_dtype;
+    uint32_t m, hidden, inter;
+    const uint8_t* w_gate_up;      /* Q4 rows [2 * inter, hidden]: gate rows, then up rows (the merged file of
+                                      q4_weights.rs:1362-1639) */
+    const uint8_t* w_down;         /* Q4 rows [hidden, inter] */
+    const lq4_lora_desc* lora_gate;   /* each may be NULL */
+    const lq4_lora_desc* lora_up;
+    const lq4_lora_desc* lora_down;
+    float* gate_up;                /* [m, 2 * inter] f32 scratch (activations.gate), OVERWRITTEN, contents
+                                      unspecified afterwards; NULL = the context's workspace */
+    float* y;                      /* [m, hidden] f32, OVERWRITTEN (activations.ffn_out) */
+} lq4_mlp_args;
+
+/* Two launches for one token: gate and up rows as one grouped launch, then down_proj, whose kernel applies
+ * silu(gate) * up to its own input while it stages the activations (no separate gating pass, no round
+ * trip of the gated vector through memory).  More tokens: the same three steps with a gating pass.
+ * hidden and inter divisible by 32 (LQ4_ERR_K otherwise). */
+lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* args, void* stream);
+
 /* ---- lm_head: vocabulary projection + exact top-k ----------------------------------------- */
 
 #define LQ4_MAX_TOP_K 256u       /* MAX_TOP_K of the reference's selection kernels (shaders/qwen35.metal:1686) */

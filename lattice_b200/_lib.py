@@ -42,6 +42,13 @@ class LinearArgs(C.Structure):
                 ("gather", C.POINTER(GatherDesc)), ("wait_gather", C.POINTER(GatherDesc))]
 
 
+class MlpArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("m", C.c_uint32), ("hidden", C.c_uint32),
+                ("inter", C.c_uint32), ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p),
+                ("lora_gate", C.POINTER(LoraDesc)), ("lora_up", C.POINTER(LoraDesc)),
+                ("lora_down", C.POINTER(LoraDesc)), ("gate_up", C.c_void_p), ("y", C.c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "lq4_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(C.c_void_p)]),
@@ -64,6 +71,7 @@ SIGNATURES = {
     "lq4_peer_buf_open": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "lq4_peer_buf_close": (C.c_int32, [C.c_void_p]),
     "lq4_gather_wait": (C.c_int32, [C.c_void_p, C.POINTER(GatherDesc), C.c_void_p]),
+    "lq4_mlp_block": (C.c_int32, [C.c_void_p, C.POINTER(MlpArgs), C.c_void_p]),
     "lq4_logits_topk": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]),
     "lq4_lm_head_topk": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_uint32, C.c_void_p, C.c_void_p]),
     "lq4_lora_apply": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32, C.c_uint32, C.c_void_p,

@@ -412,6 +412,30 @@ class CudaQ4Backend:
         self.dispatch_gemm_q4(x.contiguous(), 0, qw, y, 0, m, qw.n, k, lora=lora, rot=rot, path=path)
         return y
 
+    # ---- dense MLP block ------------------------------------------------------------------
+    def mlp_block(self, x: torch.Tensor, w_gate_up: Q4WeightBuf, w_down: Q4WeightBuf, *,
+                  lora_gate: Optional[LoraDesc] = None, lora_up: Optional[LoraDesc] = None,
+                  lora_down: Optional[LoraDesc] = None, gate_up: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The FFN half of the reference's ``encode_mlp_block`` for dense layers: merged gate||up projection
+        (``w_gate_up`` is ``[2 * inter, hidden]``), ``silu(gate) * up``, ``down_proj``; ``x`` is ``[m, hidden]``."""
+        from ._lib import MlpArgs
+        x = x.contiguous()
+        m, hidden = x.shape
+        inter = w_gate_up.n // 2
+        self._require_k("mlp_block", hidden)
+        self._require_k("mlp_block", inter)
+        if w_gate_up.k != hidden or w_gate_up.n != 2 * inter or w_down.k != inter or w_down.n != hidden:
+            raise ValueError("mlp_block: w_gate_up must be [2 * inter, hidden] and w_down [hidden, inter]")
+        y = out if out is not None else torch.empty((m, hidden), dtype=torch.float32, device=x.device)
+        args = MlpArgs(x.data_ptr(), self._dtype_of(x), m, hidden, inter, w_gate_up.payload_ptr, w_down.payload_ptr,
+                       C.pointer(lora_gate) if lora_gate is not None else None,
+                       C.pointer(lora_up) if lora_up is not None else None,
+                       C.pointer(lora_down) if lora_down is not None else None,
+                       gate_up.data_ptr() if gate_up is not None else None, y.data_ptr())
+        check(_lib.lib().lq4_mlp_block(self._ctx, C.byref(args), _stream()))
+        return y
+
     # ---- lm_head: vocabulary projection + exact top-k --------------------------------------
     @staticmethod
     def _split_candidates(cand: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

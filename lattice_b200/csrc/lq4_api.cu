@@ -49,7 +49,7 @@ struct lq4_ctx {
     uint64_t launches = 0;
     int32_t* status = nullptr;    // device status word
     uint32_t* tsync = nullptr;    // 64-bit launch counter of the decode kernels
-    Buf xrot, xs, t, tmsg, partials, hx, hy, gemm, logits, topk, topk_ctr;   // xs: activation limb records of the dense decode kernel
+    Buf xrot, xs, t, tmsg, partials, hx, hy, gemm, logits, topk, topk_ctr, mlp, mlp_h;   // xs: activation limb records of the dense decode kernel
     bool allow_grow = true;
     int pdl = 1;
 };
@@ -209,12 +209,15 @@ lq4_status run_dense(lq4_ctx* ctx, GemvParams* ps, uint32_t count, cudaStream_t 
 // One projection of at most 16 tokens through the decode kernels: a single token whose row fits
 // in shared memory takes the resident kernel, everything else the dense one.
 lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dtype, const float* signs,
-                        uint32_t m, float* y, uint64_t ldy, cudaStream_t s) {
+                        uint32_t m, float* y, uint64_t ldy, cudaStream_t s, const float* x_mul = nullptr) {
     GemvParams p;
     fill_params(ctx, a, x, x_dtype, m, y, ldy, p);
     lq4_status st;
+    if (x_mul && !(m == 1 && !signs && x_dtype == LQ4_DTYPE_F32 && gemv_resident_fits(1, a->k, false)))
+        return fail(LQ4_ERR_UNSUPPORTED, "a gated input needs one f32 token whose row fits the resident kernel");
     if (m == 1 && gemv_resident_fits(1, a->k, signs != nullptr)) {
         p.signs = signs;
+        p.x_mul = x_mul;
         const uint64_t total = (uint64_t)p.tiles * p.kg;
         const int grid = (int)(total < (uint64_t)ctx->sm_count ? total : (uint64_t)ctx->sm_count);
         if ((st = ensure(ctx, ctx->partials, (size_t)grid * kGemvTileRows * 4 * 8, true, s))) return st;
@@ -294,7 +297,7 @@ void lq4_ctx_destroy(lq4_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
-    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk, &ctx->topk_ctr})
+    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk, &ctx->topk_ctr, &ctx->mlp, &ctx->mlp_h})
         if (b->p) cudaFree(b->p);
     if (ctx->status) cudaFree(ctx->status);
     delete ctx;
@@ -605,6 +608,54 @@ lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* a, void* stream)
     }
     LQ4_CUDA(cudaStreamSynchronize(s));
     return LQ4_OK;
+}
+
+lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (!a) return fail(LQ4_ERR_NULL, "args is NULL");
+    if (a->m == 0) return LQ4_OK;
+    if (a->hidden == 0 || a->inter == 0) return fail(LQ4_ERR_SHAPE, "hidden and inter must be non-zero");
+    if (a->hidden % 32 != 0 || a->inter % 32 != 0) return fail(LQ4_ERR_K, "hidden and inter must be divisible by 32");
+    if (!a->x || !a->w_gate_up || !a->w_down || !a->y) return fail(LQ4_ERR_NULL, "x, w_gate_up, w_down and y must be non-NULL");
+    if ((uint64_t)a->m * 2 * a->inter > 0xffffffffull) return fail(LQ4_ERR_OVERFLOW, "m * 2 * inter does not fit");
+    cudaStream_t s = (cudaStream_t)stream;
+    lq4_status st;
+    float* gate_up = a->gate_up;
+    if (!gate_up) {
+        if ((st = ensure(ctx, ctx->mlp, (size_t)a->m * 2 * a->inter * 4, false, s))) return st;
+        gate_up = (float*)ctx->mlp.p;
+    }
+    // 1. gate rows and up rows of the merged matrix, each with its own adapter, into the two halves of
+    //    gate_up: two problems that share x, one launch where the shapes allow it
+    lq4_linear_args g[2] = {};
+    for (int i = 0; i < 2; ++i) {
+        g[i].x = a->x; g[i].x_dtype = a->x_dtype;
+        g[i].m = a->m; g[i].n = a->inter; g[i].k = a->hidden;
+        g[i].w = a->w_gate_up + (size_t)i * a->inter * (a->hidden / 32) * 20;
+        g[i].y = gate_up + (size_t)i * a->inter;
+        g[i].ldy = 2ull * a->inter;
+        g[i].lora = i == 0 ? a->lora_gate : a->lora_up;
+        g[i].path = LQ4_PATH_AUTO;
+    }
+    if ((st = lq4_linear_group(ctx, g, 2, stream))) return st;
+    // 2. down_proj on silu(gate) * up.  One token: the decode kernel gates its own input while it builds
+    //    the activation limbs (and in the adapter's projection); otherwise a gating pass of its own.
+    lq4_linear_args d = {};
+    d.x = gate_up; d.x_dtype = LQ4_DTYPE_F32;
+    d.m = a->m; d.n = a->hidden; d.k = a->inter;
+    d.w = a->w_down; d.y = a->y; d.ldy = 0;
+    d.lora = a->lora_down;
+    d.path = LQ4_PATH_AUTO;
+    if ((st = validate_linear(&d))) return st;
+    const uint32_t rank = d.lora ? d.lora->rank : 0;
+    const bool fused = a->m == 1 && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) && (a->inter % 4 == 0) &&
+                       rank <= (uint32_t)kGemvMaxRank && gemv_resident_fits(1, d.k, false);
+    if (fused) return run_gemv_mma(ctx, &d, gate_up, LQ4_DTYPE_F32, nullptr, 1, d.y, d.n, s, gate_up + a->inter);
+    if ((st = ensure(ctx, ctx->mlp_h, (size_t)a->m * a->inter * 4, false, s))) return st;
+    LQ4_CUDA(launch_silu_mul_rows(gate_up, a->m, a->inter, (float*)ctx->mlp_h.p, ctx->sm_count, s));
+    ctx->launches += 1;
+    d.x = ctx->mlp_h.p;
+    return lq4_linear(ctx, &d, stream);
 }
 
 lq4_status lq4_logits_topk(lq4_ctx* ctx, const float* logits, uint32_t n, uint32_t top_k, lq4_topk_candidate* out,

@@ -207,6 +207,27 @@ cudaError_t launch_cross_head_rows(const float* x, const float* signs, uint32_t 
     return cudaGetLastError();
 }
 
+// h[row][i] = silu(gate_up[row][i]) * gate_up[row][inter + i]: the gating between the merged gate||up
+// projection and down_proj, for the shapes whose down_proj kernel does not gate its own input.
+__global__ void __launch_bounds__(256) silu_mul_rows_kernel(const float* __restrict__ gate_up, uint32_t inter,
+                                                            uint64_t total, float* __restrict__ h) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const uint64_t row = i / inter, c = i - row * inter;
+        const float* g = gate_up + row * 2 * inter;
+        h[i] = silu_mul(g[c], g[inter + c]);
+    }
+}
+
+cudaError_t launch_silu_mul_rows(const float* gate_up, uint32_t rows, uint32_t inter, float* h, int sm_count,
+                                 cudaStream_t s) {
+    const uint64_t total = (uint64_t)rows * inter;
+    if (total == 0) return cudaSuccess;
+    const uint64_t want = (total + 255) / 256, cap = (uint64_t)sm_count * 8;
+    silu_mul_rows_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, s>>>(gate_up, inter, total, h);
+    return cudaGetLastError();
+}
+
 // splitmix64 sign stream: state_i = seed + (i + 2) * gamma, sign = +1 when the mixed low bit is 0.
 __global__ void rot_signs_kernel(uint64_t seed, uint32_t dim, float* __restrict__ signs) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -82,6 +82,10 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
+// SwiGLU gating as the reference's silu_mul_fused computes it: gate / (1 + exp(-gate)) * up
+// (crates/inference/src/forward/shaders/qwen35.metal:712-722).
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.0f + expf(-gate)) * up; }
+
 // ---- programmatic dependent launch ----------------------------------------------
 __device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -18,6 +18,8 @@ cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs,
                                  float* out, cudaStream_t s, uint32_t sign_rows = 1);
 cudaError_t launch_cross_head_rows(const float* x, const float* signs, uint32_t num_heads, uint32_t head_dim,
                                    uint32_t rows, float* out, cudaStream_t s);
+cudaError_t launch_silu_mul_rows(const float* gate_up, uint32_t rows, uint32_t inter, float* h, int sm_count,
+                                 cudaStream_t s);
 void launch_block_rot_signs(uint64_t seed, uint32_t n, uint32_t block, float* signs, cudaStream_t s);
 void launch_rot_signs(uint64_t seed, uint32_t dim, float* signs, cudaStream_t s);
 
@@ -40,6 +42,7 @@ struct GemvParams {
     uint32_t tiles;         // ceil(n / 128)
     uint32_t nstages;
     const void* x;          // activations [m, k]
+    const float* x_mul;      // resident kernel, one f32 token, no rotation: the activations are silu(x[i]) * x_mul[i] (NULL: x itself)
     int32_t x_dtype;
     const float* signs;     // resident kernel only; non-NULL: rotate in the prologue (k a power of two)
     const uint8_t* xs_g;    // dense kernel: activation limb records prepared by launch_dense_prep

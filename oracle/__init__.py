@@ -92,6 +92,8 @@ def lib() -> C.CDLL:
         L.orc_gemv_q4_decode_form.argtypes = [vp, vp, vp, sz, sz]
         L.orc_topk.argtypes = [vp, sz, sz, vp, vp]
         L.orc_block_hadamard_check.argtypes = [sz, sz]
+        L.orc_silu_mul.argtypes = [vp, sz, vp]
+        L.orc_silu_mul.restype = None
         L.orc_cross_head_rotation_f32.argtypes = [vp, sz, sz, vp]
         L.orc_block_hadamard_signs.argtypes = [u64, sz, sz, vp]
         L.orc_block_hadamard_apply_f32.argtypes = [vp, sz, sz, vp, C.c_int]
@@ -357,3 +359,27 @@ def cross_head_rotation(signs, data, head_dim: int) -> np.ndarray:
         raise OracleError(ERR_SHAPE, "cross_head_rotation")
     _check(lib().orc_cross_head_rotation_f32(_p(s), s.size, head_dim, _p(d)), "cross_head_rotation")
     return d
+
+
+def silu_mul(gate_up, inter: int) -> np.ndarray:
+    """silu_mul_fused on rows of merged gate || up values: [m, 2 * inter] -> [m, inter]."""
+    g = _c(gate_up, np.float32).reshape(-1, 2 * inter)
+    out = np.zeros((g.shape[0], inter), np.float32)
+    for r in range(g.shape[0]):
+        row = np.ascontiguousarray(g[r])
+        o = np.zeros(inter, np.float32)
+        lib().orc_silu_mul(_p(row), inter, _p(o))
+        out[r] = o
+    return out
+
+
+def mlp_block(x, w_gate_up_payload, w_down_payload, m: int, hidden: int, inter: int,
+              lora_gate=None, lora_up=None, lora_down=None) -> np.ndarray:
+    """The dense FFN of encode_mlp_block (inner/layers/mod.rs:93-148): merged gate||up matmul with the
+    gate_proj / up_proj adapters on its two halves, silu_mul_fused, down_proj with its adapter."""
+    p = _c(w_gate_up_payload, np.uint8).reshape(-1)
+    half = inter * (hidden // 32) * 20
+    gate = q4_linear(x, p[:half], m, inter, hidden, lora=lora_gate)
+    up = q4_linear(x, p[half:2 * half], m, inter, hidden, lora=lora_up)
+    h = silu_mul(np.concatenate([gate, up], axis=1), inter)
+    return q4_linear(h, w_down_payload, m, hidden, inter, lora=lora_down)

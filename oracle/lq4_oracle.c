@@ -857,6 +857,16 @@ int orc_cross_head_rotation_f32(const float* signs, size_t num_heads, size_t hea
     return rc;
 }
 
+/* silu_mul_fused (crates/inference/src/forward/shaders/qwen35.metal:712-722) on one token's merged
+ * gate || up row: out[i] = gate[i] / (1 + exp(-gate[i])) * up[i], gate = data[0, count), up = data[count, 2 count). */
+void orc_silu_mul(const float* gate_up, size_t count, float* out) {
+    for (size_t i = 0; i < count; ++i) {
+        float gate = gate_up[i], up = gate_up[count + i];
+        float s = gate / (1.0f + expf(-gate));
+        out[i] = s * up;
+    }
+}
+
 /* Exact top-k of a logit row in the reference's candidate order:
  * topk_better (crates/inference/src/forward/shaders/qwen35.metal:1697-1703) ranks the higher logit
  * first and breaks ties towards the lower token id; a NaN logit becomes the sentinel

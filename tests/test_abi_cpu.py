@@ -165,3 +165,9 @@ def test_block_rotation_entry_points_refuse_what_the_reference_constructor_refus
     rot = _lib.RotDesc(C.cast(buf, C.c_void_p).value, 48)
     assert L.lq4_block_hadamard_rows(buf, buf, 1, 96, C.byref(rot), None) == _lib.ERR_ROT
     assert L.lq4_block_hadamard_rows(None, buf, 1, 96, C.byref(rot), None) == _lib.ERR_NULL
+
+
+def test_mlp_block_validates_without_a_device(L):
+    assert L.lq4_mlp_block(None, None, None) == _lib.ERR_NULL
+    args = _lib.MlpArgs()
+    assert L.lq4_mlp_block(None, C.byref(args), None) == _lib.ERR_NULL

@@ -405,3 +405,11 @@ def test_cross_head_rotation_is_the_kronecker_factor_and_cancels_through_o_proj(
     assert np.max(np.abs(w_rot.astype(np.float64) @ y - w.astype(np.float64) @ x)) < 1e-4
     with pytest.raises(oracle.OracleError):
         oracle.cross_head_rotation(np.ones(6, np.float32), np.zeros(6 * 4, np.float32), 4)
+
+
+def test_silu_mul_matches_the_shader_formula():
+    g = np.array([[-20.0, -1.0, 0.0, 0.5, 3.0, 30.0, 2.0, -0.5, 1.5, 0.25, -3.0, 7.0]], np.float32)
+    out = oracle.silu_mul(g, 6)
+    gate, up = g[0, :6].astype(np.float64), g[0, 6:].astype(np.float64)
+    assert np.max(np.abs(out[0] - gate / (1.0 + np.exp(-gate)) * up)) < 1e-6
+    assert out[0, 2] == 0.0
