@@ -648,7 +648,8 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
     d.path = LQ4_PATH_AUTO;
     if ((st = validate_linear(&d))) return st;
     const uint32_t rank = d.lora ? d.lora->rank : 0;
-    const bool fused = a->m == 1 && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) && (a->inter % 4 == 0) &&
+    const bool fused = a->m == 1 && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) &&
+                       (!d.lora || aligned(d.lora->a, 16)) &&
                        rank <= (uint32_t)kGemvMaxRank && gemv_resident_fits(1, d.k, false);
     if (fused) return run_gemv_mma(ctx, &d, gate_up, LQ4_DTYPE_F32, nullptr, 1, d.y, d.n, s, gate_up + a->inter);
     if ((st = ensure(ctx, ctx->mlp_h, (size_t)a->m * a->inter * 4, false, s))) return st;

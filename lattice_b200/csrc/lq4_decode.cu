@@ -193,12 +193,19 @@ __device__ void decode_prologue(const GemvParams& p, uint8_t* smem, int ctid, ui
                         for (int e = 0; e < 8; ++e) v[u][e] = xrot[mp * K + o * 8 + e];
                     } else {
                         load8(p.x, p.x_dtype, (size_t)mp * K + (size_t)o * 8, v[u]);
-                        if (p.x_mul) {                        // gated input (one f32 token): silu(gate) * up
-                            float up[8];
-                            load8(p.x_mul, LQ4_DTYPE_F32, (size_t)o * 8, up);
+                    }
+                }
+            }
+            if (p.x_mul) {                                    // gated input (one f32 token): silu(gate) * up
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) v[u][e] = silu_mul(v[u][e], up[e]);
-                        }
+                for (int u = 0; u < kBatch; ++u) {
+                    const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                    const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+                    if (i < noct) {
+                        float up[8];
+                        load8(p.x_mul, LQ4_DTYPE_F32, (size_t)o * 8, up);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[u][e] = silu_mul(v[u][e], up[e]);
                     }
                 }
             }
@@ -287,10 +294,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) decode_kernel(const __grid_co
                 const bool vec4 = qq.x_dtype == LQ4_DTYPE_F32 && ((reinterpret_cast<uintptr_t>(qq.x) | reinterpret_cast<uintptr_t>(qq.la)) & 15u) == 0;
                 if (qq.x_mul) {
                     // gated input: the adapter sees silu(gate) * up like the Q4 rows do
-                    const float* g = static_cast<const float*>(qq.x);
-#pragma unroll 4
-                    for (uint32_t i = i0 * 4 + lane; i < i1 * 4; i += 32)
-                        s = fmaf(__ldg(arow + i), silu_mul(g[i], qq.x_mul[i]), s);
+                    const float4* a4 = reinterpret_cast<const float4*>(arow);
+                    const float4* g4 = reinterpret_cast<const float4*>(qq.x);
+                    const float4* u4 = reinterpret_cast<const float4*>(qq.x_mul);
+#pragma unroll 8
+                    for (uint32_t i = i0 + lane; i < i1; i += 32) {
+                        const float4 a = __ldg(a4 + i), g = g4[i], u = u4[i];
+                        s = fmaf(a.x, silu_mul(g.x, u.x), s); s = fmaf(a.y, silu_mul(g.y, u.y), s);
+                        s = fmaf(a.z, silu_mul(g.z, u.z), s); s = fmaf(a.w, silu_mul(g.w, u.w), s);
+                    }
                 } else if (vec4) {
                     const float4* a4 = reinterpret_cast<const float4*>(arow);
                     const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(qq.x) + (size_t)tok * qq.k);
