@@ -309,6 +309,15 @@ class CudaQ4Backend:
             raise
         self.lora = _LoraAdapter(projections, float(scale), max_rank)
 
+    def load_lora_adapter_file(self, path: str, quarot_seed: Optional[int] = None,
+                               quarot_hidden_dim: Optional[int] = None) -> "PeftAdapter":   # noqa: F821
+        """Reads a PEFT or MLX ``.safetensors`` adapter (bounded read, the reference's key grammar and refusals,
+        ``lattice_b200/lora_safetensors.py``) and loads it with scale ``alpha / rank``."""
+        from .lora_safetensors import load_peft_safetensors
+        adapter = load_peft_safetensors(path)
+        self.load_lora_adapter(adapter.layers, adapter.scale, quarot_seed, quarot_hidden_dim)
+        return adapter
+
     def unload_lora_adapter(self) -> None:
         if self.lora is not None:
             for d in self.lora.projections:

@@ -909,3 +909,26 @@ def test_mlp_block_matches_the_three_step_reference(be, m, hidden, inter, rank):
     assert diff == 0.0, f"scratch given vs workspace: max abs difference {diff}"
     qgu.free()
     qd.free()
+
+
+def test_adapter_from_a_safetensors_file_drives_the_fused_projection(be, tmp_path):
+    st_numpy = pytest.importorskip("safetensors.numpy")
+    from lattice_b200 import Q4WeightBuf
+    k, n, r = 1024, 512, 8
+    case = make_case(2, 1, k, n)
+    a, b = synth.lora_factors(2, r, k, n, extra=3)
+    path = tmp_path / "adapter_model.safetensors"
+    st_numpy.save_file({"base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight": a,
+                        "base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight": b},
+                       str(path), metadata={"alpha": "16"})
+    adapter = be.load_lora_adapter_file(str(path))
+    try:
+        assert adapter.rank == r and adapter.scale == 2.0 and be.has_lora_adapter()
+        qw = Q4WeightBuf.from_host_payload(case["payload"], n, k)
+        y = be.linear(dev(case["x"]), qw, lora=be.lora_desc(0, "q_proj"))
+        be.check_device_status()
+        y_ref = oracle.q4_linear(case["x"], None, 1, n, k, lora=(a, b, 2.0), w_f32=case["w_deq"])
+        assert tol_ratio(y.cpu().numpy(), y_ref) <= 1.0
+        qw.free()
+    finally:
+        be.unload_lora_adapter()
