@@ -124,3 +124,47 @@ class PeerGather:
             self.full = None
             L.lq4_peer_buf_free(self._buf)
             self._buf = None
+
+
+def merge_topk_candidates(vals: torch.Tensor, ids: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The best ``top_k`` of any number of candidate lists, in the reference's candidate order (higher logit
+    first, ties to the lower token id; shaders/qwen35.metal:1697-1703).  ``vals`` f32 and ``ids`` (token ids as
+    int64, or int32 holding u32 bit patterns) have the same shape; sentinel slots (-inf, 0xFFFFFFFF) lose to
+    every real candidate.  Exact: every shard's list is an exact local top-k, so their union holds the
+    global one (the merge-pass argument of shaders/qwen35.metal:1730-1770, across GPUs instead of tiles)."""
+    v = vals.reshape(-1).to(torch.float32)
+    i = ids.reshape(-1).to(torch.int64) & 0xFFFFFFFF
+    by_id = torch.argsort(i, stable=True)
+    v, i = v[by_id], i[by_id]
+    by_logit = torch.argsort(v, descending=True, stable=True)      # stable: equal logits keep ascending ids
+    v, i = v[by_logit][:top_k], i[by_logit][:top_k]
+    return v, i
+
+
+class ShardedLmHead:
+    """Vocabulary rows sharded over the ranks (``shard_plan``): every rank selects the exact top-k of its own
+    rows on the device (``lq4_lm_head_topk``), the candidates (k pairs per rank, not the logit row) are
+    all-gathered, and every rank merges them to the same global top-k.  The exchange is ``world * k * 8`` bytes."""
+
+    def __init__(self, vocab: int, k: int, local_topk: Callable[[torch.Tensor, int], Tuple[torch.Tensor, torch.Tensor]],
+                 group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.vocab = vocab
+        self.n0, self.n1, self.byte_offset = shard_plan(vocab, k, self.world, self.rank)
+        self.local_topk = local_topk              # (x, top_k) -> (logits[top_k], shard-local row ids[top_k])
+
+    def topk(self, x: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        vals, ids = self.local_topk(x, top_k)
+        ids = ids.to(torch.int64) & 0xFFFFFFFF
+        sentinel = ids == 0xFFFFFFFF
+        ids = torch.where(sentinel, ids, ids + self.n0)                  # shard-local row -> token id
+        if self.world == 1:
+            return merge_topk_candidates(vals, ids, top_k)
+        # one exchange: [logit bits | token id] as int64 pairs
+        mine = torch.stack([vals.to(torch.float32).contiguous().view(torch.int32).to(torch.int64), ids], dim=1).contiguous()
+        both = torch.empty((self.world * top_k, 2), dtype=torch.int64, device=mine.device)
+        dist.all_gather_into_tensor(both, mine, group=self.group)
+        all_vals = both[:, 0].to(torch.int32).view(torch.float32)
+        return merge_topk_candidates(all_vals, both[:, 1], top_k)

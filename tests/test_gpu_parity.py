@@ -932,3 +932,30 @@ def test_adapter_from_a_safetensors_file_drives_the_fused_projection(be, tmp_pat
         qw.free()
     finally:
         be.unload_lora_adapter()
+
+
+def test_vocabulary_sharded_lm_head_topk_merges_to_the_global_topk(be):
+    # two vocabulary shards on one GPU (the N-sharded lm_head of a 2-GPU group): local top-k per shard on the
+    # device, candidates merged as ShardedLmHead does after its exchange
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200.sharded import merge_topk_candidates, shard_plan
+    vocab, k, top_k = 6000 + 37, 1024, 40
+    case = make_case(3, 1, k, vocab)
+    x = dev(case["x"])
+    vals, ids, rows = [], [], []
+    for r in range(2):
+        n0, n1, off = shard_plan(vocab, k, 2, r)
+        shard = case["payload"][off: off + (n1 - n0) * (k // 32) * 20]
+        qw = Q4WeightBuf.from_host_payload(shard, n1 - n0, k)
+        full = torch.empty(n1 - n0, device="cuda")
+        v, i = be.lm_head_topk(x, qw, top_k, logits_out=full)
+        i = i.to(torch.int64) & 0xFFFFFFFF
+        vals.append(v.clone())
+        ids.append(torch.where(i == 0xFFFFFFFF, i, i + n0))
+        rows.append(full.cpu().numpy())
+        qw.free()
+    be.check_device_status()
+    mv, mi = merge_topk_candidates(torch.cat(vals), torch.cat(ids), top_k)
+    rv, ri = oracle.topk(np.concatenate(rows), top_k)               # exact on the logits the shards produced
+    assert np.array_equal(mi.cpu().numpy(), ri.astype(np.int64)) and np.array_equal(mv.cpu().numpy(), rv)
+    _assert_topk_agrees(case["y_ref"].reshape(-1), ri, rv, top_k)

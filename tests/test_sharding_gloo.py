@@ -68,3 +68,41 @@ def test_three_rank_uneven_plan():
     from lattice_b200.sharded import shard_plan
     sizes = [shard_plan(100, 64, 3, r) for r in range(3)]
     assert [s[0] for s in sizes] == [0, 33, 66] and sizes[-1][1] == 100
+
+
+def _topk_worker(rank, world, port, vocab, k, top_k, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from lattice_b200.sharded import ShardedLmHead
+
+    rng = np.random.default_rng(99)
+    logits = (rng.integers(-50, 50, vocab).astype(np.float32) * np.float32(0.5))      # many ties across the shards
+    logits[[3, vocab // 2, vocab - 1]] = np.nan
+
+    def local_topk(x, kk):
+        vals, ids = oracle.topk(logits[head.n0:head.n1], kk)      # stands in for lq4_lm_head_topk on this rank's rows
+        return torch.from_numpy(vals), torch.from_numpy(ids.view(np.int32).copy())
+
+    head = ShardedLmHead(vocab, k, local_topk)
+    vals, ids = head.topk(torch.zeros(1, k), top_k)
+    np.save(os.path.join(out_dir, f"v{rank}.npy"), vals.numpy())
+    np.save(os.path.join(out_dir, f"i{rank}.npy"), ids.numpy())
+    if rank == 0:
+        rv, ri = oracle.topk(logits, top_k)
+        np.save(os.path.join(out_dir, "rv.npy"), rv)
+        np.save(os.path.join(out_dir, "ri.npy"), ri.astype(np.int64))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("vocab,top_k", [(1000, 8), (37, 50)])      # 37 rows, 50 wanted: sentinels fill the tail
+def test_two_rank_sharded_lm_head_topk_is_the_global_topk(tmp_path, vocab, top_k):
+    world = 2
+    mp.spawn(_topk_worker, args=(world, _free_port(), vocab, 64, top_k, str(tmp_path)), nprocs=world, join=True)
+    rv, ri = np.load(tmp_path / "rv.npy"), np.load(tmp_path / "ri.npy")
+    for rank in range(world):
+        assert np.array_equal(np.load(tmp_path / f"i{rank}.npy"), ri)
+        assert np.array_equal(np.load(tmp_path / f"v{rank}.npy"), rv)
