@@ -637,7 +637,6 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
         g[i].lora = i == 0 ? a->lora_gate : a->lora_up;
         g[i].path = LQ4_PATH_AUTO;
     }
-    if ((st = lq4_linear_group(ctx, g, 2, stream))) return st;
     // 2. down_proj on silu(gate) * up.  One token: the decode kernel gates its own input while it builds
     //    the activation limbs (and in the adapter's projection); otherwise a gating pass of its own.
     lq4_linear_args d = {};
@@ -646,7 +645,10 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
     d.w = a->w_down; d.y = a->y; d.ldy = 0;
     d.lora = a->lora_down;
     d.path = LQ4_PATH_AUTO;
-    if ((st = validate_linear(&d))) return st;
+    if ((st = validate_linear(&d))) return st;          // all three projections are checked before the first launch
+    for (int i = 0; i < 2; ++i)
+        if ((st = validate_linear(&g[i]))) return st;
+    if ((st = lq4_linear_group(ctx, g, 2, stream))) return st;
     const uint32_t rank = d.lora ? d.lora->rank : 0;
     const bool fused = a->m == 1 && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) &&
                        (!d.lora || aligned(d.lora->a, 16)) &&

@@ -959,3 +959,21 @@ def test_vocabulary_sharded_lm_head_topk_merges_to_the_global_topk(be):
     rv, ri = oracle.topk(np.concatenate(rows), top_k)               # exact on the logits the shards produced
     assert np.array_equal(mi.cpu().numpy(), ri.astype(np.int64)) and np.array_equal(mv.cpu().numpy(), rv)
     _assert_topk_agrees(case["y_ref"].reshape(-1), ri, rv, top_k)
+
+
+def test_mlp_block_checks_all_three_projections_before_launching(be):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc, Lq4Error
+    hidden, inter = 256, 128
+    p_gu = oracle.quantize_f32_to_q4(synth.weights(1, 2 * inter, hidden, 1))
+    p_d = oracle.quantize_f32_to_q4(synth.weights(1, hidden, inter, 2))
+    qgu, qd = Q4WeightBuf.from_host_payload(p_gu, 2 * inter, hidden), Q4WeightBuf.from_host_payload(p_d, hidden, inter)
+    a = dev(np.zeros((4, inter), np.float32))
+    b = dev(np.zeros((hidden, 4), np.float32))
+    bad = LoraDesc(a.data_ptr(), b.data_ptr(), 0, 1.0)           # rank 0 on down_proj
+    before = be.launch_count
+    with pytest.raises(Lq4Error) as e:
+        be.mlp_block(dev(synth.activations(1, 1, hidden, 0)), qgu, qd, lora_down=bad)
+    assert e.value.status == _lib.ERR_LORA and be.launch_count == before
+    qgu.free()
+    qd.free()
