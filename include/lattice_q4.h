@@ -153,15 +153,19 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* args, void* stream);
 
 /* Several independent decode projections in ONE persistent launch.  `args[0..count)` are
  * complete lq4_linear problems; none may read what another one writes.  When every problem has
- * the same m <= 4, no rotation, k % 128 == 0, 16-byte aligned w and x, LoRA rank <= 128, and
+ * the same m <= 16, no rotation, k % 128 == 0, 16-byte aligned w and x, LoRA rank <= 128, and
  * count <= 8, the work of all problems is split evenly over the SMs as one range (launch,
- * activation prologue and tail are paid once, not once per projection) after one small launch
- * that projects every adapter's t = A x.  Any other group is served problem by problem through
- * lq4_linear, with identical results.  Replaces the reference's habit of encoding a decode
+ * activation prologue and tail are paid once, not once per projection).  Any other group is served
+ * problem by problem through lq4_linear, with identical results.  Replaces the reference's habit of encoding a decode
  * step's projections back to back into one Metal command buffer
  * (crates/inference/src/forward/metal_qwen35.rs:4458-4462, one encoder for all layers) and its
  * merged-row GEMVs with per-range adapters (inner/layers/gdn.rs:69-105,293-300: one GEMV over
- * qkv||z rows, then LoRA into sub-ranges): q/k/v, or gate/up, share x and go in one group. */
+ * qkv||z rows, then LoRA into sub-ranges): q/k/v, or gate/up, share x and go in one group.
+ * The adapters are projected inside the same launch by its producer warps (no launch of their own); the
+ * one-launch form takes m <= 16.  count == 1 is allowed: the single projection then runs on the grouped
+ * kernel (a group of one).  A decode step that interleaves grouped launches with single projections
+ * (o_proj, down_proj) should issue those this way: two different kernels in turn start every launch with
+ * a cold instruction cache (about 2.5 us per switch on B200), one kernel for both does not. */
 lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t count, void* stream);
 
 /* ---- peer buffers for the fused all-gather ------------------------------------ */

@@ -209,7 +209,8 @@ lq4_status run_dense(lq4_ctx* ctx, GemvParams* ps, uint32_t count, cudaStream_t 
 // One projection of at most 16 tokens through the decode kernels: a single token whose row fits
 // in shared memory takes the resident kernel, everything else the dense one.
 lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dtype, const float* signs,
-                        uint32_t m, float* y, uint64_t ldy, cudaStream_t s, const float* x_mul = nullptr) {
+                        uint32_t m, float* y, uint64_t ldy, cudaStream_t s, const float* x_mul = nullptr,
+                        bool as_group = false) {
     GemvParams p;
     fill_params(ctx, a, x, x_dtype, m, y, ldy, p);
     lq4_status st;
@@ -229,6 +230,22 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
         }
         const size_t smem = decode_plan_smem(p);
         if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "resident plan does not fit");
+        // Decode steps alternate grouped launches (q/k/v, gate/up) with single ones (o_proj, down_proj), and two
+        // different kernels in turn start each launch with a cold instruction cache: about 2.5 us per switch
+        // here.  A caller that knows a grouped launch comes before (lq4_mlp_block; lq4_linear_group with one
+        // problem) asks for the grouped kernel's instantiation, as a group of one.  On its own the single
+        // kernel's plan (more stages, whole-tile mode) is about 1.5 us quicker per launch.
+        if (as_group && !signs) {
+            GemvParams g = p;
+            const size_t gsmem = decode_group_plan_smem(&g, 1);
+            if (gsmem) {
+                const uint64_t gunits = decode_group_units(&g, 1);
+                const int ggrid = (int)(gunits < (uint64_t)ctx->sm_count ? gunits : (uint64_t)ctx->sm_count);
+                LQ4_CUDA(launch_decode_group(&g, 1, gsmem, ggrid, s));
+                ctx->launches += 1;
+                return LQ4_OK;
+            }
+        }
         const uint64_t units = decode_units(p);
         const int dgrid = (int)(units < (uint64_t)ctx->sm_count ? units : (uint64_t)ctx->sm_count);
         LQ4_CUDA(launch_decode(p, smem, dgrid, s));
@@ -435,6 +452,17 @@ lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t 
 
     // One launch serves the whole group when every problem is a decode-kernel case of the same
     // token count; anything else runs problem by problem with the same results.
+    if (count == 1) {
+        // a group of one: the same result as lq4_linear, on the grouped kernel's instantiation where the
+        // shape allows it (for callers that interleave single projections with grouped launches)
+        const lq4_linear_args& a = args[0];
+        const uint32_t rank = a.lora ? a.lora->rank : 0;
+        const bool fits = a.m == 1 && a.n > 0 && !a.rot && (a.k % 128 == 0) && aligned(a.w, 16) && aligned(a.x, 16) &&
+                          rank <= (uint32_t)kGemvMaxRank && (a.path == LQ4_PATH_AUTO || a.path == LQ4_PATH_GEMV_MMA) &&
+                          !(a.wait_gather && a.wait_gather->world > 1) && gemv_resident_fits(1, a.k, false);
+        if (!fits) return lq4_linear(ctx, &a, stream);
+        return run_gemv_mma(ctx, &a, a.x, a.x_dtype, nullptr, 1, a.y, a.ldy ? a.ldy : a.n, s, nullptr, true);
+    }
     bool one_launch = count >= 2 && count <= (uint32_t)kMaxGroup;
     GemvParams ps[kMaxGroup];
     const uint32_t m = args[0].m;
@@ -653,7 +681,7 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
     const bool fused = a->m == 1 && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) &&
                        (!d.lora || aligned(d.lora->a, 16)) &&
                        rank <= (uint32_t)kGemvMaxRank && gemv_resident_fits(1, d.k, false);
-    if (fused) return run_gemv_mma(ctx, &d, gate_up, LQ4_DTYPE_F32, nullptr, 1, d.y, d.n, s, gate_up + a->inter);
+    if (fused) return run_gemv_mma(ctx, &d, gate_up, LQ4_DTYPE_F32, nullptr, 1, d.y, d.n, s, gate_up + a->inter, true);
     if ((st = ensure(ctx, ctx->mlp_h, (size_t)a->m * a->inter * 4, false, s))) return st;
     LQ4_CUDA(launch_silu_mul_rows(gate_up, a->m, a->inter, (float*)ctx->mlp_h.p, ctx->sm_count, s));
     ctx->launches += 1;

@@ -977,3 +977,18 @@ def test_mlp_block_checks_all_three_projections_before_launching(be):
     assert e.value.status == _lib.ERR_LORA and be.launch_count == before
     qgu.free()
     qd.free()
+
+
+def test_group_of_one_runs_the_single_projection_on_the_grouped_kernel(be):
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    case = make_case(2, 1, 2048, 1536, rank=16, alpha=32.0)
+    qw = Q4WeightBuf.from_host_payload(case["payload"], case["n"], case["k"])
+    a, b, s = case["lora"]
+    ad, bd = dev(a), dev(b)
+    before = be.launch_count
+    (y,) = be.linear_group([(dev(case["x"]), qw, LoraDesc(ad.data_ptr(), bd.data_ptr(), 16, s))])
+    assert be.launch_count == before + 1
+    be.check_device_status()
+    assert tol_ratio(y.cpu().numpy(), case["y_ref"]) <= 1.0
+    qw.free()
