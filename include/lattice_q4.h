@@ -230,6 +230,10 @@ typedef struct {
     float* gate_up;                /* [m, 2 * inter] f32 scratch (activations.gate), OVERWRITTEN, contents
                                       unspecified afterwards; NULL = the context's workspace */
     float* y;                      /* [m, hidden] f32, OVERWRITTEN (activations.ffn_out) */
+    const lq4_rot_desc* rot_down;  /* NULL, or the online rotation of silu(gate) * up in front of down_proj
+                                      (R4: block-diagonal, dim = block size; OnlineRotationSpec::r4_dense_mlp,
+                                      quant/quarot/plan.rs); the gated vector is then formed by a pass of its
+                                      own and rotated before the projection reads it */
 } lq4_mlp_args;
 
 /* Two launches for one token: gate and up rows as one grouped launch, then down_proj, whose kernel applies

@@ -46,7 +46,8 @@ class MlpArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("m", C.c_uint32), ("hidden", C.c_uint32),
                 ("inter", C.c_uint32), ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p),
                 ("lora_gate", C.POINTER(LoraDesc)), ("lora_up", C.POINTER(LoraDesc)),
-                ("lora_down", C.POINTER(LoraDesc)), ("gate_up", C.c_void_p), ("y", C.c_void_p)]
+                ("lora_down", C.POINTER(LoraDesc)), ("gate_up", C.c_void_p), ("y", C.c_void_p),
+                ("rot_down", C.POINTER(RotDesc))]
 
 
 # name -> (restype, argtypes); every symbol the header declares

@@ -425,7 +425,7 @@ class CudaQ4Backend:
     def mlp_block(self, x: torch.Tensor, w_gate_up: Q4WeightBuf, w_down: Q4WeightBuf, *,
                   lora_gate: Optional[LoraDesc] = None, lora_up: Optional[LoraDesc] = None,
                   lora_down: Optional[LoraDesc] = None, gate_up: Optional[torch.Tensor] = None,
-                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  out: Optional[torch.Tensor] = None, rot_down: Optional[RotDesc] = None) -> torch.Tensor:
         """The FFN half of the reference's ``encode_mlp_block`` for dense layers: merged gate||up projection
         (``w_gate_up`` is ``[2 * inter, hidden]``), ``silu(gate) * up``, ``down_proj``; ``x`` is ``[m, hidden]``."""
         from ._lib import MlpArgs
@@ -441,7 +441,8 @@ class CudaQ4Backend:
                        C.pointer(lora_gate) if lora_gate is not None else None,
                        C.pointer(lora_up) if lora_up is not None else None,
                        C.pointer(lora_down) if lora_down is not None else None,
-                       gate_up.data_ptr() if gate_up is not None else None, y.data_ptr())
+                       gate_up.data_ptr() if gate_up is not None else None, y.data_ptr(),
+                       C.pointer(rot_down) if rot_down is not None else None)
         check(_lib.lib().lq4_mlp_block(self._ctx, C.byref(args), _stream()))
         return y
 

@@ -672,13 +672,14 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
     d.m = a->m; d.n = a->hidden; d.k = a->inter;
     d.w = a->w_down; d.y = a->y; d.ldy = 0;
     d.lora = a->lora_down;
+    d.rot = a->rot_down;
     d.path = LQ4_PATH_AUTO;
     if ((st = validate_linear(&d))) return st;          // all three projections are checked before the first launch
     for (int i = 0; i < 2; ++i)
         if ((st = validate_linear(&g[i]))) return st;
     if ((st = lq4_linear_group(ctx, g, 2, stream))) return st;
     const uint32_t rank = d.lora ? d.lora->rank : 0;
-    const bool fused = a->m == 1 && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) &&
+    const bool fused = a->m == 1 && !d.rot && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) &&
                        (!d.lora || aligned(d.lora->a, 16)) &&
                        rank <= (uint32_t)kGemvMaxRank && gemv_resident_fits(1, d.k, false);
     if (fused) return run_gemv_mma(ctx, &d, gate_up, LQ4_DTYPE_F32, nullptr, 1, d.y, d.n, s, gate_up + a->inter, true);

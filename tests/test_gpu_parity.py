@@ -992,3 +992,27 @@ def test_group_of_one_runs_the_single_projection_on_the_grouped_kernel(be):
     be.check_device_status()
     assert tol_ratio(y.cpu().numpy(), case["y_ref"]) <= 1.0
     qw.free()
+
+
+@pytest.mark.parametrize("m", [1, 3])
+def test_mlp_block_with_the_r4_rotation_in_front_of_down_proj(be, m):
+    # down_proj's rows were rotated block by block offline; the gated activations get the same rotation online
+    from lattice_b200 import Q4WeightBuf
+    hidden, inter, block = 1024, 3584, 128
+    x = synth.activations(4, m, hidden, 0)
+    p_gu = oracle.quantize_f32_to_q4(synth.weights(4, 2 * inter, hidden, 1))
+    p_d = oracle.quantize_f32_to_q4(synth.weights(4, hidden, inter, 2))
+    signs_h = oracle.block_hadamard_signs(0xD0, inter, block)
+    half = inter * (hidden // 32) * 20
+    gate = oracle.q4_linear(x, p_gu[:half], m, inter, hidden)
+    up = oracle.q4_linear(x, p_gu[half:], m, inter, hidden)
+    h = oracle.silu_mul(np.concatenate([gate, up], axis=1), inter)
+    hr = np.stack([oracle.block_hadamard_apply(signs_h, h[i], block) for i in range(m)])
+    y_ref = oracle.q4_linear(hr, p_d, m, hidden, inter)
+    qgu, qd = Q4WeightBuf.from_host_payload(p_gu, 2 * inter, hidden), Q4WeightBuf.from_host_payload(p_d, hidden, inter)
+    signs = dev(signs_h)
+    y = be.mlp_block(dev(x), qgu, qd, rot_down=be.rot_desc(signs, block))
+    be.check_device_status()
+    assert tol_ratio(y.cpu().numpy(), y_ref) <= 1.0
+    qgu.free()
+    qd.free()
