@@ -792,6 +792,27 @@ def run_only(args):
         be.check_device_status()
         print("ok", args.only)
         return
+    elif args.only == "mlp-block":         # M=1 dense FFN, hidden 5120, inter 17408, three r=16 adapters
+        hidden, inter = 5120, 17408
+        w = torch.randn((2 * inter, hidden), device=dev) * 0.02
+        qgu = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), 2 * inter, hidden)
+        del w
+        w = torch.randn((hidden, inter), device=dev) * 0.02
+        qd = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), hidden, inter)
+        del w
+        keep, descs = [], []
+        for k_in, n_out in ((hidden, inter), (hidden, inter), (inter, hidden)):
+            a = torch.randn((LORA_RANK, k_in), device=dev) * 0.02
+            b = torch.randn((n_out, LORA_RANK), device=dev) * 0.02
+            keep += [a, b]
+            descs.append(LoraDesc(a.data_ptr(), b.data_ptr(), LORA_RANK, 2.0))
+        x = torch.randn((1, hidden), device=dev)
+        for _ in range(3):
+            y = be.mlp_block(x, qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2])
+        torch.cuda.synchronize()
+        be.check_device_status()
+        print("ok", args.only, float(y.abs().max()))
+        return
     elif args.only == "lm-head":           # M=1, vocabulary projection 5120 -> 248320 + exact top-50
         vocab, k = 248320, 5120
         parts = []
@@ -842,7 +863,7 @@ def main():
                          "diagnostics (no waiting for the peers / no exchange at all): their values are not results")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
-    ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set | lm-head: three launches of one case, for profiling")
+    ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set | mlp-block | lm-head: three launches of one case, for profiling")
     ap.add_argument("--no-aux", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
