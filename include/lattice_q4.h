@@ -238,7 +238,8 @@ typedef struct {
 
 /* Two launches for one token: gate and up rows as one grouped launch, then down_proj, whose kernel applies
  * silu(gate) * up to its own input while it stages the activations (no separate gating pass, no round
- * trip of the gated vector through memory).  More tokens: the same three steps with a gating pass.
+ * trip of the gated vector through memory); likewise up to 16 tokens (the record builder of the dense decode
+ * kernel gates).  More tokens: the same three steps with a gating pass.
  * hidden and inter divisible by 32 (LQ4_ERR_K otherwise). */
 lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* args, void* stream);
 

@@ -210,15 +210,16 @@ lq4_status run_dense(lq4_ctx* ctx, GemvParams* ps, uint32_t count, cudaStream_t 
 // in shared memory takes the resident kernel, everything else the dense one.
 lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, int x_dtype, const float* signs,
                         uint32_t m, float* y, uint64_t ldy, cudaStream_t s, const float* x_mul = nullptr,
-                        bool as_group = false) {
+                        bool as_group = false, uint32_t ldx = 0) {
     GemvParams p;
     fill_params(ctx, a, x, x_dtype, m, y, ldy, p);
     lq4_status st;
-    if (x_mul && !(m == 1 && !signs && x_dtype == LQ4_DTYPE_F32 && gemv_resident_fits(1, a->k, false)))
-        return fail(LQ4_ERR_UNSUPPORTED, "a gated input needs one f32 token whose row fits the resident kernel");
+    if (x_mul && (signs || x_dtype != LQ4_DTYPE_F32))
+        return fail(LQ4_ERR_UNSUPPORTED, "a gated input is f32 and takes no rotation");
+    p.x_mul = x_mul;
+    p.ldx = ldx;
     if (m == 1 && gemv_resident_fits(1, a->k, signs != nullptr)) {
         p.signs = signs;
-        p.x_mul = x_mul;
         const uint64_t total = (uint64_t)p.tiles * p.kg;
         const int grid = (int)(total < (uint64_t)ctx->sm_count ? total : (uint64_t)ctx->sm_count);
         if ((st = ensure(ctx, ctx->partials, (size_t)grid * kGemvTileRows * 4 * 8, true, s))) return st;
@@ -679,10 +680,14 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
         if ((st = validate_linear(&g[i]))) return st;
     if ((st = lq4_linear_group(ctx, g, 2, stream))) return st;
     const uint32_t rank = d.lora ? d.lora->rank : 0;
-    const bool fused = a->m == 1 && !d.rot && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) &&
-                       (!d.lora || aligned(d.lora->a, 16)) &&
-                       rank <= (uint32_t)kGemvMaxRank && gemv_resident_fits(1, d.k, false);
-    if (fused) return run_gemv_mma(ctx, &d, gate_up, LQ4_DTYPE_F32, nullptr, 1, d.y, d.n, s, gate_up + a->inter, true);
+    // up to 16 tokens: the decode kernels gate their own input (the resident kernel in its prologue, the dense
+    // kernel's record builder for 2..16 tokens), so the gated vector is never written
+    const bool fused = a->m <= (uint32_t)kGemvMaxM && !d.rot && d.k % 128 == 0 && aligned(d.w, 16) && aligned(gate_up, 16) &&
+                       (!d.lora || aligned(d.lora->a, 16)) && rank <= (uint32_t)kGemvMaxRank &&
+                       (a->m > 1 || gemv_resident_fits(1, d.k, false));
+    if (fused)
+        return run_gemv_mma(ctx, &d, gate_up, LQ4_DTYPE_F32, nullptr, a->m, d.y, d.n, s, gate_up + a->inter, true,
+                            2 * a->inter);
     if ((st = ensure(ctx, ctx->mlp_h, (size_t)a->m * a->inter * 4, false, s))) return st;
     LQ4_CUDA(launch_silu_mul_rows(gate_up, a->m, a->inter, (float*)ctx->mlp_h.p, ctx->sm_count, s));
     ctx->launches += 1;

@@ -153,13 +153,20 @@ struct DecodeArgs {
 
 // One CTA of 256 threads computes t[pr] = sum_k A[j][k] * x[tok][k] for pr = tok * rank + j, with a
 // fixed reduction order.
+// With x_mul the input is silu(x) * x_mul (f32, rows ldx floats apart).
 __device__ __forceinline__ void project_one(const void* __restrict__ x, int x_dtype, uint32_t k,
                                             const float* __restrict__ la, uint32_t rank, float* __restrict__ t,
-                                            uint32_t pr, int vec4) {
+                                            uint32_t pr, int vec4, const float* __restrict__ x_mul = nullptr,
+                                            uint32_t ldx = 0) {
     const uint32_t tok = pr / rank, j = pr - tok * rank;
     const float* arow = la + (size_t)j * k;
     float s = 0.0f;
-    if (vec4) {
+    if (x_mul) {
+        const float* g = static_cast<const float*>(x) + (size_t)tok * ldx;
+        const float* u = x_mul + (size_t)tok * ldx;
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < k; i += 256) s = fmaf(__ldg(arow + i), silu_mul(g[i], u[i]), s);
+    } else if (vec4) {
         const float4* a4 = reinterpret_cast<const float4*>(arow);
         const float4* x4 = reinterpret_cast<const float4*>(static_cast<const float*>(x) + (size_t)tok * k);
 #pragma unroll 4

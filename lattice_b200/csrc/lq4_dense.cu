@@ -32,6 +32,8 @@ __host__ __device__ constexpr uint32_t rec_bytes(uint32_t ng) { return ng * 288u
 
 struct PrepArgs {
     const void* x[kMaxGroup];
+    const float* x_mul[kMaxGroup];           // non-NULL: the input is silu(x) * x_mul, rows ldx floats apart
+    uint32_t ldx[kMaxGroup];
     const float* la[kMaxGroup];
     float* t[kMaxGroup];
     uint8_t* rec[kMaxGroup];
@@ -63,7 +65,8 @@ __global__ void __launch_bounds__(256) dense_prep_kernel(const __grid_constant__
         const uint32_t b = blockIdx.x - nlimb;
         uint32_t pi = 0;
         while (pi + 1 < a.count && b >= a.proj_start[pi + 1]) ++pi;
-        project_one(a.x[pi], a.x_dtype[pi], a.k[pi], a.la[pi], a.rank[pi], a.t[pi], b - a.proj_start[pi], a.vec4[pi]);
+        project_one(a.x[pi], a.x_dtype[pi], a.k[pi], a.la[pi], a.rank[pi], a.t[pi], b - a.proj_start[pi], a.vec4[pi],
+                    a.x_mul[pi], a.ldx[pi]);
         return;
     }
     uint32_t pi = 0;
@@ -75,7 +78,18 @@ __global__ void __launch_bounds__(256) dense_prep_kernel(const __grid_constant__
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-    if (in_range && slot < a.m) load8(a.x[pi], a.x_dtype[pi], (size_t)slot * K + (size_t)blk * 32 + t * 8, v);
+    if (in_range && slot < a.m) {
+        if (a.x_mul[pi]) {                       // gated input: silu(gate) * up, f32
+            const size_t at = (size_t)slot * a.ldx[pi] + (size_t)blk * 32 + t * 8;
+            float up[8];
+            load8(a.x[pi], LQ4_DTYPE_F32, at, v);
+            load8(a.x_mul[pi], LQ4_DTYPE_F32, at, up);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = silu_mul(v[i], up[i]);
+        } else {
+            load8(a.x[pi], a.x_dtype[pi], (size_t)slot * K + (size_t)blk * 32 + t * 8, v);
+        }
+    }
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
@@ -485,6 +499,7 @@ cudaError_t launch_dense_prep(const GemvParams* ps, uint32_t count, uint8_t* con
     for (uint32_t i = 0; i < count; ++i) {
         const GemvParams& p = ps[i];
         a.x[i] = p.x; a.x_dtype[i] = p.x_dtype; a.k[i] = p.k;
+        a.x_mul[i] = p.x_mul; a.ldx[i] = p.ldx ? p.ldx : p.k;
         a.la[i] = p.la; a.rank[i] = p.rank; a.t[i] = t[i]; a.rec[i] = rec[i];
         a.vec4[i] = p.x_dtype == LQ4_DTYPE_F32 && p.k % 4 == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
                     (reinterpret_cast<uintptr_t>(p.la) & 15) == 0;

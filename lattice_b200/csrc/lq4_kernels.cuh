@@ -42,7 +42,8 @@ struct GemvParams {
     uint32_t tiles;         // ceil(n / 128)
     uint32_t nstages;
     const void* x;          // activations [m, k]
-    const float* x_mul;      // resident kernel, one f32 token, no rotation: the activations are silu(x[i]) * x_mul[i] (NULL: x itself)
+    const float* x_mul;      // f32 activations, no rotation: the input is silu(x[i]) * x_mul[i] (NULL: x itself)
+    uint32_t ldx;            // with x_mul: floats between token rows of x and of x_mul (0: k)
     int32_t x_dtype;
     const float* signs;     // resident kernel only; non-NULL: rotate in the prologue (k a power of two)
     const uint8_t* xs_g;    // dense kernel: activation limb records prepared by launch_dense_prep
