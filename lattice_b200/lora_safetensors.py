@@ -247,3 +247,40 @@ def read_lora_file_bounded(path: str, max_bytes: int = MAX_LORA_SIZE) -> bytes:
 
 def load_peft_safetensors(path: str, max_bytes: int = MAX_LORA_SIZE) -> PeftAdapter:
     return load_peft_safetensors_bytes(read_lora_file_bounded(path, max_bytes))
+
+
+def _block_of(module: str) -> str:
+    """The transformer block a module's key is written under (safetensors.rs:526-530)."""
+    return "mlp" if module in ("gate_proj", "up_proj", "down_proj") else "self_attn"
+
+
+def save_peft_safetensors(path: str, layers, rank: int, alpha: float, target_modules: Optional[List[str]] = None,
+                          extra_metadata: Optional[Dict[str, str]] = None) -> None:
+    """PEFT-compatible export (safetensors.rs:505-585): F32 tensors ``base_model.model.model.layers.{i}.{block}.
+    {module}.lora_A.weight`` ``(rank, d_in)`` and ``...lora_B.weight`` ``(d_out, rank)``, header metadata ``rank``,
+    ``alpha`` and ``target_modules``; layers whose factors are empty are skipped."""
+    entries = []
+    for l in sorted(layers, key=lambda l: (l.layer_idx, l.module)):
+        a = np.ascontiguousarray(l.a, dtype="<f4")
+        b = np.ascontiguousarray(l.b, dtype="<f4")
+        if a.size == 0 or b.size == 0:
+            continue
+        if a.size != l.rank * l.d_in or b.size != l.d_out * l.rank:
+            raise LoraFileError(f"layer {l.layer_idx} module '{l.module}': factor sizes do not match rank, d_in, d_out")
+        stem = f"base_model.model.model.layers.{l.layer_idx}.{_block_of(l.module)}.{l.module}"
+        entries.append((stem + ".lora_A.weight", [l.rank, l.d_in], a.tobytes()))
+        entries.append((stem + ".lora_B.weight", [l.d_out, l.rank], b.tobytes()))
+    if target_modules is None:
+        target_modules = sorted({l.module for l in layers})
+    meta = {"rank": str(rank), "alpha": str(np.float32(alpha)) if float(alpha) != int(alpha) else str(int(alpha)),      # f32 Display
+            "target_modules": ",".join(target_modules)}
+    meta.update(extra_metadata or {})
+    header: Dict[str, object] = {"__metadata__": meta}
+    blob = bytearray()
+    for name, shape, raw in sorted(entries):                    # tensors in name order, offsets back to back
+        header[name] = {"dtype": "F32", "shape": shape, "data_offsets": [len(blob), len(blob) + len(raw)]}
+        blob += raw
+    h = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    h += b" " * ((8 - len(h) % 8) % 8)                          # the format pads the header to 8 bytes with spaces
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h + bytes(blob))

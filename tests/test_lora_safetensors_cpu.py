@@ -129,3 +129,43 @@ def test_container_checks_and_size_bound(tmp_path):
         ls.read_lora_file_bounded(str(path), max_bytes=len(good) - 1)
     with pytest.raises(ls.LoraFileError):
         ls.read_lora_file_bounded(str(tmp_path / "missing.safetensors"))
+
+
+def test_key_known_answers_of_the_reference_tests():
+    # crates/tune/src/lora/safetensors.rs:623-720
+    kat = {
+        "base_model.model.model.layers.5.self_attn.q_proj.lora_A.weight": (5, "q_proj", "A", False),
+        "base_model.model.model.layers.12.mlp.gate_proj.lora_B.weight": (12, "gate_proj", "B", False),
+        "model.layers.0.self_attn.v_proj.lora_A.weight": (0, "v_proj", "A", False),
+        "base_model.model.model.layers.3.mlp.up_proj.lora_B": (3, "up_proj", "B", False),
+        "model.layers.3.self_attn.q_proj.lora_a": (3, "q_proj", "A", True),
+        "model.layers.7.mlp.down_proj.lora_b": (7, "down_proj", "B", True),
+    }
+    for key, (layer, module, matrix, mlx) in kat.items():
+        k = ls.parse_peft_key(key)
+        assert (k.layer_idx, k.module, k.matrix, k.transposed) == (layer, module, matrix, mlx), key
+    for key in ("model.layers.0.self_attn.q_proj.weight", "some_random_tensor", ""):
+        assert ls.parse_peft_key(key) is None
+    for block, module in (("self_attn", "q_proj"), ("self_attn", "k_proj"), ("self_attn", "v_proj"), ("self_attn", "o_proj"),
+                          ("mlp", "gate_proj"), ("mlp", "up_proj"), ("mlp", "down_proj")):
+        k = ls.parse_peft_key(f"base_model.model.model.layers.7.{block}.{module}.lora_A.weight")
+        assert (k.layer_idx, k.module) == (7, module)
+
+
+def test_export_round_trips_and_is_readable_by_an_independent_reader(tmp_path):
+    from lattice_b200 import LoraLayerData
+    rng = np.random.default_rng(5)
+    layers = []
+    for layer, module in ((0, "q_proj"), (0, "down_proj"), (3, "in_proj_qkv")):
+        a, b = _factors(rng, 4, 16, 8)
+        layers.append(LoraLayerData(layer, module, a, b, 4, 16, 8))
+    path = tmp_path / "out.safetensors"
+    ls.save_peft_safetensors(str(path), layers, rank=4, alpha=8.0)
+    ad = ls.load_peft_safetensors(str(path))
+    assert ad.rank == 4 and ad.alpha == 8.0 and ad.metadata["target_modules"] == "down_proj,in_proj_qkv,q_proj"
+    got = {(l.layer_idx, l.module): l for l in ad.layers}
+    for l in layers:
+        assert np.array_equal(got[(l.layer_idx, l.module)].a, l.a) and np.array_equal(got[(l.layer_idx, l.module)].b, l.b)
+    other = st_numpy.load_file(str(path))
+    assert np.array_equal(other["base_model.model.model.layers.0.mlp.down_proj.lora_A.weight"], layers[1].a)
+    assert np.array_equal(other["base_model.model.model.layers.3.self_attn.in_proj_qkv.lora_B.weight"], layers[2].b)
