@@ -80,7 +80,7 @@ lq4_status ensure(lq4_ctx* ctx, Buf& b, size_t bytes, bool zero, cudaStream_t s)
     b.cap = 0;
     size_t cap = (bytes + 255) / 256 * 256;
     LQ4_CUDA(cudaMalloc(&b.p, cap));
-    if (zero) LQ4_CUDA(cudaMemset(b.p, 0, cap));
+    if (zero) LQ4_CUDA(cudaMemsetAsync(b.p, 0, cap, s));      // on the caller's stream: ordered before the first launch that reads it
     b.cap = cap;
     return LQ4_OK;
 }
