@@ -54,7 +54,7 @@ enum {
     LQ4_ERR_NOSPACE = 15       /* request exceeds a fixed capacity */
 };
 
-enum { LQ4_DTYPE_F32 = 0, LQ4_DTYPE_BF16 = 1 };
+enum { LQ4_DTYPE_F32 = 0, LQ4_DTYPE_BF16 = 1, LQ4_DTYPE_F64 = 2 };   /* F64: converter-side calls only */
 enum { LQ4_QUANT_ASYMMETRIC = 0, LQ4_QUANT_SYMMETRIC = 1 };
 
 /* Which kernel family lq4_linear picks.  AUTO is the product path. */
@@ -153,7 +153,7 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* args, void* stream);
 
 /* Several independent decode projections in ONE persistent launch.  `args[0..count)` are
  * complete lq4_linear problems; none may read what another one writes.  When every problem has
- * the same m <= 16, no rotation, k % 128 == 0, 16-byte aligned w and x, LoRA rank <= 128, and
+ * the same m <= 16, no rotation, k % 128 == 0, 16-byte aligned w and x, LoRA rank <= 512, and
  * count <= 8, the work of all problems is split evenly over the SMs as one range (launch,
  * activation prologue and tail are paid once, not once per projection).  Any other group is served
  * problem by problem through lq4_linear, with identical results.  Replaces the reference's habit of encoding a decode
@@ -204,6 +204,11 @@ lq4_status lq4_gather_wait(lq4_ctx* ctx, const lq4_gather_desc* gather, void* st
  * last call's contents (messages in it carry a per-launch tag, so nothing stale is reused): calls that
  * overlap on the GPU race, so order them on one stream.  `args->path` is ignored. */
 lq4_status lq4_linear_decode_noalloc(const lq4_linear_args* args, void* stream);
+/* The status word of lq4_linear_decode_noalloc lives in the same built-in array (that entry point has no
+ * context to ask).  Drains `stream`, reads the word of the current device with a 4-byte copy (no
+ * allocation), clears it, and returns LQ4_ERR_DEVICE if a kernel launched through the entry point gave up
+ * on a bounded wait since the last check.  No counterpart in the reference. */
+lq4_status lq4_noalloc_check(void* stream);
 
 /* Same call with HOST activations and HOST output: copies x to the device,
  * runs lq4_linear, copies y back and waits for it.  Weights and LoRA factors
@@ -288,6 +293,43 @@ lq4_status lq4_dequant_f32(const uint8_t* payload, uint64_t n_blocks, float* out
  * had a non-finite input or unrepresentable metadata. */
 lq4_status lq4_quantize_f32(const float* data, uint64_t len, int32_t mode, uint8_t* payload,
                             int32_t* status_out, void* stream);
+
+/* The other quantizer entry points of the reference, on the device.  `data` holds rows * cols values
+ * of `dtype`:
+ *   F32,  per_row = 0  quantize_f32_to_q4 (flat 32-value chunks across row ends; q4_weights.rs:470-487)
+ *   F32,  per_row = 1  quantize_tensor_q4_0 / quantize_row_q4_0 (every row ends in its own zero-padded
+ *                      block when cols % 32 != 0; q4_weights.rs:312-328, 364-388)
+ *   BF16, per_row = 0  quantize_bf16_to_q4 / stream_quantize_shard (widened exactly; :428-447, 580-606)
+ *   F64,  per_row = 0  quantize_f64_to_q4_mode: every value is narrowed to f32 first, as `v as f32`
+ *                      does (:514-553); mode SYMMETRIC is quantize_f64_to_q4, the QuaRot quantizer
+ * `payload` receives rows * ceil(cols / 32) blocks (per_row) or ceil(rows * cols / 32) blocks (flat);
+ * bit-identical to the reference.  Non-finite input (also an f64 beyond the f32 range) or metadata
+ * that f16 cannot hold sets *status_out to LQ4_ERR_BAD_BLOCK, like the reference's InvalidInput. */
+lq4_status lq4_quantize_tensor(const void* data, int32_t dtype, uint64_t rows, uint64_t cols, int32_t per_row,
+                               int32_t mode, uint8_t* payload, int32_t* status_out, void* stream);
+
+/* Rotation absorption of the offline QuaRot conversion, in place on a row-major [rows, cols] matrix of
+ * f32 or f64 (`dtype`) on the device, bit-identical to the reference's loops:
+ *   lq4_absorb_input_rotation   W <- W R^T, R applied to every row; rot->dim must equal cols
+ *     (absorb_input_rotation / absorb_input_rotation_f64,
+ *      crates/inference/src/quant/quarot/rotation.rs:86-107, 146-166)
+ *   lq4_absorb_output_rotation  W <- R W, R applied to every column; rot->dim must equal rows
+ *     (absorb_output_rotation / absorb_output_rotation_f64, rotation.rs:115-142, 169-195)
+ * These are what absorb_rotations (quant/quarot/pipeline.rs:202-235) calls per planned tensor with the
+ * f64 forms.  A dimension mismatch or a dim that is not a power of two returns LQ4_ERR_ROT (the
+ * reference's Err).  Row rotation: dim <= 16384 (f64) / 32768 (f32), the row is staged in shared memory. */
+lq4_status lq4_absorb_input_rotation(void* w, int32_t dtype, uint64_t rows, uint64_t cols,
+                                     const lq4_rot_desc* rot, void* stream);
+lq4_status lq4_absorb_output_rotation(void* w, int32_t dtype, uint64_t rows, uint64_t cols,
+                                      const lq4_rot_desc* rot, void* stream);
+
+/* Writes a `.q4` file exactly as save_q4_file does (crates/inference/src/weights/q4_weights.rs:623-645):
+ * "KHQ4", u32 version 2, u32 ndim, u64 shape[ndim], u64 original_len, then ceil(original_len / 32)
+ * blocks read from the DEVICE pointer `payload` (copied to the host on `stream`, which is drained).
+ * The product of `h_shape` must equal original_len (what the reference's constructors guarantee);
+ * ndim 1..8.  A file written here loads through lq4_weights_load_q4_file when it is 2-D. */
+lq4_status lq4_q4_file_write(const char* h_path, const uint64_t* h_shape, uint32_t ndim, uint64_t original_len,
+                             const uint8_t* payload, void* stream);
 
 /* Applies x' = H (D x) to `rows` rows of length `dim` (a power of two <= 16384),
  * f32 in and out, bit-identical to RandomizedHadamard::apply

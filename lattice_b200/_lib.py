@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "liblattice_q4.so")
 # status codes (include/lattice_q4.h)
 OK, ERR_NULL, ERR_K, ERR_OVERFLOW, ERR_ALIGN, ERR_DTYPE, ERR_LORA, ERR_ROT, ERR_BAD_BLOCK, ERR_CUDA, \
     ERR_UNSUPPORTED, ERR_DEVICE, ERR_FORMAT, ERR_IO, ERR_SHAPE, ERR_NOSPACE = range(16)
-DTYPE_F32, DTYPE_BF16 = 0, 1
+DTYPE_F32, DTYPE_BF16, DTYPE_F64 = 0, 1, 2
 QUANT_ASYMMETRIC, QUANT_SYMMETRIC = 0, 1
 PATH_AUTO, PATH_GEMV_MMA, PATH_GEMV_GENERIC, PATH_GEMM_TC = 0, 1, 2, 3
 
@@ -63,6 +63,7 @@ SIGNATURES = {
     "lq4_linear": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_void_p]),
     "lq4_linear_host": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_void_p]),
     "lq4_linear_decode_noalloc": (C.c_int32, [C.POINTER(LinearArgs), C.c_void_p]),
+    "lq4_noalloc_check": (C.c_int32, [C.c_void_p]),
     "lq4_linear_group": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_uint32, C.c_void_p]),
     "lq4_peer_buf_create": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p)]),
     "lq4_peer_buf_free": (None, [C.c_void_p]),
@@ -79,6 +80,11 @@ SIGNATURES = {
                                    C.c_uint32, C.c_uint64, C.POINTER(LoraDesc), C.c_void_p]),
     "lq4_dequant_f32": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]),
     "lq4_quantize_f32": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lq4_quantize_tensor": (C.c_int32, [C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_void_p,
+                                        C.c_void_p, C.c_void_p]),
+    "lq4_absorb_input_rotation": (C.c_int32, [C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(RotDesc), C.c_void_p]),
+    "lq4_absorb_output_rotation": (C.c_int32, [C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.POINTER(RotDesc), C.c_void_p]),
+    "lq4_q4_file_write": (C.c_int32, [C.c_char_p, C.POINTER(C.c_uint64), C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p]),
     "lq4_hadamard_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(RotDesc), C.c_void_p]),
     "lq4_rot_signs_from_seed": (C.c_int32, [C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p]),
     "lq4_block_hadamard_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(RotDesc), C.c_void_p]),

@@ -369,6 +369,40 @@ class CudaQ4Backend:
             raise Lq4Error(_lib.ERR_BAD_BLOCK, "a block had a non-finite value or unrepresentable scale/bias")
         return out
 
+    _QUANT_DTYPES = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16, torch.float64: _lib.DTYPE_F64}
+
+    def quantize_tensor(self, data: torch.Tensor, symmetric: bool = False, per_row: bool = False) -> torch.Tensor:
+        """The reference's other quantizer entry points on the device, chosen by ``data``'s dtype: f32 flat
+        (``quantize_f32_to_q4``) or per row (``quantize_tensor_q4_0``), bf16 (``quantize_bf16_to_q4``), f64
+        (``quantize_f64_to_q4_mode``; ``symmetric=True`` is ``quantize_f64_to_q4``).  ``data`` is 1-D or 2-D."""
+        assert data.is_cuda and data.is_contiguous() and data.dtype in self._QUANT_DTYPES
+        rows, cols = (1, data.numel()) if data.dim() == 1 else (data.shape[0], data.shape[1])
+        nb = rows * ((cols + 31) // 32) if per_row else (rows * cols + 31) // 32
+        out = torch.empty(nb * 20, dtype=torch.uint8, device=data.device)
+        st = torch.zeros(1, dtype=torch.int32, device=data.device)
+        check(_lib.lib().lq4_quantize_tensor(data.data_ptr(), self._QUANT_DTYPES[data.dtype], rows, cols, int(per_row),
+                                             int(symmetric), out.data_ptr(), st.data_ptr(), _stream()))
+        if int(st.item()) != 0:
+            raise Lq4Error(_lib.ERR_BAD_BLOCK, "a block had a non-finite value or unrepresentable scale/bias")
+        return out
+
+    def absorb_rotation(self, w: torch.Tensor, signs: torch.Tensor, side: str = "input") -> torch.Tensor:
+        """``absorb_input_rotation{,_f64}`` (``W <- W R^T``) or ``absorb_output_rotation{,_f64}`` (``W <- R W``)
+        in place on a 2-D f32 / f64 device tensor (crates/inference/src/quant/quarot/rotation.rs:86-195)."""
+        assert w.is_cuda and w.is_contiguous() and w.dim() == 2 and w.dtype in (torch.float32, torch.float64)
+        rot = self.rot_desc(signs)
+        fn = _lib.lib().lq4_absorb_input_rotation if side == "input" else _lib.lib().lq4_absorb_output_rotation
+        check(fn(w.data_ptr(), self._QUANT_DTYPES[w.dtype], w.shape[0], w.shape[1], C.byref(rot), _stream()))
+        return w
+
+    def save_q4_file(self, path: str, payload: torch.Tensor, shape) -> None:
+        """``save_q4_file`` (q4_weights.rs:623-645) for a device payload of ``prod(shape)`` weights."""
+        assert payload.is_cuda and payload.dtype == torch.uint8
+        shp = (C.c_uint64 * len(shape))(*shape)
+        n = int(np.prod(shape)) if len(shape) else 0
+        assert payload.numel() >= ((n + 31) // 32) * 20
+        check(_lib.lib().lq4_q4_file_write(str(path).encode(), shp, len(shape), n, payload.data_ptr(), _stream()))
+
     def rot_signs(self, seed: int, dim: int) -> torch.Tensor:
         s = torch.empty(dim, dtype=torch.float32, device=f"cuda:{self.device}")
         check(_lib.lib().lq4_rot_signs_from_seed(seed & (2 ** 64 - 1), dim, s.data_ptr(), _stream()))

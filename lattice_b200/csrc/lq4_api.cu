@@ -340,6 +340,9 @@ lq4_status lq4_ctx_reserve(lq4_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uin
         const size_t need = gemm_workspace_bytes(m, n, k, rank);
         if ((st = ensure(ctx, ctx->gemm, need, false, s))) return st;
     }
+    // the clears above ran on the legacy default stream, which does not order a later launch on a
+    // non-blocking stream behind them: finish them here (set-up time, not the hot path)
+    LQ4_CUDA(cudaStreamSynchronize(s));
     return LQ4_OK;
 }
 
@@ -373,10 +376,10 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     if (path == LQ4_PATH_AUTO) {
         if (!fast_layout) path = LQ4_PATH_GEMV_GENERIC;
         else if (a->m <= (uint32_t)kGemvMaxM) path = LQ4_PATH_GEMV_MMA;                          // decode kernels
-        else path = gemm_supported(a->m, a->n, a->k, rank) ? LQ4_PATH_GEMM_TC : LQ4_PATH_GEMV_MMA;
+        else path = gemm_supported(a->m, a->n, a->k, rank > (uint32_t)kGemmMaxRank ? 0u : rank) ? LQ4_PATH_GEMM_TC : LQ4_PATH_GEMV_MMA;
     }
     if (path != LQ4_PATH_GEMV_GENERIC && !fast_layout)
-        return fail(LQ4_ERR_ALIGN, "fast paths need k % 128 == 0, 16-byte aligned w and x, rank <= 128");
+        return fail(LQ4_ERR_ALIGN, "fast paths need k % 128 == 0, 16-byte aligned w and x, rank <= 512");
     if (a->gather && a->gather->world > 1 && (path != LQ4_PATH_GEMV_MMA || a->m > (uint32_t)kGemvMaxM))
         return fail(LQ4_ERR_UNSUPPORTED, "the fused all-gather is built into the decode kernels only (m <= 16, fast layout)");
 
@@ -414,17 +417,23 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
         return LQ4_OK;
     }
     if (path == LQ4_PATH_GEMM_TC) {
-        if (!gemm_supported(a->m, a->n, a->k, rank)) return fail(LQ4_ERR_UNSUPPORTED, "shape not handled by the tensor-core kernel");
-        const size_t need = gemm_workspace_bytes(a->m, a->n, a->k, rank);
+        // An adapter wider than the tensor-core kernel carries along (a blend of several adapters adds their
+        // ranks) is applied as the reference applies every adapter: the projection first, then
+        // y += scale * B (A x) in a pass of its own.
+        const bool wide = rank > (uint32_t)kGemmMaxRank;
+        const uint32_t grank = wide ? 0u : rank;
+        if (!gemm_supported(a->m, a->n, a->k, grank)) return fail(LQ4_ERR_UNSUPPORTED, "shape not handled by the tensor-core kernel");
+        const size_t need = gemm_workspace_bytes(a->m, a->n, a->k, grank);
         if ((st = ensure(ctx, ctx->gemm, need, false, s))) return st;
         int launches = 0;
         std::string err;
         cudaError_t e = launch_gemm_tc(x, x_dtype, a->w, a->y, ldy, a->m, a->n, a->k,
-                                       a->lora ? a->lora->a : nullptr, a->lora ? a->lora->b : nullptr, rank,
-                                       a->lora ? a->lora->scale : 0.0f, ctx->gemm.p, ctx->gemm.cap, ctx->status,
+                                       grank ? a->lora->a : nullptr, grank ? a->lora->b : nullptr, grank,
+                                       grank ? a->lora->scale : 0.0f, ctx->gemm.p, ctx->gemm.cap, ctx->status,
                                        ctx->sm_count, s, &launches, &err);
         ctx->launches += launches;
         if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, "tensor-core GEMM: " + err + ": " + cudaGetErrorString(e));
+        if (wide) return lq4_lora_apply(ctx, x, x_dtype, a->m, a->k, a->y, a->n, ldy, a->lora, stream);
         return LQ4_OK;
     }
     // generic
@@ -775,8 +784,96 @@ lq4_status lq4_quantize_f32(const float* data, uint64_t len, int32_t mode, uint8
     int dev = 0, sms = 0;
     LQ4_CUDA(cudaGetDevice(&dev));
     LQ4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    launch_quantize(data, len, mode == LQ4_QUANT_SYMMETRIC, payload, status_out, sms, (cudaStream_t)stream);
+    launch_quantize(data, LQ4_DTYPE_F32, 1, len, mode == LQ4_QUANT_SYMMETRIC, payload, status_out, sms, (cudaStream_t)stream);
     LQ4_CUDA(cudaGetLastError());
+    return LQ4_OK;
+}
+
+lq4_status lq4_quantize_tensor(const void* data, int32_t dtype, uint64_t rows, uint64_t cols, int32_t per_row,
+                               int32_t mode, uint8_t* payload, int32_t* status_out, void* stream) {
+    if (mul_overflows(rows, cols, (uint64_t)1 << 48))
+        return fail(LQ4_ERR_OVERFLOW, "Q4 tensor shape overflows the supported element count");   // checked first, as the reference does
+    if (rows == 0 || cols == 0) return LQ4_OK;
+    if (!data || !payload) return fail(LQ4_ERR_NULL, "data and payload must be non-NULL");
+    if (mode != LQ4_QUANT_ASYMMETRIC && mode != LQ4_QUANT_SYMMETRIC) return fail(LQ4_ERR_UNSUPPORTED, "unknown mode");
+    size_t esz;
+    switch (dtype) {
+        case LQ4_DTYPE_F32: esz = 4; break;
+        case LQ4_DTYPE_BF16: esz = 2; break;
+        case LQ4_DTYPE_F64: esz = 8; break;
+        default: return fail(LQ4_ERR_DTYPE, "unknown dtype");
+    }
+    if (!aligned(payload, 4) || !aligned(data, esz)) return fail(LQ4_ERR_ALIGN, "payload needs 4-byte alignment, data its element alignment");
+    int dev = 0, sms = 0;
+    LQ4_CUDA(cudaGetDevice(&dev));
+    LQ4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (per_row) launch_quantize(data, dtype, rows, cols, mode == LQ4_QUANT_SYMMETRIC, payload, status_out, sms, (cudaStream_t)stream);
+    else launch_quantize(data, dtype, 1, rows * cols, mode == LQ4_QUANT_SYMMETRIC, payload, status_out, sms, (cudaStream_t)stream);
+    LQ4_CUDA(cudaGetLastError());
+    return LQ4_OK;
+}
+
+static lq4_status check_absorb(const void* w, int32_t dtype, uint64_t rows, uint64_t cols, const lq4_rot_desc* rot,
+                               uint64_t must_match, const char* which) {
+    if (mul_overflows(rows, cols, (uint64_t)1 << 48)) return fail(LQ4_ERR_OVERFLOW, "rows*cols overflow");   // rotation.rs:64-68
+    if (!rot || !rot->signs) return fail(LQ4_ERR_NULL, "rot and rot->signs must be non-NULL");
+    if (dtype != LQ4_DTYPE_F32 && dtype != LQ4_DTYPE_F64) return fail(LQ4_ERR_DTYPE, "absorption takes f32 or f64 weights");
+    if (!is_pow2(rot->dim)) return fail(LQ4_ERR_ROT, "rotation needs a power-of-two dim");
+    if ((uint64_t)rot->dim != must_match)
+        return fail(LQ4_ERR_ROT, std::string("rotation.dim()=") + std::to_string(rot->dim) + " but weight." + which + "=" + std::to_string(must_match));
+    if (rows && cols && !w) return fail(LQ4_ERR_NULL, "w is NULL");
+    if (!aligned(w, dtype == LQ4_DTYPE_F64 ? 8 : 4)) return fail(LQ4_ERR_ALIGN, "w needs its element alignment");
+    return LQ4_OK;
+}
+
+lq4_status lq4_absorb_input_rotation(void* w, int32_t dtype, uint64_t rows, uint64_t cols, const lq4_rot_desc* rot,
+                                     void* stream) {
+    lq4_status st = check_absorb(w, dtype, rows, cols, rot, cols, "cols");
+    if (st) return st;
+    if ((uint64_t)rot->dim * (dtype == LQ4_DTYPE_F64 ? 8 : 4) > 128 * 1024)
+        return fail(LQ4_ERR_UNSUPPORTED, "row rotation stages the row in shared memory: dim <= 16384 (f64) or 32768 (f32)");
+    LQ4_CUDA(launch_absorb_input(w, dtype, rows, rot->dim, rot->signs, (cudaStream_t)stream));
+    return LQ4_OK;
+}
+
+lq4_status lq4_absorb_output_rotation(void* w, int32_t dtype, uint64_t rows, uint64_t cols, const lq4_rot_desc* rot,
+                                      void* stream) {
+    lq4_status st = check_absorb(w, dtype, rows, cols, rot, rows, "rows");
+    if (st) return st;
+    int dev = 0, sms = 0;
+    LQ4_CUDA(cudaGetDevice(&dev));
+    LQ4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    LQ4_CUDA(launch_absorb_output(w, dtype, rot->dim, cols, rot->signs, sms, (cudaStream_t)stream));
+    return LQ4_OK;
+}
+
+lq4_status lq4_q4_file_write(const char* h_path, const uint64_t* h_shape, uint32_t ndim, uint64_t original_len,
+                             const uint8_t* payload, void* stream) {
+    if (!h_path || !h_shape) return fail(LQ4_ERR_NULL, "path and shape must be non-NULL");
+    if (ndim == 0 || ndim > 8) return fail(LQ4_ERR_SHAPE, "ndim must be 1..8");
+    uint64_t prod = 1;
+    for (uint32_t i = 0; i < ndim; ++i) {
+        if (mul_overflows(prod, h_shape[i], (uint64_t)1 << 48)) return fail(LQ4_ERR_OVERFLOW, "shape product overflows");
+        prod *= h_shape[i];
+    }
+    if (prod != original_len) return fail(LQ4_ERR_SHAPE, "shape product does not equal original_len");
+    const uint64_t nb = (original_len + 31) / 32;
+    if (nb && !payload) return fail(LQ4_ERR_NULL, "payload is NULL");
+    std::vector<uint8_t> host((size_t)nb * 20);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (nb) {
+        LQ4_CUDA(cudaMemcpyAsync(host.data(), payload, host.size(), cudaMemcpyDeviceToHost, s));
+        LQ4_CUDA(cudaStreamSynchronize(s));
+    }
+    FILE* f = fopen(h_path, "wb");
+    if (!f) return fail(LQ4_ERR_IO, std::string("cannot create ") + h_path);
+    const uint32_t ver = 2;
+    bool ok = fwrite("KHQ4", 1, 4, f) == 4 && fwrite(&ver, 4, 1, f) == 1 && fwrite(&ndim, 4, 1, f) == 1;
+    for (uint32_t i = 0; ok && i < ndim; ++i) ok = fwrite(&h_shape[i], 8, 1, f) == 1;
+    ok = ok && fwrite(&original_len, 8, 1, f) == 1;
+    ok = ok && (host.empty() || fwrite(host.data(), 1, host.size(), f) == host.size());
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) return fail(LQ4_ERR_IO, std::string("short write to ") + h_path);
     return LQ4_OK;
 }
 

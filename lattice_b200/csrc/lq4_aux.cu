@@ -57,16 +57,32 @@ __device__ __forceinline__ bool scale_survives_f16(float s) {
     return isfinite(r) && r > 0.0f;
 }
 
-__global__ void __launch_bounds__(256) quantize_kernel(const float* __restrict__ data, uint64_t len,
+// Input element `idx` as the f32 the reference's block quantizer sees: f32 as is, bf16 widened
+// (quantize_bf16_to_q4), f64 narrowed with round-to-nearest-even like Rust's `as f32`
+// (quantize_f64_to_q4_mode); an f64 beyond the f32 range becomes infinite and is refused below.
+template <typename T>
+__device__ __forceinline__ float quant_input(const T* data, uint64_t idx);
+template <>
+__device__ __forceinline__ float quant_input<float>(const float* data, uint64_t idx) { return data[idx]; }
+template <>
+__device__ __forceinline__ float quant_input<uint16_t>(const uint16_t* data, uint64_t idx) { return bf16_to_f32(data[idx]); }
+template <>
+__device__ __forceinline__ float quant_input<double>(const double* data, uint64_t idx) { return __double2float_rn(data[idx]); }
+
+// `row_len` elements form one run of blocks: the whole flattened tensor for the flat entry points
+// (blocks cross row ends), one row for quantize_tensor_q4_0 (every row ends in its own padded block).
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ data, uint64_t rows, uint64_t row_len,
                                                        int symmetric, uint8_t* __restrict__ payload,
                                                        int32_t* __restrict__ status) {
     const uint32_t lane = threadIdx.x & 31;
-    const uint64_t n_blocks = (len + 31) / 32;
+    const uint64_t bpr = (row_len + 31) / 32;
+    const uint64_t n_blocks = rows * bpr;
     const uint64_t warps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
     for (uint64_t blk = (((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5); blk < n_blocks; blk += warps) {
-        const uint64_t idx = blk * 32 + lane;
-        const bool real = idx < len;
-        const float v = real ? data[idx] : 0.0f;       // padding slots hold zero
+        const uint64_t r = blk / bpr, col = (blk - r * bpr) * 32 + lane;
+        const bool real = col < row_len;
+        const float v = real ? quant_input<T>(data, r * row_len + col) : 0.0f;       // padding slots hold zero
         const bool finite = isfinite(v);
         float scale, bias, sub;
         if (symmetric) {
@@ -110,14 +126,19 @@ __global__ void __launch_bounds__(256) quantize_kernel(const float* __restrict__
     }
 }
 
-void launch_quantize(const float* data, uint64_t len, int symmetric, uint8_t* payload, int32_t* status,
-                     int sm_count, cudaStream_t s) {
-    const uint64_t n_blocks = (len + 31) / 32;
+void launch_quantize(const void* data, int dtype, uint64_t rows, uint64_t row_len, int symmetric, uint8_t* payload,
+                     int32_t* status, int sm_count, cudaStream_t s) {
+    const uint64_t n_blocks = rows * ((row_len + 31) / 32);
     uint64_t blocks = (n_blocks + 7) / 8;
     const uint64_t cap = (uint64_t)sm_count * 16;
     if (blocks > cap) blocks = cap;
     if (blocks == 0) return;
-    quantize_kernel<<<(unsigned)blocks, 256, 0, s>>>(data, len, symmetric, payload, status);
+    if (dtype == LQ4_DTYPE_BF16)
+        quantize_kernel<uint16_t><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint16_t*>(data), rows, row_len, symmetric, payload, status);
+    else if (dtype == LQ4_DTYPE_F64)
+        quantize_kernel<double><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const double*>(data), rows, row_len, symmetric, payload, status);
+    else
+        quantize_kernel<float><<<(unsigned)blocks, 256, 0, s>>>(static_cast<const float*>(data), rows, row_len, symmetric, payload, status);
 }
 
 // ---------------------------------------------------------------------------
@@ -162,6 +183,139 @@ cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs,
     if (rows == 0) return cudaSuccess;
     hadamard_rows_kernel<<<rows, dim >= 1024 ? 512 : (dim >= 128 ? dim / 2 : 64), smem, s>>>(x, x_dtype, signs, dim, sign_rows ? sign_rows : 1, out);
     return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Rotation absorption into weights (offline conversion), f32 or f64, in place.
+// Input side, W <- W R^T: R applied to every ROW (one CTA per row, the row in shared memory).
+// Output side, W <- R W: R applied to every COLUMN; the butterflies of a stage pair whole rows, so
+// they run over the matrix in place, three stages per pass, a thread per (column, group of 8 rows).
+// Every value is produced by the same single IEEE operation, on the same operands, as in the
+// reference's sequential loops, so the result is bit-identical.
+// ---------------------------------------------------------------------------
+template <typename T> struct Ieee;
+template <> struct Ieee<float> {
+    static __device__ __forceinline__ float mul(float a, float b) { return __fmul_rn(a, b); }
+    static __device__ __forceinline__ float add(float a, float b) { return __fadd_rn(a, b); }
+    static __device__ __forceinline__ float sub(float a, float b) { return __fsub_rn(a, b); }
+    static __device__ __forceinline__ float inv_sqrt(uint32_t n) { return __fdiv_rn(1.0f, __fsqrt_rn((float)n)); }
+};
+template <> struct Ieee<double> {
+    static __device__ __forceinline__ double mul(double a, double b) { return __dmul_rn(a, b); }
+    static __device__ __forceinline__ double add(double a, double b) { return __dadd_rn(a, b); }
+    static __device__ __forceinline__ double sub(double a, double b) { return __dsub_rn(a, b); }
+    static __device__ __forceinline__ double inv_sqrt(uint32_t n) { return __ddiv_rn(1.0, __dsqrt_rn((double)n)); }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(512) absorb_rows_kernel(T* __restrict__ w, const float* __restrict__ signs, uint32_t dim) {
+    extern __shared__ __align__(16) unsigned char absorb_smem[];
+    T* row = reinterpret_cast<T*>(absorb_smem);
+    T* g = w + (size_t)blockIdx.x * dim;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) row[i] = Ieee<T>::mul(g[i], (T)signs[i]);
+    __syncthreads();
+    for (uint32_t h = 1; h < dim; h <<= 1) {
+        for (uint32_t b = threadIdx.x; b < dim / 2; b += blockDim.x) {
+            const uint32_t j = ((b / h) * 2 * h) + (b % h);
+            const T p = row[j], q = row[j + h];
+            row[j] = Ieee<T>::add(p, q);
+            row[j + h] = Ieee<T>::sub(p, q);
+        }
+        __syncthreads();
+    }
+    const T sc = Ieee<T>::inv_sqrt(dim);
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) g[i] = Ieee<T>::mul(row[i], sc);
+}
+
+// One pass of the output-side transform: `stages` (1..3) butterfly levels starting at row distance h.
+// first: multiply by the signs on the way in; last: scale on the way out.
+template <typename T, int ST>
+__global__ void __launch_bounds__(256) absorb_cols_kernel(T* __restrict__ w, const float* __restrict__ signs, uint32_t dim,
+                                                          uint64_t cols, uint32_t h, int first, int last) {
+    constexpr uint32_t span = 1u << ST;                       // rows a thread combines
+    const uint64_t groups = dim / span;
+    const uint64_t total = groups * cols;
+    const T sc = Ieee<T>::inv_sqrt(dim);
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t gi = idx / cols, c = idx - gi * cols;
+        // group gi: rows base + i * h, i < span, where base keeps the bits below h and those above h * span
+        const uint64_t lowbits = gi % h, high = gi / h;
+        const uint64_t base = high * h * span + lowbits;
+        T v[span];
+#pragma unroll
+        for (uint32_t i = 0; i < span; ++i) {
+            const uint64_t r = base + (uint64_t)i * h;
+            T t = w[r * cols + c];
+            if (first) t = Ieee<T>::mul(t, (T)signs[r]);
+            v[i] = t;
+        }
+#pragma unroll
+        for (uint32_t hh = 1; hh < span; hh <<= 1)
+#pragma unroll
+            for (uint32_t i = 0; i < span; ++i) {
+                if (i & hh) continue;
+                const T p = v[i], q = v[i + hh];
+                v[i] = Ieee<T>::add(p, q);
+                v[i + hh] = Ieee<T>::sub(p, q);
+            }
+#pragma unroll
+        for (uint32_t i = 0; i < span; ++i) {
+            const uint64_t r = base + (uint64_t)i * h;
+            w[r * cols + c] = last ? Ieee<T>::mul(v[i], sc) : v[i];
+        }
+    }
+}
+
+template <typename T>
+static cudaError_t absorb_input_t(T* w, uint64_t rows, uint32_t dim, const float* signs, cudaStream_t s) {
+    const size_t smem = (size_t)dim * sizeof(T);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(absorb_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    const unsigned threads = dim >= 1024 ? 512 : (dim >= 128 ? dim / 2 : 64);
+    // the grid's x extent is a 31-bit count: rows beyond that go in further launches
+    for (uint64_t r0 = 0; r0 < rows; r0 += 0x40000000ull) {
+        const uint64_t nr = rows - r0 < 0x40000000ull ? rows - r0 : 0x40000000ull;
+        absorb_rows_kernel<T><<<(unsigned)nr, threads, smem, s>>>(w + r0 * dim, signs, dim);
+    }
+    return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t absorb_output_t(T* w, uint32_t dim, uint64_t cols, const float* signs, int sm_count, cudaStream_t s) {
+    uint32_t levels = 0;
+    while ((1u << levels) < dim) ++levels;
+    auto grid_for = [&](uint32_t st) {
+        const uint64_t total = (uint64_t)(dim >> st) * cols;
+        const uint64_t want = (total + 255) / 256, cap = (uint64_t)sm_count * 16;
+        return (unsigned)(want < cap ? want : cap);
+    };
+    if (levels == 0) {          // dim == 1: x * sign * 1
+        absorb_cols_kernel<T, 0><<<grid_for(0), 256, 0, s>>>(w, signs, dim, cols, 1, 1, 1);
+        return cudaGetLastError();
+    }
+    for (uint32_t l = 0; l < levels;) {
+        const uint32_t st = levels - l >= 3 ? 3 : levels - l;
+        const int first = l == 0, last = l + st == levels;
+        if (st == 3) absorb_cols_kernel<T, 3><<<grid_for(3), 256, 0, s>>>(w, signs, dim, cols, 1u << l, first, last);
+        else if (st == 2) absorb_cols_kernel<T, 2><<<grid_for(2), 256, 0, s>>>(w, signs, dim, cols, 1u << l, first, last);
+        else absorb_cols_kernel<T, 1><<<grid_for(1), 256, 0, s>>>(w, signs, dim, cols, 1u << l, first, last);
+        l += st;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_absorb_input(void* w, int dtype, uint64_t rows, uint32_t dim, const float* signs, cudaStream_t s) {
+    if (rows == 0) return cudaSuccess;
+    return dtype == LQ4_DTYPE_F64 ? absorb_input_t(static_cast<double*>(w), rows, dim, signs, s)
+                                  : absorb_input_t(static_cast<float*>(w), rows, dim, signs, s);
+}
+cudaError_t launch_absorb_output(void* w, int dtype, uint32_t dim, uint64_t cols, const float* signs, int sm_count,
+                                 cudaStream_t s) {
+    if (cols == 0) return cudaSuccess;
+    return dtype == LQ4_DTYPE_F64 ? absorb_output_t(static_cast<double*>(w), dim, cols, signs, sm_count, s)
+                                  : absorb_output_t(static_cast<float*>(w), dim, cols, signs, sm_count, s);
 }
 
 // The cross-head rotation H_NH (x) I_head_dim of an activation [NH * head_dim] ("Hadamard heads", the R3

@@ -676,11 +676,10 @@ inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 template <int MT, int NP>
 cudaError_t launch_mt(const DecodeArgs<NP>& ga, size_t smem, int grid, cudaStream_t s) {
     auto kern = decode_kernel<MT, NP>;
-    static bool attr_set = false;      // one opt-in to the full shared-memory carve-out per kernel
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - 1024);
+    static DeviceOnce once;            // the shared-memory opt-in is per device and per kernel instantiation
+    {
+        cudaError_t e = opt_in_smem(reinterpret_cast<const void*>(kern), kMaxSmem - 1024, once);
         if (e != cudaSuccess) return e;
-        attr_set = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);

@@ -421,11 +421,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) dense_kernel(const __grid_con
 template <int NG, int NP>
 cudaError_t launch_ng(const DecodeArgs<NP>& ga, size_t smem, int grid, cudaStream_t s) {
     auto kern = dense_kernel<NG, NP>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem - 1024);
+    static DeviceOnce once;            // the shared-memory opt-in is per device and per kernel instantiation
+    {
+        cudaError_t e = opt_in_smem(reinterpret_cast<const void*>(kern), kMaxSmem - 1024, once);
         if (e != cudaSuccess) return e;
-        attr_set = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);

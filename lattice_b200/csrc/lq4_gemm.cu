@@ -560,12 +560,11 @@ GemmWorkspace plan_workspace(uint32_t m, uint32_t n, uint32_t k, uint32_t rank, 
 
 cudaError_t launch_kernel(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tda,
                           const CUtensorMap& tdb, int sm_count, cudaStream_t s) {
-    static bool attr_set = false;
+    static DeviceOnce once;            // the shared-memory opt-in is per device
     const size_t smem = kGemmSmem + 1024;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        cudaError_t e = opt_in_smem(reinterpret_cast<const void*>(gemm_tc_kernel), (int)smem, once);
         if (e != cudaSuccess) return e;
-        attr_set = true;
     }
     const uint32_t tiles = p.n_tiles * p.m_tiles * p.ksplit;
     const uint32_t grid = tiles < (uint32_t)sm_count ? tiles : (uint32_t)sm_count;
@@ -576,7 +575,7 @@ cudaError_t launch_kernel(const GemmParams& p, const CUtensorMap& tx, const CUte
 }  // namespace
 
 bool gemm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t rank) {
-    return m > 0 && n > 0 && k > 0 && k % 128 == 0 && rank <= 128;
+    return m > 0 && n > 0 && k > 0 && k % 128 == 0 && rank <= (uint32_t)kGemmMaxRank;
 }
 
 size_t gemm_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, uint32_t rank) {

@@ -3,8 +3,20 @@
 #pragma once
 
 #include "lq4_common.cuh"
+#include "lq4_once.h"
 
 namespace lq4 {
+
+// Opts kernel `fn` in to `bytes` of dynamic shared memory on the CURRENT device, once per device.
+inline cudaError_t opt_in_smem(const void* fn, int bytes, DeviceOnce& once) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (!once.needs(dev)) return cudaSuccess;
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) once.mark(dev);
+    return e;
+}
 
 // ---- lq4_api.cu ---------------------------------------------------------------
 // Stores the message lq4_last_error() returns on the calling thread.
@@ -12,8 +24,14 @@ void set_last_error(const char* msg);
 
 // ---- lq4_aux.cu ---------------------------------------------------------------
 void launch_dequant(const uint8_t* payload, uint64_t n_blocks, float* out, int sm_count, cudaStream_t s);
-void launch_quantize(const float* data, uint64_t len, int symmetric, uint8_t* payload, int32_t* status,
-                     int sm_count, cudaStream_t s);
+// `rows` runs of `row_len` values of type `dtype` (LQ4_DTYPE_*), each run cut into 32-value blocks of its own.
+void launch_quantize(const void* data, int dtype, uint64_t rows, uint64_t row_len, int symmetric, uint8_t* payload,
+                     int32_t* status, int sm_count, cudaStream_t s);
+// Rotation absorption into a row-major weight matrix, in place (f32 or f64): R applied to every row of
+// length `dim`, or to every column of a matrix with `dim` rows.
+cudaError_t launch_absorb_input(void* w, int dtype, uint64_t rows, uint32_t dim, const float* signs, cudaStream_t s);
+cudaError_t launch_absorb_output(void* w, int dtype, uint32_t dim, uint64_t cols, const float* signs, int sm_count,
+                                 cudaStream_t s);
 cudaError_t launch_hadamard_rows(const void* x, int x_dtype, const float* signs, uint32_t dim, uint32_t rows,
                                  float* out, cudaStream_t s, uint32_t sign_rows = 1);
 cudaError_t launch_cross_head_rows(const float* x, const float* signs, uint32_t num_heads, uint32_t head_dim,
@@ -28,7 +46,8 @@ constexpr int kGemvTileRows = 128;        // output rows per tile: 8 consumer wa
 constexpr int kGemvGranuleBlocks = 4;     // stream-K split granularity along k (16-byte aligned pieces)
 constexpr int kGemvThreads = 288;         // 8 consumer warps + 1 producer warp
 constexpr int kGemvMaxM = 16;             // tokens per decode launch
-constexpr int kGemvMaxRank = 128;
+constexpr int kGemvMaxRank = 512;        // decode kernels (m <= 16); a blend of adapters adds their ranks
+constexpr int kGemmMaxRank = 128;        // tensor-core kernel: the adapter rides along as extra k segments
 constexpr int kMaxSmem = 232448;          // 227 KB opt-in limit per CTA
 
 // One projection as the decode kernels see it.
@@ -82,9 +101,10 @@ size_t decode_plan_smem(GemvParams& p);
 uint64_t decode_units(const GemvParams& p);
 cudaError_t launch_decode(const GemvParams& p, size_t smem, int grid, cudaStream_t s);
 // Pieces the resident kernel cuts each LoRA projection dot product into along k (one warp each).
+constexpr uint32_t kDecodeMaxTsplit = 8;
 inline uint32_t decode_tsplit(uint32_t k) {
     const uint32_t s = (k / 4 + 767) / 768;
-    return s < 1 ? 1 : (s > 8 ? 8 : s);
+    return s < 1 ? 1 : (s > kDecodeMaxTsplit ? kDecodeMaxTsplit : s);
 }
 // Several independent projections of the same token count in ONE persistent launch: the work
 // units of all problems form one stream-K range, so launch, prologue and tail are paid once.

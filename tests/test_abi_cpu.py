@@ -171,3 +171,66 @@ def test_mlp_block_validates_without_a_device(L):
     assert L.lq4_mlp_block(None, None, None) == _lib.ERR_NULL
     args = _lib.MlpArgs()
     assert L.lq4_mlp_block(None, C.byref(args), None) == _lib.ERR_NULL
+
+
+def test_converter_entry_points_validate_without_a_device(L, tmp_path):
+    buf = (C.c_float * 64)()
+    ptr = C.cast(buf, C.c_void_p).value
+    # empty tensors are no-ops; NULL and unknown dtypes are refused before any launch
+    assert L.lq4_quantize_tensor(None, _lib.DTYPE_F32, 0, 32, 0, 0, None, None, None) == _lib.OK
+    assert L.lq4_quantize_tensor(None, _lib.DTYPE_F32, 2, 32, 0, 0, None, None, None) == _lib.ERR_NULL
+    assert L.lq4_quantize_tensor(ptr, 7, 2, 32, 0, 0, ptr, None, None) == _lib.ERR_DTYPE
+    assert L.lq4_quantize_tensor(ptr, _lib.DTYPE_F32, 1 << 40, 1 << 40, 0, 0, ptr, None, None) == _lib.ERR_OVERFLOW
+    # rotation absorption: the reference's shape check (rotation.rs:55-80) comes first
+    rot = _lib.RotDesc(ptr, 64)
+    assert L.lq4_absorb_input_rotation(ptr, _lib.DTYPE_F64, 4, 32, C.byref(rot), None) == _lib.ERR_ROT
+    assert b"rotation.dim()=64 but weight.cols=32" in L.lq4_last_error()
+    assert L.lq4_absorb_output_rotation(ptr, _lib.DTYPE_F32, 32, 4, C.byref(rot), None) == _lib.ERR_ROT
+    assert b"weight.rows=32" in L.lq4_last_error()
+    bad = _lib.RotDesc(ptr, 48)
+    assert L.lq4_absorb_input_rotation(ptr, _lib.DTYPE_F32, 4, 48, C.byref(bad), None) == _lib.ERR_ROT
+    assert L.lq4_absorb_input_rotation(ptr, _lib.DTYPE_BF16, 4, 64, C.byref(rot), None) == _lib.ERR_DTYPE
+    assert L.lq4_absorb_input_rotation(ptr, _lib.DTYPE_F32, 4, 64, None, None) == _lib.ERR_NULL
+    # the writer: header rules without a device (an empty tensor has no payload to fetch)
+    shp = (C.c_uint64 * 2)(0, 32)
+    path = tmp_path / "empty.q4"
+    assert L.lq4_q4_file_write(str(path).encode(), shp, 2, 0, None, None) == _lib.OK
+    assert path.read_bytes() == oracle.q4_file_bytes([0, 32], 0, np.zeros(0, np.uint8))
+    shp = (C.c_uint64 * 2)(4, 32)
+    assert L.lq4_q4_file_write(str(path).encode(), shp, 2, 127, None, None) == _lib.ERR_SHAPE
+    assert L.lq4_q4_file_write(str(path).encode(), shp, 0, 128, None, None) == _lib.ERR_SHAPE
+    assert L.lq4_q4_file_write(None, shp, 2, 128, None, None) == _lib.ERR_NULL
+    assert L.lq4_q4_file_write(str(path).encode(), shp, 2, 128, None, None) == _lib.ERR_NULL
+
+
+def test_kernel_attribute_bookkeeping_is_per_device(tmp_path):
+    """The shared-memory opt-in of a kernel is a per-device attribute: the bookkeeping that decides whether
+    to repeat it must answer per device, not per process (a process may drive several GPUs)."""
+    import subprocess
+    src = tmp_path / "once.cc"
+    src.write_text('''
+#include "lq4_once.h"
+#include <cstdio>
+#include <initializer_list>
+int main() {
+    static lq4::DeviceOnce once;
+    int bad = 0;
+    for (int d : {0, 1, 63, 64, 255}) bad += !once.needs(d);
+    once.mark(0);
+    bad += once.needs(0);              // device 0 is done ...
+    bad += !once.needs(1);             // ... device 1 is not
+    once.mark(64); once.mark(255);
+    bad += once.needs(64) + once.needs(255) + !once.needs(63) + !once.needs(65);
+    bad += !once.needs(-1) + !once.needs(256);      // outside the table: always repeat (harmless)
+    once.mark(256); once.mark(-1);
+    once.reset();
+    bad += !once.needs(0) + !once.needs(64);
+    std::printf("%d\\n", bad);
+    return bad;
+}
+''')
+    exe = tmp_path / "once"
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "lattice_b200", "csrc"), str(src), "-o", str(exe)],
+                   check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0 and res.stdout.strip() == "0"
