@@ -395,6 +395,48 @@ void lq4_lora_free(lq4_lora* l);
 lq4_status lq4_shard_plan(uint64_t n, uint64_t k, uint32_t world, uint32_t rank,
                           uint64_t* n0, uint64_t* n1, uint64_t* byte_offset);
 
+/* ---- N-sharded linear with the slices gathered over NCCL ------------------------------------ */
+
+/* The communicator is the caller's: a Rust host passes the ncclComm_t of its own NCCL binding.  The three
+ * calls below wrap ncclGetUniqueId / ncclCommInitRank / ncclCommDestroy for hosts without one: rank 0
+ * draws an id, hands its 128 bytes to the other ranks by any transport, and every rank (its GPU current)
+ * creates the communicator.  The library binds NCCL at run time (the libnccl.so.2 already loaded in the
+ * process, else the system's); without one these calls return LQ4_ERR_UNSUPPORTED.  No counterpart in
+ * the reference (single GPU). */
+#define LQ4_NCCL_ID_BYTES 128
+lq4_status lq4_nccl_unique_id(uint8_t* h_id_out);
+lq4_status lq4_nccl_comm_create(const uint8_t* h_id, uint32_t world, uint32_t rank, void** comm_out);
+void lq4_nccl_comm_destroy(void* comm);
+
+typedef struct {
+    void* nccl_comm;      /* ncclComm_t, one rank per GPU */
+    uint32_t world, rank;
+    uint64_t n_total;     /* rows of the whole weight = columns of the gathered output */
+    float* y_full;        /* [m, ldy_full] f32 on this GPU, OVERWRITTEN with every rank's columns */
+    uint64_t ldy_full;    /* elements between rows of y_full; 0 means n_total */
+} lq4_shard_desc;
+
+/* Column-parallel linear: `local` describes THIS rank's rows of the weight exactly as a plain lq4_linear
+ * call would (w = payload + lq4_shard_plan's byte offset, n = n1 - n0, the same rows of LoRA B; its y and
+ * the fused-gather fields are ignored), the library computes the slice and all-gathers the [m, n / world]
+ * slices of all ranks into y_full[:, n0_r : n1_r] with ncclAllGather (equal slices) or grouped
+ * ncclBroadcast (unequal), on a second stream, tile-row block by block so that the exchange of one block
+ * overlaps the product of the next; a placement pass moves each block from NCCL's rank-major order into
+ * the row-major y_full.  On return the work is ordered on `stream`.  Every rank must make the same call.
+ * Not capturable in a CUDA graph (NCCL collectives on an internal stream).  The addressing is the
+ * qw_extra_offset row-slice addressing of dispatch_gemm_q4_at
+ * (crates/inference/src/forward/metal_qwen35/inner/dispatch.rs:1037-1097); the reference itself runs on
+ * one GPU. */
+lq4_status lq4_linear_sharded(lq4_ctx* ctx, const lq4_linear_args* local, const lq4_shard_desc* shard, void* stream);
+
+/* The placement pass of lq4_linear_sharded on its own, for hosts that run the collective themselves:
+ * `gathered` holds what an all-gather of the [rows, n_r] slices delivers, rank after rank
+ * ([world][rows][n_r], n_r = the rows of lq4_shard_plan(n_total, world, r)); they are moved to the
+ * row-major y_full[rows, ldy_full] (0 = n_total), slice r to columns [n0_r, n1_r).  No counterpart in the
+ * reference. */
+lq4_status lq4_place_slices(const float* gathered, float* y_full, uint64_t ldy_full, uint32_t rows, uint64_t n_total,
+                            uint32_t world, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

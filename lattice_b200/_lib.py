@@ -35,6 +35,14 @@ class GatherDesc(C.Structure):
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("bases", C.c_void_p * MAX_PEERS)]
 
 
+NCCL_ID_BYTES = 128
+
+
+class ShardDesc(C.Structure):
+    _fields_ = [("nccl_comm", C.c_void_p), ("world", C.c_uint32), ("rank", C.c_uint32), ("n_total", C.c_uint64),
+                ("y_full", C.c_void_p), ("ldy_full", C.c_uint64)]
+
+
 class LinearArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("x_dtype", C.c_int32), ("m", C.c_uint32), ("n", C.c_uint32),
                 ("k", C.c_uint32), ("w", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_uint64),
@@ -100,6 +108,11 @@ SIGNATURES = {
                                     C.c_uint64, C.c_float, C.POINTER(C.c_void_p)]),
     "lq4_lora_desc_for_rows": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(LoraDesc)]),
     "lq4_lora_free": (None, [C.c_void_p]),
+    "lq4_nccl_unique_id": (C.c_int32, [C.c_void_p]),
+    "lq4_nccl_comm_create": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "lq4_nccl_comm_destroy": (None, [C.c_void_p]),
+    "lq4_linear_sharded": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.POINTER(ShardDesc), C.c_void_p]),
+    "lq4_place_slices": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint64, C.c_uint32, C.c_void_p]),
     "lq4_shard_plan": (C.c_int32, [C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint64),
                                    C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
 }

@@ -3,6 +3,8 @@
 // contract: m == 0 or n == 0 is a no-op, k must be a non-zero multiple of 32
 // (crates/inference/src/forward/metal_qwen35/inner/dispatch.rs:181-188), element
 // counts are overflow-checked first (crates/inference/src/forward/cpu/gemm_validate.rs:1-60).
+#include <dlfcn.h>
+
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -50,6 +52,9 @@ struct lq4_ctx {
     int32_t* status = nullptr;    // device status word
     uint32_t* tsync = nullptr;    // 64-bit launch counter of the decode kernels
     Buf xrot, xs, t, tmsg, partials, hx, hy, gemm, logits, topk, topk_ctr, mlp, mlp_h;   // xs: activation limb records of the dense decode kernel
+    Buf shard_send, shard_recv;   // staging of lq4_linear_sharded: local slices, NCCL's rank-major blocks
+    cudaStream_t comm_stream = nullptr;      // second stream of lq4_linear_sharded (created on first use)
+    cudaEvent_t ev_block[4] = {nullptr, nullptr, nullptr, nullptr}, ev_comm = nullptr;
     bool allow_grow = true;
     int pdl = 1;
 };
@@ -315,8 +320,12 @@ void lq4_ctx_destroy(lq4_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
-    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk, &ctx->topk_ctr, &ctx->mlp, &ctx->mlp_h})
+    for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk, &ctx->topk_ctr, &ctx->mlp, &ctx->mlp_h, &ctx->shard_send, &ctx->shard_recv})
         if (b->p) cudaFree(b->p);
+    for (cudaEvent_t e : ctx->ev_block)
+        if (e) cudaEventDestroy(e);
+    if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);
+    if (ctx->comm_stream) cudaStreamDestroy(ctx->comm_stream);
     if (ctx->status) cudaFree(ctx->status);
     delete ctx;
 }
@@ -1099,6 +1108,225 @@ lq4_status lq4_shard_plan(uint64_t n, uint64_t k, uint32_t world, uint32_t rank,
     *n0 = n * rank / world;
     *n1 = n * (rank + 1) / world;
     *byte_offset = *n0 * (k / 32) * 20;
+    return LQ4_OK;
+}
+
+// ---- N-sharded linear over NCCL ------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+// The handful of NCCL entry points this path needs, bound at run time so that the library loads (and
+// every other entry point works) on a machine without NCCL.  Types follow NCCL's public C API.
+struct NcclId { char internal[LQ4_NCCL_ID_BYTES]; };
+typedef void* NcclComm;
+constexpr int kNcclFloat = 7;       // ncclFloat32
+struct NcclApi {
+    int (*GetUniqueId)(NcclId*) = nullptr;
+    int (*CommInitRank)(NcclComm*, int, NcclId, int) = nullptr;
+    int (*CommDestroy)(NcclComm) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t) = nullptr;
+    int (*Broadcast)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+
+const NcclApi& nccl_api() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        // the copy the process already holds (a framework's bundled NCCL) first, then the system's
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return;
+        auto sym = [&](const char* name) { return dlsym(h, name); };
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+        api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+        api.Broadcast = reinterpret_cast<decltype(api.Broadcast)>(sym("ncclBroadcast"));
+        api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+        api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+        api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.Broadcast &&
+                 api.GroupStart && api.GroupEnd && api.GetErrorString;
+    });
+    return api;
+}
+
+lq4_status nccl_fail(int rc, const char* what) {
+    return fail(LQ4_ERR_CUDA, std::string(what) + ": NCCL: " + nccl_api().GetErrorString(rc));
+}
+#define LQ4_NCCL(call)                                   \
+    do {                                                 \
+        int rc__ = (call);                               \
+        if (rc__ != 0) return nccl_fail(rc__, #call);    \
+    } while (0)
+
+// NCCL delivers block b as [rank][rows][n_r] (rank-major); y_full wants [rows][n_total] (row-major).
+// One thread per four output floats of a row; every global access is a coalesced 16-byte one when the
+// slice widths and the row pitch are multiples of four floats, a 4-byte one otherwise.
+__global__ void __launch_bounds__(256) place_slices_kernel(const float* __restrict__ recv, float* __restrict__ y,
+                                                           uint64_t ldy, uint32_t rows, uint64_t n_total, uint32_t world,
+                                                           int vec4) {
+    // slice r covers columns [n_total * r / world, n_total * (r + 1) / world)
+    const uint64_t per_row = vec4 ? n_total / 4 : n_total;
+    const uint64_t total = per_row * rows;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = i / per_row, c = (i - row * per_row) * (vec4 ? 4 : 1);
+        uint32_t r = (uint32_t)(((c + 1) * world - 1) / n_total);          // owner of column c
+        while (n_total * r / world > c) --r;
+        while (n_total * (r + 1) / world <= c) ++r;
+        const uint64_t n0 = n_total * r / world, n1 = n_total * (r + 1) / world;
+        const float* src = recv + n0 * rows + row * (n1 - n0) + (c - n0);     // blocks of earlier ranks hold n0 * rows floats
+        float* dst = y + row * ldy + c;
+        if (vec4) *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+        else *dst = *src;
+    }
+}
+
+cudaError_t place_slices(const float* gathered, float* y, uint64_t ldy, uint32_t rows, uint64_t n_total, uint32_t world,
+                         int sm_count, cudaStream_t s) {
+    const int vec4 = (n_total % ((uint64_t)4 * world) == 0 && ldy % 4 == 0 && aligned(y, 16) && aligned(gathered, 16)) ? 1 : 0;
+    const uint64_t work = (vec4 ? n_total / 4 : n_total) * rows;
+    const uint64_t want = (work + 255) / 256, cap_blocks = (uint64_t)sm_count * 8;
+    place_slices_kernel<<<(unsigned)(want < cap_blocks ? want : cap_blocks), 256, 0, s>>>(gathered, y, ldy, rows, n_total, world, vec4);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+lq4_status lq4_nccl_unique_id(uint8_t* h_id_out) {
+    if (!h_id_out) return fail(LQ4_ERR_NULL, "id_out is NULL");
+    const NcclApi& nc = nccl_api();
+    if (!nc.ok) return fail(LQ4_ERR_UNSUPPORTED, "no NCCL library (libnccl.so.2) could be loaded");
+    NcclId id;
+    LQ4_NCCL(nc.GetUniqueId(&id));
+    memcpy(h_id_out, &id, sizeof(id));
+    return LQ4_OK;
+}
+
+lq4_status lq4_nccl_comm_create(const uint8_t* h_id, uint32_t world, uint32_t rank, void** comm_out) {
+    if (!comm_out) return fail(LQ4_ERR_NULL, "comm_out is NULL");
+    *comm_out = nullptr;
+    if (!h_id) return fail(LQ4_ERR_NULL, "id is NULL");
+    if (world == 0 || rank >= world) return fail(LQ4_ERR_SHAPE, "rank must be below world");
+    const NcclApi& nc = nccl_api();
+    if (!nc.ok) return fail(LQ4_ERR_UNSUPPORTED, "no NCCL library (libnccl.so.2) could be loaded");
+    NcclId id;
+    memcpy(&id, h_id, sizeof(id));
+    NcclComm comm = nullptr;
+    LQ4_NCCL(nc.CommInitRank(&comm, (int)world, id, (int)rank));
+    *comm_out = comm;
+    return LQ4_OK;
+}
+
+void lq4_nccl_comm_destroy(void* comm) {
+    if (comm && nccl_api().ok) nccl_api().CommDestroy(comm);
+}
+
+lq4_status lq4_place_slices(const float* gathered, float* y_full, uint64_t ldy_full, uint32_t rows, uint64_t n_total,
+                            uint32_t world, void* stream) {
+    if (rows == 0 || n_total == 0) return LQ4_OK;
+    if (!gathered || !y_full) return fail(LQ4_ERR_NULL, "gathered and y_full must be non-NULL");
+    if (world == 0) return fail(LQ4_ERR_SHAPE, "world must be non-zero");
+    const uint64_t ldy = ldy_full ? ldy_full : n_total;
+    if (ldy < n_total) return fail(LQ4_ERR_SHAPE, "ldy_full is smaller than n_total");
+    if (!aligned(gathered, 4) || !aligned(y_full, 4)) return fail(LQ4_ERR_ALIGN, "buffers need 4-byte alignment");
+    int dev = 0, sms = 0;
+    LQ4_CUDA(cudaGetDevice(&dev));
+    LQ4_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    LQ4_CUDA(place_slices(gathered, y_full, ldy, rows, n_total, world, sms, (cudaStream_t)stream));
+    return LQ4_OK;
+}
+
+lq4_status lq4_linear_sharded(lq4_ctx* ctx, const lq4_linear_args* local, const lq4_shard_desc* sh, void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (!local || !sh) return fail(LQ4_ERR_NULL, "local and shard must be non-NULL");
+    if (sh->world == 0 || sh->rank >= sh->world) return fail(LQ4_ERR_SHAPE, "shard: rank must be below world");
+    if (local->gather || local->wait_gather) return fail(LQ4_ERR_UNSUPPORTED, "lq4_linear_sharded gathers over NCCL: no fused all-gather fields");
+    if (local->m == 0 || sh->n_total == 0) return LQ4_OK;
+    if (local->k == 0 || local->k % 32 != 0) return fail(LQ4_ERR_K, "k must be non-zero and divisible by 32");
+    const uint64_t n_total = sh->n_total, world = sh->world;
+    if (n_total > 0xffffffffull) return fail(LQ4_ERR_OVERFLOW, "n_total does not fit");
+    const uint64_t n0 = n_total * sh->rank / world, n1 = n_total * (sh->rank + 1) / world;
+    if (local->n != n1 - n0) return fail(LQ4_ERR_SHAPE, "local->n must be this rank's rows of lq4_shard_plan(n_total, world, rank)");
+    if (!sh->y_full) return fail(LQ4_ERR_NULL, "y_full is NULL");
+    const uint64_t ldy = sh->ldy_full ? sh->ldy_full : n_total;
+    if (ldy < n_total) return fail(LQ4_ERR_SHAPE, "ldy_full is smaller than n_total");
+    if (!aligned(sh->y_full, 4)) return fail(LQ4_ERR_ALIGN, "y_full needs 4-byte alignment");
+    if (world > 1 && !sh->nccl_comm) return fail(LQ4_ERR_NULL, "nccl_comm is NULL");
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t m = local->m;
+    lq4_status st;
+
+    if (world == 1) {                         // nothing to exchange: the slice is the output
+        lq4_linear_args a = *local;
+        a.y = sh->y_full;
+        a.ldy = ldy;
+        return lq4_linear(ctx, &a, stream);
+    }
+    const NcclApi& nc = nccl_api();
+    if (!nc.ok) return fail(LQ4_ERR_UNSUPPORTED, "no NCCL library (libnccl.so.2) could be loaded");
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    LQ4_CUDA(cudaStreamIsCapturing(s, &cap));
+    if (cap != cudaStreamCaptureStatusNone) return fail(LQ4_ERR_UNSUPPORTED, "lq4_linear_sharded cannot be captured in a CUDA graph");
+
+    // tile-row blocks: as many as keep every block's product at about one wave of 256 x 256 tiles
+    const uint64_t nl = n1 - n0;
+    uint32_t blocks = 1;
+    if (m > 256) {
+        const uint64_t tiles = ((nl + 255) / 256) * ((m + 255) / 256);
+        blocks = (uint32_t)((tiles + ctx->sm_count / 2) / ctx->sm_count);
+        blocks = blocks < 1 ? 1 : (blocks > 4 ? 4 : blocks);
+    }
+    const uint32_t rows_per = ((m + blocks - 1) / blocks + 255) / 256 * 256;
+    blocks = (m + rows_per - 1) / rows_per;
+
+    if ((st = ensure(ctx, ctx->shard_send, (size_t)m * nl * 4, false, s))) return st;
+    if ((st = ensure(ctx, ctx->shard_recv, (size_t)m * n_total * 4, false, s))) return st;
+    if (!ctx->comm_stream) {
+        LQ4_CUDA(cudaStreamCreateWithFlags(&ctx->comm_stream, cudaStreamNonBlocking));
+        for (cudaEvent_t& e : ctx->ev_block) LQ4_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        LQ4_CUDA(cudaEventCreateWithFlags(&ctx->ev_comm, cudaEventDisableTiming));
+    }
+    bool equal = true;
+    for (uint64_t r = 0; r < world; ++r) equal = equal && (n_total * (r + 1) / world - n_total * r / world) == nl;
+    const size_t esz = local->x_dtype == LQ4_DTYPE_BF16 ? 2 : 4;
+
+    for (uint32_t b = 0; b < blocks; ++b) {
+        const uint32_t r0 = b * rows_per, rows = m - r0 < rows_per ? m - r0 : rows_per;
+        float* send = (float*)ctx->shard_send.p + (size_t)r0 * nl;
+        float* recv = (float*)ctx->shard_recv.p + (size_t)r0 * n_total;
+        lq4_linear_args a = *local;
+        a.x = static_cast<const uint8_t*>(local->x) + (size_t)r0 * local->k * esz;
+        a.m = rows;
+        a.y = send;
+        a.ldy = nl;
+        if ((st = lq4_linear(ctx, &a, stream))) return st;
+        LQ4_CUDA(cudaEventRecord(ctx->ev_block[b], s));
+        LQ4_CUDA(cudaStreamWaitEvent(ctx->comm_stream, ctx->ev_block[b], 0));
+        if (equal) {
+            LQ4_NCCL(nc.AllGather(send, recv, (size_t)rows * nl, kNcclFloat, sh->nccl_comm, ctx->comm_stream));
+        } else {
+            LQ4_NCCL(nc.GroupStart());
+            for (uint64_t r = 0; r < world; ++r) {
+                const uint64_t q0 = n_total * r / world, q1 = n_total * (r + 1) / world;
+                int rc = nc.Broadcast(send, recv + q0 * rows, (size_t)rows * (q1 - q0), kNcclFloat, (int)r, sh->nccl_comm, ctx->comm_stream);
+                if (rc != 0) { nc.GroupEnd(); return nccl_fail(rc, "ncclBroadcast"); }
+            }
+            LQ4_NCCL(nc.GroupEnd());
+        }
+        LQ4_CUDA(place_slices(recv, sh->y_full + (size_t)r0 * ldy, ldy, rows, n_total, (uint32_t)world, ctx->sm_count, ctx->comm_stream));
+        ctx->launches += 1;
+    }
+    LQ4_CUDA(cudaEventRecord(ctx->ev_comm, ctx->comm_stream));
+    LQ4_CUDA(cudaStreamWaitEvent(s, ctx->ev_comm, 0));
     return LQ4_OK;
 }
 

@@ -61,6 +61,91 @@ class ShardedLinear:
         return torch.cat(parts, dim=1)
 
 
+def exchange_nccl_id(group: Optional[dist.ProcessGroup] = None) -> bytes:
+    """Rank 0 draws an NCCL unique id through the library and every rank of `group` receives its 128 bytes
+    (over whatever backend the group runs on: the id is host data)."""
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    box: List[Optional[bytes]] = [None]
+    if rank == 0:
+        buf = (C.c_uint8 * _lib.NCCL_ID_BYTES)()
+        _lib.check(_lib.lib().lq4_nccl_unique_id(buf))
+        box[0] = bytes(buf)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    assert box[0] is not None and len(box[0]) == _lib.NCCL_ID_BYTES
+    return box[0]
+
+
+def row_blocks(m: int, n_local: int, sm_count: int = 148) -> List[Tuple[int, int]]:
+    """The tile-row blocks ``lq4_linear_sharded`` pipelines (row ranges ``[r0, r1)``): as many blocks as keep
+    each block's product at about one wave of 256 x 256 tiles, at most four, in multiples of 256 rows."""
+    blocks = 1
+    if m > 256:
+        tiles = ((n_local + 255) // 256) * ((m + 255) // 256)
+        blocks = min(4, max(1, (tiles + sm_count // 2) // sm_count))
+    rows_per = ((m + blocks - 1) // blocks + 255) // 256 * 256
+    return [(r0, min(m, r0 + rows_per)) for r0 in range(0, m, rows_per)]
+
+
+def place_slices_host(gathered, rows: int, n_total: int, world: int):
+    """Host restatement of the placement pass (``lq4_place_slices``): ``gathered`` is the flat rank-major
+    result of an all-gather of ``[rows, n_r]`` slices; returns the row-major ``[rows, n_total]`` array."""
+    import numpy as np
+    g = np.asarray(gathered, dtype=np.float32).reshape(-1)
+    y = np.empty((rows, n_total), np.float32)
+    for r in range(world):
+        n0, n1 = n_total * r // world, n_total * (r + 1) // world
+        y[:, n0:n1] = g[n0 * rows: n1 * rows].reshape(rows, n1 - n0)
+    return y
+
+
+class NcclShardedLinear:
+    """One N-sharded Q4 linear through ``lq4_linear_sharded``: this rank's rows of the weight (and of LoRA B) on
+    its GPU, the ``[m, n / world]`` slices gathered into a full ``[m, n]`` output on every rank over NCCL.
+
+    ``qw_local`` holds rows ``[n0, n1)`` of the weight (``shard_plan``); ``lora`` is a descriptor whose ``b``
+    already points at those rows.  The communicator is created by the library from an id exchanged over
+    `group` (any backend), or passed in as a raw ``ncclComm_t`` address."""
+
+    def __init__(self, backend, qw_local, n_total: int, lora=None, group: Optional[dist.ProcessGroup] = None,
+                 nccl_comm: Optional[int] = None):
+        self.be = backend
+        self.qw = qw_local
+        self.lora = lora
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_total, self.k = n_total, qw_local.k
+        self.n0, self.n1, self.byte_offset = shard_plan(n_total, self.k, self.world, self.rank)
+        if qw_local.n != self.n1 - self.n0:
+            raise ValueError(f"rank {self.rank} must hold rows [{self.n0}, {self.n1}) of the weight, got {qw_local.n} rows")
+        self._own_comm = False
+        self.comm = nccl_comm
+        if self.world > 1 and self.comm is None:
+            ident = exchange_nccl_id(group)
+            h = C.c_void_p()
+            raw = (C.c_uint8 * _lib.NCCL_ID_BYTES).from_buffer_copy(ident)
+            _lib.check(_lib.lib().lq4_nccl_comm_create(raw, self.world, self.rank, C.byref(h)))
+            self.comm, self._own_comm = h.value, True
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = x.contiguous()
+        m = x.shape[0]
+        y = out if out is not None else torch.empty((m, self.n_total), dtype=torch.float32, device=x.device)
+        assert y.is_cuda and y.dtype == torch.float32 and y.shape == (m, self.n_total) and y.stride(1) == 1
+        args = _lib.LinearArgs(x.data_ptr(), self.be._dtype_of(x), m, self.qw.n, self.k, self.qw.payload_ptr, None, 0,
+                               C.pointer(self.lora) if self.lora is not None else None, None, _lib.PATH_AUTO, None, None)
+        desc = _lib.ShardDesc(self.comm, self.world, self.rank, self.n_total, y.data_ptr(), y.stride(0))
+        _lib.check(_lib.lib().lq4_linear_sharded(self.be._ctx, C.byref(args), C.byref(desc),
+                                                 torch.cuda.current_stream().cuda_stream))
+        return y
+
+    def close(self) -> None:
+        if self._own_comm and self.comm:
+            torch.cuda.synchronize()
+            _lib.lib().lq4_nccl_comm_destroy(self.comm)
+            self.comm, self._own_comm = None, False
+
+
 class _DeviceArray:
     """Exposes a raw device address range to torch through ``__cuda_array_interface__``."""
 

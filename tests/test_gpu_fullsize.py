@@ -1,0 +1,163 @@
+"""GPU parity at the sizes the benchmark runs: the grouped decode launch over the four full-size
+large-layer shapes (one, four and sixteen tokens), the group-of-one down_proj launch of the MLP block,
+the QuaRot layer at its full 11008 rows, and the prefill GEMM on at least a thousand sampled output
+features with the distribution of the tolerance ratio printed.
+
+Weights are drawn on the device and quantized by the library's own quantizer (bit-exact against the
+oracle in test_gpu_parity.py); the oracle then works from the same Q4 payload bytes."""
+import numpy as np
+import pytest
+
+import oracle
+from lattice_b200 import synth
+from tests._cases import TOL, tol_ratio
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+SHAPES = [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)]      # (k, n) of the large-layer decode set
+RANK, SCALE = 16, 2.0
+
+
+@pytest.fixture(scope="module")
+def be():
+    from lattice_b200 import CudaQ4Backend
+    b = CudaQ4Backend(0)
+    yield b
+    b.check_device_status()
+    b.close()
+
+
+@pytest.fixture(scope="module")
+def layer(be):
+    """One full-size set: device payloads and adapters plus their host copies for the oracle."""
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    g = torch.Generator(device="cuda")
+    out = []
+    for i, (k, n) in enumerate(SHAPES):
+        g.manual_seed(9100 + i)
+        w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+        payload = be.quantize(w.reshape(-1))
+        del w
+        a = torch.randn((RANK, k), generator=g, device="cuda") * 0.02
+        b = torch.randn((n, RANK), generator=g, device="cuda") * 0.02
+        out.append(dict(k=k, n=n, payload=payload, qw=Q4WeightBuf.from_device_payload(payload, n, k), a=a, b=b,
+                        lora=LoraDesc(a.data_ptr(), b.data_ptr(), RANK, SCALE),
+                        payload_h=payload.cpu().numpy(), a_h=a.cpu().numpy(), b_h=b.cpu().numpy()))
+    assert all(oracle.first_invalid_block(p["payload_h"]) == -1 for p in out)
+    return out
+
+
+def _oracle(p, x):
+    return oracle.q4_linear(x, p["payload_h"], x.shape[0], p["n"], p["k"], lora=(p["a_h"], p["b_h"], SCALE))
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_benchmarked_group_launch_at_full_size(be, layer, m):
+    """The headline problem exactly: ONE lq4_linear_group call over 5120->5120, 5120->1024, 5120->17408 and
+    17408->5120 with a rank-16 adapter each; every output row of every projection against the oracle."""
+    g = torch.Generator(device="cuda"); g.manual_seed(77 + m)
+    xs = {k: torch.randn((m, k), generator=g, device="cuda") for k in (5120, 17408)}
+    outs = [torch.full((m, p["n"]), float("nan"), device="cuda") for p in layer]
+    before = be.launch_count
+    be.linear_group([(xs[p["k"]], p["qw"], p["lora"]) for p in layer], outs)
+    launches = be.launch_count - before
+    be.check_device_status()
+    assert launches == (1 if m == 1 else 2)           # one persistent launch (plus the record builder for m > 1)
+    for p, y in zip(layer, outs):
+        y = y.cpu().numpy()
+        assert np.isfinite(y).all()
+        r = tol_ratio(y, _oracle(p, xs[p["k"]].cpu().numpy()))
+        assert r <= 1.0, (p["k"], p["n"], m, r)
+    # the same step twice gives the same bits (fixed summation order across the stream-K split)
+    outs2 = [torch.empty_like(o) for o in outs]
+    be.linear_group([(xs[p["k"]], p["qw"], p["lora"]) for p in layer], outs2)
+    assert all(torch.equal(a, b) for a, b in zip(outs, outs2))
+
+
+@pytest.mark.parametrize("idx", [0, 3])
+def test_group_of_one_at_full_size(be, layer, idx):
+    """5120->5120 and the MLP block's down_proj 17408->5120 as a group of one on the grouped kernel."""
+    p = layer[idx]
+    g = torch.Generator(device="cuda"); g.manual_seed(300 + idx)
+    x = torch.randn((1, p["k"]), generator=g, device="cuda")
+    y = torch.full((1, p["n"]), float("nan"), device="cuda")
+    be.linear_group([(x, p["qw"], p["lora"])], [y])
+    be.check_device_status()
+    assert tol_ratio(y.cpu().numpy(), _oracle(p, x.cpu().numpy())) <= 1.0
+    # and through the single-projection kernel
+    y1 = be.linear(x, p["qw"], lora=p["lora"])
+    assert tol_ratio(y1.cpu().numpy(), _oracle(p, x.cpu().numpy())) <= 1.0
+
+
+def _config5(be, m):
+    """configs[4] at full size: weights rotated (f64) and symmetric-quantized by the device converter."""
+    from lattice_b200 import Q4WeightBuf
+    n, k = 11008, 4096
+    g = torch.Generator(device="cuda"); g.manual_seed(555)
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.02).double()
+    signs = be.rot_signs(synth.QUAROT_DEFAULT_SEED, k)
+    payload = be.quantize_tensor(be.absorb_rotation(w, signs, "input"), symmetric=True)
+    del w
+    x = synth.activations(5, m, k, extra=m)
+    x[:, synth.outlier_channels(5, k)] *= np.float32(20.0)
+    return n, k, payload, Q4WeightBuf.from_device_payload(payload, n, k), signs, x
+
+
+def test_config5_full_size_one_token(be):
+    n, k, payload, qw, signs, x = _config5(be, 1)
+    y = be.linear(torch.from_numpy(x).cuda(), qw, rot=be.rot_desc(signs))
+    be.check_device_status()
+    y_ref = oracle.q4_linear(x, payload.cpu().numpy(), 1, n, k, rot_signs=signs.cpu().numpy())
+    assert np.isfinite(y.cpu().numpy()).all()
+    assert tol_ratio(y.cpu().numpy(), y_ref) <= 1.0
+
+
+def test_config5_full_size_512_tokens_sampled_features(be):
+    n, k, payload, qw, signs, x = _config5(be, 512)
+    y = be.linear(torch.from_numpy(x).cuda(), qw, rot=be.rot_desc(signs))
+    be.check_device_status()
+    assert bool(torch.isfinite(y).all())
+    sel = np.unique(np.concatenate([np.arange(0, 16), np.arange(n - 16, n), np.random.default_rng(5).integers(0, n, 2048)]))
+    rows = payload.view(n, (k // 32) * 20)[torch.from_numpy(sel).cuda()].cpu().numpy().reshape(-1)
+    y_ref = oracle.q4_linear(x, rows, 512, len(sel), k, rot_signs=signs.cpu().numpy())
+    got = y[:, torch.from_numpy(sel).cuda()].cpu().numpy()
+    assert tol_ratio(got, y_ref) <= 1.0
+
+
+def test_config4_full_size_tolerance_histogram(be):
+    """configs[3] (M=2048, K=5120, N=17408, LoRA r=64, bf16): the tensor-core kernel rounds dequantized weights
+    to f16, which leaves a thin margin under the 1e-3 bound; the ratio |y - y_ref| / (1e-3 (|y_ref| + rms)) is
+    taken on 1100+ output features x 2048 tokens and its distribution is printed."""
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    m, k, n, r = 2048, 5120, 17408, 64
+    g = torch.Generator(device="cuda"); g.manual_seed(4)
+    w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+    payload = be.quantize(w.reshape(-1))
+    del w
+    x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    a = torch.randn((r, k), generator=g, device="cuda") * 0.02
+    b = torch.randn((n, r), generator=g, device="cuda") * 0.02
+    qw = Q4WeightBuf.from_device_payload(payload, n, k)
+    y = be.linear(x, qw, lora=LoraDesc(a.data_ptr(), b.data_ptr(), r, 2.0))
+    be.check_device_status()
+    assert bool(torch.isfinite(y).all())
+    sel = np.unique(np.concatenate([np.arange(0, 8), np.arange(120, 136), np.arange(n - 8, n),
+                                    np.random.default_rng(1).integers(0, n, 1100)]))
+    assert len(sel) >= 1024
+    rows = payload.view(n, (k // 32) * 20)[torch.from_numpy(sel).cuda()].cpu().numpy().reshape(-1)
+    y_ref = oracle.q4_linear(x.float().cpu().numpy(), rows, m, len(sel), k,
+                             lora=(a.cpu().numpy(), b.cpu().numpy()[sel], 2.0)).astype(np.float64)
+    got = y[:, torch.from_numpy(sel).cuda()].cpu().numpy().astype(np.float64)
+    rms = float(np.sqrt(np.mean(y_ref ** 2)))
+    ratio = np.abs(got - y_ref) / (TOL * (np.abs(y_ref) + rms))
+    edges = [0.0, 0.1, 0.2, 0.3, 0.4, 0.5, 0.6, 0.7, 0.8, 0.9, 1.0, np.inf]
+    hist, _ = np.histogram(ratio, bins=edges)
+    print(f"\nconfig4 tolerance ratio over {ratio.size} outputs ({len(sel)} features x {m} tokens): "
+          f"max {ratio.max():.4f}  p99.9 {np.quantile(ratio, 0.999):.4f}  p99 {np.quantile(ratio, 0.99):.4f}  "
+          f"median {np.median(ratio):.4f}  count>0.9 {int((ratio > 0.9).sum())}  count>1 {int((ratio > 1.0).sum())}  "
+          f"err_rms/rms(y) {np.sqrt(np.mean((got - y_ref) ** 2)) / rms:.3e}")
+    print("histogram (bin upper edges 0.1 .. 1.0, >1): " + " ".join(str(int(h)) for h in hist))
+    assert ratio.max() <= 1.0

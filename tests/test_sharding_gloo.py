@@ -106,3 +106,60 @@ def test_two_rank_sharded_lm_head_topk_is_the_global_topk(tmp_path, vocab, top_k
     for rank in range(world):
         assert np.array_equal(np.load(tmp_path / f"i{rank}.npy"), ri)
         assert np.array_equal(np.load(tmp_path / f"v{rank}.npy"), rv)
+
+
+def _nccl_host_logic_worker(rank, world, port, m, k, n, out_dir):
+    """What lq4_linear_sharded does on the host side, with the oracle as each rank's product and gloo as the
+    transport: the id exchange, the tile-row blocks, the rank-major gather and the placement."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from lattice_b200 import _lib
+    from lattice_b200.sharded import exchange_nccl_id, place_slices_host, row_blocks, shard_plan
+    from tests._cases import make_case
+
+    ident = exchange_nccl_id()                      # rank 0 draws it through the library, all ranks hold it
+    assert len(ident) == _lib.NCCL_ID_BYTES
+    ids = [None] * world
+    dist.all_gather_object(ids, ident)
+    assert all(i == ids[0] for i in ids)
+
+    case = make_case(3, m, k, n, rank=4, alpha=8.0, extra=9)
+    n0, n1, off = shard_plan(n, k, world, rank)
+    payload = case["payload"][off: off + (n1 - n0) * (k // 32) * 20]
+    a, b, s = case["lora"]
+    sizes = [shard_plan(n, k, world, r)[1] - shard_plan(n, k, world, r)[0] for r in range(world)]
+    y = np.empty((m, n), np.float32)
+    blocks = row_blocks(m, n1 - n0, sm_count=2)     # a tiny "device" so that several blocks appear
+    assert blocks[0][0] == 0 and blocks[-1][1] == m and all(b0[1] == b1[0] for b0, b1 in zip(blocks, blocks[1:]))
+    for r0, r1 in blocks:
+        mine = oracle.q4_linear(case["x"][r0:r1], payload, r1 - r0, n1 - n0, k, lora=(a, b[n0:n1], s))
+        parts = [torch.empty((r1 - r0) * sz) for sz in sizes]
+        dist.all_gather(parts, torch.from_numpy(mine.reshape(-1)))
+        y[r0:r1] = place_slices_host(torch.cat(parts).numpy(), r1 - r0, n, world)
+    np.save(os.path.join(out_dir, f"y{rank}.npy"), y)
+    if rank == 0:
+        np.save(os.path.join(out_dir, "ref.npy"), case["y_ref"])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("m,k,n", [(600, 64, 70), (3, 128, 96)])      # 35-row slices (not a multiple of four); 600 tokens: 3 row blocks
+def test_two_rank_nccl_sharded_host_logic(tmp_path, m, k, n):
+    world = 2
+    mp.spawn(_nccl_host_logic_worker, args=(world, _free_port(), m, k, n, str(tmp_path)), nprocs=world, join=True)
+    ref = np.load(tmp_path / "ref.npy")
+    for r in range(world):
+        assert np.array_equal(np.load(tmp_path / f"y{r}.npy"), ref)
+
+
+def test_row_blocks_follow_the_library_rule():
+    from lattice_b200.sharded import row_blocks
+    assert row_blocks(1, 2176) == [(0, 1)]
+    assert row_blocks(256, 8704) == [(0, 256)]
+    assert row_blocks(2048, 8704) == [(0, 1024), (1024, 2048)]         # two ranks: 272 tiles, two blocks of one wave
+    assert row_blocks(2048, 4352) == [(0, 2048)]                       # four ranks: 136 tiles, one block
+    assert row_blocks(2048, 2176) == [(0, 2048)]
+    assert row_blocks(2048, 17408)[0] == (0, 512) and len(row_blocks(2048, 17408)) == 4
