@@ -73,7 +73,7 @@ def test_quantize_per_row_when_cols_is_not_a_multiple_of_32(be, rows, cols):
     # the flat entry point on the same data crosses row ends instead
     flat = be.quantize_tensor(dev(w)).cpu().numpy()
     assert flat.tobytes() == oracle.quantize_f32_to_q4(w.reshape(-1)).tobytes()
-    if cols % 32:
+    if cols % 32 and rows > 1:
         assert flat.size != got.size or flat.tobytes() != got.tobytes()
 
 
