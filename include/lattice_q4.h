@@ -168,8 +168,54 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* args, void* stream);
  * a cold instruction cache (about 2.5 us per switch on B200), one kernel for both does not. */
 lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t count, void* stream);
 
-/* ---- peer buffers for the fused all-gather ------------------------------------ */
 typedef struct lq4_peer_buf lq4_peer_buf;
+
+/* ---- a whole decode step in one launch -------------------------------------------------------- */
+
+/* A step buffer holds the activations that travel between the groups of a step (and between the GPUs of
+ * an N-sharded step): `payload_floats` f32 values followed by the library's mailbox for them.  It is a peer
+ * buffer (lq4_peer_buf_export / _open / _close / _base / _payload / _free apply): with several GPUs every
+ * rank creates one of the same size and maps the others'.  Allocates (cudaMalloc), zero-filled. */
+lq4_status lq4_step_buf_create(uint64_t payload_floats, lq4_peer_buf** out);
+
+typedef struct {
+    const lq4_linear_args* args;   /* independent one-token projections, as for lq4_linear_group */
+    uint32_t count;
+} lq4_step_group;
+
+typedef struct {
+    const float* start;            /* inside this rank's step-buffer payload */
+    uint64_t count;                /* floats */
+} lq4_step_range;
+
+typedef struct {
+    const lq4_gather_desc* bufs;   /* the ranks' step buffers: bases[rank] this GPU's own (world 1: just that one) */
+    const lq4_step_range* gathered;   /* ranges of the payload that are complete, as plain f32, on THIS GPU when
+                                         the launch completes: the full rows (all ranks' columns) of the outputs
+                                         the caller reads afterwards.  With world > 1 every output must be covered. */
+    uint32_t n_gathered;
+} lq4_step_desc;
+
+/* Runs groups[0], groups[1], ... in ONE persistent launch.  The projections of a group are independent;
+ * a projection of a later group may take its activations from what earlier groups of the same call wrote:
+ * its x then points into the step buffer's payload at the place where those outputs' y pointed (for an
+ * N-sharded step: at the full row that the ranks' column slices form together).  Such an input is read
+ * through the mailbox as the values arrive - from this GPU's CTAs or, over NVLink, from the peers' - so
+ * the weight stream of the next group never stops for a launch boundary, a fence or a collective.  When
+ * the launch completes on a rank, every `gathered` range is complete there as plain f32.  Replaces the
+ * reference's one command buffer per decode step (crates/inference/src/forward/metal_qwen35.rs:4458-4462:
+ * all of a step's dispatches are encoded back to back and committed once), whose dispatches are ordered
+ * by the encoder; here the order is carried by the data.
+ * Every problem: m == 1, no rotation, k % 128 == 0, 16-byte aligned w and x, LoRA rank <= 512, the row
+ * fits in shared memory (k <= about 50k), fused-gather fields NULL; at most 24 problems in 8 groups;
+ * inputs taken from the step buffer are f32.  Outputs outside the step buffer are written as usual but
+ * cannot feed later groups.  `step` may be NULL when no group depends on another and there is one GPU.
+ * All ranks of an N-sharded step must issue the same sequence of lq4_decode_step calls on their buffers.
+ * Every wait is bounded (about two seconds, then LQ4_ERR_DEVICE through lq4_ctx_check). */
+lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
+                           void* stream);
+
+/* ---- peer buffers for the fused all-gather ------------------------------------ */
 #define LQ4_PEER_HANDLE_BYTES 64
 /* Allocates (cudaMalloc, zero-filled) a buffer other processes on the same node can map:
  * 256 control bytes (arrival counter, launch sequence, CTA counter) followed by `payload_bytes` of output. */

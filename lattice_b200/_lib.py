@@ -38,6 +38,18 @@ class GatherDesc(C.Structure):
 NCCL_ID_BYTES = 128
 
 
+class StepGroup(C.Structure):
+    _fields_ = [("args", C.c_void_p), ("count", C.c_uint32)]
+
+
+class StepRange(C.Structure):
+    _fields_ = [("start", C.c_void_p), ("count", C.c_uint64)]
+
+
+class StepDesc(C.Structure):
+    _fields_ = [("bufs", C.POINTER(GatherDesc)), ("gathered", C.c_void_p), ("n_gathered", C.c_uint32)]
+
+
 class ShardDesc(C.Structure):
     _fields_ = [("nccl_comm", C.c_void_p), ("world", C.c_uint32), ("rank", C.c_uint32), ("n_total", C.c_uint64),
                 ("y_full", C.c_void_p), ("ldy_full", C.c_uint64)]
@@ -73,6 +85,8 @@ SIGNATURES = {
     "lq4_linear_decode_noalloc": (C.c_int32, [C.POINTER(LinearArgs), C.c_void_p]),
     "lq4_noalloc_check": (C.c_int32, [C.c_void_p]),
     "lq4_linear_group": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_uint32, C.c_void_p]),
+    "lq4_step_buf_create": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p)]),
+    "lq4_decode_step": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(StepDesc), C.c_void_p]),
     "lq4_peer_buf_create": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p)]),
     "lq4_peer_buf_free": (None, [C.c_void_p]),
     "lq4_peer_buf_base": (C.c_void_p, [C.c_void_p]),

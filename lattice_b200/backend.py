@@ -126,6 +126,18 @@ class PreparedGroup:
         return self.outs
 
 
+class PreparedStep:
+    """Argument blocks of one ``lq4_decode_step`` call, reusable while its tensors live."""
+
+    def __init__(self, backend: "CudaQ4Backend", garr, ngroups: int, desc, keep):
+        self._be, self._garr, self._ngroups, self._desc, self._keep = backend, garr, ngroups, desc, keep
+        self._fn = _lib.lib().lq4_decode_step
+
+    def __call__(self) -> None:
+        check(self._fn(self._be._ctx, C.cast(self._garr, C.c_void_p), self._ngroups,
+                       C.byref(self._desc) if self._desc is not None else None, _stream()))
+
+
 class CudaQ4Backend:
     """One instance per device and owning thread, like the reference's GPU state."""
 
@@ -544,6 +556,37 @@ class CudaQ4Backend:
                                 C.pointer(wait_gather) if wait_gather is not None else None)
         keep += [gather, wait_gather]
         return PreparedGroup(self, arr, n_prob, ys, keep)
+
+    def prepare_step(self, groups, step_buffer=None, gathered=None) -> "PreparedStep":
+        """Builds the argument blocks of one ``lq4_decode_step`` call; calling the result launches it.
+
+        ``groups`` is a list of groups, each a list of ``(x, qw, lora, y)`` with ``x`` ``[1, k]`` or ``[k]`` and
+        ``y`` ``[n]`` (or ``[1, n]``) device tensors.  A later group's ``x`` may be a slice of
+        ``step_buffer.payload`` where earlier groups' ``y`` slices lie.  ``gathered`` lists the payload slices
+        that must be complete on this rank when the launch completes."""
+        from ._lib import StepDesc, StepGroup, StepRange
+        keep, garr = [], (StepGroup * max(len(groups), 1))()
+        for gi, grp in enumerate(groups):
+            arr = (LinearArgs * max(len(grp), 1))()
+            for i, (x, qw, lora, y) in enumerate(grp):
+                k = x.numel()
+                self._require_k("decode_step", k)
+                assert x.is_cuda and y.is_cuda and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+                assert k == qw.k and y.numel() == qw.n
+                arr[i] = LinearArgs(x.data_ptr(), self._dtype_of(x), 1, qw.n, k, qw.payload_ptr, y.data_ptr(), 0,
+                                    C.pointer(lora) if lora is not None else None, None, _lib.PATH_AUTO, None, None)
+                keep.append((x, qw, lora, y))
+            keep.append(arr)
+            garr[gi] = StepGroup(C.cast(arr, C.c_void_p).value, len(grp))
+        desc = None
+        if step_buffer is not None:
+            rng = (StepRange * max(len(gathered or []), 1))()
+            for i, t in enumerate(gathered or []):
+                assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()
+                rng[i] = StepRange(t.data_ptr(), t.numel())
+            desc = StepDesc(C.pointer(step_buffer.desc), C.cast(rng, C.c_void_p).value, len(gathered or []))
+            keep += [rng, step_buffer, gathered]
+        return PreparedStep(self, garr, len(groups), desc, keep)
 
     def gather_wait(self, gather: GatherDesc) -> None:
         """Stream-ordered wait until every peer's results of the gathered launches issued so far are here."""

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblattice_q4.so")
-SOURCES = ["lq4_aux.cu", "lq4_gemv.cu", "lq4_decode.cu", "lq4_dense.cu", "lq4_gemm.cu", "lq4_topk.cu", "lq4_api.cu", "lq4_noalloc.cu"]
+SOURCES = ["lq4_aux.cu", "lq4_gemv.cu", "lq4_decode.cu", "lq4_dense.cu", "lq4_step.cu", "lq4_gemm.cu", "lq4_topk.cu", "lq4_api.cu", "lq4_noalloc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 

@@ -12,8 +12,12 @@
 #include <string>
 #include <vector>
 
+#include <map>
+
 #include "lq4_gemm.cuh"
 #include "lq4_kernels.cuh"
+#include "lq4_step.cuh"
+#include "lq4_decode_common.cuh"
 
 using namespace lq4;
 
@@ -52,6 +56,7 @@ struct lq4_ctx {
     int32_t* status = nullptr;    // device status word
     uint32_t* tsync = nullptr;    // 64-bit launch counter of the decode kernels
     Buf xrot, xs, t, tmsg, partials, hx, hy, gemm, logits, topk, topk_ctr, mlp, mlp_h;   // xs: activation limb records of the dense decode kernel
+    lq4_peer_buf* mlp_step = nullptr;   // step buffer of lq4_mlp_block's one-launch form (gate||up row + mailbox)
     Buf shard_send, shard_recv;   // staging of lq4_linear_sharded: local slices, NCCL's rank-major blocks
     cudaStream_t comm_stream = nullptr;      // second stream of lq4_linear_sharded (created on first use)
     cudaEvent_t ev_block[4] = {nullptr, nullptr, nullptr, nullptr}, ev_comm = nullptr;
@@ -322,6 +327,7 @@ void lq4_ctx_destroy(lq4_ctx* ctx) {
     cudaDeviceSynchronize();
     for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk, &ctx->topk_ctr, &ctx->mlp, &ctx->mlp_h, &ctx->shard_send, &ctx->shard_recv})
         if (b->p) cudaFree(b->p);
+    if (ctx->mlp_step) lq4_peer_buf_free(ctx->mlp_step);
     for (cudaEvent_t e : ctx->ev_block)
         if (e) cudaEventDestroy(e);
     if (ctx->ev_comm) cudaEventDestroy(ctx->ev_comm);
@@ -527,7 +533,54 @@ lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t 
 struct lq4_peer_buf {
     void* base = nullptr;
     uint64_t payload_bytes = 0;
+    uint64_t mailbox_off = 0;      // step buffers: bytes from base to the mailbox (0: none)
+    uint64_t mailbox_half = 0;     // entries per half
 };
+
+namespace {
+// Layout of the buffers created in this process, by base address: the C ABI passes bases, and the
+// peers' buffers have the layout of the own one.
+std::mutex g_peer_mu;
+std::map<void*, lq4_peer_buf> g_peer_bufs;
+
+bool peer_buf_info(void* base, lq4_peer_buf* out) {
+    std::lock_guard<std::mutex> lk(g_peer_mu);
+    auto it = g_peer_bufs.find(base);
+    if (it == g_peer_bufs.end()) return false;
+    *out = it->second;
+    return true;
+}
+
+lq4_status peer_buf_alloc(uint64_t payload_bytes, bool mailbox, lq4_peer_buf** out) {
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    *out = nullptr;
+    if (payload_bytes == 0) return fail(LQ4_ERR_SHAPE, "payload size is 0");
+    if (payload_bytes > ((uint64_t)1 << 40)) return fail(LQ4_ERR_OVERFLOW, "payload too large");
+    lq4_peer_buf* b = new lq4_peer_buf();
+    const uint64_t pay = (payload_bytes + 255) / 256 * 256;
+    uint64_t bytes = 256 + pay;
+    if (mailbox) {
+        b->mailbox_off = bytes;
+        b->mailbox_half = pay / 4;                 // one 8-byte entry per payload float, twice
+        bytes += 2 * b->mailbox_half * 8;
+    }
+    cudaError_t e = cudaMalloc(&b->base, bytes);
+    if (e == cudaSuccess) e = cudaMemset(b->base, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        if (b->base) cudaFree(b->base);
+        delete b;
+        return cuda_fail(e, "peer buffer allocation");
+    }
+    b->payload_bytes = payload_bytes;
+    {
+        std::lock_guard<std::mutex> lk(g_peer_mu);
+        g_peer_bufs[b->base] = *b;
+    }
+    *out = b;
+    return LQ4_OK;
+}
+}  // namespace
 
 namespace {
 // One thread.  With programmatic dependent launch it first lets the launch after it start (a decode
@@ -556,23 +609,23 @@ lq4_status lq4_peer_buf_create(uint64_t payload_bytes, lq4_peer_buf** out) {
     if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
     *out = nullptr;
     if (payload_bytes == 0) return fail(LQ4_ERR_SHAPE, "payload_bytes is 0");
-    lq4_peer_buf* b = new lq4_peer_buf();
-    const size_t bytes = 256 + (size_t)((payload_bytes + 255) / 256 * 256);
-    cudaError_t e = cudaMalloc(&b->base, bytes);
-    if (e == cudaSuccess) e = cudaMemset(b->base, 0, bytes);
-    if (e == cudaSuccess) e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) {
-        if (b->base) cudaFree(b->base);
-        delete b;
-        return cuda_fail(e, "peer buffer allocation");
-    }
-    b->payload_bytes = payload_bytes;
-    *out = b;
-    return LQ4_OK;
+    return peer_buf_alloc(payload_bytes, false, out);
+}
+
+lq4_status lq4_step_buf_create(uint64_t payload_floats, lq4_peer_buf** out) {
+    if (!out) return fail(LQ4_ERR_NULL, "out is NULL");
+    *out = nullptr;
+    if (payload_floats == 0) return fail(LQ4_ERR_SHAPE, "payload_floats is 0");
+    if (payload_floats > 0x7fffffffull) return fail(LQ4_ERR_OVERFLOW, "a step buffer holds fewer than 2^31 floats");
+    return peer_buf_alloc(payload_floats * 4, true, out);
 }
 
 void lq4_peer_buf_free(lq4_peer_buf* b) {
     if (!b) return;
+    {
+        std::lock_guard<std::mutex> lk(g_peer_mu);
+        g_peer_bufs.erase(b->base);
+    }
     if (b->base) cudaFree(b->base);
     delete b;
 }
@@ -625,6 +678,217 @@ lq4_status lq4_gather_wait(lq4_ctx* ctx, const lq4_gather_desc* g, void* stream)
     LQ4_CUDA(cudaLaunchKernelEx(&cfg, gather_wait_kernel, own, own + 1, g->world, ctx->status, ctx->pdl));
     ctx->launches += 1;
     return LQ4_OK;
+}
+
+namespace {
+
+struct StepSpec {
+    lq4_linear_args a;
+    const float* x_mul;      // gating row for this problem's input (silu(x) * x_mul), or NULL
+};
+
+// Core of lq4_decode_step: `specs` are the problems in group order, `gsize[g]` the size of group g.
+lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize, uint32_t ngroups, const lq4_step_desc* step,
+                     cudaStream_t s) {
+    uint32_t np = 0;
+    for (uint32_t g = 0; g < ngroups; ++g) np += gsize[g];
+    if (ngroups == 0 || np == 0) return LQ4_OK;
+    if (ngroups > (uint32_t)kStepMaxGroups) return fail(LQ4_ERR_NOSPACE, "a step holds at most 8 groups");
+    if (np > (uint32_t)kStepMaxProblems) return fail(LQ4_ERR_NOSPACE, "a step holds at most 24 projections");
+    lq4_status st;
+
+    // the step buffer, if any
+    lq4_peer_buf info{};
+    const lq4_gather_desc* gd = step ? step->bufs : nullptr;
+    uint32_t world = 1, grank = 0;
+    char* base = nullptr;
+    if (gd) {
+        if (gd->world < 1 || gd->world > LQ4_MAX_PEERS || gd->rank >= gd->world) return fail(LQ4_ERR_SHAPE, "step: world must be 1..8 and rank < world");
+        world = gd->world; grank = gd->rank;
+        for (uint32_t r = 0; r < world; ++r)
+            if (!gd->bases[r] || !aligned(gd->bases[r], 256)) return fail(LQ4_ERR_NULL, "step: a buffer base is NULL or misaligned");
+        base = static_cast<char*>(gd->bases[grank]);
+        if (!peer_buf_info(base, &info) || info.mailbox_off == 0)
+            return fail(LQ4_ERR_SHAPE, "step: bases[rank] is not a step buffer created by lq4_step_buf_create in this process");
+    } else if (step) {
+        return fail(LQ4_ERR_NULL, "step->bufs is NULL");
+    }
+    float* payload = base ? reinterpret_cast<float*>(base + 256) : nullptr;
+    const uint64_t pfloats = base ? info.payload_bytes / 4 : 0;
+    auto in_payload = [&](const void* p, uint64_t count) {
+        if (!payload) return false;
+        const char* c = static_cast<const char*>(p);
+        return c >= reinterpret_cast<const char*>(payload) && c + count * 4 <= reinterpret_cast<const char*>(payload + pfloats);
+    };
+
+    thread_local StepArgs sa;
+    sa = StepArgs{};
+    sa.ngroups = ngroups;
+    sa.use_pdl = ctx->pdl;
+    sa.tsync = ctx->tsync;
+    sa.status = ctx->status;
+    sa.world = world;
+    sa.grank = grank;
+    uint32_t max_kb = 0, max_rank = 0;
+    size_t items_total = 0;
+    uint32_t pi = 0;
+    uint64_t max_units = 0;
+    for (uint32_t g = 0; g < ngroups; ++g) {
+        sa.group_begin[g] = pi;
+        uint64_t units = 0;
+        for (uint32_t i = 0; i < gsize[g]; ++i, ++pi) {
+            const lq4_linear_args& a = specs[pi].a;
+            if ((st = validate_linear(&a))) return st;
+            const uint32_t rank = a.lora ? a.lora->rank : 0;
+            if (a.m != 1 || a.n == 0) return fail(LQ4_ERR_SHAPE, "a step takes one-token projections (m == 1, n > 0)");
+            if (a.rot) return fail(LQ4_ERR_UNSUPPORTED, "a step takes no online rotation");
+            if (a.gather || a.wait_gather) return fail(LQ4_ERR_UNSUPPORTED, "a step's exchange is described by lq4_step_desc, not per projection");
+            if (a.k % 128 != 0 || !aligned(a.w, 16) || !aligned(a.x, 16) || rank > (uint32_t)kGemvMaxRank)
+                return fail(LQ4_ERR_ALIGN, "a step needs k % 128 == 0, 16-byte aligned w and x, rank <= 512");
+            if (a.lora && !aligned(a.lora->a, 16)) return fail(LQ4_ERR_ALIGN, "a step needs 16-byte aligned LoRA A");
+            if (a.path != LQ4_PATH_AUTO && a.path != LQ4_PATH_GEMV_MMA) return fail(LQ4_ERR_UNSUPPORTED, "a step runs on the decode kernel");
+            StepProblem& q = sa.p[pi];
+            q.y = a.y;
+            q.x = a.x;
+            q.x_mul = specs[pi].x_mul;
+            q.x_dtype = a.x_dtype;
+            q.n = a.n; q.k = a.k; q.kb = a.k / 32; q.kg = q.kb / kGemvGranuleBlocks;
+            q.tiles = (a.n + kGemvTileRows - 1) / kGemvTileRows;
+            q.x_slot = q.xmul_slot = q.y_slot = kNoSlot;
+            q.rank = rank;
+            q.tsplit = 1;
+            if (rank) { q.la = a.lora->a; q.lb = a.lora->b; q.lscale = a.lora->scale; q.tsplit = decode_tsplit(a.k); }
+            q.dot_begin = 0;
+            if (in_payload(a.y, a.n)) q.y_slot = (uint32_t)(a.y - payload);
+            else if (world > 1) return fail(LQ4_ERR_SHAPE, "N-sharded step: every output must lie in the step buffer's payload");
+            max_kb = q.kb > max_kb ? q.kb : max_kb;
+            max_rank = rank > max_rank ? rank : max_rank;
+            items_total += (size_t)rank * q.tsplit;
+            units += (uint64_t)q.tiles * q.kg;
+        }
+        max_units = units > max_units ? units : max_units;
+    }
+    sa.group_begin[ngroups] = pi;
+
+    // which inputs come from earlier groups of this launch
+    auto overlaps = [](const char* a0, const char* a1, const char* b0, const char* b1) { return a0 < b1 && b0 < a1; };
+    for (uint32_t g = 0; g < ngroups; ++g) {
+        for (uint32_t i = sa.group_begin[g]; i < sa.group_begin[g + 1]; ++i) {
+            StepProblem& q = sa.p[i];
+            const lq4_linear_args& a = specs[i].a;
+            const size_t esz = a.x_dtype == LQ4_DTYPE_BF16 ? 2 : 4;
+            const char* x0 = static_cast<const char*>(a.x);
+            const char* x1 = x0 + (size_t)a.k * esz;
+            const char* u0 = reinterpret_cast<const char*>(specs[i].x_mul);
+            const char* u1 = u0 ? u0 + (size_t)a.k * 4 : nullptr;
+            bool x_internal = false, u_internal = false;
+            for (uint32_t j = 0; j < np; ++j) {
+                const char* y0 = reinterpret_cast<const char*>(sa.p[j].y);
+                const char* y1 = y0 + (size_t)sa.p[j].n * 4;
+                const bool earlier = j < sa.group_begin[g];
+                const bool hx = overlaps(x0, x1, y0, y1), hu = u0 && overlaps(u0, u1, y0, y1);
+                if ((hx || hu) && !earlier)
+                    return fail(LQ4_ERR_SHAPE, "a projection reads what a projection of the same or a later group writes");
+                x_internal = x_internal || hx;
+                u_internal = u_internal || hu;
+            }
+            if (x_internal || u_internal) {
+                if (a.x_dtype != LQ4_DTYPE_F32) return fail(LQ4_ERR_DTYPE, "inputs taken from earlier groups are f32");
+                if (!in_payload(a.x, a.k) || (u0 && !in_payload(u0, a.k)))
+                    return fail(LQ4_ERR_SHAPE, "inputs taken from earlier groups must lie in the step buffer's payload");
+                if (u0 && x_internal != u_internal) return fail(LQ4_ERR_UNSUPPORTED, "a gated input and its multiplier must both come from earlier groups");
+                q.x_slot = (uint32_t)(static_cast<const float*>(a.x) - payload);
+                if (u0) q.xmul_slot = (uint32_t)(specs[i].x_mul - payload);
+                if ((q.x_slot & 3u) || (u0 && (q.xmul_slot & 3u))) return fail(LQ4_ERR_ALIGN, "inputs taken from earlier groups need 16-byte alignment");
+            }
+            if (u0 && !aligned(u0, 16)) return fail(LQ4_ERR_ALIGN, "the gating row needs 16-byte alignment");
+        }
+    }
+
+    const size_t smem = step_plan_smem(sa, max_kb, max_rank);
+    if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "a row of this step does not fit in shared memory");
+    const int grid = (int)(max_units < (uint64_t)ctx->sm_count ? max_units : (uint64_t)ctx->sm_count);
+
+    // CTA shares and projection items per group
+    if ((st = ensure(ctx, ctx->tmsg, (items_total + 1) * sizeof(uint2), true, s))) return st;
+    if ((st = ensure(ctx, ctx->partials, (size_t)ngroups * grid * kGemvTileRows * 8, true, s))) return st;
+    sa.partials = (float*)ctx->partials.p;
+    size_t item_off = 0;
+    for (uint32_t g = 0; g < ngroups; ++g) {
+        const uint32_t b = sa.group_begin[g], cnt = sa.group_begin[g + 1] - b;
+        GemvParams tmp[kStepMaxProblems];
+        uint32_t cta_begin[kStepMaxProblems + 1];
+        for (uint32_t i = 0; i < cnt; ++i) { tmp[i] = GemvParams{}; tmp[i].tiles = sa.p[b + i].tiles; tmp[i].kg = sa.p[b + i].kg; }
+        if ((uint32_t)grid < cnt) return fail(LQ4_ERR_UNSUPPORTED, "a group has more projections than the launch has CTAs");
+        dec::split_ctas(tmp, cnt, (uint32_t)grid, cta_begin);
+        uint32_t dots = 0;
+        for (uint32_t i = 0; i < cnt; ++i) {
+            StepProblem& q = sa.p[b + i];
+            q.cta_begin = cta_begin[i];
+            q.cta_count = cta_begin[i + 1] - cta_begin[i];
+            q.dot_begin = dots;
+            q.tmsg = (uint2*)ctx->tmsg.p + item_off + dots;
+            dots += q.rank * q.tsplit;
+            const dec::MapEntry* e = dec::maps_for(specs[b + i].a.w, q.n, q.kb);
+            if (!e) return fail(LQ4_ERR_CUDA, "tensor map encoding failed");
+            for (int j = 0; j < 3; ++j) sa.maps[b + i][j] = e->m[j];
+        }
+        sa.group_items[g] = dots;
+        item_off += dots;
+    }
+
+    // mailbox and the ranges to hand back as plain f32
+    sa.step_counter = ctx->tsync;
+    if (base) {
+        sa.mbox = reinterpret_cast<unsigned long long*>(base + info.mailbox_off);
+        sa.mbox_half = (uint32_t)info.mailbox_half;
+        sa.step_counter = reinterpret_cast<uint32_t*>(base + 32);
+        sa.payload = payload;
+        for (uint32_t r = 0; r < world; ++r)
+            sa.peer_mbox_off[r] = static_cast<const char*>(gd->bases[r]) - base;
+        if (step->n_gathered > (uint32_t)kStepMaxRanges) return fail(LQ4_ERR_NOSPACE, "a step hands back at most 8 ranges");
+        if (step->n_gathered && !step->gathered) return fail(LQ4_ERR_NULL, "step->gathered is NULL");
+        for (uint32_t u = 0; u < step->n_gathered; ++u) {
+            const lq4_step_range& rg = step->gathered[u];
+            if (!in_payload(rg.start, rg.count)) return fail(LQ4_ERR_SHAPE, "a gathered range lies outside the step buffer's payload");
+            sa.range_begin[u] = (uint32_t)(rg.start - payload);
+            sa.range_count[u] = (uint32_t)rg.count;
+        }
+        sa.n_ranges = step->n_gathered;
+        if (world > 1) {
+            // every output must come back: what a peer wrote is only in the mailbox until the gather moves it
+            for (uint32_t i = 0; i < np; ++i) {
+                bool covered = false;
+                for (uint32_t u = 0; u < sa.n_ranges; ++u)
+                    covered = covered || (sa.p[i].y_slot >= sa.range_begin[u] && sa.p[i].y_slot + sa.p[i].n <= sa.range_begin[u] + sa.range_count[u]);
+                if (!covered) return fail(LQ4_ERR_SHAPE, "N-sharded step: every output must lie inside a gathered range");
+            }
+        }
+    }
+    LQ4_CUDA(launch_decode_step(sa, smem, grid, s));
+    ctx->launches += 1;
+    return LQ4_OK;
+}
+
+}  // namespace
+
+lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
+                           void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (ngroups == 0) return LQ4_OK;
+    if (!groups) return fail(LQ4_ERR_NULL, "groups is NULL");
+    if (ngroups > (uint32_t)kStepMaxGroups) return fail(LQ4_ERR_NOSPACE, "a step holds at most 8 groups");
+    StepSpec specs[kStepMaxProblems];
+    uint32_t gsize[kStepMaxGroups];
+    uint32_t np = 0;
+    for (uint32_t g = 0; g < ngroups; ++g) {
+        if (groups[g].count && !groups[g].args) return fail(LQ4_ERR_NULL, "a group's args is NULL");
+        if (groups[g].count == 0) return fail(LQ4_ERR_SHAPE, "a group is empty");
+        if (np + groups[g].count > (uint32_t)kStepMaxProblems) return fail(LQ4_ERR_NOSPACE, "a step holds at most 24 projections");
+        for (uint32_t i = 0; i < groups[g].count; ++i) { specs[np].a = groups[g].args[i]; specs[np].x_mul = nullptr; ++np; }
+        gsize[g] = groups[g].count;
+    }
+    return step_core(ctx, specs, gsize, ngroups, step, (cudaStream_t)stream);
 }
 
 lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
@@ -696,6 +960,43 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
     if ((st = validate_linear(&d))) return st;          // all three projections are checked before the first launch
     for (int i = 0; i < 2; ++i)
         if ((st = validate_linear(&g[i]))) return st;
+    // One token with the gate||up row in the library's own buffer: the whole block is ONE launch.  The row
+    // lives in a step buffer, gate and up rows form the first group, down_proj the second; its CTAs read
+    // silu(gate) * up through the mailbox as the values arrive (lq4_step.cu).
+    static const bool two_launches = [] { const char* e = getenv("LQ4_MLP_TWO_LAUNCHES"); return e && e[0] == '1'; }();
+    if (a->m == 1 && !a->gate_up && !a->rot_down && !two_launches && a->hidden % 128 == 0 && a->inter % 128 == 0 &&
+        aligned(a->x, 16) && aligned(a->w_gate_up, 16) && aligned(a->w_down, 16) &&
+        gemv_resident_fits(1, a->hidden > a->inter ? a->hidden : a->inter, false)) {
+        bool lora_ok = true;
+        for (const lq4_lora_desc* l : {a->lora_gate, a->lora_up, a->lora_down})
+            lora_ok = lora_ok && (!l || (l->rank <= (uint32_t)kGemvMaxRank && aligned(l->a, 16)));
+        if (lora_ok) {
+            const uint64_t need = 2ull * a->inter;
+            if (!ctx->mlp_step || ctx->mlp_step->payload_bytes < need * 4) {
+                if (!ctx->allow_grow) return fail(LQ4_ERR_NOSPACE, "workspace too small and growth is disabled");
+                LQ4_CUDA(cudaStreamSynchronize(s));
+                if (ctx->mlp_step) { lq4_peer_buf_free(ctx->mlp_step); ctx->mlp_step = nullptr; }
+                if ((st = lq4_step_buf_create(need, &ctx->mlp_step))) return st;
+            }
+            float* row = static_cast<float*>(lq4_peer_buf_payload(ctx->mlp_step));
+            StepSpec specs[3];
+            for (int i = 0; i < 2; ++i) {
+                specs[i].a = g[i];
+                specs[i].a.y = row + (size_t)i * a->inter;
+                specs[i].a.ldy = 0;
+                specs[i].x_mul = nullptr;
+            }
+            specs[2].a = d;
+            specs[2].a.x = row;
+            specs[2].x_mul = row + a->inter;
+            const uint32_t gsize[2] = {2, 1};
+            lq4_gather_desc gd{};
+            gd.world = 1; gd.rank = 0; gd.bases[0] = lq4_peer_buf_base(ctx->mlp_step);
+            lq4_step_desc sd{};
+            sd.bufs = &gd;
+            return step_core(ctx, specs, gsize, 2, &sd, s);
+        }
+    }
     if ((st = lq4_linear_group(ctx, g, 2, stream))) return st;
     const uint32_t rank = d.lora ? d.lora->rank : 0;
     // up to 16 tokens: the decode kernels gate their own input (the resident kernel in its prologue, the dense

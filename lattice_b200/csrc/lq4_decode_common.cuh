@@ -133,6 +133,27 @@ __device__ __forceinline__ Limbs8 make_limbs8(const float (&v)[8], float amax) {
     return r;
 }
 
+// Limbs of eight activations (octet `o` of token slot `mp`) into the resident layout:
+// limbs [block][token][limb 0, limb 1][32 B], per-block info {scale, sum of the 32 activations}.
+__device__ __forceinline__ void store_limbs(uint8_t* xs, float2* sx, uint32_t MT, uint32_t mp, uint32_t o,
+                                            bool active, const float (&v)[8]) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
+    sum += __shfl_xor_sync(kFull, sum, 1);
+    sum += __shfl_xor_sync(kFull, sum, 2);
+    if (!active) return;
+    const Limbs8 l = make_limbs8(v, amax);
+    const uint32_t blk = o >> 2, j = o & 3;
+    uint8_t* dst = xs + ((size_t)blk * MT + mp) * 64 + j * 8;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(l.l0a, l.l0b);
+    *reinterpret_cast<uint2*>(dst + 32) = make_uint2(l.l1a, l.l1b);
+    if (j == 0) sx[(size_t)blk * MT + mp] = make_float2(l.scale, sum);
+}
+
 // Granules (4 blocks each) the next stage takes when `left` remain in the segment: 5, 3 or 1.
 // Row strides of 100, 60 and 20 words keep the consumer loads free of bank conflicts.
 __device__ __forceinline__ uint32_t stage_granules(uint32_t left) { return left >= 5 ? 5u : (left >= 3 ? 3u : 1u); }

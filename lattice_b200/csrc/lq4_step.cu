@@ -1,0 +1,657 @@
+// Decode step kernel: an ordered list of groups of one-token Q4 (+LoRA) projections in ONE persistent
+// launch.  The projections of a group are independent; a projection of a later group may read what an
+// earlier group wrote (the next layer's input, or gate / up in front of down_proj), on this GPU or - with the
+// output rows sharded over several GPUs - on the peers.
+//
+// Why one launch: a decode step is a chain of 20-microsecond weight streams, and per launch the resident
+// kernel pays a fixed price (programmatic hand-over, activation prologue, the spread of CTA end times, and
+// across GPUs a release / acquire round trip) that does not shrink with the shard.  Here the CTAs stay
+// resident: the TMA warp keeps streaming the NEXT group's weights into the ring while the consumers finish
+// the current group and wait for their inputs, so only the data dependency itself is left between groups.
+//
+// How groups hand data over without fences (a fence in mid-stream waits for the SM's loads in flight):
+// every published output is an 8-byte {value, step tag} mailbox entry written with one store, into the
+// mailbox of EVERY rank (plain stores over NVLink for the peers).  A reader polls the entries of the k range
+// it needs until they carry this step's tag (bounded; a status bit on timeout).  The tag comes from a
+// counter every step launch advances by exactly 256 on every rank, so it agrees across the ranks of a
+// group; the two halves of the mailbox alternate between steps, so a rank that is one step ahead never
+// overwrites what a slower rank still reads.  At the end of the launch every CTA moves its share of the
+// gathered ranges from the mailbox to plain f32: when the launch completes on a rank, that rank holds the
+// results of all ranks (no wait kernel, no collective).
+//
+// Inside a group the work is split as in the grouped decode kernel: every problem gets a contiguous share
+// of the CTAs in proportion to its cost, stream-K over (128-row tile, 4-block granule), the owner of a
+// tile's first k part adds the others' tagged partial sums in CTA order.  Warps: eight consumers (int8
+// tensor-core MMAs on nibble codes x two-limb activations), one TMA producer, one projection warp that
+// computes the adapters' t = A x for all groups and publishes it as tagged messages.
+#include "lq4_step.cuh"
+
+#include "lq4_decode_common.cuh"
+
+namespace lq4 {
+
+namespace {
+
+using namespace gemv;
+using namespace dec;
+
+constexpr int kStepThreads = 320;      // 8 consumer warps + TMA warp + projection warp
+
+__device__ __forceinline__ unsigned long long mbox_pack(float v, uint32_t tag) {
+    return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+}
+// One 8-byte store: the tag arrives with the value (single-copy atomic), on this GPU or on a peer.
+__device__ __forceinline__ void mbox_store(unsigned long long* p, unsigned long long e) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(e) : "memory");
+}
+__device__ __forceinline__ unsigned long long mbox_load(const unsigned long long* p) {
+    unsigned long long e;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(e) : "l"(p) : "memory");
+    return e;
+}
+__device__ __forceinline__ void mbox_load2(const unsigned long long* p, unsigned long long& e0, unsigned long long& e1) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(e0), "=l"(e1) : "l"(p) : "memory");
+}
+// Eight consecutive entries (32-byte aligned) -> values; true if all carry `stag`.
+__device__ __forceinline__ bool mbox_load8(const unsigned long long* p, uint32_t stag, float (&v)[8]) {
+    unsigned long long e[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) mbox_load2(p + 2 * i, e[2 * i], e[2 * i + 1]);
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        ok = ok && (uint32_t)(e[i] >> 32) == stag;
+        v[i] = __uint_as_float((uint32_t)e[i]);
+    }
+    return ok;
+}
+__device__ __forceinline__ bool mbox_load4(const unsigned long long* p, uint32_t stag, float4& v) {
+    unsigned long long e0, e1, e2, e3;
+    mbox_load2(p, e0, e1);
+    mbox_load2(p + 2, e2, e3);
+    v = make_float4(__uint_as_float((uint32_t)e0), __uint_as_float((uint32_t)e1), __uint_as_float((uint32_t)e2),
+                    __uint_as_float((uint32_t)e3));
+    return (uint32_t)(e0 >> 32) == stag && (uint32_t)(e1 >> 32) == stag && (uint32_t)(e2 >> 32) == stag &&
+           (uint32_t)(e3 >> 32) == stag;
+}
+
+// mbarrier wait that also gives up as soon as another wait of this CTA has failed.
+__device__ __forceinline__ bool mbar_wait_step(uint64_t* bar, uint32_t parity, volatile int* err) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = wait_clock();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*err || wait_expired(t0)) return false;
+    }
+}
+
+// This CTA's share of group g: its problem and its range of work units, or nothing.
+struct Share {
+    uint32_t pi;
+    uint64_t r0, r1;
+    bool any;
+};
+__device__ __forceinline__ Share step_share(const StepArgs& a, uint32_t g, uint32_t cta) {
+    Share s;
+    s.pi = 0; s.r0 = s.r1 = 0; s.any = false;
+    for (uint32_t i = a.group_begin[g]; i < a.group_begin[g + 1]; ++i) {
+        const StepProblem& q = a.p[i];
+        if (cta >= q.cta_begin && cta < q.cta_begin + q.cta_count) {
+            const uint64_t total = (uint64_t)q.tiles * q.kg;
+            s.pi = i;
+            s.r0 = range_begin(cta - q.cta_begin, total, q.cta_count);
+            s.r1 = range_begin(cta - q.cta_begin + 1, total, q.cta_count);
+            s.any = s.r1 > s.r0;
+            break;
+        }
+    }
+    return s;
+}
+
+// The 256 consumer threads turn the k range(s) this CTA touches into two int8 limbs per activation.
+__device__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* smem, int ctid, uint64_t r0, uint64_t r1,
+                              const unsigned long long* mb, uint32_t stag, volatile int* s_err) {
+    uint8_t* xs = smem + a.off_xs;
+    float2* sx = reinterpret_cast<float2*>(smem + a.off_sx);
+    const uint32_t opg = kGemvGranuleBlocks * 4;              // octets (8 activations) per granule
+    uint32_t a0 = 0, a1 = q.k / 8, b0 = 0, b1 = 0;            // two octet ranges [a0,a1) and [b0,b1)
+    if (r1 - r0 < q.kg) {
+        const uint32_t g0 = (uint32_t)(r0 % q.kg), len = (uint32_t)(r1 - r0);
+        if (g0 + len <= q.kg) { a0 = g0 * opg; a1 = (g0 + len) * opg; }
+        else { a0 = g0 * opg; a1 = q.kg * opg; b0 = 0; b1 = (g0 + len - q.kg) * opg; }
+    }
+    const uint32_t na = a1 - a0, noct = na + (b1 - b0);
+    if (q.x_slot == kNoSlot) {
+        // plain memory: several octets per thread and pass, all loads issued before the first use
+        constexpr int kBatch = 8;
+        for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * kConsumerThreads) {
+            float v[kBatch][8];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[u][e] = 0.0f;
+                if (i < noct) load8(q.x, q.x_dtype, (size_t)o * 8, v[u]);
+            }
+            if (q.x_mul) {
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                    const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+                    if (i < noct) {
+                        float up[8];
+                        load8(q.x_mul, LQ4_DTYPE_F32, (size_t)o * 8, up);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[u][e] = silu_mul(v[u][e], up[e]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+                store_limbs(xs, sx, 1, 0, o, i < noct, v[u]);
+            }
+        }
+    } else {
+        // mailbox: the entries are polled until they carry this step's tag.  The loop is warp-uniform (the
+        // limb conversion below uses quad shuffles), bounded, and backs off between sweeps.
+        constexpr int kBatch = 4;
+        const unsigned long long* xm = mb + q.x_slot;
+        const unsigned long long* um = q.xmul_slot != kNoSlot ? mb + q.xmul_slot : nullptr;
+        for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * kConsumerThreads) {
+            float v[kBatch][8];
+            const long long t0 = wait_clock();
+            for (;;) {
+                bool ready = true;
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                    const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[u][e] = 0.0f;
+                    if (i < noct) {
+                        ready = mbox_load8(xm + (size_t)o * 8, stag, v[u]) && ready;
+                        if (um) {
+                            float up[8];
+                            ready = mbox_load8(um + (size_t)o * 8, stag, up) && ready;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[u][e] = silu_mul(v[u][e], up[e]);
+                        }
+                    }
+                }
+                if (__all_sync(kFull, ready)) break;
+                if (__any_sync(kFull, *s_err != 0 || wait_expired(t0))) {
+                    if ((ctid & 31) == 0) atomicOr(a.status, kDevErrGridWaitTimeout);
+                    *s_err = 1;
+                    break;
+                }
+                __nanosleep(64);
+            }
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+                store_limbs(xs, sx, 1, 0, o, i < noct, v[u]);
+            }
+        }
+    }
+    named_bar_sync(kBarConsumers, kConsumerThreads);
+}
+
+__global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __grid_constant__ StepArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    uint64_t* empty = full + kMaxStages;
+    __shared__ int s_err_mem;
+    volatile int* s_err = &s_err_mem;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t NST = a.nstages;
+    if (tid == 0) {
+        for (uint32_t s = 0; s < NST; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 8);
+        }
+        s_err_mem = 0;
+        for (int i = 0; i < 8; ++i) reinterpret_cast<uint32_t*>(smem + kZeroOffset)[i] = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (a.use_pdl) pdl_launch_dependents();
+    uint32_t issued = 0;
+
+    if (warp == 8) {
+        // ------------------------------ TMA producer ------------------------------
+        // Walks the CTA's shares of ALL groups back to back: weights do not depend on anything, so the ring
+        // keeps filling with the next group's tiles while the consumers finish the current group.
+        const uint64_t pol = l2_policy_evict_first();
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t g = 0; g < a.ngroups && ok; ++g) {
+            const Share sh = step_share(a, g, blockIdx.x);
+            if (!sh.any) continue;
+            const StepProblem& q = a.p[sh.pi];
+            for (uint64_t pos = sh.r0; pos < sh.r1 && ok;) {
+                const uint32_t tile = (uint32_t)(pos / q.kg);
+                const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
+                const uint64_t left = sh.r1 - pos;
+                const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
+                for (uint32_t gs = g0; gs < g1; ++it) {
+                    const uint32_t ngr = stage_granules(g1 - gs);
+                    const uint32_t s = it % NST;
+                    bool got = true;
+                    if (lane == 0) got = mbar_wait_step(&empty[s], ((it / NST) & 1u) ^ 1u, s_err);
+                    if (!__shfl_sync(kFull, got, 0)) { ok = false; break; }
+                    if (lane == 0) {
+                        uint8_t* st = smem + a.off_stage + (size_t)s * kSlotBytes;
+                        mbar_arrive_expect_tx(&full[s], ngr * kSmallBytes);
+                        tma_load_2d(st, &a.maps[sh.pi][ngr == 5 ? 0 : (ngr == 3 ? 1 : 2)], (int32_t)(gs * kGemvGranuleBlocks * 5),
+                                    (int32_t)(tile * kGemvTileRows), &full[s], pol);
+                    }
+                    gs += ngr;
+                }
+                pos += g1 - g0;
+            }
+        }
+        issued = it;
+        if (!ok && lane == 0) {
+            atomicOr(a.status, kDevErrBarrierTimeout);
+            *s_err = 1;
+        }
+    } else if (warp == 9) {
+        // ------------------------------ adapter projections ------------------------------
+        // Work item e of group g = (problem, rank row j, k piece): item e belongs to CTA e mod grid.  Items
+        // of a later group wait (inside the dot product) for their inputs' mailbox entries.
+        if (a.use_pdl) pdl_wait_prior_grids();
+        const uint32_t tag = launch_tag(a.tsync);
+        const uint32_t stag = launch_tag(a.step_counter);
+        const unsigned long long* mb = a.mbox + (size_t)(stag & 1u) * a.mbox_half;
+        for (uint32_t g = 0; g < a.ngroups; ++g) {
+            const uint32_t nitems = a.group_items[g];
+            uint32_t pj = a.group_begin[g];
+            const uint32_t pend = a.group_begin[g + 1];
+            for (uint32_t e = blockIdx.x; e < nitems; e += gridDim.x) {
+                while (pj + 1 < pend && e >= a.p[pj + 1].dot_begin) ++pj;
+                const StepProblem& q = a.p[pj];
+                const uint32_t local = e - q.dot_begin;
+                const uint32_t j = local / q.tsplit, sp = local - j * q.tsplit;
+                const uint32_t k4 = q.k / 4;
+                const uint32_t chunk4 = ((k4 + q.tsplit - 1) / q.tsplit + 31u) & ~31u;
+                const uint32_t i0 = sp * chunk4, i1 = min(k4, i0 + chunk4);
+                const float* arow = q.la + (size_t)j * q.k;
+                const float4* a4 = reinterpret_cast<const float4*>(arow);
+                float s = 0.0f;
+                if (q.x_slot != kNoSlot) {
+                    const unsigned long long* xm = mb + q.x_slot;
+                    const unsigned long long* um = q.xmul_slot != kNoSlot ? mb + q.xmul_slot : nullptr;
+                    const long long t0 = wait_clock();
+                    for (;;) {
+                        bool ready = true;
+                        s = 0.0f;
+#pragma unroll 4
+                        for (uint32_t i = i0 + lane; i < i1; i += 32) {
+                            const float4 av = __ldg(a4 + i);
+                            float4 xv;
+                            ready = mbox_load4(xm + (size_t)i * 4, stag, xv) && ready;
+                            if (um) {
+                                float4 uv;
+                                ready = mbox_load4(um + (size_t)i * 4, stag, uv) && ready;
+                                xv = make_float4(silu_mul(xv.x, uv.x), silu_mul(xv.y, uv.y), silu_mul(xv.z, uv.z), silu_mul(xv.w, uv.w));
+                            }
+                            s = fmaf(av.x, xv.x, s); s = fmaf(av.y, xv.y, s); s = fmaf(av.z, xv.z, s); s = fmaf(av.w, xv.w, s);
+                        }
+                        if (__all_sync(kFull, ready)) break;
+                        if (__any_sync(kFull, *s_err != 0 || wait_expired(t0))) {
+                            if (lane == 0) atomicOr(a.status, kDevErrGridWaitTimeout);
+                            *s_err = 1;
+                            break;
+                        }
+                        __nanosleep(128);
+                    }
+                } else if (q.x_mul) {
+                    const float4* g4 = reinterpret_cast<const float4*>(q.x);
+                    const float4* u4 = reinterpret_cast<const float4*>(q.x_mul);
+#pragma unroll 8
+                    for (uint32_t i = i0 + lane; i < i1; i += 32) {
+                        const float4 av = __ldg(a4 + i), gv = g4[i], uv = u4[i];
+                        s = fmaf(av.x, silu_mul(gv.x, uv.x), s); s = fmaf(av.y, silu_mul(gv.y, uv.y), s);
+                        s = fmaf(av.z, silu_mul(gv.z, uv.z), s); s = fmaf(av.w, silu_mul(gv.w, uv.w), s);
+                    }
+                } else if (q.x_dtype == LQ4_DTYPE_F32) {
+                    const float4* x4 = reinterpret_cast<const float4*>(q.x);
+#pragma unroll 8
+                    for (uint32_t i = i0 + lane; i < i1; i += 32) {
+                        const float4 av = __ldg(a4 + i), b = x4[i];
+                        s = fmaf(av.x, b.x, s); s = fmaf(av.y, b.y, s); s = fmaf(av.z, b.z, s); s = fmaf(av.w, b.w, s);
+                    }
+                } else {
+#pragma unroll 8
+                    for (uint32_t i = i0 * 4 + lane; i < i1 * 4; i += 32)
+                        s = fmaf(__ldg(arow + i), load_act(q.x, q.x_dtype, i), s);
+                }
+#pragma unroll
+                for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
+                if (lane == 0) msg_store(q.tmsg + local, s, tag);
+            }
+        }
+    } else {
+        // ------------------------------ consumers ------------------------------
+        const int gq = lane >> 2, t = lane & 3;
+        if (a.use_pdl) pdl_wait_prior_grids();
+        const uint32_t tag = launch_tag(a.tsync);
+        const uint32_t stag = launch_tag(a.step_counter);
+        unsigned long long* mb = a.mbox + (size_t)(stag & 1u) * a.mbox_half;
+
+        const bool has_b = (gq >> 1) == t;
+        const uint8_t* xs_lane = smem + a.off_xs + (size_t)(gq & 1) * 32;
+        const uint8_t* zeros = smem + kZeroOffset;
+        const float2* sx_all = reinterpret_cast<const float2*>(smem + a.off_sx);
+        float* t_sm = reinterpret_cast<float*>(smem + a.off_t);
+
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t g = 0; g < a.ngroups && ok; ++g) {
+            const Share sh = step_share(a, g, blockIdx.x);
+            if (!sh.any) continue;                                 // the same for every thread of the CTA
+            const StepProblem& q = a.p[sh.pi];
+            const uint64_t total = (uint64_t)q.tiles * q.kg;
+            // everyone is done with the previous group's limbs and projection before they are replaced
+            named_bar_sync(kBarConsumers, kConsumerThreads);
+            step_prologue(a, q, smem, tid, sh.r0, sh.r1, mb, stag, s_err);
+            bool t_loaded = false;
+            // Gathers t = A x of this problem from the projection warps' messages into shared memory, adding
+            // the k pieces of every dot product in order.  All consumer warps call it at the same point.
+            auto gather_t = [&]() {
+                bool good = true;
+                for (uint32_t idx = tid; idx < q.rank; idx += kConsumerThreads) {
+                    const uint2* src = q.tmsg + (size_t)idx * q.tsplit;
+                    float sum = 0.0f;
+                    for (uint32_t s0 = 0; s0 < q.tsplit; s0 += 8) {
+                        uint2 msg[8];
+                        const long long t0 = wait_clock();
+                        for (;;) {
+                            bool all = true;
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                if (s0 + u >= q.tsplit) continue;
+                                msg[u] = msg_load(src + s0 + u);
+                                all = all && (msg[u].y == tag);
+                            }
+                            if (all) break;
+                            if (*s_err != 0 || wait_expired(t0)) { good = false; break; }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (s0 + u < q.tsplit) sum += __uint_as_float(msg[u].x);
+                    }
+                    t_sm[idx] = sum;
+                }
+                if (!good) { atomicOr(a.status, kDevErrGridWaitTimeout); *s_err = 1; }
+                named_bar_sync(kBarConsumers, kConsumerThreads);
+                t_loaded = true;
+            };
+            uint32_t git = 0;                                      // stages of this group consumed so far
+            for (uint64_t pos = sh.r0; pos < sh.r1 && ok;) {
+                const uint32_t tile = (uint32_t)(pos / q.kg);
+                const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
+                const uint64_t left = sh.r1 - pos;
+                const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
+                pos += g1 - g0;
+
+                float acc0 = 0.0f, acc1 = 0.0f;
+                if (q.rank && g0 == 0) {
+                    // this CTA will finish the tile: pull the warp's 16 rows of LoRA B towards L2 now
+                    const uint32_t rfirst = tile * kGemvTileRows + warp * 16;
+                    const uint32_t rows = rfirst < q.n ? min(16u, q.n - rfirst) : 0u;
+                    const char* bb = reinterpret_cast<const char*>(q.lb + (size_t)rfirst * q.rank);
+                    for (uint32_t off = lane * 128; off < rows * q.rank * 4; off += 32 * 128)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(bb + off));
+                }
+                for (uint32_t gs = g0; gs < g1; ++it, ++git) {
+                    const uint32_t ngr = stage_granules(g1 - gs);
+                    const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
+                    const uint32_t s = it % NST;
+                    if (!mbar_wait_step(&full[s], (it / NST) & 1u, s_err)) { ok = false; break; }
+                    if (git == 6 && q.rank && !t_loaded) gather_t();
+                    const uint8_t* st = smem + a.off_stage + (size_t)s * kSlotBytes;
+                    const uint8_t* row0 = st + (warp * 16 + gq) * rs + t * kBlockBytes;
+                    const uint8_t* row1 = row0 + 8 * rs;
+#pragma unroll 1
+                    for (uint32_t gi = 0; gi < ngr; ++gi) {
+                        const uint32_t blk = (gs + gi) * kGemvGranuleBlocks + t;     // this thread's block
+                        const uint32_t* q0 = reinterpret_cast<const uint32_t*>(row0 + gi * (4 * kBlockBytes));
+                        const uint32_t* q1 = reinterpret_cast<const uint32_t*>(row1 + gi * (4 * kBlockBytes));
+                        const uint32_t meta0 = q0[0], meta1 = q1[0];
+                        uint32_t w0[4], w1[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { w0[j] = q0[1 + j]; w1[j] = q1[1 + j]; }
+                        const uint8_t* xb = has_b ? xs_lane + (size_t)blk * 64 : zeros;
+                        const uint4 bq0 = *reinterpret_cast<const uint4*>(xb);
+                        const uint4 bq1 = *reinterpret_cast<const uint4*>(xb + 16);
+                        const float2 info = sx_all[blk];
+                        int c[4] = {0, 0, 0, 0};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t av[4];
+                            av[0] = w0[j] & 0x0F0F0F0Fu;
+                            av[1] = w1[j] & 0x0F0F0F0Fu;
+                            av[2] = (w0[j] >> 4) & 0x0F0F0F0Fu;
+                            av[3] = (w1[j] >> 4) & 0x0F0F0F0Fu;
+                            const uint4 bq = (j >> 1) ? bq1 : bq0;
+                            imma_16832(c, av, (j & 1) ? bq.z : bq.x, (j & 1) ? bq.w : bq.y);
+                        }
+                        const float d0 = h2f_bits(meta0 & 0xffffu), bb0 = h2f_bits(meta0 >> 16);
+                        const float d1 = h2f_bits(meta1 & 0xffffu), bb1 = h2f_bits(meta1 >> 16);
+                        const float dot0 = fmaf((float)c[1], 1.0f / kLimb1Ratio, (float)c[0]);
+                        const float dot1 = fmaf((float)c[3], 1.0f / kLimb1Ratio, (float)c[2]);
+                        acc0 = fmaf(d0 * info.x, dot0, fmaf(bb0, info.y, acc0));
+                        acc1 = fmaf(d1 * info.x, dot1, fmaf(bb1, info.y, acc1));
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[s]);
+                    gs += ngr;
+                }
+                if (!ok) break;
+
+                // each thread of a quad covered blocks = t (mod 4): add the four
+                float v0 = acc0, v1 = acc1;
+                v0 += __shfl_xor_sync(kFull, v0, 1);
+                v0 += __shfl_xor_sync(kFull, v0, 2);
+                v1 += __shfl_xor_sync(kFull, v1, 1);
+                v1 += __shfl_xor_sync(kFull, v1, 2);
+                const bool complete = (g0 == 0 && g1 == q.kg);
+                const uint32_t rowa = tile * kGemvTileRows + warp * 16 + gq, rowb = rowa + 8;
+                const float* bra = q.lb + (size_t)(rowa < q.n ? rowa : 0) * q.rank;
+                const float* brb = q.lb + (size_t)(rowb < q.n ? rowb : 0) * q.rank;
+                float ba0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, bb0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (q.rank && (complete || g0 == 0)) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t j = t + 4 * u;
+                        if (j < q.rank) { ba0[u] = __ldg(bra + j); bb0[u] = __ldg(brb + j); }
+                    }
+                }
+                uint2* part = reinterpret_cast<uint2*>(a.partials) + (size_t)g * gridDim.x * kGemvTileRows;
+                if (!complete && g0 != 0) {
+                    // contributor: publish the partial sums as tagged messages and go on
+                    uint2* dst = part + (size_t)blockIdx.x * kGemvTileRows + warp * 16;
+                    if (t == 0) {
+                        msg_store(dst + gq, v0, tag);
+                        msg_store(dst + gq + 8, v1, tag);
+                    }
+                    continue;
+                }
+                if (!complete) {
+                    // finisher: add the contributors' messages in CTA order (warp-uniform loop, bounded)
+                    const uint32_t c_last = q.cta_begin + owner_of((uint64_t)(tile + 1) * q.kg - 1, total, q.cta_count);
+                    constexpr int CB = 4;
+                    bool good = true;
+                    for (uint32_t c0 = blockIdx.x + 1; c0 <= c_last && good; c0 += CB) {
+                        uint2 msg[CB][2];
+                        const long long t0 = wait_clock();
+                        for (;;) {
+                            bool all = true;
+#pragma unroll
+                            for (int cb = 0; cb < CB; ++cb) {
+                                if (c0 + cb > c_last) continue;
+                                const uint2* src = part + (size_t)(c0 + cb) * kGemvTileRows + warp * 16;
+                                msg[cb][0] = msg_load(src + gq);
+                                msg[cb][1] = msg_load(src + gq + 8);
+                            }
+#pragma unroll
+                            for (int cb = 0; cb < CB; ++cb) {
+                                if (c0 + cb > c_last) continue;
+                                all = all && msg[cb][0].y == tag && msg[cb][1].y == tag;
+                            }
+                            if (__all_sync(kFull, all)) break;
+                            if (__any_sync(kFull, *s_err != 0 || wait_expired(t0))) { good = false; break; }
+                        }
+#pragma unroll
+                        for (int cb = 0; cb < CB; ++cb) {
+                            if (c0 + cb > c_last) continue;
+                            v0 += __uint_as_float(msg[cb][0].x);
+                            v1 += __uint_as_float(msg[cb][1].x);
+                        }
+                    }
+                    if (!good) {
+                        if (lane == 0) atomicOr(a.status, kDevErrGridWaitTimeout);
+                        *s_err = 1;
+                    }
+                }
+
+                // epilogue: LoRA term (the quad splits the rank), then quad thread 0 stores
+                if (q.rank) {
+                    if (!t_loaded) gather_t();
+                    float la = 0.0f, lb2 = 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t j = t + 4 * u;
+                        const float tv = j < q.rank ? t_sm[j] : 0.0f;
+                        la = fmaf(ba0[u], tv, la);
+                        lb2 = fmaf(bb0[u], tv, lb2);
+                    }
+#pragma unroll 4
+                    for (uint32_t j = t + 16; j < q.rank; j += 4) {
+                        const float tv = t_sm[j];
+                        la = fmaf(__ldg(bra + j), tv, la);
+                        lb2 = fmaf(__ldg(brb + j), tv, lb2);
+                    }
+                    la += __shfl_xor_sync(kFull, la, 1);
+                    la += __shfl_xor_sync(kFull, la, 2);
+                    lb2 += __shfl_xor_sync(kFull, lb2, 1);
+                    lb2 += __shfl_xor_sync(kFull, lb2, 2);
+                    v0 += q.lscale * la;
+                    v1 += q.lscale * lb2;
+                }
+                if (t == 0) {
+                    // plain f32 for whoever reads after the launch, a tagged mailbox entry on every rank for the
+                    // later groups of this launch (and for the final gather)
+                    if (rowa < q.n) {
+                        q.y[rowa] = v0;
+                        if (q.y_slot != kNoSlot) {
+                            const unsigned long long e = mbox_pack(v0, stag);
+                            char* own = reinterpret_cast<char*>(mb + q.y_slot + rowa);
+                            for (uint32_t r = 0; r < a.world; ++r) mbox_store(reinterpret_cast<unsigned long long*>(own + a.peer_mbox_off[r]), e);
+                        }
+                    }
+                    if (rowb < q.n) {
+                        q.y[rowb] = v1;
+                        if (q.y_slot != kNoSlot) {
+                            const unsigned long long e = mbox_pack(v1, stag);
+                            char* own = reinterpret_cast<char*>(mb + q.y_slot + rowb);
+                            for (uint32_t r = 0; r < a.world; ++r) mbox_store(reinterpret_cast<unsigned long long*>(own + a.peer_mbox_off[r]), e);
+                        }
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            if (lane == 0) atomicOr(a.status, kDevErrBarrierTimeout);
+            *s_err = 1;
+        }
+        // Gather: every entry of the listed ranges, whoever wrote it, becomes plain f32 in this GPU's payload.
+        // A thread polls its own entries (no shuffles follow, so the warp may split); bounded.
+        for (uint32_t u = 0; u < a.n_ranges; ++u) {
+            const unsigned long long* src = mb + a.range_begin[u];
+            float* dst = a.payload + a.range_begin[u];
+            const uint32_t cnt = a.range_count[u];
+            for (uint32_t i = blockIdx.x * kConsumerThreads + tid; i < cnt; i += gridDim.x * kConsumerThreads) {
+                unsigned long long e = mbox_load(src + i);
+                if ((uint32_t)(e >> 32) != stag) {
+                    const long long t0 = wait_clock();
+                    for (;;) {
+                        __nanosleep(64);
+                        e = mbox_load(src + i);
+                        if ((uint32_t)(e >> 32) == stag) break;
+                        if (*s_err != 0 || wait_expired(t0)) {
+                            atomicOr(a.status, kDevErrGridWaitTimeout);
+                            *s_err = 1;
+                            break;
+                        }
+                    }
+                }
+                dst[i] = __uint_as_float((uint32_t)e);
+            }
+        }
+    }
+
+    __syncthreads();
+    if (tid == 0) {
+        launch_done(a.tsync, blockIdx.x, gridDim.x);
+        if (a.step_counter != a.tsync) launch_done(a.step_counter, blockIdx.x, gridDim.x);
+    }
+    // After a failed wait some TMA loads may still be in flight towards this CTA's shared memory: wait
+    // (bounded) for the stages that were issued before leaving.
+    if (*s_err && warp == 8 && lane == 0) {
+        const uint32_t first = issued > NST ? issued - NST : 0;
+        for (uint32_t j = first; j < issued; ++j) mbar_wait(&full[j % NST], (j / NST) & 1u);
+    }
+}
+
+inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank) {
+    if (max_kb == 0 || max_kb % kGemvGranuleBlocks != 0) return 0;
+    uint32_t off = 2 * kMaxStages * 8 + 128;      // mbarriers, then the block of zeros
+    a.off_t = off;
+    off += align_up(max_rank * 4, 128);
+    a.off_xs = off;
+    off += align_up(max_kb * 64, 128);
+    a.off_sx = off;
+    off += align_up(max_kb * 8, 128);
+    a.off_stage = off;
+    const uint32_t budget = (uint32_t)kMaxSmem - 1024;    // static shared memory and driver reserve
+    if (off + 2 * kSlotBytes > budget) return 0;
+    uint32_t nst = (budget - off) / kSlotBytes;
+    if (nst > 4) nst = 4;
+    a.nstages = nst;
+    return (size_t)off + (size_t)nst * kSlotBytes;
+}
+
+cudaError_t launch_decode_step(const StepArgs& a, size_t smem, int grid, cudaStream_t s) {
+    static DeviceOnce once;            // the shared-memory opt-in is per device
+    cudaError_t e = opt_in_smem(reinterpret_cast<const void*>(decode_step_kernel), kMaxSmem - 1024, once);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kStepThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (a.use_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, decode_step_kernel, a);
+}
+
+}  // namespace lq4

@@ -211,6 +211,57 @@ class PeerGather:
             self._buf = None
 
 
+class StepBuffer:
+    """The buffer a decode step's activations travel through (``lq4_step_buf_create``): ``payload`` is a flat
+    f32 device tensor; outputs whose ``y`` is a slice of it can feed later groups of the same
+    ``lq4_decode_step`` call, on this GPU and - with a process group - on every rank (each rank creates a buffer
+    of the same size, the handles travel over the group, every rank maps the others')."""
+
+    def __init__(self, n_floats: int, group: Optional[dist.ProcessGroup] = None, device: Optional[int] = None):
+        L = _lib.lib()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > _lib.MAX_PEERS:
+            raise ValueError(f"at most {_lib.MAX_PEERS} ranks")
+        if device is not None:
+            torch.cuda.set_device(device)
+        h = C.c_void_p()
+        _lib.check(L.lq4_step_buf_create(n_floats, C.byref(h)))
+        self._buf = h.value
+        self._opened: List[int] = []
+        bases = [0] * self.world
+        bases[self.rank] = L.lq4_peer_buf_base(self._buf)
+        if self.world > 1:
+            handle = (C.c_uint8 * _lib.PEER_HANDLE_BYTES)()
+            _lib.check(L.lq4_peer_buf_export(self._buf, handle))
+            handles: List[Optional[bytes]] = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                raw = (C.c_uint8 * _lib.PEER_HANDLE_BYTES).from_buffer_copy(handles[r])
+                p = C.c_void_p()
+                _lib.check(L.lq4_peer_buf_open(raw, C.byref(p)))
+                self._opened.append(p.value)
+                bases[r] = p.value
+        self.desc = _lib.GatherDesc(self.world, self.rank, (C.c_void_p * _lib.MAX_PEERS)(*bases))
+        self.payload = torch.as_tensor(_DeviceArray(L.lq4_peer_buf_payload(self._buf), (n_floats,), self), device="cuda")
+
+    def close(self) -> None:
+        L = _lib.lib()
+        if dist.is_initialized() and self.world > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)       # nobody unmaps while a peer may still write
+        for p in self._opened:
+            L.lq4_peer_buf_close(p)
+        self._opened = []
+        if self._buf:
+            self.payload = None
+            L.lq4_peer_buf_free(self._buf)
+            self._buf = None
+
+
 def merge_topk_candidates(vals: torch.Tensor, ids: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """The best ``top_k`` of any number of candidate lists, in the reference's candidate order (higher logit
     first, ties to the lower token id; shaders/qwen35.metal:1697-1703).  ``vals`` f32 and ``ids`` (token ids as
