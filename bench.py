@@ -3,7 +3,7 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Headline workload (config.workload): the large-layer decode set of BASELINE.json's configs[2]
+Headline workload (config.workload): the large-layer decode set
 - per "layer" the four projections 5120->5120, 5120->1024, 5120->17408, 17408->5120 with Q4
 weights quantized from N(0, 0.02^2) and a LoRA adapter of rank 16 on every projection, one
 token (M = 1) - repeated over `--layers` layers with distinct weights (4 x 131 MB by default,
@@ -37,11 +37,35 @@ UNIT = "GB/s"
 LORA_RANK, LORA_ALPHA = 16, 32.0
 SHAPES = [(5120, 5120), (5120, 1024), (5120, 17408), (17408, 5120)]      # (k, n)
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per projection (decode kernel + its LoRA projection
-# kernel), averaged over the four shapes of a layer, from the ncu capture summarised in profiles/
-# dram bytes per decode launch from the ncu launch list in profiles/decode_kernel_large_layer_set.md
-# (None: not captured for the current kernel)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"per-projection": None, "grouped": 138.64e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu capture of
+# `python bench.py --only decode-set` / `--only decode-step` (None: not captured for the current kernel).
+# A capture belongs to the kernel source it was taken on: the entry carries the hash of the kernel files
+# (kernel_source_hash below) at capture time, and the figure is reported only while that still matches.
+NCU_TRAFFIC = {
+    "grouped": {"bytes_per_launch": 138.64e6, "kernel": "decode_kernel<1, 8>", "source_hash": None},
+    "per-projection": {"bytes_per_launch": None, "kernel": "decode_kernel<1, 1>", "source_hash": None},
+    "step": {"bytes_per_launch": None, "kernel": "decode_step_kernel", "source_hash": None},
+}
+
+
+def kernel_source_hash(files=("lq4_decode.cu", "lq4_decode_common.cuh", "lq4_step.cu", "lq4_step.cuh", "lq4_common.cuh")):
+    import hashlib
+    h = hashlib.sha256()
+    for f in files:
+        p = os.path.join(ROOT, "lattice_b200", "csrc", f)
+        if os.path.exists(p):
+            h.update(open(p, "rb").read())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic(launch):
+    """(bytes per launch or None, note): the captured DRAM traffic if it was taken on the current kernel source."""
+    e = NCU_TRAFFIC.get(launch) or {}
+    if e.get("bytes_per_launch") is None:
+        return None, "not captured"
+    if e.get("source_hash") != kernel_source_hash():
+        return None, f"captured on an earlier version of {e['kernel']} ({e['bytes_per_launch'] / 1e6:.2f} MB per launch then)"
+    return e["bytes_per_launch"], f"ncu capture of {e['kernel']} on this kernel source"
 
 
 def algorithmic_bytes(m, n, k, rank):
@@ -176,10 +200,15 @@ def workload_config(args, world):
     return {"workload": "configs[2] large-layer decode set: (5120->5120, 5120->1024, 5120->17408, 17408->5120) "
                         f"x {args.layers} layers, M={args.m}, Q4 weights ~N(0,0.02^2), LoRA r={LORA_RANK} alpha={LORA_ALPHA:g}",
             "m": args.m, "layers": args.layers, "lora_rank": LORA_RANK,
-            "launch": ("one lq4_linear_group call per set: the four independent projections share one persistent launch"
-                       if args.launch == "grouped" else "one lq4_linear call per projection"),
+            "launch": {"grouped": "one lq4_linear_group call per set: the four independent projections share one persistent launch",
+                       "per-projection": "one lq4_linear call per projection",
+                       "step": "one lq4_decode_step call per step: the sets are the groups of ONE persistent launch" +
+                               (", chained (a set's 5120- and 17408-wide inputs are the previous set's gathered down/up outputs, "
+                                "read through the mailbox as they arrive)" if not args.independent else ", independent sets")}[args.launch],
             "parallelism": (f"N-sharded column-parallel x{world}, " +
-                            ("all-gather fused into the decode kernel's epilogue (peer stores over NVLink + arrival counters)"
+                            ("outputs published to every rank's mailbox from the kernel's epilogue (8-byte tagged stores over NVLink), "
+                             "gathered to plain f32 at the end of the same launch" if args.launch == "step" else
+                             "all-gather fused into the decode kernel's epilogue (peer stores over NVLink + arrival counters)"
                              if args.gather == "peer" else "one NCCL all-gather per set")) if world > 1 else "single GPU",
             "l2": "inputs larger than L2: every launch streams distinct weights, "
                   f"{args.layers * 131.072:.0f} MB of Q4 payload per step per job"}
@@ -231,13 +260,16 @@ def run_ours(args):
         layers.append(projs)
     gen.manual_seed(99)
     xs = {k: torch.randn((m, k), generator=gen, device=dev) for k in (5120, 17408)}
+    step_mode = args.launch == "step"
+    if step_mode and m != 1:
+        raise SystemExit("--launch step takes one token (--m 1)")
     # The outputs of one set sit side by side in one buffer, each projection writing its column range
     # (ldy = row pitch).  One GPU: [m, sum(n)].  Several GPUs: the same [m, sum(n)] buffer exists on
     # every rank as a peer buffer, a rank computes the columns of its N-shards and the decode kernels'
     # epilogue writes them into every rank's copy (--gather peer); or, the plain way, the local slices
     # are exchanged with ONE NCCL all-gather per set (--gather nccl).
     from lattice_b200.sharded import PeerGather
-    peer_mode = world > 1 and args.gather in ("peer", "peer-nowait")
+    peer_mode = world > 1 and args.gather in ("peer", "peer-nowait") and not step_mode
     peer_wait = args.gather == "peer"
     nls = [layers[0][si]["nl"] for si in range(len(SHAPES))]
     offs = [sum(nls[:si]) for si in range(len(SHAPES))]
@@ -303,6 +335,80 @@ def run_ours(args):
         if peer_mode and peer_wait:
             be.gather_wait(gdesc)                  # stream-ordered: the last set's peer columns have arrived
 
+    step_check = None
+    if step_mode:
+        # ONE launch per step.  Every set's full output row (all ranks' columns side by side) lives in the step
+        # buffer; set li > 0 takes its 5120-wide input from set li-1's 17408->5120 output and its 17408-wide input
+        # from set li-1's 5120->17408 output (chained), so a set can only start when the previous set's columns
+        # of ALL ranks have arrived - the dependency a decode step really has.
+        from lattice_b200.sharded import StepBuffer
+        S = sum(full_n)
+        sbuf = StepBuffer(args.layers * S, device=local_rank)
+        pay = sbuf.payload
+        chained = not args.independent
+
+        def row_of(li, si):
+            return pay[li * S + full_offs[si]: li * S + full_offs[si] + full_n[si]]
+
+        def y_of(li, si):
+            b0 = li * S + full_offs[si] + layers[li][si]["n0"]
+            return pay[b0: b0 + nls[si]]
+
+        def build_step(x_ext):
+            groups = []
+            for li, projs in enumerate(layers):
+                grp = []
+                for si, p in enumerate(projs):
+                    if li == 0 or not chained:
+                        x = x_ext[p["k"]]
+                    else:
+                        x = row_of(li - 1, 3) if p["k"] == 5120 else row_of(li - 1, 2)
+                    grp.append((x, p["qw"], p["lora"], y_of(li, si)))
+                groups.append(grp)
+            return be.prepare_step(groups, sbuf, gathered=[pay[li * S:(li + 1) * S] for li in range(args.layers)])
+
+        step = build_step(xs)
+
+        # checked once before timing against the same chain issued set by set (one grouped launch per set,
+        # the slices exchanged by NCCL between the sets)
+        def reference_chain():
+            x_of = dict(xs)
+            rows = []
+            for li, projs in enumerate(layers):
+                outs = [torch.empty((1, p["nl"]), device=dev) for p in projs]
+                be.linear_group([(x_of[p["k"]], p["qw"], p["lora"]) for p in projs], outs)
+                full = []
+                for o in outs:
+                    if world > 1:
+                        parts = [torch.empty_like(o) for _ in range(world)]
+                        dist.all_gather(parts, o)
+                        full.append(torch.cat(parts, dim=1))
+                    else:
+                        full.append(o)
+                rows.append(torch.cat(full, dim=1))
+                if chained:
+                    x_of = {5120: full[3].contiguous(), 17408: full[2].contiguous()}
+            return torch.cat(rows, dim=1).reshape(-1)
+
+        step()
+        torch.cuda.synchronize()
+        be.check_device_status()
+        ref = reference_chain()
+        torch.cuda.synchronize()
+        rms = float(ref.double().pow(2).mean().sqrt())
+        ratio = float(((pay - ref).abs().double() / (1e-3 * (ref.abs().double() + rms))).max())
+        if not (ratio <= 1.0) or not bool(torch.isfinite(pay).all()):
+            raise SystemExit(f"step launch differs from the set-by-set chain on rank {rank}: tolerance ratio {ratio}")
+        if world > 1:
+            lo, hi = pay.clone(), pay.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            if not torch.equal(lo, hi):
+                raise SystemExit("ranks hold different gathered rows after the step launch")
+        step_check = {"against": "the same chain issued as one grouped launch per set" + (" + NCCL all-gather between sets" if world > 1 else ""),
+                      "max_tolerance_ratio": ratio, "all_ranks_identical": True}
+        note(f"step launch checked, tolerance ratio {ratio:.3g}")
+
     # pinned host buffers for the end-to-end variant
     hx = {k: torch.randn((m, k)).pin_memory() for k in (5120, 17408)}
     hy = torch.empty((args.layers,) + tuple(y_full.shape)).pin_memory()      # one result per set
@@ -311,7 +417,13 @@ def run_ours(args):
     # One GPU: the inputs of the step's sets sit in one pinned buffer and go in with ONE copy, every set
     # has its own device inputs and output, and the results come back with ONE copy: a copy-engine
     # operation costs several microseconds however small it is.
-    batched = world == 1
+    batched = world == 1 and not step_mode
+    if step_mode:
+        # one pinned buffer in (the step's external inputs), one launch, one pinned buffer out (every set's rows)
+        hx_cat = torch.randn(5120 + 17408).pin_memory()
+        dx_cat = torch.empty(5120 + 17408, device=dev)
+        hy_step = torch.empty(args.layers * S).pin_memory()
+        e2e_step_call = build_step({5120: dx_cat[:5120].view(1, -1), 17408: dx_cat[5120:].view(1, -1)})
     if batched:
         xw = 5120 + 17408
         hx_all = torch.randn((args.layers, m, xw)).pin_memory()
@@ -335,6 +447,11 @@ def run_ours(args):
 
     def e2e_body():
         # host activations in (pinned -> device), the public call per set, host results out
+        if step_mode:
+            dx_cat.copy_(hx_cat, non_blocking=True)
+            e2e_step_call()
+            hy_step.copy_(pay, non_blocking=True)
+            return
         if batched:
             dx_all.copy_(hx_all, non_blocking=True)
             for li, projs in enumerate(layers):
@@ -365,7 +482,7 @@ def run_ours(args):
             with torch.cuda.graph(e2e_graph, stream=side):
                 e2e_body()
             e2e_info["mode"] = ("cuda-graph replay of the step's copies and kernels" +
-                                (" (one copy in, one copy out per step)" if batched else "") + ", one wait per step")
+                                (" (one copy in, one copy out per step)" if batched or step_mode else "") + ", one wait per step")
         except Exception as e:
             e2e_graph = None
             e2e_info["mode"] = "plain calls, one wait per step (graph capture failed: %r)" % (e,)
@@ -454,7 +571,7 @@ def run_ours(args):
     value = per_step_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e_value = per_step_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
     hbm_peak, tc_peak, tc_sust, which = measured_peaks()
-    n_lin = args.layers * (1 if grouped else len(SHAPES))
+    n_lin = 1 if step_mode else args.layers * (1 if grouped else len(SHAPES))
     # the step's launches are the decode kernel, one per set when grouped, else one per projection (at
     # M = 1 nothing else runs; at M > 1 a small preparation kernel is chained in front of each), so the
     # average launch duration is the event time over the decode launches, and algorithmic bytes per
@@ -467,10 +584,11 @@ def run_ours(args):
             "config": workload_config(args, world),
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / e2e_steps,
                     "mode": e2e_info["mode"],
-                    "h2d_bytes_per_step": int(args.layers * sum(m * k * 4 for k in (5120, 17408))),
+                    "h2d_bytes_per_step": int((1 if step_mode else args.layers) * sum(m * k * 4 for k in (5120, 17408))),
                     "d2h_bytes_per_step": int(args.layers * sum(m * n * 4 for _, n in SHAPES))},
             "gpu_launches": int(launches), "launch_mode": graph_info["mode"],
-            "roofline": {"bound": "hbm", "kernel": ("decode_kernel<1, 8>: one persistent launch per set of four projections" if grouped
+            "roofline": {"bound": "hbm", "kernel": ("decode_step_kernel: one persistent launch per step (all sets)" if step_mode else
+                                                 "decode_kernel<1, 8>: one persistent launch per set of four projections" if grouped
                                                  else "decode_kernel<1, 1>: one launch per projection") +
                                                 ", LoRA projection inside the same launch" if m == 1 else
                                                 "dense_kernel + dense_prep_kernel (activation limbs, LoRA projection) per " +
@@ -478,8 +596,11 @@ def run_ours(args):
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
                          "avg_launch_us": avg_launch_us, "algorithmic_bytes_per_launch": per_step_bytes / world / n_lin,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH[args.launch] if m == 1 and world == 1 else None},
+                         "traffic": ncu_traffic(args.launch)[0] if m == 1 and world == 1 else None,
+                         "traffic_note": ncu_traffic(args.launch)[1]},
             "clocks": clocks}
+    if step_check is not None:
+        line["checked_before_timing"] = step_check
 
     if rank == 0 and world == 1 and not args.no_aux:
         line["aux"] = aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust)
@@ -505,13 +626,20 @@ def run_ours(args):
             return {"GB/s": v, "frac_hbm": v / hbm_peak, "us_per_set": gms * 1e3 / nsteps / args.layers}
         for mm in (1, 4, 16):
             for grp in (True, False):
-                if mm == m and grp == grouped:
+                if not step_mode and mm == m and grp == grouped:
                     continue
                 line["aux"][f"decode_set_M{mm}_" + ("grouped" if grp else "per_projection")] = time_sets(mm, grp)
+    if world > 1 and not args.no_aux:
+        sharded = aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust)      # every rank takes part
+        if rank == 0:
+            line.setdefault("aux", {})["config4_prefill_M2048_K5120_N17408_lora64_bf16_sharded"] = sharded
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(layers[0])
     if rank == 0:
         print(json.dumps(line))
+    if step_mode:
+        torch.cuda.synchronize()
+        sbuf.close()
     if world > 1:
         if pg is not None:
             prepared.clear()
@@ -566,6 +694,74 @@ def cpu_baseline(gpu_layer):
             "sample": f"{reps} repeats of one token-set (4 projections of layer 0, M=1, LoRA r=16), single thread as "
                       f"the reference's matmul_bt is; kernel {oracle.matmul_bt_kernel(1, 5120, 5120)}; "
                       f"f32 weights pre-dequantized at load (untimed)", "ms_per_token_set": dt / reps * 1e3}
+
+
+def aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust):
+    """The prefill GEMM (M=2048, K=5120, N=17408, LoRA r=64, bf16 activations) with its output rows sharded over
+    the ranks and the [M, N / world] slices gathered over NCCL through lq4_linear_sharded: plain calls, CUDA events
+    from the first launch to the gathered y, MAX over ranks; beside it the local product alone."""
+    import torch
+    import torch.distributed as dist
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import LoraDesc
+    from lattice_b200.sharded import NcclShardedLinear, shard_plan
+    m, k, n, r = 2048, 5120, 17408, 64
+    out = {}
+    try:
+        n0, n1, _ = shard_plan(n, k, world, rank)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(4400 + rank)
+        w = torch.randn((n1 - n0, k), generator=gen, device=dev) * 0.02
+        qw = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), n1 - n0, k)
+        del w
+        gen.manual_seed(4500)
+        a = torch.randn((r, k), generator=gen, device=dev) * 0.02
+        x = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
+        gen.manual_seed(4600 + rank)
+        b = torch.randn((n1 - n0, r), generator=gen, device=dev) * 0.02
+        lora = LoraDesc(a.data_ptr(), b.data_ptr(), r, 2.0)
+        lin = NcclShardedLinear(be, qw, n, lora=lora)
+        y = torch.empty((m, n), device=dev)
+        y_local = torch.empty((m, n1 - n0), device=dev)
+
+        def timed_max(fn, reps):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        us_total = timed_max(lambda: lin.forward(x, out=y), 10)
+        be.check_device_status()
+        # every rank's columns of the gathered output are what that rank computed
+        be.dispatch_gemm_q4(x, 0, qw, y_local, 0, m, n1 - n0, k, lora=lora)
+        torch.cuda.synchronize()
+        same = torch.tensor([int(torch.equal(y[:, n0:n1], y_local))], device=dev)
+        parts = [torch.empty_like(y_local) for _ in range(world)]
+        dist.all_gather(parts, y_local)
+        same &= int(torch.equal(torch.cat(parts, dim=1), y))
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        us_local = timed_max(lambda: be.dispatch_gemm_q4(x, 0, qw, y_local, 0, m, n1 - n0, k, lora=lora), 10)
+        flops = 2 * m * n * k + 2 * m * r * (k + n)
+        out = {"us_per_call": us_total, "TFLOP/s_aggregate": flops / us_total / 1e6,
+               "frac_bf16_burst_per_gpu": flops / us_total / 1e6 / world / tc_peak if tc_peak else None,
+               "us_local_product_alone": us_local, "us_exchange_and_placement_not_hidden": us_total - us_local,
+               "gathered_bytes_per_rank": int(m * n * 4 * (world - 1) // world),
+               "gathered_output_checked": bool(int(same.item())), "timing": "plain calls, CUDA events, max over ranks",
+               "exchange": "ncclAllGather per tile-row block on a second stream + placement pass"}
+        lin.close()
+    except Exception as e:                                   # an aux failure must not hide the headline
+        out = {"error": repr(e)}
+    return out
 
 
 def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
@@ -717,10 +913,12 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
         gu = torch.empty((1, 2 * inter), device=dev)
         hbuf = torch.empty((1, inter), device=dev)
         res = {}
-        for what in ("block", "separate"):
+        for what in ("block", "two_launches", "separate"):
             def call(i):
                 qgu, qd = sets[i % copies]
-                if what == "block":
+                if what == "block":              # gate||up row in the library's step buffer: ONE launch
+                    be.mlp_block(x, qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2], out=y)
+                elif what == "two_launches":     # caller's gate||up scratch: grouped gate/up launch, then down_proj gating its input
                     be.mlp_block(x, qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2], gate_up=gu, out=y)
                 else:
                     be.dispatch_gemm_q4_at(x, 0, qgu, 0, gu, 0, 1, inter, hidden, lora=descs[0])
@@ -746,7 +944,7 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
             res[what] = e0.elapsed_time(e1) * 1e3 / reps
         byts = 3 * inter * (hidden // 32) * 20 + 4 * rank * 3 * (hidden + inter)
         us = res["block"]
-        out[name] = {"us_per_block": us, "us_separate_calls": res["separate"], "GB/s": byts / us / 1e3,
+        out[name] = {"us_per_block": us, "us_two_launches": res["two_launches"], "us_separate_calls": res["separate"], "GB/s": byts / us / 1e3,
                      "frac_hbm": byts / us / 1e3 / hbm_peak, "weight_copies": copies, "timing": "cuda-graph replay"}
 
     try:
@@ -791,6 +989,38 @@ def run_only(args):
         torch.cuda.synchronize()
         be.check_device_status()
         print("ok", args.only)
+        return
+    elif args.only == "decode-step":       # M=1, --layers chained sets of the four large-layer shapes in ONE launch
+        from lattice_b200.sharded import StepBuffer
+        S = sum(n for _, n in SHAPES)
+        offs_full = [sum(n for _, n in SHAPES[:i]) for i in range(len(SHAPES))]
+        sbuf = StepBuffer(args.layers * S)
+        pay = sbuf.payload
+        keep, groups = [], []
+        x_ext = {k: torch.randn((1, k), device=dev) for k in (5120, 17408)}
+        for li in range(args.layers):
+            grp = []
+            for si, (k, n) in enumerate(SHAPES):
+                w = torch.randn((n, k), device=dev) * 0.02
+                qw = Q4WeightBuf.from_device_payload(be.quantize(w.reshape(-1)), n, k)
+                del w
+                a = torch.randn((LORA_RANK, k), device=dev) * 0.02
+                b = torch.randn((n, LORA_RANK), device=dev) * 0.02
+                keep += [a, b]
+                if li == 0:
+                    x = x_ext[k]
+                else:
+                    src = 3 if k == 5120 else 2
+                    x = pay[(li - 1) * S + offs_full[src]: (li - 1) * S + offs_full[src] + SHAPES[src][1]]
+                grp.append((x, qw, LoraDesc(a.data_ptr(), b.data_ptr(), LORA_RANK, 2.0),
+                            pay[li * S + offs_full[si]: li * S + offs_full[si] + n]))
+            groups.append(grp)
+        step = be.prepare_step(groups, sbuf, gathered=[])
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        be.check_device_status()
+        print("ok", args.only, float(pay.abs().max()))
         return
     elif args.only == "mlp-block":         # M=1 dense FFN, hidden 5120, inter 17408, three r=16 adapters
         hidden, inter = 5120, 17408
@@ -854,16 +1084,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--m", type=int, default=1)
-    ap.add_argument("--launch", default="grouped", choices=["grouped", "per-projection"],
-                    help="grouped: one persistent launch per set of four projections (lq4_linear_group); "
+    ap.add_argument("--launch", default="grouped", choices=["step", "grouped", "per-projection"],
+                    help="step: one persistent launch per step, the sets are its groups (lq4_decode_step); "
+                         "grouped: one persistent launch per set of four projections (lq4_linear_group); "
                          "per-projection: one lq4_linear call each")
+    ap.add_argument("--independent", action="store_true",
+                    help="with --launch step: the sets do not feed one another (every set reads the external inputs)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "peer-nowait", "none"],
                     help="several GPUs: peer = all-gather fused into the kernel epilogue (stores into every "
                          "rank's buffer over NVLink); nccl = one NCCL all-gather per set; peer-nowait and none are "
                          "diagnostics (no waiting for the peers / no exchange at all): their values are not results")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
-    ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set | mlp-block | lm-head: three launches of one case, for profiling")
+    ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set | decode-step | mlp-block | lm-head: three launches of one case, for profiling")
     ap.add_argument("--no-aux", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

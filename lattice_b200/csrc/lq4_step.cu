@@ -351,9 +351,12 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         const float2* sx_all = reinterpret_cast<const float2*>(smem + a.off_sx);
         float* t_sm = reinterpret_cast<float*>(smem + a.off_t);
 
+        // A failed wait (its time limit, or another wait of this CTA failed before) never changes the control
+        // flow: every warp keeps walking the same groups, tiles and stages, so the named barriers below always
+        // see all eight warps; once s_err is set every later wait returns at once and the walk is short.
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t g = 0; g < a.ngroups && ok; ++g) {
+        for (uint32_t g = 0; g < a.ngroups; ++g) {
             const Share sh = step_share(a, g, blockIdx.x);
             if (!sh.any) continue;                                 // the same for every thread of the CTA
             const StepProblem& q = a.p[sh.pi];
@@ -394,7 +397,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 t_loaded = true;
             };
             uint32_t git = 0;                                      // stages of this group consumed so far
-            for (uint64_t pos = sh.r0; pos < sh.r1 && ok;) {
+            for (uint64_t pos = sh.r0; pos < sh.r1;) {
                 const uint32_t tile = (uint32_t)(pos / q.kg);
                 const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
                 const uint64_t left = sh.r1 - pos;
@@ -414,7 +417,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     const uint32_t ngr = stage_granules(g1 - gs);
                     const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
                     const uint32_t s = it % NST;
-                    if (!mbar_wait_step(&full[s], (it / NST) & 1u, s_err)) { ok = false; break; }
+                    if (!mbar_wait_step(&full[s], (it / NST) & 1u, s_err)) { ok = false; *s_err = 1; }
                     if (git == 6 && q.rank && !t_loaded) gather_t();
                     const uint8_t* st = smem + a.off_stage + (size_t)s * kSlotBytes;
                     const uint8_t* row0 = st + (warp * 16 + gq) * rs + t * kBlockBytes;
@@ -454,7 +457,6 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     if (lane == 0) mbar_arrive(&empty[s]);
                     gs += ngr;
                 }
-                if (!ok) break;
 
                 // each thread of a quad covered blocks = t (mod 4): add the four
                 float v0 = acc0, v1 = acc1;
