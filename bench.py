@@ -81,15 +81,17 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons (every 100 ms, with the host time each sample was read)
+    while the process measures; `window(t0, t1)` summarises the samples that fall into a timed region."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.idx = gpu_index
         self.proc = None
-        self.lines = []
+        self.samples = []          # (host time, sm MHz, max sm MHz, set of active reasons)
 
     def start(self):
         try:
@@ -102,33 +104,41 @@ class ClockSampler:
 
     def _read(self):
         for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm, mx = float(f[1]), float(f[2])
+            except ValueError:
+                continue
+            reasons = {n for n, v in zip(self.NAMES, f[5:9]) if v.lower().startswith("active")}
+            self.samples.append((time.time(), sm, mx, reasons))
+
+    def window(self, t0: float, t1: float):
+        """Clocks seen in the host-time window [t0, t1] (widened by one sampling period on both sides, since a
+        timed region may be shorter than the period)."""
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        if time.time() < t1 + 0.12:
+            time.sleep(max(0.0, t1 + 0.12 - time.time()))
+        pick = [x for x in self.samples if t0 - 0.11 <= x[0] <= t1 + 0.11]
+        if not pick:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        reasons = set()
+        for x in pick:
+            reasons |= x[3]
+        sm = [x[1] for x in pick]
+        return {"sm_mhz": float(np.median(sm)), "sm_min_mhz": float(min(sm)), "sm_max_mhz": float(max(x[2] for x in pick)),
+                "reasons": sorted(reasons), "samples": len(pick)}
 
     def stop(self):
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        for ln in self.lines:
-            f = [s.strip() for s in ln.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm)}
 
 
 # ----------------------------------------------------------------------------- reference arm
@@ -207,7 +217,8 @@ def workload_config(args, world):
                                 "read through the mailbox as they arrive)" if not args.independent else ", independent sets")}[args.launch],
             "parallelism": (f"N-sharded column-parallel x{world}, " +
                             ("outputs published to every rank's mailbox from the kernel's epilogue (8-byte tagged stores over NVLink), "
-                             "gathered to plain f32 at the end of the same launch" if args.launch == "step" else
+                             "gathered to plain f32 at the end of the same launch" +
+                             ("" if args.chained else "; no set waits for another set's exchange") if args.launch == "step" else
                              "all-gather fused into the decode kernel's epilogue (peer stores over NVLink + arrival counters)"
                              if args.gather == "peer" else "one NCCL all-gather per set")) if world > 1 else "single GPU",
             "l2": "inputs larger than L2: every launch streams distinct weights, "
@@ -336,78 +347,90 @@ def run_ours(args):
             be.gather_wait(gdesc)                  # stream-ordered: the last set's peer columns have arrived
 
     step_check = None
+    step_variants = {}
     if step_mode:
-        # ONE launch per step.  Every set's full output row (all ranks' columns side by side) lives in the step
-        # buffer; set li > 0 takes its 5120-wide input from set li-1's 17408->5120 output and its 17408-wide input
-        # from set li-1's 5120->17408 output (chained), so a set can only start when the previous set's columns
-        # of ALL ranks have arrived - the dependency a decode step really has.
+        # ONE launch per step: the sets are the ordered groups of a single lq4_decode_step call and every set's
+        # full output row (all ranks' columns side by side) lives in the step buffer.
+        #   independent: every set reads the step's external inputs (the workload as it is defined: four
+        #                projections per set, nothing links the sets); with several GPUs no set waits for another,
+        #                and when the launch completes every rank holds every rank's columns.
+        #   chained:     set li > 0 takes its 5120-wide input from set li-1's 17408->5120 output and its 17408-wide
+        #                input from set li-1's 5120->17408 output, so a set can only start when the previous set's
+        #                columns of ALL ranks have arrived - the dependency a real decode step has.
         from lattice_b200.sharded import StepBuffer
         S = sum(full_n)
-        sbuf = StepBuffer(args.layers * S, device=local_rank)
-        pay = sbuf.payload
-        chained = not args.independent
 
-        def row_of(li, si):
-            return pay[li * S + full_offs[si]: li * S + full_offs[si] + full_n[si]]
+        def make_step_variant(chained):
+            sbuf = StepBuffer(args.layers * S, device=local_rank)
+            pay = sbuf.payload
 
-        def y_of(li, si):
-            b0 = li * S + full_offs[si] + layers[li][si]["n0"]
-            return pay[b0: b0 + nls[si]]
+            def row_of(li, si):
+                return pay[li * S + full_offs[si]: li * S + full_offs[si] + full_n[si]]
 
-        def build_step(x_ext):
-            groups = []
-            for li, projs in enumerate(layers):
-                grp = []
-                for si, p in enumerate(projs):
-                    if li == 0 or not chained:
-                        x = x_ext[p["k"]]
-                    else:
-                        x = row_of(li - 1, 3) if p["k"] == 5120 else row_of(li - 1, 2)
-                    grp.append((x, p["qw"], p["lora"], y_of(li, si)))
-                groups.append(grp)
-            return be.prepare_step(groups, sbuf, gathered=[pay[li * S:(li + 1) * S] for li in range(args.layers)])
+            def y_of(li, si):
+                b0 = li * S + full_offs[si] + layers[li][si]["n0"]
+                return pay[b0: b0 + nls[si]]
 
-        step = build_step(xs)
+            def build(x_ext):
+                groups = []
+                for li, projs in enumerate(layers):
+                    grp = []
+                    for si, p in enumerate(projs):
+                        if li == 0 or not chained:
+                            x = x_ext[p["k"]]
+                        else:
+                            x = row_of(li - 1, 3) if p["k"] == 5120 else row_of(li - 1, 2)
+                        grp.append((x, p["qw"], p["lora"], y_of(li, si)))
+                    groups.append(grp)
+                return be.prepare_step(groups, sbuf, gathered=[pay[li * S:(li + 1) * S] for li in range(args.layers)])
 
-        # checked once before timing against the same chain issued set by set (one grouped launch per set,
-        # the slices exchanged by NCCL between the sets)
-        def reference_chain():
-            x_of = dict(xs)
-            rows = []
-            for li, projs in enumerate(layers):
-                outs = [torch.empty((1, p["nl"]), device=dev) for p in projs]
-                be.linear_group([(x_of[p["k"]], p["qw"], p["lora"]) for p in projs], outs)
-                full = []
-                for o in outs:
-                    if world > 1:
-                        parts = [torch.empty_like(o) for _ in range(world)]
-                        dist.all_gather(parts, o)
-                        full.append(torch.cat(parts, dim=1))
-                    else:
-                        full.append(o)
-                rows.append(torch.cat(full, dim=1))
-                if chained:
-                    x_of = {5120: full[3].contiguous(), 17408: full[2].contiguous()}
-            return torch.cat(rows, dim=1).reshape(-1)
+            run = build(xs)
 
-        step()
-        torch.cuda.synchronize()
-        be.check_device_status()
-        ref = reference_chain()
-        torch.cuda.synchronize()
-        rms = float(ref.double().pow(2).mean().sqrt())
-        ratio = float(((pay - ref).abs().double() / (1e-3 * (ref.abs().double() + rms))).max())
-        if not (ratio <= 1.0) or not bool(torch.isfinite(pay).all()):
-            raise SystemExit(f"step launch differs from the set-by-set chain on rank {rank}: tolerance ratio {ratio}")
-        if world > 1:
-            lo, hi = pay.clone(), pay.clone()
-            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-            if not torch.equal(lo, hi):
-                raise SystemExit("ranks hold different gathered rows after the step launch")
-        step_check = {"against": "the same chain issued as one grouped launch per set" + (" + NCCL all-gather between sets" if world > 1 else ""),
-                      "max_tolerance_ratio": ratio, "all_ranks_identical": True}
-        note(f"step launch checked, tolerance ratio {ratio:.3g}")
+            # checked once before timing against the same work issued set by set (one grouped launch per set, the
+            # slices exchanged by NCCL between the sets)
+            def reference():
+                x_of = dict(xs)
+                rows = []
+                for li, projs in enumerate(layers):
+                    outs = [torch.empty((1, p["nl"]), device=dev) for p in projs]
+                    be.linear_group([(x_of[p["k"]], p["qw"], p["lora"]) for p in projs], outs)
+                    full = []
+                    for o in outs:
+                        if world > 1:
+                            parts = [torch.empty_like(o) for _ in range(world)]
+                            dist.all_gather(parts, o)
+                            full.append(torch.cat(parts, dim=1))
+                        else:
+                            full.append(o)
+                    rows.append(torch.cat(full, dim=1))
+                    if chained:
+                        x_of = {5120: full[3].contiguous(), 17408: full[2].contiguous()}
+                return torch.cat(rows, dim=1).reshape(-1)
+
+            run()
+            torch.cuda.synchronize()
+            be.check_device_status()
+            ref = reference()
+            torch.cuda.synchronize()
+            rms = float(ref.double().pow(2).mean().sqrt())
+            ratio = float(((pay - ref).abs().double() / (1e-3 * (ref.abs().double() + rms))).max())
+            if not (ratio <= 1.0) or not bool(torch.isfinite(pay).all()):
+                raise SystemExit(f"step launch differs from the set-by-set form on rank {rank}: tolerance ratio {ratio}")
+            if world > 1:
+                lo, hi = pay.clone(), pay.clone()
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+                dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                if not torch.equal(lo, hi):
+                    raise SystemExit("ranks hold different gathered rows after the step launch")
+            check = {"against": "the same work issued as one grouped launch per set" + (" + NCCL all-gather between sets" if world > 1 else ""),
+                     "max_tolerance_ratio": ratio, "all_ranks_identical": True}
+            return dict(run=run, build=build, sbuf=sbuf, pay=pay, check=check)
+
+        step_variants["chained" if args.chained else "independent"] = make_step_variant(args.chained)
+        head = step_variants["chained" if args.chained else "independent"]
+        step, pay, step_check = head["run"], head["pay"], head["check"]
+        build_step = head["build"]
+        note(f"step launch checked, tolerance ratio {step_check['max_tolerance_ratio']:.3g}")
 
     # pinned host buffers for the end-to-end variant
     hx = {k: torch.randn((m, k)).pin_memory() for k in (5120, 17408)}
@@ -557,11 +580,14 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        time.sleep(0.25)                    # the first sample is there before the timed region starts
     step_fn, per_step_launches = make_graphed(step)
     note("launch mode: " + graph_info["mode"])
+    t_host0 = time.time()
     ms, launches = timed(step_fn, args.steps, args.warmup, per_step_launches)
+    t_host1 = time.time()
     note("device-timed leg done")
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.window(t_host0, t_host1) if rank == 0 else None
     be.check_device_status()
     e2e_ms, _ = timed(e2e_step, max(1, min(args.steps, 20)), 3)
     e2e_steps = max(1, min(args.steps, 20))
@@ -602,8 +628,12 @@ def run_ours(args):
     if step_check is not None:
         line["checked_before_timing"] = step_check
 
+    if world == 1 and not args.no_aux:
+        # the headline step replayed back to back for about two seconds: the rate a decode loop sustains once
+        # clocks and power have settled, with the sampled SM clock and the rate binned by clock
+        line.setdefault("aux", {})["sustained"] = sustained_run(step_fn, per_step_bytes, sampler, hbm_peak)
     if rank == 0 and world == 1 and not args.no_aux:
-        line["aux"] = aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust)
+        line["aux"].update(aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust, sampler))
         # the same decode set at other token counts and with the other launch mode, timed the same way
         def time_sets(mm, grp):
             xs_m = {k: torch.randn((mm, k), device=dev) for k in (5120, 17408)}
@@ -629,6 +659,22 @@ def run_ours(args):
                 if not step_mode and mm == m and grp == grouped:
                     continue
                 line["aux"][f"decode_set_M{mm}_" + ("grouped" if grp else "per_projection")] = time_sets(mm, grp)
+    if step_mode and not args.no_aux:
+        # the other form of the step, timed the same way on every rank (graph replay, max over ranks)
+        other = "independent" if args.chained else "chained"
+        var = make_step_variant(other == "chained")
+        step_variants[other] = var
+        gfn, gl = make_graphed(var["run"])
+        nsteps = min(args.steps, 20)
+        gms, _ = timed(gfn, nsteps, 3, gl)
+        be.check_device_status()
+        v = per_step_bytes * nsteps / (gms * 1e-3) / 1e9
+        if rank == 0:
+            line.setdefault("aux", {})[f"decode_step_M1_{other}"] = {
+                "GB/s": v, "frac_hbm_per_gpu": v / world / hbm_peak, "us_per_step": gms * 1e3 / nsteps,
+                "checked_before_timing": var["check"],
+                "what": ("every set's inputs are the previous set's gathered outputs: a set starts when the previous set's "
+                         "columns of all ranks have arrived" if other == "chained" else "nothing links the sets")}
     if world > 1 and not args.no_aux:
         sharded = aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust)      # every rank takes part
         if rank == 0:
@@ -636,10 +682,12 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(layers[0])
     if rank == 0:
+        sampler.stop()
         print(json.dumps(line))
     if step_mode:
         torch.cuda.synchronize()
-        sbuf.close()
+        for var in step_variants.values():
+            var["sbuf"].close()
     if world > 1:
         if pg is not None:
             prepared.clear()
@@ -694,6 +742,44 @@ def cpu_baseline(gpu_layer):
             "sample": f"{reps} repeats of one token-set (4 projections of layer 0, M=1, LoRA r=16), single thread as "
                       f"the reference's matmul_bt is; kernel {oracle.matmul_bt_kernel(1, 5120, 5120)}; "
                       f"f32 weights pre-dequantized at load (untimed)", "ms_per_token_set": dt / reps * 1e3}
+
+
+def sustained_run(step_fn, per_step_bytes, sampler, hbm_peak, seconds=2.0, chunk=100):
+    """Replays the step back to back for `seconds`, timing every chunk of `chunk` replays with CUDA events (no
+    host synchronisation inside), and relates each chunk's rate to the SM clock sampled closest to it."""
+    import torch
+    step_fn()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True)]
+    t0 = time.time()
+    evs[0].record()
+    while time.time() - t0 < seconds and len(evs) < 4000:
+        for _ in range(chunk):
+            step_fn()
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        evs.append(e)
+        if len(evs) % 8 == 0:
+            evs[-1].synchronize()          # keeps the queue a few chunks deep so the host clock tracks the device
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(len(evs) - 1)]
+    total_ms = sum(ms)
+    rates = [per_step_bytes * chunk / (x * 1e-3) / 1e9 for x in ms]
+    clk = sampler.window(t0, t1)
+    # chunk i ran at about t0 + (time of the chunks before it): pair it with the nearest clock sample
+    bins = {}
+    acc = 0.0
+    for x, r in zip(ms, rates):
+        mid = t0 + (acc + x / 2) * 1e-3
+        acc += x
+        near = min(sampler.samples, key=lambda q: abs(q[0] - mid), default=None)
+        if near is not None:
+            bins.setdefault(int(round(near[1] / 15.0) * 15), []).append(r)
+    return {"seconds": total_ms * 1e-3, "replays": chunk * len(ms), "GB/s": per_step_bytes * chunk * len(ms) / (total_ms * 1e-3) / 1e9,
+            "frac_hbm": per_step_bytes * chunk * len(ms) / (total_ms * 1e-3) / 1e9 / hbm_peak,
+            "GB/s_first_chunk": rates[0], "GB/s_last_chunk": rates[-1], "GB/s_min_chunk": min(rates),
+            "clocks": clk, "GB/s_by_sm_mhz": {str(k): float(np.mean(v)) for k, v in sorted(bins.items())}}
 
 
 def aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust):
@@ -764,8 +850,9 @@ def aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust):
     return out
 
 
-def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
-    """Secondary configurations, each timed with CUDA events over distinct weight copies."""
+def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust, sampler=None):
+    """Secondary configurations, each timed with CUDA events over distinct weight copies; every entry carries
+    the SM clock sampled while it was measured."""
     import torch
     from lattice_b200 import Q4WeightBuf
     from lattice_b200._lib import LoraDesc
@@ -947,17 +1034,23 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust):
         out[name] = {"us_per_block": us, "us_two_launches": res["two_launches"], "us_separate_calls": res["separate"], "GB/s": byts / us / 1e3,
                      "frac_hbm": byts / us / 1e3 / hbm_peak, "weight_copies": copies, "timing": "cuda-graph replay"}
 
+    def clocked(fn, name, *a, **kw):
+        t0 = time.time()
+        fn(name, *a, **kw)
+        if sampler is not None and name in out:
+            out[name]["clocks"] = sampler.window(t0, time.time())
+
     try:
-        bench_mlp("mlp_block_M1_hidden5120_inter17408_lora16", 5120, 17408, 16, 2, 40)
-        bench_linear("config1_M1_K1024_N3584_cold", 1, 1024, 3584, 0, 128, 512)
-        bench_linear("config1_M1_K1024_N3584_warm", 1, 1024, 3584, 0, 1, 512)
-        bench_linear("config2_M1_lora16_cold", 1, 1024, 3584, 16, 128, 512)
-        bench_linear("config2_M8_lora16_cold", 8, 1024, 3584, 16, 128, 512)
-        bench_linear("config5_quarot_M1_K4096_N11008", 1, 4096, 11008, 0, 8, 200, rot=True)
-        bench_linear("config4_prefill_M2048_K5120_N17408_lora64_bf16", 2048, 5120, 17408, 64, 1, 10,
-                     x_dtype=torch.bfloat16)
-        bench_linear("config5_quarot_M512_K4096_N11008", 512, 4096, 11008, 0, 1, 5, rot=True)
-        bench_lm_head("lm_head_topk50_vocab248320_K5120", 248320, 5120, 50, 20)
+        clocked(bench_mlp, "mlp_block_M1_hidden5120_inter17408_lora16", 5120, 17408, 16, 2, 40)
+        clocked(bench_linear, "config1_M1_K1024_N3584_cold", 1, 1024, 3584, 0, 128, 512)
+        clocked(bench_linear, "config1_M1_K1024_N3584_warm", 1, 1024, 3584, 0, 1, 512)
+        clocked(bench_linear, "config2_M1_lora16_cold", 1, 1024, 3584, 16, 128, 512)
+        clocked(bench_linear, "config2_M8_lora16_cold", 8, 1024, 3584, 16, 128, 512)
+        clocked(bench_linear, "config5_quarot_M1_K4096_N11008", 1, 4096, 11008, 0, 8, 200, rot=True)
+        clocked(bench_linear, "config4_prefill_M2048_K5120_N17408_lora64_bf16", 2048, 5120, 17408, 64, 1, 50,
+                x_dtype=torch.bfloat16)
+        clocked(bench_linear, "config5_quarot_M512_K4096_N11008", 512, 4096, 11008, 0, 1, 20, rot=True)
+        clocked(bench_lm_head, "lm_head_topk50_vocab248320_K5120", 248320, 5120, 50, 20)
     except Exception as e:                                   # an aux failure must not hide the headline
         out["error"] = repr(e)
     return out
@@ -1084,12 +1177,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--m", type=int, default=1)
-    ap.add_argument("--launch", default="grouped", choices=["step", "grouped", "per-projection"],
+    ap.add_argument("--launch", default="step", choices=["step", "grouped", "per-projection"],
                     help="step: one persistent launch per step, the sets are its groups (lq4_decode_step); "
                          "grouped: one persistent launch per set of four projections (lq4_linear_group); "
                          "per-projection: one lq4_linear call each")
-    ap.add_argument("--independent", action="store_true",
-                    help="with --launch step: the sets do not feed one another (every set reads the external inputs)")
+    ap.add_argument("--chained", action="store_true",
+                    help="with --launch step: every set's inputs are the previous set's gathered outputs (the dependent "
+                         "form; reported in aux otherwise)")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "peer-nowait", "none"],
                     help="several GPUs: peer = all-gather fused into the kernel epilogue (stores into every "
                          "rank's buffer over NVLink); nccl = one NCCL all-gather per set; peer-nowait and none are "
