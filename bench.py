@@ -214,11 +214,12 @@ def workload_config(args, world):
                        "per-projection": "one lq4_linear call per projection",
                        "step": "one lq4_decode_step call per step: the sets are the groups of ONE persistent launch" +
                                (", chained (a set's 5120- and 17408-wide inputs are the previous set's gathered down/up outputs, "
-                                "read through the mailbox as they arrive)" if not args.independent else ", independent sets")}[args.launch],
+                                "read through the mailbox as they arrive)" if args.chained else
+                                ", the sets in order, nothing links them (every set reads the step's external inputs)")}[args.launch],
             "parallelism": (f"N-sharded column-parallel x{world}, " +
-                            ("outputs published to every rank's mailbox from the kernel's epilogue (8-byte tagged stores over NVLink), "
-                             "gathered to plain f32 at the end of the same launch" +
-                             ("" if args.chained else "; no set waits for another set's exchange") if args.launch == "step" else
+                            (("outputs published to every rank's mailbox from the kernel's epilogue (8-byte tagged stores over NVLink), "
+                              "gathered to plain f32 at the end of the same launch" +
+                              ("" if args.chained else "; no set waits for another set's exchange")) if args.launch == "step" else
                              "all-gather fused into the decode kernel's epilogue (peer stores over NVLink + arrival counters)"
                              if args.gather == "peer" else "one NCCL all-gather per set")) if world > 1 else "single GPU",
             "l2": "inputs larger than L2: every launch streams distinct weights, "
