@@ -228,6 +228,16 @@ def workload_config(args, world):
 
 # ----------------------------------------------------------------------------- our arm
 def run_ours(args):
+    # The one JSON line is the only thing that may reach stdout: libraries loaded below (NCCL prints its version
+    # there) get stderr as their file descriptor 1, and the line is written to the saved descriptor at the end.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(obj) + "\n").encode())
+
     import torch
     import torch.distributed as dist
     from lattice_b200 import CudaQ4Backend, Q4WeightBuf
@@ -684,7 +694,7 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline(layers[0])
     if rank == 0:
         sampler.stop()
-        print(json.dumps(line))
+        emit(line)
     if step_mode:
         torch.cuda.synchronize()
         for var in step_variants.values():
@@ -839,7 +849,31 @@ def aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust):
         dist.all_reduce(same, op=dist.ReduceOp.MIN)
         us_local = timed_max(lambda: be.dispatch_gemm_q4(x, 0, qw, y_local, 0, m, n1 - n0, k, lora=lora), 10)
         flops = 2 * m * n * k + 2 * m * r * (k + n)
-        out = {"us_per_call": us_total, "TFLOP/s_aggregate": flops / us_total / 1e6,
+        # the same product with the all-gather fused into the tensor-core kernel's epilogue: every rank's slice is
+        # stored straight into every rank's [M, N] buffer over NVLink while the MMAs go on, a signal kernel and a
+        # wait kernel close the exchange (no NCCL, no staging, no placement pass)
+        from lattice_b200.sharded import PeerGather
+        pg = PeerGather(m, n, device=dev.index)
+        out_slice = pg.full[:, n0:n1]
+
+        def fused_call():
+            be.dispatch_gemm_q4(x, 0, qw, out_slice, 0, m, n1 - n0, k, lora=lora, ldy=n, gather=pg.desc)
+            be.gather_wait(pg.desc)
+
+        us_fused = timed_max(fused_call, 10)
+        be.check_device_status()
+        torch.cuda.synchronize()
+        dist.barrier()
+        same_fused = torch.tensor([int(torch.equal(pg.full, y))], device=dev)
+        dist.all_reduce(same_fused, op=dist.ReduceOp.MIN)
+        fused = {"us_per_call": us_fused, "TFLOP/s_aggregate": flops / us_fused / 1e6,
+                 "frac_bf16_burst_per_gpu": flops / us_fused / 1e6 / world / tc_peak if tc_peak else None,
+                 "us_exchange_not_hidden": us_fused - us_local,
+                 "nvlink_bytes_out_per_rank": int(m * (n1 - n0) * 4 * (world - 1)),
+                 "gathered_output_checked": bool(int(same_fused.item())),
+                 "exchange": "peer stores from the tensor-core kernel's epilogue + signal / wait kernels"}
+        pg.close()
+        out = {"fused_peer_store": fused, "us_per_call": us_total, "TFLOP/s_aggregate": flops / us_total / 1e6,
                "frac_bf16_burst_per_gpu": flops / us_total / 1e6 / world / tc_peak if tc_peak else None,
                "us_local_product_alone": us_local, "us_exchange_and_placement_not_hidden": us_total - us_local,
                "gathered_bytes_per_rank": int(m * n * 4 * (world - 1) // world),

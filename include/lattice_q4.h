@@ -119,7 +119,9 @@ typedef struct {
     const lq4_lora_desc* lora;   /* NULL = no adapter for this projection */
     const lq4_rot_desc* rot;     /* NULL = no online rotation */
     int32_t path;         /* LQ4_PATH_* */
-    const lq4_gather_desc* gather;   /* NULL = results stay on this GPU; else m <= 16 decode shapes only */
+    const lq4_gather_desc* gather;   /* NULL = results stay on this GPU; else the epilogue also stores every result
+                                        into each peer's buffer: decode shapes (m <= 16) and the tensor-core kernel
+                                        (m > 16, adapter rank <= 128); fast layout only */
     const lq4_gather_desc* wait_gather;   /* non-NULL: x holds gathered results (it lives in the own peer buffer):
                                              before x is read, wait (bounded) until every peer's results of all
                                              gathered launches this rank has issued so far have arrived; the

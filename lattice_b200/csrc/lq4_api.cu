@@ -267,11 +267,25 @@ lq4_status run_gemv_mma(lq4_ctx* ctx, const lq4_linear_args* a, const void* x, i
     return run_dense(ctx, &p, 1, s);
 }
 
+// Completion signal of a gathered tensor-core product (see lq4_linear): a system-scope fence, one remote
+// reduction of 256 on every peer's arrival counter, 256 on this rank's own sequence counter.
+struct GatherSignal {
+    unsigned long long* arrive[LQ4_MAX_PEERS];    // every rank's buffer base: arrival counter at [0], sequence at [1]
+    uint32_t world, rank;
+};
+__global__ void gather_signal_kernel(const GatherSignal g) {
+    __threadfence_system();
+    for (uint32_t r = 0; r < g.world; ++r)
+        if (r != g.rank)
+            asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(g.arrive[r]), "l"(256ull) : "memory");
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(g.arrive[g.rank] + 1), "l"(256ull) : "memory");
+}
+
 }  // namespace
 
 extern "C" {
 
-int32_t lq4_abi_version(void) { return 2; }
+int32_t lq4_abi_version(void) { return 3; }
 
 const char* lq4_last_error(void) { return g_last_error.c_str(); }
 
@@ -395,8 +409,13 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     }
     if (path != LQ4_PATH_GEMV_GENERIC && !fast_layout)
         return fail(LQ4_ERR_ALIGN, "fast paths need k % 128 == 0, 16-byte aligned w and x, rank <= 512");
-    if (a->gather && a->gather->world > 1 && (path != LQ4_PATH_GEMV_MMA || a->m > (uint32_t)kGemvMaxM))
-        return fail(LQ4_ERR_UNSUPPORTED, "the fused all-gather is built into the decode kernels only (m <= 16, fast layout)");
+    if (a->gather && a->gather->world > 1) {
+        const bool decode = path == LQ4_PATH_GEMV_MMA && a->m <= (uint32_t)kGemvMaxM;
+        const bool prefill = path == LQ4_PATH_GEMM_TC && rank <= (uint32_t)kGemmMaxRank;
+        if (!decode && !prefill)
+            return fail(LQ4_ERR_UNSUPPORTED, "the fused all-gather is built into the decode kernels (m <= 16) and the tensor-core "
+                                             "kernel (adapter rank <= 128), fast layout");
+    }
 
     const void* x = a->x;
     int x_dtype = a->x_dtype;
@@ -442,12 +461,29 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
         if ((st = ensure(ctx, ctx->gemm, need, false, s))) return st;
         int launches = 0;
         std::string err;
+        int64_t peer_off[LQ4_MAX_PEERS];
+        uint32_t n_peers = 0;
+        const lq4_gather_desc* gd = (a->gather && a->gather->world > 1) ? a->gather : nullptr;
+        if (gd)
+            for (uint32_t r = 0; r < gd->world; ++r)
+                if (r != gd->rank) peer_off[n_peers++] = static_cast<const char*>(gd->bases[r]) - static_cast<const char*>(gd->bases[gd->rank]);
         cudaError_t e = launch_gemm_tc(x, x_dtype, a->w, a->y, ldy, a->m, a->n, a->k,
                                        grank ? a->lora->a : nullptr, grank ? a->lora->b : nullptr, grank,
                                        grank ? a->lora->scale : 0.0f, ctx->gemm.p, ctx->gemm.cap, ctx->status,
-                                       ctx->sm_count, s, &launches, &err);
+                                       ctx->sm_count, s, &launches, &err, peer_off, n_peers);
         ctx->launches += launches;
         if (e != cudaSuccess) return fail(LQ4_ERR_CUDA, "tensor-core GEMM: " + err + ": " + cudaGetErrorString(e));
+        if (gd) {
+            // the product's stores into the peers' buffers are complete when its kernel is; the kernel behind it
+            // tells every peer (one remote reduction each) and advances this rank's sequence, exactly what the
+            // last CTA of a gathered decode launch does, so lq4_gather_wait serves both
+            GatherSignal sig{};
+            sig.world = gd->world; sig.rank = gd->rank;
+            for (uint32_t r = 0; r < gd->world; ++r) sig.arrive[r] = static_cast<unsigned long long*>(gd->bases[r]);
+            gather_signal_kernel<<<1, 1, 0, s>>>(sig);
+            LQ4_CUDA(cudaGetLastError());
+            ctx->launches += 1;
+        }
         if (wide) return lq4_lora_apply(ctx, x, x_dtype, a->m, a->k, a->y, a->n, ldy, a->lora, stream);
         return LQ4_OK;
     }

@@ -235,6 +235,10 @@ struct GemmParams {
     uint32_t ksplit;         // all-dense products only: the k range is cut into ksplit pieces, one output tile each;
     uint64_t split_stride;   // piece s adds s * seg_len blocks to every segment offset and writes y + s * split_stride
     int32_t* status;
+    // fused all-gather of an N-sharded product: every result is also stored at the same place of each peer's
+    // output buffer (plain stores over NVLink from the epilogue warps, tile by tile while the MMAs go on)
+    uint32_t n_peers;
+    int64_t peer_off[LQ4_MAX_PEERS - 1];     // bytes from an element of y to the same element in a peer
 };
 
 // A CTA works on TWO 128-row sub-tiles of the weights against one activation tile: the activation
@@ -459,7 +463,12 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const uint32_t m = m0 + c0 + j;
-                            if (c0 + j < p.tt && m < p.m) yout[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
+                            if (c0 + j < p.tt && m < p.m) {
+                                float* dst = yout + (size_t)m * p.ldy + n;
+                                *dst = __uint_as_float(v[j]);
+                                for (uint32_t r = 0; r < p.n_peers; ++r)
+                                    *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_off[r]) = __uint_as_float(v[j]);
+                            }
                         }
                     }
                 }
@@ -585,7 +594,7 @@ size_t gemm_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, uint32_t rank) {
 cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* y, uint64_t ldy, uint32_t m,
                            uint32_t n, uint32_t k, const float* la, const float* lb, uint32_t rank, float lscale,
                            void* workspace, size_t workspace_bytes, int32_t* status, int sm_count, cudaStream_t s,
-                           int* launches, std::string* err) {
+                           int* launches, std::string* err, const int64_t* peer_off, uint32_t n_peers) {
     auto fail = [&](const char* what, cudaError_t e) {
         if (err) *err = what;
         return e;
@@ -681,6 +690,9 @@ cudaError_t launch_gemm_tc(const void* x, int x_dtype, const uint8_t* w, float* 
     p.m_tiles = (m + tt - 1) / tt;
     p.kblocks = k / kBlockK;
     p.ksplit = 1;
+    if (n_peers > (uint32_t)(LQ4_MAX_PEERS - 1)) return fail("too many peers", cudaErrorInvalidValue);
+    p.n_peers = peer_off ? n_peers : 0;
+    for (uint32_t r = 0; r < p.n_peers; ++r) p.peer_off[r] = peer_off[r];
     if ((e = launch_kernel(p, tm_x, tm_w, tm_da, tm_db, sm_count, s)) != cudaSuccess) return fail("GEMM launch", e);
     ++nl;
     if (launches) *launches = nl;

@@ -75,6 +75,24 @@ __device__ __forceinline__ bool mbox_load4(const unsigned long long* p, uint32_t
            (uint32_t)(e3 >> 32) == stag;
 }
 
+// Cheap gate in front of a mailbox sweep: ONE lane of the warp polls ONE entry, with a growing pause,
+// until it carries this step's tag; the warp follows.  Readers get here microseconds before their inputs
+// exist; if every waiting thread swept its whole range meanwhile, the polling traffic of 148 CTAs would
+// compete in L2 with the weight stream of the CTAs that still produce those inputs.  The probe says
+// nothing about the other entries: the sweep after it still checks every tag.
+__device__ __forceinline__ void mbox_probe_wait(const unsigned long long* p, uint32_t stag, volatile int* err) {
+    if ((threadIdx.x & 31) == 0) {
+        unsigned ns = 128;
+        const long long t0 = wait_clock();
+        while ((uint32_t)(mbox_load(p) >> 32) != stag) {
+            if (*err || wait_expired(t0)) break;       // the sweep that follows reports the failure
+            __nanosleep(ns);
+            ns = ns < 1024 ? ns * 2 : 1024;
+        }
+    }
+    __syncwarp();
+}
+
 // mbarrier wait that also gives up as soon as another wait of this CTA has failed.
 __device__ __forceinline__ bool mbar_wait_step(uint64_t* bar, uint32_t parity, volatile int* err) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -163,6 +181,14 @@ __device__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* 
         const unsigned long long* um = q.xmul_slot != kNoSlot ? mb + q.xmul_slot : nullptr;
         for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * kConsumerThreads) {
             float v[kBatch][8];
+            {
+                // probe the first entry this warp reads in this pass (lane 0's first octet)
+                const uint32_t i = o0 + (ctid & ~31);
+                if (i < noct) {
+                    const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+                    mbox_probe_wait(xm + (size_t)o * 8, stag, s_err);
+                }
+            }
             const long long t0 = wait_clock();
             for (;;) {
                 bool ready = true;
@@ -188,7 +214,7 @@ __device__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* 
                     *s_err = 1;
                     break;
                 }
-                __nanosleep(64);
+                __nanosleep(256);
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
@@ -287,6 +313,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 if (q.x_slot != kNoSlot) {
                     const unsigned long long* xm = mb + q.x_slot;
                     const unsigned long long* um = q.xmul_slot != kNoSlot ? mb + q.xmul_slot : nullptr;
+                    if (i0 < i1) mbox_probe_wait(xm + (size_t)(i1 - 1) * 4, stag, s_err);
                     const long long t0 = wait_clock();
                     for (;;) {
                         bool ready = true;
@@ -309,7 +336,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                             *s_err = 1;
                             break;
                         }
-                        __nanosleep(128);
+                        __nanosleep(512);
                     }
                 } else if (q.x_mul) {
                     const float4* g4 = reinterpret_cast<const float4*>(q.x);
@@ -584,8 +611,10 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 unsigned long long e = mbox_load(src + i);
                 if ((uint32_t)(e >> 32) != stag) {
                     const long long t0 = wait_clock();
+                    unsigned ns = 128;
                     for (;;) {
-                        __nanosleep(64);
+                        __nanosleep(ns);
+                        ns = ns < 1024 ? ns * 2 : 1024;
                         e = mbox_load(src + i);
                         if ((uint32_t)(e >> 32) == stag) break;
                         if (*s_err != 0 || wait_expired(t0)) {

@@ -563,14 +563,74 @@ def test_fused_all_gather_writes_every_peer_and_signals(be, m):
         be.check_device_status()
         assert be.launch_count - before >= 2          # the wait kernel and the GEMM's kernels
         assert tol_ratio(yb.cpu().numpy(), big_case["y_ref"]) <= 1.0
-        # the fused gather is a decode-kernel feature: the tensor-core path refuses it
-        big = torch.zeros((64, k), device="cuda")
-        with pytest.raises(_lib.Lq4Error):
-            be.dispatch_gemm_q4(big, 0, keep[0], full[0][:1, :1024].expand(64, 1024), 0, 64, 1024, k, gather=keep[3])
     finally:
         torch.cuda.synchronize()
         for b in bufs:
             L.lq4_peer_buf_free(b)
+
+
+@pytest.mark.parametrize("m,bf16", [(40, False), (300, True)])
+def test_fused_all_gather_from_the_tensor_core_epilogue(be, m, bf16):
+    """Prefill shapes: two peer buffers on one GPU stand in for two ranks; each "rank" runs the tensor-core kernel
+    on its rows of the weight and its epilogue stores the slice into BOTH buffers; a signal kernel behind it
+    advances the arrival counters that lq4_gather_wait reads."""
+    from lattice_b200 import Q4WeightBuf
+    from lattice_b200._lib import GatherDesc, LoraDesc
+    L = _lib.lib()
+    n_total, k, r = 512 + 384, 512, 8
+    bufs, bases = [], []
+    for _ in range(2):
+        h = C.c_void_p()
+        _lib.check(L.lq4_peer_buf_create(m * n_total * 4, C.byref(h)))
+        bufs.append(h.value)
+        bases.append(L.lq4_peer_buf_base(h.value))
+    try:
+        case = make_case(4, m, k, n_total, r, 2.0 * r, bf16_x=bf16, extra=310)
+        a, b, s = case["lora"]
+        ad = dev(a)
+        full = [_as_tensor(L.lq4_peer_buf_payload(bf), (m, n_total)) for bf in bufs]
+        for f in full:
+            f.fill_(float("nan"))
+        ctrl = [_as_tensor(bs, (64,)).view(torch.int64) for bs in bases]
+        x = dev(case["x"]).to(torch.bfloat16) if bf16 else dev(case["x"])
+        keep, descs = [], []
+        for rk, (n0, n1) in enumerate([(0, 512), (512, n_total)]):
+            desc = GatherDesc(2, rk, (C.c_void_p * _lib.MAX_PEERS)(*bases))
+            off = n0 * (k // 32) * 20
+            qw = Q4WeightBuf.from_host_payload(case["payload"][off: off + (n1 - n0) * (k // 32) * 20], n1 - n0, k)
+            bd = dev(b[n0:n1])
+            keep += [qw, bd]
+            descs.append(desc)
+            out = full[rk][:, n0:n1]
+            be.dispatch_gemm_q4(x, 0, qw, out, 0, m, n1 - n0, k, lora=LoraDesc(ad.data_ptr(), bd.data_ptr(), r, s),
+                                ldy=n_total, gather=desc)
+        for desc in descs:
+            be.gather_wait(desc)
+        be.check_device_status()
+        for f in full:
+            got = f.cpu().numpy()
+            assert not np.isnan(got).any()
+            assert tol_ratio(got, case["y_ref"]) <= 1.0
+        assert np.array_equal(full[0].cpu().numpy().view(np.uint32), full[1].cpu().numpy().view(np.uint32))
+        assert [int(c[0]) for c in ctrl] == [256, 256] and [int(c[1]) for c in ctrl] == [256, 256]
+        # an adapter too wide to ride along in the tensor-core kernel is applied in a second pass: no fused gather
+        wide_a, wide_b = torch.zeros((160, k), device="cuda"), torch.zeros((512, 160), device="cuda")
+        with pytest.raises(_lib.Lq4Error):
+            be.dispatch_gemm_q4(x, 0, keep[0], full[0][:, 0:512], 0, m, 512, k,
+                                lora=LoraDesc(wide_a.data_ptr(), wide_b.data_ptr(), 160, 1.0), ldy=n_total, gather=descs[0])
+    finally:
+        torch.cuda.synchronize()
+        for bf in bufs:
+            L.lq4_peer_buf_free(bf)
+
+
+def test_wide_adapter_takes_the_second_pass_on_prefill_shapes_and_the_decode_kernels_below(be):
+    """A blend of adapters adds their ranks: rank 192 runs inside the decode kernels (m <= 16) and, for prefill
+    shapes, as the tensor-core product followed by the adapter pass."""
+    for m in (1, 4, 40):
+        case = make_case(3, m, 512, 384, 192, 384.0, extra=320 + m)
+        y = run_case(be, case)
+        assert tol_ratio(y, case["y_ref"]) <= 1.0
 
 
 @pytest.mark.parametrize("k", [256, 2048, 4096, 8192, 16384])
