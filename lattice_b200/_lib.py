@@ -16,6 +16,7 @@ OK, ERR_NULL, ERR_K, ERR_OVERFLOW, ERR_ALIGN, ERR_DTYPE, ERR_LORA, ERR_ROT, ERR_
 DTYPE_F32, DTYPE_BF16, DTYPE_F64 = 0, 1, 2
 QUANT_ASYMMETRIC, QUANT_SYMMETRIC = 0, 1
 PATH_AUTO, PATH_GEMV_MMA, PATH_GEMV_GENERIC, PATH_GEMM_TC = 0, 1, 2, 3
+OPT_MLP_ONE_LAUNCH, OPT_PDL, OPT_ALLOW_GROW = 1, 2, 3
 
 
 class LoraDesc(C.Structure):
@@ -76,6 +77,7 @@ SIGNATURES = {
     "lq4_ctx_destroy": (None, [C.c_void_p]),
     "lq4_ctx_reserve": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
     "lq4_ctx_check": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "lq4_ctx_set_option": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32]),
     "lq4_ctx_launch_count": (C.c_uint64, [C.c_void_p]),
     "lq4_last_error": (C.c_char_p, []),
     "lq4_status_string": (C.c_char_p, [C.c_int32]),

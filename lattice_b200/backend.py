@@ -176,6 +176,10 @@ class CudaQ4Backend:
         """Synchronises the current stream and raises if a kernel gave up on a bounded wait."""
         check(_lib.lib().lq4_ctx_check(self._ctx, _stream()))
 
+    def set_option(self, option: int, value: int) -> None:
+        """Per-context switches of the library (``_lib.OPT_*``)."""
+        check(_lib.lib().lq4_ctx_set_option(self._ctx, option, int(value)))
+
     def reserve(self, m: int, n: int, k: int, rank: int = 0) -> None:
         check(_lib.lib().lq4_ctx_reserve(self._ctx, m, n, k, rank))
 

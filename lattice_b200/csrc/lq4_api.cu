@@ -62,6 +62,7 @@ struct lq4_ctx {
     cudaEvent_t ev_block[4] = {nullptr, nullptr, nullptr, nullptr}, ev_comm = nullptr;
     bool allow_grow = true;
     int pdl = 1;
+    int mlp_one_launch = 0;       // LQ4_OPT_MLP_ONE_LAUNCH
 };
 
 struct lq4_weights {
@@ -331,6 +332,8 @@ lq4_status lq4_ctx_create(int32_t device, lq4_ctx** out) {
     ctx->tsync = reinterpret_cast<uint32_t*>(ctx->status) + 16;
     const char* env = getenv("LQ4_DISABLE_PDL");
     if (env && env[0] == '1') ctx->pdl = 0;
+    env = getenv("LQ4_MLP_ONE_LAUNCH");
+    if (env && env[0] == '1') ctx->mlp_one_launch = 1;
     *out = ctx;
     return lq4_ctx_reserve(ctx, 16, 32768, 32768, 128);
 }
@@ -390,6 +393,16 @@ lq4_status lq4_ctx_check(lq4_ctx* ctx, void* stream) {
 }
 
 uint64_t lq4_ctx_launch_count(const lq4_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+lq4_status lq4_ctx_set_option(lq4_ctx* ctx, int32_t option, int32_t value) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    switch (option) {
+        case LQ4_OPT_MLP_ONE_LAUNCH: ctx->mlp_one_launch = value != 0; return LQ4_OK;
+        case LQ4_OPT_PDL: ctx->pdl = value != 0; return LQ4_OK;
+        case LQ4_OPT_ALLOW_GROW: ctx->allow_grow = value != 0; return LQ4_OK;
+        default: return fail(LQ4_ERR_UNSUPPORTED, "unknown option");
+    }
+}
 
 lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
@@ -835,13 +848,25 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
                 if (u0 && x_internal != u_internal) return fail(LQ4_ERR_UNSUPPORTED, "a gated input and its multiplier must both come from earlier groups");
                 q.x_slot = (uint32_t)(static_cast<const float*>(a.x) - payload);
                 if (u0) q.xmul_slot = (uint32_t)(specs[i].x_mul - payload);
+                if (q.rank) {
+                    // short pieces: one lane of the projection warp keeps a whole piece's loads in flight
+                    const uint32_t per_piece = 32u * (uint32_t)kStepMailboxStrides;       // float4 per piece
+                    uint32_t ts = (a.k / 4 + per_piece - 1) / per_piece;
+                    q.tsplit = ts < 1 ? 1 : (ts > kStepMaxTsplit ? kStepMaxTsplit : ts);
+                }
                 if ((q.x_slot & 3u) || (u0 && (q.xmul_slot & 3u))) return fail(LQ4_ERR_ALIGN, "inputs taken from earlier groups need 16-byte alignment");
             }
             if (u0 && !aligned(u0, 16)) return fail(LQ4_ERR_ALIGN, "the gating row needs 16-byte alignment");
         }
     }
 
-    const size_t smem = step_plan_smem(sa, max_kb, max_rank);
+    items_total = 0;
+    uint32_t max_items = 0;
+    for (uint32_t i = 0; i < np; ++i) {
+        items_total += (size_t)sa.p[i].rank * sa.p[i].tsplit;
+        max_items = sa.p[i].rank * sa.p[i].tsplit > max_items ? sa.p[i].rank * sa.p[i].tsplit : max_items;
+    }
+    const size_t smem = step_plan_smem(sa, max_kb, max_rank, max_items);
     if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "a row of this step does not fit in shared memory");
     const int grid = (int)(max_units < (uint64_t)ctx->sm_count ? max_units : (uint64_t)ctx->sm_count);
 
@@ -856,7 +881,7 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
         uint32_t cta_begin[kStepMaxProblems + 1];
         for (uint32_t i = 0; i < cnt; ++i) { tmp[i] = GemvParams{}; tmp[i].tiles = sa.p[b + i].tiles; tmp[i].kg = sa.p[b + i].kg; }
         if ((uint32_t)grid < cnt) return fail(LQ4_ERR_UNSUPPORTED, "a group has more projections than the launch has CTAs");
-        dec::split_ctas(tmp, cnt, (uint32_t)grid, cta_begin);
+        dec::split_ctas(tmp, cnt, (uint32_t)grid, cta_begin, 3);
         uint32_t dots = 0;
         for (uint32_t i = 0; i < cnt; ++i) {
             StepProblem& q = sa.p[b + i];
@@ -999,8 +1024,7 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
     // One token with the gate||up row in the library's own buffer: the whole block is ONE launch.  The row
     // lives in a step buffer, gate and up rows form the first group, down_proj the second; its CTAs read
     // silu(gate) * up through the mailbox as the values arrive (lq4_step.cu).
-    static const bool two_launches = [] { const char* e = getenv("LQ4_MLP_TWO_LAUNCHES"); return e && e[0] == '1'; }();
-    if (a->m == 1 && !a->gate_up && !a->rot_down && !two_launches && a->hidden % 128 == 0 && a->inter % 128 == 0 &&
+    if (a->m == 1 && !a->gate_up && !a->rot_down && ctx->mlp_one_launch && a->hidden % 128 == 0 && a->inter % 128 == 0 &&
         aligned(a->x, 16) && aligned(a->w_gate_up, 16) && aligned(a->w_down, 16) &&
         gemv_resident_fits(1, a->hidden > a->inter ? a->hidden : a->inter, false)) {
         bool lora_ok = true;

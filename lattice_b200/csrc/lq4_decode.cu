@@ -30,6 +30,7 @@
 //    the launch's last CTA signals the peers' arrival counters.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "lq4_decode_common.cuh"
@@ -696,8 +697,15 @@ cudaError_t launch_args(const DecodeArgs<kMaxGroup>& ga, size_t smem, int grid, 
 }  // namespace
 
 namespace dec {
-void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* cta_begin) {
-    constexpr uint64_t kTileCharge = 8;          // fix-up and epilogue of a tile, in work units
+void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* cta_begin, uint32_t tile_charge) {
+    // fix-up and epilogue of a tile, in work units (a work unit streams in about 0.24 us).  Measured on the
+    // large-layer set: 8 suits a launch per set, whose tail the next launch covers; the step kernel, where a
+    // CTA walks straight into the next group, is quickest with 3 (LQ4_TILE_CHARGE overrides both).
+    static const int env_charge = [] {
+        const char* e = getenv("LQ4_TILE_CHARGE");
+        return e ? atoi(e) : -1;
+    }();
+    const uint64_t kTileCharge = env_charge >= 0 ? (uint64_t)env_charge : (uint64_t)tile_charge;
     uint64_t cost[kMaxGroup], units[kMaxGroup];
     uint32_t n[kMaxGroup];
     for (uint32_t i = 0; i < count; ++i) {

@@ -211,7 +211,7 @@ __device__ __forceinline__ void project_one(const void* __restrict__ x, int x_dt
 // (work units of 4 blocks x 128 rows, plus a fixed charge per tile for the fix-up and epilogue), so
 // that no CTA has to switch problems.  Needs grid >= count; a problem never gets more CTAs than
 // it has units.
-void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* cta_begin);
+void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* cta_begin, uint32_t tile_charge = 8);
 
 // Host side: the three tensor maps of a payload (boxes of 20, 12 and 4 blocks x 128 rows), from a
 // per-thread cache keyed by (pointer, n, k).  NULL if the driver entry point is missing or the

@@ -463,11 +463,17 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm_x, con
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             const uint32_t m = m0 + c0 + j;
-                            if (c0 + j < p.tt && m < p.m) {
-                                float* dst = yout + (size_t)m * p.ldy + n;
-                                *dst = __uint_as_float(v[j]);
-                                for (uint32_t r = 0; r < p.n_peers; ++r)
-                                    *reinterpret_cast<float*>(reinterpret_cast<char*>(dst) + p.peer_off[r]) = __uint_as_float(v[j]);
+                            if (c0 + j < p.tt && m < p.m) yout[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
+                        }
+                        // fused all-gather: the same 32 values go to the same place of every peer's buffer (the
+                        // accumulator is not double-buffered at 256 tokens per tile, so the stores are kept in
+                        // straight runs per peer and out of the single-GPU path)
+                        for (uint32_t r = 0; r < p.n_peers; ++r) {
+                            float* py = reinterpret_cast<float*>(reinterpret_cast<char*>(yout) + p.peer_off[r]);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const uint32_t m = m0 + c0 + j;
+                                if (c0 + j < p.tt && m < p.m) py[(size_t)m * p.ldy + n] = __uint_as_float(v[j]);
                             }
                         }
                     }

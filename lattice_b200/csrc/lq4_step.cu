@@ -37,6 +37,21 @@ using namespace dec;
 
 constexpr int kStepThreads = 320;      // 8 consumer warps + TMA warp + projection warp
 
+// Development aid, compiled only with -DLQ4_STEP_TIMELINE: nanosecond stamps per CTA and group.
+#ifdef LQ4_STEP_TIMELINE
+constexpr int kTlSlots = 8;            // per (cta, group): 0 group start, 1 prologue done, 2 last stage consumed,
+                                       // 3 last epilogue done, 4 projection start, 5 projection done, 6 first stage consumed
+__device__ unsigned long long g_step_timeline[160 * kStepMaxGroups * kTlSlots + 8];
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TL_STAMP(g, slot) do { g_step_timeline[((size_t)blockIdx.x * kStepMaxGroups + (g)) * kTlSlots + (slot)] = tl_now(); } while (0)
+#else
+#define TL_STAMP(g, slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ unsigned long long mbox_pack(float v, uint32_t tag) {
     return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
 }
@@ -49,14 +64,22 @@ __device__ __forceinline__ unsigned long long mbox_load(const unsigned long long
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(e) : "l"(p) : "memory");
     return e;
 }
+// Two entries with one 16-byte load that is served by L2 and never by this SM's L1 (.cg).  Deliberately not a
+// system-scope "strong" load: measured on B200, strong loads of one thread complete one after the other
+// (about 0.2 us each), which made a 90-load dot product take 20 us; the sweeps below need dozens of loads in
+// flight.  L2 is where stores from this GPU and from the peers (over NVLink) land, each 8-byte entry is written
+// by a single store, and every sweep is re-executed until the tags match, so what a sweep sees is either the
+// old entry or the new one.
 __device__ __forceinline__ void mbox_load2(const unsigned long long* p, unsigned long long& e0, unsigned long long& e1) {
-    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(e0), "=l"(e1) : "l"(p) : "memory");
+    asm volatile("ld.global.cg.v2.u64 {%0, %1}, [%2];" : "=l"(e0), "=l"(e1) : "l"(p) : "memory");
 }
-// Eight consecutive entries (32-byte aligned) -> values; true if all carry `stag`.
-__device__ __forceinline__ bool mbox_load8(const unsigned long long* p, uint32_t stag, float (&v)[8]) {
-    unsigned long long e[8];
+// Eight consecutive entries (32-byte aligned), loads only: the caller issues the loads of a whole batch before
+// it looks at the first tag, so a batch costs one L2 round trip.
+__device__ __forceinline__ void mbox_load8_raw(const unsigned long long* p, unsigned long long (&e)[8]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) mbox_load2(p + 2 * i, e[2 * i], e[2 * i + 1]);
+}
+__device__ __forceinline__ bool mbox_unpack8(const unsigned long long (&e)[8], uint32_t stag, float (&v)[8]) {
     bool ok = true;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -64,15 +87,6 @@ __device__ __forceinline__ bool mbox_load8(const unsigned long long* p, uint32_t
         v[i] = __uint_as_float((uint32_t)e[i]);
     }
     return ok;
-}
-__device__ __forceinline__ bool mbox_load4(const unsigned long long* p, uint32_t stag, float4& v) {
-    unsigned long long e0, e1, e2, e3;
-    mbox_load2(p, e0, e1);
-    mbox_load2(p + 2, e2, e3);
-    v = make_float4(__uint_as_float((uint32_t)e0), __uint_as_float((uint32_t)e1), __uint_as_float((uint32_t)e2),
-                    __uint_as_float((uint32_t)e3));
-    return (uint32_t)(e0 >> 32) == stag && (uint32_t)(e1 >> 32) == stag && (uint32_t)(e2 >> 32) == stag &&
-           (uint32_t)(e3 >> 32) == stag;
 }
 
 // Cheap gate in front of a mailbox sweep: ONE lane of the warp polls ONE entry, with a growing pause,
@@ -127,8 +141,68 @@ __device__ __forceinline__ Share step_share(const StepArgs& a, uint32_t g, uint3
     return s;
 }
 
+// Activation limbs from mailbox entries.  An L2 round trip costs about a microsecond while the weight stream is
+// running, and a thread's loads only overlap if they are issued before the first result is used: a sweep issues
+// the loads of KB octets (4 x 16 bytes each) back to back, then looks at the tags; entries that are not there yet
+// repeat the sweep.  Warp-uniform (the conversion uses quad shuffles), bounded, with a pause between sweeps.
+template <int KB, bool GATED>
+__device__ __forceinline__ void prologue_from_mailbox(const StepArgs& a, uint8_t* xs, float2* sx, const unsigned long long* xm,
+                                                      const unsigned long long* um, uint32_t a0, uint32_t na, uint32_t b0,
+                                                      uint32_t noct, int ctid, uint32_t stag, volatile int* s_err) {
+    for (uint32_t o0 = 0; o0 < noct; o0 += KB * kConsumerThreads) {
+        float v[KB][8];
+        {
+            const uint32_t i = o0 + (uint32_t)(ctid & ~31);      // the first octet this warp reads in this sweep
+            if (i < noct) mbox_probe_wait(xm + (size_t)(i < na ? a0 + i : b0 + (i - na)) * 8, stag, s_err);
+        }
+        const long long t0 = wait_clock();
+        for (;;) {
+            bool ready = true;
+            unsigned long long ex[KB][8], eu[GATED ? KB : 1][8];
+#pragma unroll
+            for (int u = 0; u < KB; ++u) {
+                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                if (i < noct) {
+                    const size_t o = (size_t)(i < na ? a0 + i : b0 + (i - na)) * 8;
+                    mbox_load8_raw(xm + o, ex[u]);
+                    if (GATED) mbox_load8_raw(um + o, eu[GATED ? u : 0]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < KB; ++u) {
+                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[u][e] = 0.0f;
+                if (i < noct) {
+                    ready = mbox_unpack8(ex[u], stag, v[u]) && ready;
+                    if (GATED) {
+                        float up[8];
+                        ready = mbox_unpack8(eu[GATED ? u : 0], stag, up) && ready;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[u][e] = silu_mul(v[u][e], up[e]);
+                    }
+                }
+            }
+            if (__all_sync(kFull, ready)) break;
+            if (__any_sync(kFull, *s_err != 0 || wait_expired(t0))) {
+                if ((ctid & 31) == 0) atomicOr(a.status, kDevErrGridWaitTimeout);
+                *s_err = 1;
+                break;
+            }
+            __nanosleep(256);
+        }
+#pragma unroll
+        for (int u = 0; u < KB; ++u) {
+            const uint32_t i = o0 + u * kConsumerThreads + ctid;
+            const uint32_t o = i < na ? a0 + i : b0 + (i - na);
+            store_limbs(xs, sx, 1, 0, o, i < noct, v[u]);
+        }
+    }
+}
+
 // The 256 consumer threads turn the k range(s) this CTA touches into two int8 limbs per activation.
-__device__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* smem, int ctid, uint64_t r0, uint64_t r1,
+template <bool MB>
+__device__ __forceinline__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* smem, int ctid, uint64_t r0, uint64_t r1,
                               const unsigned long long* mb, uint32_t stag, volatile int* s_err) {
     uint8_t* xs = smem + a.off_xs;
     float2* sx = reinterpret_cast<float2*>(smem + a.off_sx);
@@ -140,7 +214,7 @@ __device__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* 
         else { a0 = g0 * opg; a1 = q.kg * opg; b0 = 0; b1 = (g0 + len - q.kg) * opg; }
     }
     const uint32_t na = a1 - a0, noct = na + (b1 - b0);
-    if (q.x_slot == kNoSlot) {
+    if (!MB || q.x_slot == kNoSlot) {
         // plain memory: several octets per thread and pass, all loads issued before the first use
         constexpr int kBatch = 8;
         for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * kConsumerThreads) {
@@ -173,60 +247,138 @@ __device__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* 
                 store_limbs(xs, sx, 1, 0, o, i < noct, v[u]);
             }
         }
-    } else {
+    } else if constexpr (MB) {
         // mailbox: the entries are polled until they carry this step's tag.  The loop is warp-uniform (the
-        // limb conversion below uses quad shuffles), bounded, and backs off between sweeps.
-        constexpr int kBatch = 4;
+        // limb conversion uses quad shuffles), bounded, and backs off between sweeps.
         const unsigned long long* xm = mb + q.x_slot;
-        const unsigned long long* um = q.xmul_slot != kNoSlot ? mb + q.xmul_slot : nullptr;
-        for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * kConsumerThreads) {
-            float v[kBatch][8];
-            {
-                // probe the first entry this warp reads in this pass (lane 0's first octet)
-                const uint32_t i = o0 + (ctid & ~31);
-                if (i < noct) {
-                    const uint32_t o = i < na ? a0 + i : b0 + (i - na);
-                    mbox_probe_wait(xm + (size_t)o * 8, stag, s_err);
-                }
-            }
-            const long long t0 = wait_clock();
-            for (;;) {
-                bool ready = true;
-#pragma unroll
-                for (int u = 0; u < kBatch; ++u) {
-                    const uint32_t i = o0 + u * kConsumerThreads + ctid;
-                    const uint32_t o = i < na ? a0 + i : b0 + (i - na);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) v[u][e] = 0.0f;
-                    if (i < noct) {
-                        ready = mbox_load8(xm + (size_t)o * 8, stag, v[u]) && ready;
-                        if (um) {
-                            float up[8];
-                            ready = mbox_load8(um + (size_t)o * 8, stag, up) && ready;
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) v[u][e] = silu_mul(v[u][e], up[e]);
-                        }
-                    }
-                }
-                if (__all_sync(kFull, ready)) break;
-                if (__any_sync(kFull, *s_err != 0 || wait_expired(t0))) {
-                    if ((ctid & 31) == 0) atomicOr(a.status, kDevErrGridWaitTimeout);
-                    *s_err = 1;
-                    break;
-                }
-                __nanosleep(256);
-            }
-#pragma unroll
-            for (int u = 0; u < kBatch; ++u) {
-                const uint32_t i = o0 + u * kConsumerThreads + ctid;
-                const uint32_t o = i < na ? a0 + i : b0 + (i - na);
-                store_limbs(xs, sx, 1, 0, o, i < noct, v[u]);
-            }
-        }
+        if (q.xmul_slot != kNoSlot) prologue_from_mailbox<2, true>(a, xs, sx, xm, mb + q.xmul_slot, a0, na, b0, noct, ctid, stag, s_err);
+        else prologue_from_mailbox<4, false>(a, xs, sx, xm, nullptr, a0, na, b0, noct, ctid, stag, s_err);
     }
     named_bar_sync(kBarConsumers, kConsumerThreads);
 }
 
+// The projection warp (one per CTA): the adapters' t = A x for every group, published as tagged messages.
+// Work item e of group g = (problem, rank row j, k piece): item e belongs to CTA e mod grid.  Items of a later
+// group wait (inside the dot product) for their inputs' mailbox entries.
+template <bool MB>
+__device__ __forceinline__ void step_projections(const StepArgs& a, volatile int* s_err) {
+    const int lane = threadIdx.x & 31;
+            // Work item e of group g = (problem, rank row j, k piece): item e belongs to CTA e mod grid.  Items
+            // of a later group wait (inside the dot product) for their inputs' mailbox entries.
+            if (a.use_pdl) pdl_wait_prior_grids();
+            const uint32_t tag = launch_tag(a.tsync);
+            const uint32_t stag = launch_tag(a.step_counter);
+            const unsigned long long* mb = a.mbox + (size_t)(stag & 1u) * a.mbox_half;
+            for (uint32_t g = 0; g < a.ngroups; ++g) {
+                const uint32_t nitems = a.group_items[g];
+                uint32_t pj = a.group_begin[g];
+                const uint32_t pend = a.group_begin[g + 1];
+                if (lane == 0) TL_STAMP(g, 4);
+                for (uint32_t e = blockIdx.x; e < nitems; e += gridDim.x) {
+                    while (pj + 1 < pend && e >= a.p[pj + 1].dot_begin) ++pj;
+                    const StepProblem& q = a.p[pj];
+                    const uint32_t local = e - q.dot_begin;
+                    const uint32_t j = local / q.tsplit, sp = local - j * q.tsplit;
+                    const uint32_t k4 = q.k / 4;
+                    const uint32_t chunk4 = ((k4 + q.tsplit - 1) / q.tsplit + 31u) & ~31u;
+                    const uint32_t i0 = sp * chunk4, i1 = min(k4, i0 + chunk4);
+                    const float* arow = q.la + (size_t)j * q.k;
+                    const float4* a4 = reinterpret_cast<const float4*>(arow);
+                    float s = 0.0f;
+                    if (MB && q.x_slot != kNoSlot) {
+                        const unsigned long long* xm = mb + q.x_slot;
+                        const unsigned long long* um = q.xmul_slot != kNoSlot ? mb + q.xmul_slot : nullptr;
+                        if (i0 < i1) mbox_probe_wait(xm + (size_t)(i1 - 1) * 4, stag, s_err);
+                        // The host cuts the dot products of mailbox-fed problems into pieces of at most
+                        // kStepMailboxPiece4 float4 per lane stride x 32 lanes, so a lane has at most UB strides: all
+                        // its loads are in flight together and an attempt costs one L2 round trip per row.
+                        constexpr int UB = kStepMailboxStrides;
+                        const long long t0 = wait_clock();
+                        for (;;) {
+                            bool ready = true;
+                            s = 0.0f;
+                            for (uint32_t ib = i0 + lane; ib < i1; ib += 32 * UB) {
+                                unsigned long long ex[UB][4];
+                                float4 av[UB];
+                                float xv[UB][4];
+                                unsigned long long eu[UB][4];
+#pragma unroll
+                                for (int b = 0; b < UB; ++b) {
+                                    const uint32_t i = ib + 32 * b;
+                                    if (i < i1) {
+                                        av[b] = __ldg(a4 + i);
+                                        mbox_load2(xm + (size_t)i * 4, ex[b][0], ex[b][1]);
+                                        mbox_load2(xm + (size_t)i * 4 + 2, ex[b][2], ex[b][3]);
+                                        if (um) {
+                                            mbox_load2(um + (size_t)i * 4, eu[b][0], eu[b][1]);
+                                            mbox_load2(um + (size_t)i * 4 + 2, eu[b][2], eu[b][3]);
+                                        }
+                                    }
+                                }
+#pragma unroll
+                                for (int b = 0; b < UB; ++b) {
+                                    const uint32_t i = ib + 32 * b;
+                                    if (i < i1) {
+#pragma unroll
+                                        for (int c = 0; c < 4; ++c) {
+                                            ready = ready && (uint32_t)(ex[b][c] >> 32) == stag;
+                                            xv[b][c] = __uint_as_float((uint32_t)ex[b][c]);
+                                            if (um) {
+                                                ready = ready && (uint32_t)(eu[b][c] >> 32) == stag;
+                                                xv[b][c] = silu_mul(xv[b][c], __uint_as_float((uint32_t)eu[b][c]));
+                                            }
+                                        }
+                                    }
+                                }
+#pragma unroll
+                                for (int b = 0; b < UB; ++b) {
+                                    const uint32_t i = ib + 32 * b;
+                                    if (i < i1) {
+                                        s = fmaf(av[b].x, xv[b][0], s); s = fmaf(av[b].y, xv[b][1], s);
+                                        s = fmaf(av[b].z, xv[b][2], s); s = fmaf(av[b].w, xv[b][3], s);
+                                    }
+                                }
+                            }
+                            if (__all_sync(kFull, ready)) break;
+                            if (__any_sync(kFull, *s_err != 0 || wait_expired(t0))) {
+                                if (lane == 0) atomicOr(a.status, kDevErrGridWaitTimeout);
+                                *s_err = 1;
+                                break;
+                            }
+                            __nanosleep(512);
+                        }
+                    } else if (q.x_mul) {
+                        const float4* g4 = reinterpret_cast<const float4*>(q.x);
+                        const float4* u4 = reinterpret_cast<const float4*>(q.x_mul);
+    #pragma unroll 8
+                        for (uint32_t i = i0 + lane; i < i1; i += 32) {
+                            const float4 av = __ldg(a4 + i), gv = g4[i], uv = u4[i];
+                            s = fmaf(av.x, silu_mul(gv.x, uv.x), s); s = fmaf(av.y, silu_mul(gv.y, uv.y), s);
+                            s = fmaf(av.z, silu_mul(gv.z, uv.z), s); s = fmaf(av.w, silu_mul(gv.w, uv.w), s);
+                        }
+                    } else if (q.x_dtype == LQ4_DTYPE_F32) {
+                        const float4* x4 = reinterpret_cast<const float4*>(q.x);
+    #pragma unroll 8
+                        for (uint32_t i = i0 + lane; i < i1; i += 32) {
+                            const float4 av = __ldg(a4 + i), b = x4[i];
+                            s = fmaf(av.x, b.x, s); s = fmaf(av.y, b.y, s); s = fmaf(av.z, b.z, s); s = fmaf(av.w, b.w, s);
+                        }
+                    } else {
+    #pragma unroll 8
+                        for (uint32_t i = i0 * 4 + lane; i < i1 * 4; i += 32)
+                            s = fmaf(__ldg(arow + i), load_act(q.x, q.x_dtype, i), s);
+                    }
+    #pragma unroll
+                    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
+                    if (lane == 0) msg_store(q.tmsg + local, s, tag);
+                }
+                if (lane == 0) TL_STAMP(g, 5);
+            }
+}
+
+// MB: some projection of the launch takes its input from the mailbox.  Launches without such inputs run the
+// instantiation that holds none of the polling code (the kernel sits at the register limit of a 10-warp CTA).
+template <bool MB>
 __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __grid_constant__ StepArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
@@ -288,82 +440,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             *s_err = 1;
         }
     } else if (warp == 9) {
-        // ------------------------------ adapter projections ------------------------------
-        // Work item e of group g = (problem, rank row j, k piece): item e belongs to CTA e mod grid.  Items
-        // of a later group wait (inside the dot product) for their inputs' mailbox entries.
-        if (a.use_pdl) pdl_wait_prior_grids();
-        const uint32_t tag = launch_tag(a.tsync);
-        const uint32_t stag = launch_tag(a.step_counter);
-        const unsigned long long* mb = a.mbox + (size_t)(stag & 1u) * a.mbox_half;
-        for (uint32_t g = 0; g < a.ngroups; ++g) {
-            const uint32_t nitems = a.group_items[g];
-            uint32_t pj = a.group_begin[g];
-            const uint32_t pend = a.group_begin[g + 1];
-            for (uint32_t e = blockIdx.x; e < nitems; e += gridDim.x) {
-                while (pj + 1 < pend && e >= a.p[pj + 1].dot_begin) ++pj;
-                const StepProblem& q = a.p[pj];
-                const uint32_t local = e - q.dot_begin;
-                const uint32_t j = local / q.tsplit, sp = local - j * q.tsplit;
-                const uint32_t k4 = q.k / 4;
-                const uint32_t chunk4 = ((k4 + q.tsplit - 1) / q.tsplit + 31u) & ~31u;
-                const uint32_t i0 = sp * chunk4, i1 = min(k4, i0 + chunk4);
-                const float* arow = q.la + (size_t)j * q.k;
-                const float4* a4 = reinterpret_cast<const float4*>(arow);
-                float s = 0.0f;
-                if (q.x_slot != kNoSlot) {
-                    const unsigned long long* xm = mb + q.x_slot;
-                    const unsigned long long* um = q.xmul_slot != kNoSlot ? mb + q.xmul_slot : nullptr;
-                    if (i0 < i1) mbox_probe_wait(xm + (size_t)(i1 - 1) * 4, stag, s_err);
-                    const long long t0 = wait_clock();
-                    for (;;) {
-                        bool ready = true;
-                        s = 0.0f;
-#pragma unroll 4
-                        for (uint32_t i = i0 + lane; i < i1; i += 32) {
-                            const float4 av = __ldg(a4 + i);
-                            float4 xv;
-                            ready = mbox_load4(xm + (size_t)i * 4, stag, xv) && ready;
-                            if (um) {
-                                float4 uv;
-                                ready = mbox_load4(um + (size_t)i * 4, stag, uv) && ready;
-                                xv = make_float4(silu_mul(xv.x, uv.x), silu_mul(xv.y, uv.y), silu_mul(xv.z, uv.z), silu_mul(xv.w, uv.w));
-                            }
-                            s = fmaf(av.x, xv.x, s); s = fmaf(av.y, xv.y, s); s = fmaf(av.z, xv.z, s); s = fmaf(av.w, xv.w, s);
-                        }
-                        if (__all_sync(kFull, ready)) break;
-                        if (__any_sync(kFull, *s_err != 0 || wait_expired(t0))) {
-                            if (lane == 0) atomicOr(a.status, kDevErrGridWaitTimeout);
-                            *s_err = 1;
-                            break;
-                        }
-                        __nanosleep(512);
-                    }
-                } else if (q.x_mul) {
-                    const float4* g4 = reinterpret_cast<const float4*>(q.x);
-                    const float4* u4 = reinterpret_cast<const float4*>(q.x_mul);
-#pragma unroll 8
-                    for (uint32_t i = i0 + lane; i < i1; i += 32) {
-                        const float4 av = __ldg(a4 + i), gv = g4[i], uv = u4[i];
-                        s = fmaf(av.x, silu_mul(gv.x, uv.x), s); s = fmaf(av.y, silu_mul(gv.y, uv.y), s);
-                        s = fmaf(av.z, silu_mul(gv.z, uv.z), s); s = fmaf(av.w, silu_mul(gv.w, uv.w), s);
-                    }
-                } else if (q.x_dtype == LQ4_DTYPE_F32) {
-                    const float4* x4 = reinterpret_cast<const float4*>(q.x);
-#pragma unroll 8
-                    for (uint32_t i = i0 + lane; i < i1; i += 32) {
-                        const float4 av = __ldg(a4 + i), b = x4[i];
-                        s = fmaf(av.x, b.x, s); s = fmaf(av.y, b.y, s); s = fmaf(av.z, b.z, s); s = fmaf(av.w, b.w, s);
-                    }
-                } else {
-#pragma unroll 8
-                    for (uint32_t i = i0 * 4 + lane; i < i1 * 4; i += 32)
-                        s = fmaf(__ldg(arow + i), load_act(q.x, q.x_dtype, i), s);
-                }
-#pragma unroll
-                for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
-                if (lane == 0) msg_store(q.tmsg + local, s, tag);
-            }
-        }
+        step_projections<MB>(a, s_err);
     } else {
         // ------------------------------ consumers ------------------------------
         const int gq = lane >> 2, t = lane & 3;
@@ -390,36 +467,38 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             const uint64_t total = (uint64_t)q.tiles * q.kg;
             // everyone is done with the previous group's limbs and projection before they are replaced
             named_bar_sync(kBarConsumers, kConsumerThreads);
-            step_prologue(a, q, smem, tid, sh.r0, sh.r1, mb, stag, s_err);
+            if (tid == 0) TL_STAMP(g, 0);
+            step_prologue<MB>(a, q, smem, tid, sh.r0, sh.r1, mb, stag, s_err);
+            if (tid == 0) TL_STAMP(g, 1);
             bool t_loaded = false;
             // Gathers t = A x of this problem from the projection warps' messages into shared memory, adding
             // the k pieces of every dot product in order.  All consumer warps call it at the same point.
             auto gather_t = [&]() {
+                // one message per thread and sweep (all in flight together), staged in shared memory, then every
+                // dot product's pieces are added in piece order by one thread: the sum does not depend on timing
+                float* stage = reinterpret_cast<float*>(smem + a.off_tstage);
+                const uint32_t nmsg = q.rank * q.tsplit;
                 bool good = true;
-                for (uint32_t idx = tid; idx < q.rank; idx += kConsumerThreads) {
-                    const uint2* src = q.tmsg + (size_t)idx * q.tsplit;
-                    float sum = 0.0f;
-                    for (uint32_t s0 = 0; s0 < q.tsplit; s0 += 8) {
-                        uint2 msg[8];
+                for (uint32_t idx = tid; idx < nmsg; idx += kConsumerThreads) {
+                    uint2 msg = msg_load(q.tmsg + idx);
+                    if (msg.y != tag) {
                         const long long t0 = wait_clock();
                         for (;;) {
-                            bool all = true;
-#pragma unroll
-                            for (int u = 0; u < 8; ++u) {
-                                if (s0 + u >= q.tsplit) continue;
-                                msg[u] = msg_load(src + s0 + u);
-                                all = all && (msg[u].y == tag);
-                            }
-                            if (all) break;
+                            __nanosleep(128);
+                            msg = msg_load(q.tmsg + idx);
+                            if (msg.y == tag) break;
                             if (*s_err != 0 || wait_expired(t0)) { good = false; break; }
                         }
-#pragma unroll
-                        for (int u = 0; u < 8; ++u)
-                            if (s0 + u < q.tsplit) sum += __uint_as_float(msg[u].x);
                     }
-                    t_sm[idx] = sum;
+                    stage[idx] = __uint_as_float(msg.x);
                 }
                 if (!good) { atomicOr(a.status, kDevErrGridWaitTimeout); *s_err = 1; }
+                named_bar_sync(kBarConsumers, kConsumerThreads);
+                for (uint32_t j = tid; j < q.rank; j += kConsumerThreads) {
+                    float sum = 0.0f;
+                    for (uint32_t sp = 0; sp < q.tsplit; ++sp) sum += stage[j * q.tsplit + sp];
+                    t_sm[j] = sum;
+                }
                 named_bar_sync(kBarConsumers, kConsumerThreads);
                 t_loaded = true;
             };
@@ -483,7 +562,9 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[s]);
                     gs += ngr;
+                    if (tid == 0 && git == 0) TL_STAMP(g, 6);
                 }
+                if (tid == 0) TL_STAMP(g, 2);
 
                 // each thread of a quad covered blocks = t (mod 4): add the four
                 float v0 = acc0, v1 = acc1;
@@ -595,6 +676,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                         }
                     }
                 }
+                if (tid == 0) TL_STAMP(g, 3);
             }
         }
         if (!ok) {
@@ -646,11 +728,19 @@ inline uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
 
-size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank) {
+#ifdef LQ4_STEP_TIMELINE
+extern "C" int lq4_debug_step_timeline(unsigned long long* host_out, size_t count) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_step_timeline, count * sizeof(unsigned long long));
+}
+#endif
+
+size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank, uint32_t max_items) {
     if (max_kb == 0 || max_kb % kGemvGranuleBlocks != 0) return 0;
     uint32_t off = 2 * kMaxStages * 8 + 128;      // mbarriers, then the block of zeros
     a.off_t = off;
     off += align_up(max_rank * 4, 128);
+    a.off_tstage = off;                           // the pieces of t = A x before they are added: rank x pieces floats
+    off += align_up(max_items * 4, 128);
     a.off_xs = off;
     off += align_up(max_kb * 64, 128);
     a.off_sx = off;
@@ -664,9 +754,10 @@ size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank) {
     return (size_t)off + (size_t)nst * kSlotBytes;
 }
 
-cudaError_t launch_decode_step(const StepArgs& a, size_t smem, int grid, cudaStream_t s) {
-    static DeviceOnce once;            // the shared-memory opt-in is per device
-    cudaError_t e = opt_in_smem(reinterpret_cast<const void*>(decode_step_kernel), kMaxSmem - 1024, once);
+template <bool MB>
+static cudaError_t launch_step_t(const StepArgs& a, size_t smem, int grid, cudaStream_t s) {
+    static DeviceOnce once;            // the shared-memory opt-in is per device and per instantiation
+    cudaError_t e = opt_in_smem(reinterpret_cast<const void*>(decode_step_kernel<MB>), kMaxSmem - 1024, once);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);
@@ -682,7 +773,13 @@ cudaError_t launch_decode_step(const StepArgs& a, size_t smem, int grid, cudaStr
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, decode_step_kernel, a);
+    return cudaLaunchKernelEx(&cfg, decode_step_kernel<MB>, a);
+}
+
+cudaError_t launch_decode_step(const StepArgs& a, size_t smem, int grid, cudaStream_t s) {
+    bool mailbox_inputs = false;
+    for (uint32_t i = 0; i < a.group_begin[a.ngroups]; ++i) mailbox_inputs = mailbox_inputs || a.p[i].x_slot != kNoSlot;
+    return mailbox_inputs ? launch_step_t<true>(a, smem, grid, s) : launch_step_t<false>(a, smem, grid, s);
 }
 
 }  // namespace lq4

@@ -12,6 +12,10 @@ constexpr int kStepMaxProblems = 24;
 constexpr int kStepMaxGroups = 8;
 constexpr int kStepMaxRanges = 8;
 constexpr uint32_t kNoSlot = 0xffffffffu;
+// Dot products t = A x whose x comes from the mailbox are cut into pieces short enough for ONE lane of the
+// projection warp to keep all its loads in flight: at most kStepMailboxStrides float4 per lane.
+constexpr int kStepMailboxStrides = 4;
+constexpr uint32_t kStepMaxTsplit = 64;
 
 // One projection of a step.  Activations come from plain memory (ready when the launch starts) or from
 // the step's mailbox (written by an earlier group of the same launch, on this GPU or on a peer).
@@ -42,7 +46,7 @@ struct StepArgs {
     uint32_t ngroups;
     uint32_t use_pdl;
     // shared-memory plan (bytes from the dynamic shared memory base)
-    uint32_t off_t, off_xs, off_sx, off_stage, nstages;
+    uint32_t off_t, off_tstage, off_xs, off_sx, off_stage, nstages;
     // cross-CTA state of this GPU
     uint32_t* tsync;           // 64-bit launch counter: tags of the partial-sum and projection messages
     float* partials;           // [group][grid][128 rows] 8-byte {partial sum, tag} messages
@@ -60,9 +64,10 @@ struct StepArgs {
     uint32_t n_ranges;
 };
 
-// Fills the shared-memory plan for the longest row (`max_kb` blocks) and the widest adapter; returns the
+// Fills the shared-memory plan for the longest row (`max_kb` blocks), the widest adapter and the largest
+// rank x pieces product of one problem; returns the
 // dynamic shared memory needed, or 0 if the row does not fit.
-size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank);
+size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank, uint32_t max_items);
 cudaError_t launch_decode_step(const StepArgs& a, size_t smem, int grid, cudaStream_t s);
 
 }  // namespace lq4

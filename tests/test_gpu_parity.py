@@ -961,7 +961,15 @@ def test_mlp_block_matches_the_three_step_reference(be, m, hidden, inter, rank):
     ratio = tol_ratio(y.cpu().numpy(), y_ref)
     assert ratio <= bound, f"tolerance ratio {ratio}"
     if m == 1 and inter % 128 == 0:
-        assert launches == 1          # the whole block in one persistent launch: down_proj reads silu(gate) * up as it arrives
+        assert launches == 2          # gate and up rows in one grouped launch; down_proj gates its own input
+        # opt-in: the whole block as ONE persistent launch (down_proj reads silu(gate) * up through the mailbox)
+        be.set_option(_lib.OPT_MLP_ONE_LAUNCH, 1)
+        before = be.launch_count
+        y1 = be.mlp_block(dev(x), qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2])
+        be.set_option(_lib.OPT_MLP_ONE_LAUNCH, 0)
+        assert be.launch_count - before == 1
+        be.check_device_status()
+        assert tol_ratio(y1.cpu().numpy(), y_ref) <= bound
     # with a caller-provided scratch (one token: gate||up launch, then down_proj gating its own input) the
     # result holds the same bound; for more tokens the two forms are the same code path
     scratch = torch.empty((m, 2 * inter), dtype=torch.float32, device="cuda")
