@@ -215,6 +215,7 @@ def workload_config(args, world):
                        "step": "one lq4_decode_step call per step: the sets are the groups of ONE persistent launch" +
                                (", chained (a set's 5120- and 17408-wide inputs are the previous set's gathered down/up outputs, "
                                 "read through the mailbox as they arrive)" if args.chained else
+                                ", all sixteen projections as one group (nothing links the sets)" if args.flat else
                                 ", the sets in order, nothing links them (every set reads the step's external inputs)")}[args.launch],
             "parallelism": (f"N-sharded column-parallel x{world}, " +
                             (("outputs published to every rank's mailbox from the kernel's epilogue (8-byte tagged stores over NVLink), "
@@ -371,7 +372,7 @@ def run_ours(args):
         from lattice_b200.sharded import StepBuffer
         S = sum(full_n)
 
-        def make_step_variant(chained):
+        def make_step_variant(chained, flat=False):
             sbuf = StepBuffer(args.layers * S, device=local_rank)
             pay = sbuf.payload
 
@@ -393,6 +394,8 @@ def run_ours(args):
                             x = row_of(li - 1, 3) if p["k"] == 5120 else row_of(li - 1, 2)
                         grp.append((x, p["qw"], p["lora"], y_of(li, si)))
                     groups.append(grp)
+                if flat:                          # nothing links the sets: the caller may as well hand them over as ONE group
+                    groups = [[pr for grp in groups for pr in grp]]
                 return be.prepare_step(groups, sbuf, gathered=[pay[li * S:(li + 1) * S] for li in range(args.layers)])
 
             run = build(xs)
@@ -437,8 +440,9 @@ def run_ours(args):
                      "max_tolerance_ratio": ratio, "all_ranks_identical": True}
             return dict(run=run, build=build, sbuf=sbuf, pay=pay, check=check)
 
-        step_variants["chained" if args.chained else "independent"] = make_step_variant(args.chained)
-        head = step_variants["chained" if args.chained else "independent"]
+        head_name = "chained" if args.chained else ("flat" if args.flat else "independent")
+        step_variants[head_name] = make_step_variant(args.chained, args.flat and not args.chained)
+        head = step_variants[head_name]
         step, pay, step_check = head["run"], head["pay"], head["check"]
         build_step = head["build"]
         note(f"step launch checked, tolerance ratio {step_check['max_tolerance_ratio']:.3g}")
@@ -672,20 +676,25 @@ def run_ours(args):
                 line["aux"][f"decode_set_M{mm}_" + ("grouped" if grp else "per_projection")] = time_sets(mm, grp)
     if step_mode and not args.no_aux:
         # the other form of the step, timed the same way on every rank (graph replay, max over ranks)
-        other = "independent" if args.chained else "chained"
-        var = make_step_variant(other == "chained")
-        step_variants[other] = var
-        gfn, gl = make_graphed(var["run"])
-        nsteps = min(args.steps, 20)
-        gms, _ = timed(gfn, nsteps, 3, gl)
-        be.check_device_status()
-        v = per_step_bytes * nsteps / (gms * 1e-3) / 1e9
-        if rank == 0:
-            line.setdefault("aux", {})[f"decode_step_M1_{other}"] = {
-                "GB/s": v, "frac_hbm_per_gpu": v / world / hbm_peak, "us_per_step": gms * 1e3 / nsteps,
-                "checked_before_timing": var["check"],
-                "what": ("every set's inputs are the previous set's gathered outputs: a set starts when the previous set's "
-                         "columns of all ranks have arrived" if other == "chained" else "nothing links the sets")}
+        what = {"chained": "every set's inputs are the previous set's gathered outputs: a set starts when the previous set's "
+                           "columns of all ranks have arrived",
+                "independent": "the sets in order as four groups, nothing links them",
+                "flat": "nothing links the sets, so all sixteen projections are handed over as ONE group: an upper bound, "
+                        "not the order a decode step has"}
+        for other in ("independent", "chained", "flat"):
+            if other in step_variants:
+                continue
+            var = make_step_variant(other == "chained", other == "flat")
+            step_variants[other] = var
+            gfn, gl = make_graphed(var["run"])
+            nsteps = min(args.steps, 50)
+            gms, _ = timed(gfn, nsteps, 3, gl)
+            be.check_device_status()
+            v = per_step_bytes * nsteps / (gms * 1e-3) / 1e9
+            if rank == 0:
+                line.setdefault("aux", {})[f"decode_step_M1_{other}"] = {
+                    "GB/s": v, "frac_hbm_per_gpu": v / world / hbm_peak, "us_per_step": gms * 1e3 / nsteps,
+                    "checked_before_timing": var["check"], "what": what[other]}
     if world > 1 and not args.no_aux:
         sharded = aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust)      # every rank takes part
         if rank == 0:
@@ -1220,6 +1229,8 @@ def main():
                     help="step: one persistent launch per step, the sets are its groups (lq4_decode_step); "
                          "grouped: one persistent launch per set of four projections (lq4_linear_group); "
                          "per-projection: one lq4_linear call each")
+    ap.add_argument("--flat", action="store_true",
+                    help="with --launch step: all projections of the step as ONE group (nothing links the sets)")
     ap.add_argument("--chained", action="store_true",
                     help="with --launch step: every set's inputs are the previous set's gathered outputs (the dependent "
                          "form; reported in aux otherwise)")

@@ -706,8 +706,10 @@ void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* c
         return e ? atoi(e) : -1;
     }();
     const uint64_t kTileCharge = env_charge >= 0 ? (uint64_t)env_charge : (uint64_t)tile_charge;
-    uint64_t cost[kMaxGroup], units[kMaxGroup];
-    uint32_t n[kMaxGroup];
+    constexpr uint32_t kMaxSplit = 32;           // problems of one launch: a group (8) or a step's group (24)
+    if (count > kMaxSplit) count = kMaxSplit;
+    uint64_t cost[kMaxSplit], units[kMaxSplit];
+    uint32_t n[kMaxSplit];
     for (uint32_t i = 0; i < count; ++i) {
         units[i] = (uint64_t)ps[i].tiles * ps[i].kg;
         cost[i] = (uint64_t)ps[i].tiles * (ps[i].kg + kTileCharge);

@@ -524,7 +524,10 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
                     const uint32_t s = it % NST;
                     if (!mbar_wait_step(&full[s], (it / NST) & 1u, s_err)) { ok = false; *s_err = 1; }
-                    if (git == 6 && q.rank && !t_loaded) gather_t();
+                    // plain inputs: the projections were published in the first microseconds, fetch them here to keep
+                    // the round trip off the end of the tile; mailbox inputs: the projection itself starts late, so
+                    // it is fetched where it is needed (the first epilogue)
+                    if (git == 6 && q.rank && !t_loaded && (!MB || q.x_slot == kNoSlot)) gather_t();
                     const uint8_t* st = smem + a.off_stage + (size_t)s * kSlotBytes;
                     const uint8_t* row0 = st + (warp * 16 + gq) * rs + t * kBlockBytes;
                     const uint8_t* row1 = row0 + 8 * rs;

@@ -8,7 +8,7 @@
 
 namespace lq4 {
 
-constexpr int kStepMaxProblems = 24;
+constexpr int kStepMaxProblems = 24;     // at most 32: dec::split_ctas sizes its tables for that
 constexpr int kStepMaxGroups = 8;
 constexpr int kStepMaxRanges = 8;
 constexpr uint32_t kNoSlot = 0xffffffffu;
