@@ -418,6 +418,14 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     if (path == LQ4_PATH_AUTO) {
         if (!fast_layout) path = LQ4_PATH_GEMV_GENERIC;
         else if (a->m <= (uint32_t)kGemvMaxM) path = LQ4_PATH_GEMV_MMA;                          // decode kernels
+        else if (a->m <= 32 || (a->m <= 64 && a->n <= 8192)) {
+            // A few dozen tokens leave the tensor-core kernel with too few 256-row tiles to fill the GPU and a
+            // serial walk over k in each (measured, 5120 -> 17408: 98 us at 32 tokens; 17408 -> 5120: 250 us);
+            // the decode kernel in chunks of 16 tokens streams the weights once per chunk and is quicker here
+            // (31 to 35 us per chunk on those shapes).  Not with a fused all-gather: that path is per launch.
+            path = (a->gather && a->gather->world > 1) ? LQ4_PATH_GEMM_TC : LQ4_PATH_GEMV_MMA;
+            if (path == LQ4_PATH_GEMM_TC && !gemm_supported(a->m, a->n, a->k, rank > (uint32_t)kGemmMaxRank ? 0u : rank)) path = LQ4_PATH_GEMV_MMA;
+        }
         else path = gemm_supported(a->m, a->n, a->k, rank > (uint32_t)kGemmMaxRank ? 0u : rank) ? LQ4_PATH_GEMM_TC : LQ4_PATH_GEMV_MMA;
     }
     if (path != LQ4_PATH_GEMV_GENERIC && !fast_layout)

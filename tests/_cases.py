@@ -6,7 +6,7 @@ import numpy as np
 import oracle
 from lattice_b200 import synth
 
-TOL = 1e-3     # |y - y_ref| <= TOL * (|y_ref| + rms(y_ref)), the bound the north star states
+TOL = 1e-3     # outputs must satisfy |y - y_ref| <= TOL * (|y_ref| + rms(y_ref)) against the reference's CPU linear
 
 
 def tol_ratio(y: np.ndarray, y_ref: np.ndarray) -> float:

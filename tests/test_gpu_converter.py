@@ -190,7 +190,7 @@ def test_composed_quarot_gate_with_the_device_pipeline(be):
 
 
 def test_config5_weights_from_the_device_converter(be):
-    """configs[4]'s weight preparation at its real row length on a slice of rows: f32 weights -> f64 ->
+    """The QuaRot layer's (K=4096) weight preparation at its real row length on a slice of rows: f32 weights -> f64 ->
     absorb_input_rotation_f64 (default converter seed) -> symmetric Q4, device against oracle, byte for byte."""
     n, k = 344, 4096
     w = synth.weights(5, n, k).astype(np.float64)

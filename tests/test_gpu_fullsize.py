@@ -92,7 +92,7 @@ def test_group_of_one_at_full_size(be, layer, idx):
 
 
 def _config5(be, m):
-    """configs[4] at full size: weights rotated (f64) and symmetric-quantized by the device converter."""
+    """The QuaRot layer (K=4096, N=11008) at full size: weights rotated (f64) and symmetric-quantized by the device converter."""
     from lattice_b200 import Q4WeightBuf
     n, k = 11008, 4096
     g = torch.Generator(device="cuda"); g.manual_seed(555)
@@ -127,7 +127,7 @@ def test_config5_full_size_512_tokens_sampled_features(be):
 
 
 def test_config4_full_size_tolerance_histogram(be):
-    """configs[3] (M=2048, K=5120, N=17408, LoRA r=64, bf16): the tensor-core kernel rounds dequantized weights
+    """The prefill GEMM (M=2048, K=5120, N=17408, LoRA r=64, bf16): the tensor-core kernel rounds dequantized weights
     to f16, which leaves a thin margin under the 1e-3 bound; the ratio |y - y_ref| / (1e-3 (|y_ref| + rms)) is
     taken on 1100+ output features x 2048 tokens and its distribution is printed."""
     from lattice_b200 import Q4WeightBuf

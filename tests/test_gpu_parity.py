@@ -313,6 +313,9 @@ def test_launches_are_counted(be):
                                               (33, 1024, 129, 5, True), (1024, 1024, 640, 64, True)])
 def test_prefill_gemm_matches_oracle(be, m, k, n, rank, bf16):
     case = make_case(4, m, k, n, rank=rank, alpha=2.0 * rank, bf16_x=bf16, extra=m + n)
+    # the tensor-core kernel explicitly (a few dozen tokens take the decode kernel in chunks by default)
+    y = run_case(be, case, bf16=bf16, path=_lib.PATH_GEMM_TC)
+    assert tol_ratio(y, case["y_ref"]) <= 1.0
     y = run_case(be, case, bf16=bf16)
     assert tol_ratio(y, case["y_ref"]) <= 1.0
     # the decode kernel, forced onto the same inputs in chunks of 16 tokens, agrees as well
@@ -343,7 +346,7 @@ def test_prefill_edge_scale_activations(be):
 
 
 def test_config4_full_size_sampled_output_features(be):
-    """configs[3] at its full size (M=2048, K=5120, N=17408, LoRA r=64, bf16 activations): the GPU result
+    """The prefill GEMM at its full size (M=2048, K=5120, N=17408, LoRA r=64, bf16 activations): the GPU result
     is checked on a sample of output features, each against the oracle run on that feature's own Q4 row."""
     from lattice_b200 import Q4WeightBuf
     from lattice_b200._lib import LoraDesc
