@@ -44,7 +44,7 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC = {
     "grouped": {"bytes_per_launch": 138.64e6, "kernel": "decode_kernel<1, 8>", "source_hash": None},
     "per-projection": {"bytes_per_launch": None, "kernel": "decode_kernel<1, 1>", "source_hash": None},
-    "step": {"bytes_per_launch": None, "kernel": "decode_step_kernel", "source_hash": None},
+    "step": {"bytes_per_launch": 555.38e6, "kernel": "decode_step_kernel<false>", "source_hash": "6c7ff2b22150110b"},
 }
 
 
@@ -1131,7 +1131,7 @@ def run_only(args):
         be.check_device_status()
         print("ok", args.only)
         return
-    elif args.only == "decode-step":       # M=1, --layers chained sets of the four large-layer shapes in ONE launch
+    elif args.only == "decode-step":       # M=1, --layers sets of the four large-layer shapes in ONE launch (--chained: each fed by the one before)
         from lattice_b200.sharded import StepBuffer
         S = sum(n for _, n in SHAPES)
         offs_full = [sum(n for _, n in SHAPES[:i]) for i in range(len(SHAPES))]
@@ -1148,7 +1148,7 @@ def run_only(args):
                 a = torch.randn((LORA_RANK, k), device=dev) * 0.02
                 b = torch.randn((n, LORA_RANK), device=dev) * 0.02
                 keep += [a, b]
-                if li == 0:
+                if li == 0 or not args.chained:
                     x = x_ext[k]
                 else:
                     src = 3 if k == 5120 else 2
