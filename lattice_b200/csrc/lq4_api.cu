@@ -874,8 +874,6 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
         items_total += (size_t)sa.p[i].rank * sa.p[i].tsplit;
         max_items = sa.p[i].rank * sa.p[i].tsplit > max_items ? sa.p[i].rank * sa.p[i].tsplit : max_items;
     }
-    const size_t smem = step_plan_smem(sa, max_kb, max_rank, max_items);
-    if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "a row of this step does not fit in shared memory");
     const int grid = (int)(max_units < (uint64_t)ctx->sm_count ? max_units : (uint64_t)ctx->sm_count);
 
     // CTA shares and projection items per group
@@ -905,6 +903,17 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
         sa.group_items[g] = dots;
         item_off += dots;
     }
+    // limb buffers: the longest k range a CTA converts in any group (the whole row when its share spans a tile)
+    uint32_t cap_blocks = 0;
+    for (uint32_t i = 0; i < np; ++i) {
+        const StepProblem& q = sa.p[i];
+        const uint64_t total = (uint64_t)q.tiles * q.kg;
+        const uint64_t share = (total + q.cta_count - 1) / q.cta_count;
+        const uint32_t blocks = share >= q.kg ? q.kb : (uint32_t)share * kGemvGranuleBlocks;
+        cap_blocks = blocks > cap_blocks ? blocks : cap_blocks;
+    }
+    const size_t smem = step_plan_smem(sa, cap_blocks, max_rank, max_items);
+    if (!smem) return fail(LQ4_ERR_UNSUPPORTED, "a row of this step does not fit in shared memory");
 
     // mailbox and the ranges to hand back as plain f32
     sa.step_counter = ctx->tsync;

@@ -35,7 +35,10 @@ namespace {
 using namespace gemv;
 using namespace dec;
 
-constexpr int kStepThreads = 320;      // 8 consumer warps + TMA warp + projection warp
+constexpr int kStepThreads = 384;      // 8 consumer warps + TMA warp + projection warp + 2 converter warps
+constexpr int kConvWarps = 2;          // (ptxas sizes the register budget for 384 threads anyway: these warps are free)
+constexpr int kConvThreads = kConvWarps * 32;
+constexpr uint32_t kXBarOffset = 2 * kMaxStages * 8 + 32;      // xready[2], xfree[2] after the ring's barriers and the zero block
 
 // Development aid, compiled only with -DLQ4_STEP_TIMELINE: nanosecond stamps per CTA and group.
 #ifdef LQ4_STEP_TIMELINE
@@ -145,11 +148,11 @@ __device__ __forceinline__ Share step_share(const StepArgs& a, uint32_t g, uint3
 // running, and a thread's loads only overlap if they are issued before the first result is used: a sweep issues
 // the loads of KB octets (4 x 16 bytes each) back to back, then looks at the tags; entries that are not there yet
 // repeat the sweep.  Warp-uniform (the conversion uses quad shuffles), bounded, with a pause between sweeps.
-template <int KB, bool GATED>
+template <int NT, int KB, bool GATED>
 __device__ __forceinline__ void prologue_from_mailbox(const StepArgs& a, uint8_t* xs, float2* sx, const unsigned long long* xm,
                                                       const unsigned long long* um, uint32_t a0, uint32_t na, uint32_t b0,
                                                       uint32_t noct, int ctid, uint32_t stag, volatile int* s_err) {
-    for (uint32_t o0 = 0; o0 < noct; o0 += KB * kConsumerThreads) {
+    for (uint32_t o0 = 0; o0 < noct; o0 += KB * NT) {
         float v[KB][8];
         {
             const uint32_t i = o0 + (uint32_t)(ctid & ~31);      // the first octet this warp reads in this sweep
@@ -161,7 +164,7 @@ __device__ __forceinline__ void prologue_from_mailbox(const StepArgs& a, uint8_t
             unsigned long long ex[KB][8], eu[GATED ? KB : 1][8];
 #pragma unroll
             for (int u = 0; u < KB; ++u) {
-                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t i = o0 + u * NT + ctid;
                 if (i < noct) {
                     const size_t o = (size_t)(i < na ? a0 + i : b0 + (i - na)) * 8;
                     mbox_load8_raw(xm + o, ex[u]);
@@ -170,7 +173,7 @@ __device__ __forceinline__ void prologue_from_mailbox(const StepArgs& a, uint8_t
             }
 #pragma unroll
             for (int u = 0; u < KB; ++u) {
-                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t i = o0 + u * NT + ctid;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v[u][e] = 0.0f;
                 if (i < noct) {
@@ -193,35 +196,46 @@ __device__ __forceinline__ void prologue_from_mailbox(const StepArgs& a, uint8_t
         }
 #pragma unroll
         for (int u = 0; u < KB; ++u) {
-            const uint32_t i = o0 + u * kConsumerThreads + ctid;
-            const uint32_t o = i < na ? a0 + i : b0 + (i - na);
-            store_limbs(xs, sx, 1, 0, o, i < noct, v[u]);
+            const uint32_t i = o0 + u * NT + ctid;
+            store_limbs(xs, sx, 1, 0, i, i < noct, v[u]);      // the buffer is indexed from the start of the range
         }
     }
 }
 
-// The 256 consumer threads turn the k range(s) this CTA touches into two int8 limbs per activation.
-template <bool MB>
-__device__ __forceinline__ void step_prologue(const StepArgs& a, const StepProblem& q, uint8_t* smem, int ctid, uint64_t r0, uint64_t r1,
-                              const unsigned long long* mb, uint32_t stag, volatile int* s_err) {
-    uint8_t* xs = smem + a.off_xs;
-    float2* sx = reinterpret_cast<float2*>(smem + a.off_sx);
+// First block and octet ranges of the k range(s) a share [r0, r1) of work units touches: the whole row when the
+// share spans a tile, else up to two pieces (the share may wrap from the end of one tile into the next).
+struct XRange {
+    uint32_t a0, na, b0, noct;     // octets: piece a = [a0, a0 + na), piece b = [b0, b0 + noct - na)
+    uint32_t base_blk;             // first block of piece a: the limb buffer is indexed from here, wrapping at k / 32
+};
+__device__ __forceinline__ XRange step_xrange(const StepProblem& q, uint64_t r0, uint64_t r1) {
     const uint32_t opg = kGemvGranuleBlocks * 4;              // octets (8 activations) per granule
-    uint32_t a0 = 0, a1 = q.k / 8, b0 = 0, b1 = 0;            // two octet ranges [a0,a1) and [b0,b1)
+    uint32_t a0 = 0, a1 = q.k / 8, b0 = 0, b1 = 0;
     if (r1 - r0 < q.kg) {
         const uint32_t g0 = (uint32_t)(r0 % q.kg), len = (uint32_t)(r1 - r0);
         if (g0 + len <= q.kg) { a0 = g0 * opg; a1 = (g0 + len) * opg; }
         else { a0 = g0 * opg; a1 = q.kg * opg; b0 = 0; b1 = (g0 + len - q.kg) * opg; }
     }
-    const uint32_t na = a1 - a0, noct = na + (b1 - b0);
-    if (!MB || q.x_slot == kNoSlot) {
+    XRange x;
+    x.a0 = a0; x.na = a1 - a0; x.b0 = b0; x.noct = x.na + (b1 - b0); x.base_blk = a0 / 4;
+    return x;
+}
+
+// NT threads turn the k range(s) of a share into two int8 limbs per activation, into the limb buffer (xs, sx).
+// MAILBOX: the input comes from the step's mailbox (polled); else from plain memory.
+template <bool MAILBOX, int NT>
+__device__ __forceinline__ void convert_activations(const StepArgs& a, const StepProblem& q, uint8_t* xs, float2* sx, int ctid,
+                                                    const XRange& xr, const unsigned long long* mb, uint32_t stag,
+                                                    volatile int* s_err) {
+    const uint32_t a0 = xr.a0, na = xr.na, b0 = xr.b0, noct = xr.noct;
+    if constexpr (!MAILBOX) {
         // plain memory: several octets per thread and pass, all loads issued before the first use
         constexpr int kBatch = 8;
-        for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * kConsumerThreads) {
+        for (uint32_t o0 = 0; o0 < noct; o0 += kBatch * NT) {
             float v[kBatch][8];
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                const uint32_t i = o0 + u * NT + ctid;
                 const uint32_t o = i < na ? a0 + i : b0 + (i - na);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v[u][e] = 0.0f;
@@ -230,7 +244,7 @@ __device__ __forceinline__ void step_prologue(const StepArgs& a, const StepProbl
             if (q.x_mul) {
 #pragma unroll
                 for (int u = 0; u < kBatch; ++u) {
-                    const uint32_t i = o0 + u * kConsumerThreads + ctid;
+                    const uint32_t i = o0 + u * NT + ctid;
                     const uint32_t o = i < na ? a0 + i : b0 + (i - na);
                     if (i < noct) {
                         float up[8];
@@ -242,19 +256,15 @@ __device__ __forceinline__ void step_prologue(const StepArgs& a, const StepProbl
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
-                const uint32_t i = o0 + u * kConsumerThreads + ctid;
-                const uint32_t o = i < na ? a0 + i : b0 + (i - na);
-                store_limbs(xs, sx, 1, 0, o, i < noct, v[u]);
+                const uint32_t i = o0 + u * NT + ctid;
+                store_limbs(xs, sx, 1, 0, i, i < noct, v[u]);      // the buffer is indexed from the start of the range
             }
         }
-    } else if constexpr (MB) {
-        // mailbox: the entries are polled until they carry this step's tag.  The loop is warp-uniform (the
-        // limb conversion uses quad shuffles), bounded, and backs off between sweeps.
+    } else {
         const unsigned long long* xm = mb + q.x_slot;
-        if (q.xmul_slot != kNoSlot) prologue_from_mailbox<2, true>(a, xs, sx, xm, mb + q.xmul_slot, a0, na, b0, noct, ctid, stag, s_err);
-        else prologue_from_mailbox<4, false>(a, xs, sx, xm, nullptr, a0, na, b0, noct, ctid, stag, s_err);
+        if (q.xmul_slot != kNoSlot) prologue_from_mailbox<NT, 2, true>(a, xs, sx, xm, mb + q.xmul_slot, a0, na, b0, noct, ctid, stag, s_err);
+        else prologue_from_mailbox<NT, 4, false>(a, xs, sx, xm, nullptr, a0, na, b0, noct, ctid, stag, s_err);
     }
-    named_bar_sync(kBarConsumers, kConsumerThreads);
 }
 
 // The projection warp (one per CTA): the adapters' t = A x for every group, published as tagged messages.
@@ -377,7 +387,7 @@ __device__ __forceinline__ void step_projections(const StepArgs& a, volatile int
 }
 
 // MB: some projection of the launch takes its input from the mailbox.  Launches without such inputs run the
-// instantiation that holds none of the polling code (the kernel sits at the register limit of a 10-warp CTA).
+// instantiation that holds none of the polling code (the kernel sits at the register limit of a 12-warp CTA).
 template <bool MB>
 __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __grid_constant__ StepArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -388,10 +398,16 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t NST = a.nstages;
+    uint64_t* xready = reinterpret_cast<uint64_t*>(smem + kXBarOffset);     // limb buffer b holds the group's limbs
+    uint64_t* xfree = xready + 2;                                           // the consumers are done with limb buffer b
     if (tid == 0) {
         for (uint32_t s = 0; s < NST; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 8);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&xready[b], kConvWarps);
+            mbar_init(&xfree[b], 8);
         }
         s_err_mem = 0;
         for (int i = 0; i < 8; ++i) reinterpret_cast<uint32_t*>(smem + kZeroOffset)[i] = 0;
@@ -441,6 +457,34 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         }
     } else if (warp == 9) {
         step_projections<MB>(a, s_err);
+    } else if (warp >= 10) {
+        // ------------------------------ activation converters ------------------------------
+        // Build the limbs of the CTA's NEXT shares while the consumers work: with two limb buffers they run a
+        // whole group ahead, so the consumers never stop to convert (during a conversion by the consumers the
+        // ring stays full and the SM requests nothing from memory: about 2 us per group).  Inputs that come from
+        // the mailbox are converted by the consumers themselves, who have four times the threads for the sweeps.
+        const int ctid = tid - 320;
+        if (a.use_pdl) pdl_wait_prior_grids();
+        uint32_t gcount = 0;
+        for (uint32_t g = 0; g < a.ngroups; ++g) {
+            const Share sh = step_share(a, g, blockIdx.x);
+            if (!sh.any) continue;
+            const StepProblem& q = a.p[sh.pi];
+            const uint32_t b = gcount % a.nxbuf, use = gcount / a.nxbuf;
+            ++gcount;
+            if (lane == 0 && !mbar_wait_step(&xfree[b], (use & 1u) ^ 1u, s_err)) {
+                atomicOr(a.status, kDevErrBarrierTimeout);
+                *s_err = 1;
+            }
+            __syncwarp();
+            if (!MB || q.x_slot == kNoSlot) {
+                uint8_t* xs = smem + a.off_xbuf + (size_t)b * a.xbuf_stride;
+                float2* sx = reinterpret_cast<float2*>(xs + a.xbuf_sx);
+                convert_activations<false, kConvThreads>(a, q, xs, sx, ctid, step_xrange(q, sh.r0, sh.r1), nullptr, 0, s_err);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xready[b]);
+        }
     } else {
         // ------------------------------ consumers ------------------------------
         const int gq = lane >> 2, t = lane & 3;
@@ -450,10 +494,9 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         unsigned long long* mb = a.mbox + (size_t)(stag & 1u) * a.mbox_half;
 
         const bool has_b = (gq >> 1) == t;
-        const uint8_t* xs_lane = smem + a.off_xs + (size_t)(gq & 1) * 32;
         const uint8_t* zeros = smem + kZeroOffset;
-        const float2* sx_all = reinterpret_cast<const float2*>(smem + a.off_sx);
         float* t_sm = reinterpret_cast<float*>(smem + a.off_t);
+        uint32_t gcount = 0;
 
         // A failed wait (its time limit, or another wait of this CTA failed before) never changes the control
         // flow: every warp keeps walking the same groups, tiles and stages, so the named barriers below always
@@ -468,7 +511,21 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             // everyone is done with the previous group's limbs and projection before they are replaced
             named_bar_sync(kBarConsumers, kConsumerThreads);
             if (tid == 0) TL_STAMP(g, 0);
-            step_prologue<MB>(a, q, smem, tid, sh.r0, sh.r1, mb, stag, s_err);
+            // this group's limb buffer: filled by the converter warps (plain inputs) or, below, by the consumers
+            const uint32_t xb_i = gcount % a.nxbuf, xb_use = gcount / a.nxbuf;
+            ++gcount;
+            uint8_t* xs_buf = smem + a.off_xbuf + (size_t)xb_i * a.xbuf_stride;
+            const float2* sx_all = reinterpret_cast<const float2*>(xs_buf + a.xbuf_sx);
+            const uint8_t* xs_lane = xs_buf + (size_t)(gq & 1) * 32;
+            const XRange xr = step_xrange(q, sh.r0, sh.r1);
+            if (!mbar_wait_step(&xready[xb_i], xb_use & 1u, s_err)) { ok = false; *s_err = 1; }
+            if constexpr (MB) {
+                if (q.x_slot != kNoSlot) {
+                    convert_activations<true, kConsumerThreads>(a, q, xs_buf, reinterpret_cast<float2*>(xs_buf + a.xbuf_sx), tid, xr,
+                                                                mb, stag, s_err);
+                    named_bar_sync(kBarConsumers, kConsumerThreads);
+                }
+            }
             if (tid == 0) TL_STAMP(g, 1);
             bool t_loaded = false;
             // Gathers t = A x of this problem from the projection warps' messages into shared memory, adding
@@ -533,7 +590,8 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     const uint8_t* row1 = row0 + 8 * rs;
 #pragma unroll 1
                     for (uint32_t gi = 0; gi < ngr; ++gi) {
-                        const uint32_t blk = (gs + gi) * kGemvGranuleBlocks + t;     // this thread's block
+                        const uint32_t blk_abs = (gs + gi) * kGemvGranuleBlocks + t;     // this thread's block of the row
+                        const uint32_t blk = blk_abs >= xr.base_blk ? blk_abs - xr.base_blk : blk_abs + q.kb - xr.base_blk;
                         const uint32_t* q0 = reinterpret_cast<const uint32_t*>(row0 + gi * (4 * kBlockBytes));
                         const uint32_t* q1 = reinterpret_cast<const uint32_t*>(row1 + gi * (4 * kBlockBytes));
                         const uint32_t meta0 = q0[0], meta1 = q1[0];
@@ -681,6 +739,9 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 }
                 if (tid == 0) TL_STAMP(g, 3);
             }
+            // the limb buffer may be refilled for a later group
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xfree[xb_i]);
         }
         if (!ok) {
             if (lane == 0) atomicOr(a.status, kDevErrBarrierTimeout);
@@ -737,24 +798,31 @@ extern "C" int lq4_debug_step_timeline(unsigned long long* host_out, size_t coun
 }
 #endif
 
-size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank, uint32_t max_items) {
-    if (max_kb == 0 || max_kb % kGemvGranuleBlocks != 0) return 0;
-    uint32_t off = 2 * kMaxStages * 8 + 128;      // mbarriers, then the block of zeros
+size_t step_plan_smem(StepArgs& a, uint32_t cap_blocks, uint32_t max_rank, uint32_t max_items) {
+    if (cap_blocks == 0) return 0;
+    uint32_t off = 2 * kMaxStages * 8 + 128;      // ring barriers, the block of zeros, the limb-buffer barriers
     a.off_t = off;
     off += align_up(max_rank * 4, 128);
     a.off_tstage = off;                           // the pieces of t = A x before they are added: rank x pieces floats
     off += align_up(max_items * 4, 128);
-    a.off_xs = off;
-    off += align_up(max_kb * 64, 128);
-    a.off_sx = off;
-    off += align_up(max_kb * 8, 128);
-    a.off_stage = off;
+    // one limb buffer: limbs (64 B per block), then {scale, sum} (8 B per block)
+    a.xbuf_sx = align_up(cap_blocks * 64, 128);
+    a.xbuf_stride = a.xbuf_sx + align_up(cap_blocks * 8, 128);
+    a.off_xbuf = off;
     const uint32_t budget = (uint32_t)kMaxSmem - 1024;    // static shared memory and driver reserve
-    if (off + 2 * kSlotBytes > budget) return 0;
-    uint32_t nst = (budget - off) / kSlotBytes;
-    if (nst > 4) nst = 4;
-    a.nstages = nst;
-    return (size_t)off + (size_t)nst * kSlotBytes;
+    // two limb buffers (conversion runs a group ahead of consumption) when that costs no ring stage
+    auto stages_with = [&](uint32_t nbuf) -> uint32_t {
+        const uint32_t o = off + nbuf * a.xbuf_stride;
+        if (o + 2 * kSlotBytes > budget) return 0;
+        const uint32_t n = (budget - o) / kSlotBytes;
+        return n > 4 ? 4 : n;
+    };
+    const uint32_t st1 = stages_with(1), st2 = stages_with(2);
+    if (st1 == 0) return 0;
+    a.nxbuf = (st2 >= st1 || st2 >= 3) ? 2 : 1;
+    a.nstages = a.nxbuf == 2 ? st2 : st1;
+    a.off_stage = off + a.nxbuf * a.xbuf_stride;
+    return (size_t)a.off_stage + (size_t)a.nstages * kSlotBytes;
 }
 
 template <bool MB>

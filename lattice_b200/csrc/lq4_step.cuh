@@ -46,7 +46,8 @@ struct StepArgs {
     uint32_t ngroups;
     uint32_t use_pdl;
     // shared-memory plan (bytes from the dynamic shared memory base)
-    uint32_t off_t, off_tstage, off_xs, off_sx, off_stage, nstages;
+    uint32_t off_t, off_tstage, off_stage, nstages;
+    uint32_t off_xbuf, xbuf_stride, xbuf_sx, nxbuf;   // limb buffers: nxbuf (1 or 2) of xbuf_stride bytes, {scale, sum} at xbuf_sx
     // cross-CTA state of this GPU
     uint32_t* tsync;           // 64-bit launch counter: tags of the partial-sum and projection messages
     float* partials;           // [group][grid][128 rows] 8-byte {partial sum, tag} messages
@@ -64,10 +65,10 @@ struct StepArgs {
     uint32_t n_ranges;
 };
 
-// Fills the shared-memory plan for the longest row (`max_kb` blocks), the widest adapter and the largest
-// rank x pieces product of one problem; returns the
-// dynamic shared memory needed, or 0 if the row does not fit.
-size_t step_plan_smem(StepArgs& a, uint32_t max_kb, uint32_t max_rank, uint32_t max_items);
+// Fills the shared-memory plan for limb buffers of `cap_blocks` Q4 blocks (the longest k range any CTA converts in
+// any group), the widest adapter and the largest rank x pieces product of one problem; returns the dynamic shared
+// memory needed, or 0 if it does not fit.
+size_t step_plan_smem(StepArgs& a, uint32_t cap_blocks, uint32_t max_rank, uint32_t max_items);
 cudaError_t launch_decode_step(const StepArgs& a, size_t smem, int grid, cudaStream_t s);
 
 }  // namespace lq4

@@ -234,3 +234,26 @@ int main() {
                    check=True)
     res = subprocess.run([str(exe)], capture_output=True, text=True)
     assert res.returncode == 0 and res.stdout.strip() == "0"
+
+
+def test_step_sharded_and_option_entry_points_validate_without_a_device(L):
+    assert L.lq4_decode_step(None, None, 0, None, None) == _lib.ERR_NULL
+    assert L.lq4_linear_sharded(None, None, None, None) == _lib.ERR_NULL
+    assert L.lq4_ctx_set_option(None, _lib.OPT_PDL, 0) == _lib.ERR_NULL
+    assert L.lq4_noalloc_check is not None
+    h = C.c_void_p()
+    assert L.lq4_step_buf_create(0, C.byref(h)) == _lib.ERR_SHAPE and h.value is None
+    assert L.lq4_step_buf_create(1 << 31, C.byref(h)) == _lib.ERR_OVERFLOW
+    assert L.lq4_step_buf_create(16, None) == _lib.ERR_NULL
+    buf = (C.c_float * 8)()
+    ptr = C.cast(buf, C.c_void_p).value
+    assert L.lq4_place_slices(None, ptr, 0, 1, 8, 2, None) == _lib.ERR_NULL
+    assert L.lq4_place_slices(ptr, ptr, 4, 1, 8, 2, None) == _lib.ERR_SHAPE       # row pitch below n_total
+    assert L.lq4_place_slices(ptr, ptr, 0, 1, 8, 0, None) == _lib.ERR_SHAPE       # world 0
+    assert L.lq4_place_slices(ptr, ptr, 0, 0, 8, 2, None) == _lib.OK              # nothing to place
+    assert L.lq4_nccl_comm_create(None, 2, 0, C.byref(h)) == _lib.ERR_NULL
+    ident = (C.c_uint8 * _lib.NCCL_ID_BYTES)()
+    assert L.lq4_nccl_comm_create(ident, 2, 2, C.byref(h)) == _lib.ERR_SHAPE      # rank >= world
+    L.lq4_nccl_comm_destroy(None)
+    # argument blocks of the step call
+    assert C.sizeof(_lib.StepGroup) == 16 and C.sizeof(_lib.StepRange) == 16 and C.sizeof(_lib.ShardDesc) == 40
