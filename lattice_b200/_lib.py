@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "liblattice_q4.so")
+# LQ4_LIB_PATH selects another build of the same library (a development build, a system-wide install)
+LIB_PATH = os.environ.get("LQ4_LIB_PATH") or os.path.join(HERE, "liblattice_q4.so")
 
 # status codes (include/lattice_q4.h)
 OK, ERR_NULL, ERR_K, ERR_OVERFLOW, ERR_ALIGN, ERR_DTYPE, ERR_LORA, ERR_ROT, ERR_BAD_BLOCK, ERR_CUDA, \

@@ -38,6 +38,7 @@ using namespace dec;
 constexpr int kStepThreads = 384;      // 8 consumer warps + TMA warp + projection warp + 2 converter warps
 constexpr int kConvWarps = 2;          // (ptxas sizes the register budget for 384 threads anyway: these warps are free)
 constexpr int kConvThreads = kConvWarps * 32;
+constexpr int kBarConverters = 2;      // named barrier of the converter warps
 constexpr uint32_t kXBarOffset = 2 * kMaxStages * 8 + 32;      // xready[2], xfree[2] after the ring's barriers and the zero block
 
 // Development aid, compiled only with -DLQ4_STEP_TIMELINE: nanosecond stamps per CTA and group.
@@ -400,6 +401,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
     const uint32_t NST = a.nstages;
     uint64_t* xready = reinterpret_cast<uint64_t*>(smem + kXBarOffset);     // limb buffer b holds the group's limbs
     uint64_t* xfree = xready + 2;                                           // the consumers are done with limb buffer b
+    uint64_t* tready = xfree + 2;                                           // t = A x of the group is in t buffer b
     if (tid == 0) {
         for (uint32_t s = 0; s < NST; ++s) {
             mbar_init(&full[s], 1);
@@ -408,6 +410,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         for (int b = 0; b < 2; ++b) {
             mbar_init(&xready[b], kConvWarps);
             mbar_init(&xfree[b], 8);
+            mbar_init(&tready[b], kConvWarps);
         }
         s_err_mem = 0;
         for (int i = 0; i < 8; ++i) reinterpret_cast<uint32_t*>(smem + kZeroOffset)[i] = 0;
@@ -465,6 +468,8 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         // the mailbox are converted by the consumers themselves, who have four times the threads for the sweeps.
         const int ctid = tid - 320;
         if (a.use_pdl) pdl_wait_prior_grids();
+        const uint32_t tag = launch_tag(a.tsync);
+        float* cstage = reinterpret_cast<float*>(smem + a.off_cstage);
         uint32_t gcount = 0;
         for (uint32_t g = 0; g < a.ngroups; ++g) {
             const Share sh = step_share(a, g, blockIdx.x);
@@ -484,6 +489,39 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&xready[b]);
+            // ... and gather the adapter projection t = A x of the same share's problem (published by the
+            // projection warps of all CTAs in the first microseconds when the input is plain), so that the
+            // consumers find it in shared memory at their first epilogue instead of fetching it themselves
+            if (q.rank && (!MB || q.x_slot == kNoSlot)) {
+                float* tb = reinterpret_cast<float*>(smem + a.off_t + (size_t)b * a.t_stride);
+                const uint32_t nmsg = q.rank * q.tsplit;
+                bool good = true;
+                for (uint32_t idx = ctid; idx < nmsg; idx += kConvThreads) {
+                    uint2 msg = msg_load(q.tmsg + idx);
+                    if (msg.y != tag) {
+                        const long long t0 = wait_clock();
+                        unsigned ns = 128;
+                        for (;;) {
+                            __nanosleep(ns);
+                            ns = ns < 1024 ? ns * 2 : 1024;
+                            msg = msg_load(q.tmsg + idx);
+                            if (msg.y == tag) break;
+                            if (*s_err != 0 || wait_expired(t0)) { good = false; break; }
+                        }
+                    }
+                    cstage[idx] = __uint_as_float(msg.x);
+                }
+                if (!good) { atomicOr(a.status, kDevErrGridWaitTimeout); *s_err = 1; }
+                named_bar_sync(kBarConverters, kConvThreads);
+                for (uint32_t j = ctid; j < q.rank; j += kConvThreads) {
+                    float sum = 0.0f;
+                    for (uint32_t sp = 0; sp < q.tsplit; ++sp) sum += cstage[j * q.tsplit + sp];      // piece order: fixed sum
+                    tb[j] = sum;
+                }
+                named_bar_sync(kBarConverters, kConvThreads);      // the staging area is free for the next group
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tready[b]);
         }
     } else {
         // ------------------------------ consumers ------------------------------
@@ -495,7 +533,6 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
 
         const bool has_b = (gq >> 1) == t;
         const uint8_t* zeros = smem + kZeroOffset;
-        float* t_sm = reinterpret_cast<float*>(smem + a.off_t);
         uint32_t gcount = 0;
 
         // A failed wait (its time limit, or another wait of this CTA failed before) never changes the control
@@ -518,6 +555,8 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             const float2* sx_all = reinterpret_cast<const float2*>(xs_buf + a.xbuf_sx);
             const uint8_t* xs_lane = xs_buf + (size_t)(gq & 1) * 32;
             const XRange xr = step_xrange(q, sh.r0, sh.r1);
+            float* t_sm = reinterpret_cast<float*>(smem + a.off_t + (size_t)xb_i * a.t_stride);
+            const bool helper_t = !MB || q.x_slot == kNoSlot;      // the converter warps gather t for plain inputs
             if (!mbar_wait_step(&xready[xb_i], xb_use & 1u, s_err)) { ok = false; *s_err = 1; }
             if constexpr (MB) {
                 if (q.x_slot != kNoSlot) {
@@ -581,10 +620,6 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     const uint32_t rs = ngr * (kGemvGranuleBlocks * kBlockBytes);
                     const uint32_t s = it % NST;
                     if (!mbar_wait_step(&full[s], (it / NST) & 1u, s_err)) { ok = false; *s_err = 1; }
-                    // plain inputs: the projections were published in the first microseconds, fetch them here to keep
-                    // the round trip off the end of the tile; mailbox inputs: the projection itself starts late, so
-                    // it is fetched where it is needed (the first epilogue)
-                    if (git == 6 && q.rank && !t_loaded && (!MB || q.x_slot == kNoSlot)) gather_t();
                     const uint8_t* st = smem + a.off_stage + (size_t)s * kSlotBytes;
                     const uint8_t* row0 = st + (warp * 16 + gq) * rs + t * kBlockBytes;
                     const uint8_t* row1 = row0 + 8 * rs;
@@ -695,7 +730,14 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
 
                 // epilogue: LoRA term (the quad splits the rank), then quad thread 0 stores
                 if (q.rank) {
-                    if (!t_loaded) gather_t();
+                    if (!t_loaded) {
+                        if (helper_t) {
+                            if (!mbar_wait_step(&tready[xb_i], xb_use & 1u, s_err)) { ok = false; *s_err = 1; }
+                            t_loaded = true;
+                        } else {
+                            gather_t();      // mailbox-fed: the projection starts late, fetch it where it is needed
+                        }
+                    }
                     float la = 0.0f, lb2 = 0.0f;
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -801,9 +843,12 @@ extern "C" int lq4_debug_step_timeline(unsigned long long* host_out, size_t coun
 size_t step_plan_smem(StepArgs& a, uint32_t cap_blocks, uint32_t max_rank, uint32_t max_items) {
     if (cap_blocks == 0) return 0;
     uint32_t off = 2 * kMaxStages * 8 + 128;      // ring barriers, the block of zeros, the limb-buffer barriers
-    a.off_t = off;
-    off += align_up(max_rank * 4, 128);
+    a.off_t = off;                                // two t buffers (one per limb buffer)
+    a.t_stride = align_up(max_rank * 4, 128);
+    off += 2 * a.t_stride;
     a.off_tstage = off;                           // the pieces of t = A x before they are added: rank x pieces floats
+    off += align_up(max_items * 4, 128);
+    a.off_cstage = off;                           // the same for the converter warps
     off += align_up(max_items * 4, 128);
     // one limb buffer: limbs (64 B per block), then {scale, sum} (8 B per block)
     a.xbuf_sx = align_up(cap_blocks * 64, 128);

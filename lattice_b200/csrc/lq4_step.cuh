@@ -46,7 +46,7 @@ struct StepArgs {
     uint32_t ngroups;
     uint32_t use_pdl;
     // shared-memory plan (bytes from the dynamic shared memory base)
-    uint32_t off_t, off_tstage, off_stage, nstages;
+    uint32_t off_t, t_stride, off_tstage, off_cstage, off_stage, nstages;
     uint32_t off_xbuf, xbuf_stride, xbuf_sx, nxbuf;   // limb buffers: nxbuf (1 or 2) of xbuf_stride bytes, {scale, sum} at xbuf_sx
     // cross-CTA state of this GPU
     uint32_t* tsync;           // 64-bit launch counter: tags of the partial-sum and projection messages
