@@ -644,6 +644,24 @@ def run_ours(args):
         line["checked_before_timing"] = step_check
 
     if world == 1 and not args.no_aux:
+        # the same STREAM-style copy the measured peak was taken with, on THIS box (the peak in the roofline stays the
+        # recorded one): boxes of the pool differ by several percent, and this says how much of a run's figure that is
+        try:
+            src = torch.empty(1 << 28, dtype=torch.float32, device=dev)
+            dst = torch.empty_like(src)
+            best = 0.0
+            for _ in range(6):
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record()
+                dst.copy_(src)
+                c1.record()
+                torch.cuda.synchronize()
+                best = max(best, 2 * src.numel() * 4 / (c0.elapsed_time(c1) * 1e-3) / 1e9)
+            del src, dst
+            line.setdefault("aux", {})["copy_bandwidth_this_box"] = {"GB/s": best, "vs_recorded_peak": best / hbm_peak,
+                                                                       "how": "torch copy of 1 GiB f32, read + write bytes, best of 6"}
+        except Exception as e:
+            line.setdefault("aux", {})["copy_bandwidth_this_box"] = {"error": repr(e)}
         # the headline step replayed back to back for about two seconds: the rate a decode loop sustains once
         # clocks and power have settled, with the sampled SM clock and the rate binned by clock
         line.setdefault("aux", {})["sustained"] = sustained_run(step_fn, per_step_bytes, sampler, hbm_peak)

@@ -482,7 +482,9 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 *s_err = 1;
             }
             __syncwarp();
-            if (!MB || q.x_slot == kNoSlot) {
+            // the first share's limbs are on the critical path of the launch: the consumers build them themselves
+            // (four times the threads) while these warps start on the second share
+            if (MB ? q.x_slot == kNoSlot : gcount != 1) {      // (only in the instantiation that has the registers for it)
                 uint8_t* xs = smem + a.off_xbuf + (size_t)b * a.xbuf_stride;
                 float2* sx = reinterpret_cast<float2*>(xs + a.xbuf_sx);
                 convert_activations<false, kConvThreads>(a, q, xs, sx, ctid, step_xrange(q, sh.r0, sh.r1), nullptr, 0, s_err);
@@ -562,6 +564,13 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 if (q.x_slot != kNoSlot) {
                     convert_activations<true, kConsumerThreads>(a, q, xs_buf, reinterpret_cast<float2*>(xs_buf + a.xbuf_sx), tid, xr,
                                                                 mb, stag, s_err);
+                    named_bar_sync(kBarConsumers, kConsumerThreads);
+                }
+            }
+            if constexpr (!MB) {
+                if (gcount == 1) {      // the first share (gcount was just advanced)
+                    convert_activations<false, kConsumerThreads>(a, q, xs_buf, reinterpret_cast<float2*>(xs_buf + a.xbuf_sx), tid,
+                                                                 xr, nullptr, 0, s_err);
                     named_bar_sync(kBarConsumers, kConsumerThreads);
                 }
             }
