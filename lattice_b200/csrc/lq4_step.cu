@@ -39,12 +39,13 @@ constexpr int kStepThreads = 384;      // 8 consumer warps + TMA warp + projecti
 constexpr int kConvWarps = 2;          // (ptxas sizes the register budget for 384 threads anyway: these warps are free)
 constexpr int kConvThreads = kConvWarps * 32;
 constexpr int kBarConverters = 2;      // named barrier of the converter warps
-constexpr uint32_t kXBarOffset = 2 * kMaxStages * 8 + 32;      // xready[2], xfree[2] after the ring's barriers and the zero block
+constexpr uint32_t kXBarOffset = 2 * kMaxStages * 8 + 32;      // xready, xfree, tready, tfree [2 each] after the ring's barriers and the zero block
 
 // Development aid, compiled only with -DLQ4_STEP_TIMELINE: nanosecond stamps per CTA and group.
 #ifdef LQ4_STEP_TIMELINE
-constexpr int kTlSlots = 8;            // per (cta, group): 0 group start, 1 prologue done, 2 last stage consumed,
-                                       // 3 last epilogue done, 4 projection start, 5 projection done, 6 first stage consumed
+constexpr int kTlSlots = 12;           // per (cta, group): 0 group start, 1 prologue done, 2 last stage consumed,
+                                       // 3 last epilogue done, 4 projection start, 5 projection done, 6 first stage consumed,
+                                       // 7 converters start, 8 limbs built, 9 projection gathered
 __device__ unsigned long long g_step_timeline[160 * kStepMaxGroups * kTlSlots + 8];
 __device__ __forceinline__ unsigned long long tl_now() {
     unsigned long long t;
@@ -111,6 +112,15 @@ __device__ __forceinline__ void mbox_probe_wait(const unsigned long long* p, uin
     __syncwarp();
 }
 
+// Requests the 128-byte lines of [p, p + bytes) into L2, the lines dealt round-robin to `nt` threads.
+__device__ __forceinline__ void prefetch_l2_range(const char* p, size_t bytes, int ctid, int nt) {
+    if (bytes == 0) return;
+    const char* first = reinterpret_cast<const char*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)127);
+    const char* end = p + bytes;
+    for (const char* l = first + (size_t)ctid * 128; l < end; l += (size_t)nt * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(l));
+}
+
 // mbarrier wait that also gives up as soon as another wait of this CTA has failed.
 __device__ __forceinline__ bool mbar_wait_step(uint64_t* bar, uint32_t parity, volatile int* err) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -125,7 +135,7 @@ __device__ __forceinline__ bool mbar_wait_step(uint64_t* bar, uint32_t parity, v
 // This CTA's share of group g: its problem and its range of work units, or nothing.
 struct Share {
     uint32_t pi;
-    uint64_t r0, r1;
+    uint32_t r0, r1;      // work units tile * kg + granule: 32 bits (the host refuses problems beyond that)
     bool any;
 };
 __device__ __forceinline__ Share step_share(const StepArgs& a, uint32_t g, uint32_t cta) {
@@ -134,10 +144,9 @@ __device__ __forceinline__ Share step_share(const StepArgs& a, uint32_t g, uint3
     for (uint32_t i = a.group_begin[g]; i < a.group_begin[g + 1]; ++i) {
         const StepProblem& q = a.p[i];
         if (cta >= q.cta_begin && cta < q.cta_begin + q.cta_count) {
-            const uint64_t total = (uint64_t)q.tiles * q.kg;
             s.pi = i;
-            s.r0 = range_begin(cta - q.cta_begin, total, q.cta_count);
-            s.r1 = range_begin(cta - q.cta_begin + 1, total, q.cta_count);
+            s.r0 = step_share_begin_t<uint32_t>(cta - q.cta_begin, q.tiles, q.kg, q.charge, q.cta_count);
+            s.r1 = step_share_begin_t<uint32_t>(cta - q.cta_begin + 1, q.tiles, q.kg, q.charge, q.cta_count);
             s.any = s.r1 > s.r0;
             break;
         }
@@ -203,13 +212,22 @@ __device__ __forceinline__ void prologue_from_mailbox(const StepArgs& a, uint8_t
     }
 }
 
+// The last CTA that works on `tile`, for the CTA that owns the tile's first granule: walks on from this CTA
+// (the next one or two, as a rule).  Runs once per finished tile.  Measured: as a call it keeps its divisions out
+// of the stage loop's register allocation (1 us per step on the plain-input instantiation); the mailbox-fed
+// instantiation, which spills either way, is quicker with it inlined.
+__device__ __forceinline__ uint32_t tile_last_cta_inline(const StepProblem& q, uint32_t tile) {
+    return q.cta_begin + step_share_last_t<uint32_t>(blockIdx.x - q.cta_begin, (tile + 1) * q.kg - 1, q.tiles, q.kg, q.charge, q.cta_count);
+}
+__device__ __noinline__ uint32_t tile_last_cta_call(const StepProblem& q, uint32_t tile) { return tile_last_cta_inline(q, tile); }
+
 // First block and octet ranges of the k range(s) a share [r0, r1) of work units touches: the whole row when the
 // share spans a tile, else up to two pieces (the share may wrap from the end of one tile into the next).
 struct XRange {
     uint32_t a0, na, b0, noct;     // octets: piece a = [a0, a0 + na), piece b = [b0, b0 + noct - na)
     uint32_t base_blk;             // first block of piece a: the limb buffer is indexed from here, wrapping at k / 32
 };
-__device__ __forceinline__ XRange step_xrange(const StepProblem& q, uint64_t r0, uint64_t r1) {
+__device__ __forceinline__ XRange step_xrange(const StepProblem& q, uint32_t r0, uint32_t r1) {
     const uint32_t opg = kGemvGranuleBlocks * 4;              // octets (8 activations) per granule
     uint32_t a0 = 0, a1 = q.k / 8, b0 = 0, b1 = 0;
     if (r1 - r0 < q.kg) {
@@ -220,6 +238,82 @@ __device__ __forceinline__ XRange step_xrange(const StepProblem& q, uint64_t r0,
     XRange x;
     x.a0 = a0; x.na = a1 - a0; x.b0 = b0; x.noct = x.na + (b1 - b0); x.base_blk = a0 / 4;
     return x;
+}
+
+// One thread builds the limbs of a whole Q4 block (32 activations): no exchange between lanes.  The converter
+// warps use this form: their quad shuffles, issued beside the consumers' shared-memory loads, took up to four
+// times as long as alone (measured with device time stamps), and a conversion that is late stops the consumers.
+// Same arithmetic and the same order of additions as store_limbs, so both give the same bytes.
+__device__ __forceinline__ void store_limbs_block(uint8_t* xs, float2* sx, uint32_t blk, const float (&v)[32]) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    float so[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float* w = v + 8 * j;
+        so[j] = ((w[0] + w[1]) + (w[2] + w[3])) + ((w[4] + w[5]) + (w[6] + w[7]));
+    }
+    const float sum = (so[0] + so[1]) + (so[2] + so[3]);
+    uint32_t l0[8], l1[8];
+    float scale = 1.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = v[8 * j + e];
+        const Limbs8 l = make_limbs8(w, amax);
+        l0[2 * j] = l.l0a; l0[2 * j + 1] = l.l0b;
+        l1[2 * j] = l.l1a; l1[2 * j + 1] = l.l1b;
+        scale = l.scale;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)blk * 64);
+    dst[0] = make_uint4(l0[0], l0[1], l0[2], l0[3]);
+    dst[1] = make_uint4(l0[4], l0[5], l0[6], l0[7]);
+    dst[2] = make_uint4(l1[0], l1[1], l1[2], l1[3]);
+    dst[3] = make_uint4(l1[4], l1[5], l1[6], l1[7]);
+    sx[blk] = make_float2(scale, sum);
+}
+
+// The converter warps' conversion of a share's k range(s) from plain memory, a block per thread and pass.
+template <int NT>
+__device__ __forceinline__ void convert_blocks_plain(const StepProblem& q, uint8_t* xs, float2* sx, int ctid, const XRange& xr) {
+    const uint32_t nblk = xr.noct / 4, nba = xr.na / 4, a0b = xr.a0 / 4, b0b = xr.b0 / 4;      // ranges are whole granules
+    constexpr int KB = 2;
+#pragma unroll 1
+    for (uint32_t i0 = 0; i0 < nblk; i0 += KB * NT) {
+        float v[KB][32];
+#pragma unroll
+        for (int u = 0; u < KB; ++u) {
+            const uint32_t i = i0 + u * NT + ctid;
+            const uint32_t o = i < nba ? a0b + i : b0b + (i - nba);
+            if (i < nblk) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) load8(q.x, q.x_dtype, (size_t)o * 32 + 8 * j, *reinterpret_cast<float(*)[8]>(&v[u][8 * j]));
+            }
+        }
+        if (q.x_mul) {
+#pragma unroll
+            for (int u = 0; u < KB; ++u) {
+                const uint32_t i = i0 + u * NT + ctid;
+                const uint32_t o = i < nba ? a0b + i : b0b + (i - nba);
+                if (i < nblk) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float up[8];
+                        load8(q.x_mul, LQ4_DTYPE_F32, (size_t)o * 32 + 8 * j, up);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) v[u][8 * j + e] = silu_mul(v[u][8 * j + e], up[e]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < KB; ++u) {
+            const uint32_t i = i0 + u * NT + ctid;
+            if (i < nblk) store_limbs_block(xs, sx, i, v[u]);
+        }
+    }
 }
 
 // NT threads turn the k range(s) of a share into two int8 limbs per activation, into the limb buffer (xs, sx).
@@ -402,6 +496,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
     uint64_t* xready = reinterpret_cast<uint64_t*>(smem + kXBarOffset);     // limb buffer b holds the group's limbs
     uint64_t* xfree = xready + 2;                                           // the consumers are done with limb buffer b
     uint64_t* tready = xfree + 2;                                           // t = A x of the group is in t buffer b
+    uint64_t* tfree = tready + 2;                                           // the consumers are done with t buffer b
     if (tid == 0) {
         for (uint32_t s = 0; s < NST; ++s) {
             mbar_init(&full[s], 1);
@@ -411,6 +506,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             mbar_init(&xready[b], kConvWarps);
             mbar_init(&xfree[b], 8);
             mbar_init(&tready[b], kConvWarps);
+            mbar_init(&tfree[b], 8);
         }
         s_err_mem = 0;
         for (int i = 0; i < 8; ++i) reinterpret_cast<uint32_t*>(smem + kZeroOffset)[i] = 0;
@@ -431,11 +527,11 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             const Share sh = step_share(a, g, blockIdx.x);
             if (!sh.any) continue;
             const StepProblem& q = a.p[sh.pi];
-            for (uint64_t pos = sh.r0; pos < sh.r1 && ok;) {
-                const uint32_t tile = (uint32_t)(pos / q.kg);
-                const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
-                const uint64_t left = sh.r1 - pos;
-                const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
+            for (uint32_t pos = sh.r0; pos < sh.r1 && ok;) {
+                const uint32_t tile = pos / q.kg;
+                const uint32_t g0 = pos - tile * q.kg;
+                const uint32_t left = sh.r1 - pos;
+                const uint32_t g1 = q.kg - g0 < left ? q.kg : g0 + left;
                 for (uint32_t gs = g0; gs < g1; ++it) {
                     const uint32_t ngr = stage_granules(g1 - gs);
                     const uint32_t s = it % NST;
@@ -477,23 +573,44 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             const StepProblem& q = a.p[sh.pi];
             const uint32_t b = gcount % a.nxbuf, use = gcount / a.nxbuf;
             ++gcount;
+            const bool convert_here = MB ? q.x_slot == kNoSlot : gcount != 1;
+            const XRange xr = step_xrange(q, sh.r0, sh.r1);
+            if (convert_here) {
+                // Pull the share's activations towards L2 while waiting for the limb buffer: a load that has to go
+                // to memory queues behind the weight stream (several microseconds per pass when the ring is being
+                // refilled), and the passes of the conversion run one after the other.
+                const uint32_t ob = q.x_dtype == LQ4_DTYPE_BF16 ? 16u : 32u;      // bytes per octet
+                prefetch_l2_range(static_cast<const char*>(q.x) + (size_t)xr.a0 * ob, (size_t)xr.na * ob, ctid, kConvThreads);
+                prefetch_l2_range(static_cast<const char*>(q.x) + (size_t)xr.b0 * ob, (size_t)(xr.noct - xr.na) * ob, ctid, kConvThreads);
+                if (q.x_mul) {
+                    prefetch_l2_range(reinterpret_cast<const char*>(q.x_mul) + (size_t)xr.a0 * 32, (size_t)xr.na * 32, ctid, kConvThreads);
+                    prefetch_l2_range(reinterpret_cast<const char*>(q.x_mul) + (size_t)xr.b0 * 32, (size_t)(xr.noct - xr.na) * 32, ctid, kConvThreads);
+                }
+            }
             if (lane == 0 && !mbar_wait_step(&xfree[b], (use & 1u) ^ 1u, s_err)) {
                 atomicOr(a.status, kDevErrBarrierTimeout);
                 *s_err = 1;
             }
             __syncwarp();
+            if (ctid == 0) TL_STAMP(g, 7);
             // the first share's limbs are on the critical path of the launch: the consumers build them themselves
             // (four times the threads) while these warps start on the second share
-            if (MB ? q.x_slot == kNoSlot : gcount != 1) {      // (only in the instantiation that has the registers for it)
+            if (convert_here) {                                // (only in the instantiation that has the registers for it)
                 uint8_t* xs = smem + a.off_xbuf + (size_t)b * a.xbuf_stride;
                 float2* sx = reinterpret_cast<float2*>(xs + a.xbuf_sx);
-                convert_activations<false, kConvThreads>(a, q, xs, sx, ctid, step_xrange(q, sh.r0, sh.r1), nullptr, 0, s_err);
+                convert_blocks_plain<kConvThreads>(q, xs, sx, ctid, xr);
             }
             __syncwarp();
+            if (ctid == 0) TL_STAMP(g, 8);
             if (lane == 0) mbar_arrive(&xready[b]);
             // ... and gather the adapter projection t = A x of the same share's problem (published by the
             // projection warps of all CTAs in the first microseconds when the input is plain), so that the
             // consumers find it in shared memory at their first epilogue instead of fetching it themselves
+            if (lane == 0 && !mbar_wait_step(&tfree[b], (use & 1u) ^ 1u, s_err)) {
+                atomicOr(a.status, kDevErrBarrierTimeout);
+                *s_err = 1;
+            }
+            __syncwarp();
             if (q.rank && (!MB || q.x_slot == kNoSlot)) {
                 float* tb = reinterpret_cast<float*>(smem + a.off_t + (size_t)b * a.t_stride);
                 const uint32_t nmsg = q.rank * q.tsplit;
@@ -523,6 +640,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 named_bar_sync(kBarConverters, kConvThreads);      // the staging area is free for the next group
             }
             __syncwarp();
+            if (ctid == 0) TL_STAMP(g, 9);
             if (lane == 0) mbar_arrive(&tready[b]);
         }
     } else {
@@ -546,7 +664,6 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             const Share sh = step_share(a, g, blockIdx.x);
             if (!sh.any) continue;                                 // the same for every thread of the CTA
             const StepProblem& q = a.p[sh.pi];
-            const uint64_t total = (uint64_t)q.tiles * q.kg;
             // everyone is done with the previous group's limbs and projection before they are replaced
             named_bar_sync(kBarConsumers, kConsumerThreads);
             if (tid == 0) TL_STAMP(g, 0);
@@ -608,11 +725,11 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 t_loaded = true;
             };
             uint32_t git = 0;                                      // stages of this group consumed so far
-            for (uint64_t pos = sh.r0; pos < sh.r1;) {
-                const uint32_t tile = (uint32_t)(pos / q.kg);
-                const uint32_t g0 = (uint32_t)(pos - (uint64_t)tile * q.kg);
-                const uint64_t left = sh.r1 - pos;
-                const uint32_t g1 = (uint64_t)(q.kg - g0) < left ? q.kg : (uint32_t)(g0 + left);
+            for (uint32_t pos = sh.r0; pos < sh.r1;) {
+                const uint32_t tile = pos / q.kg;
+                const uint32_t g0 = pos - tile * q.kg;
+                const uint32_t left = sh.r1 - pos;
+                const uint32_t g1 = q.kg - g0 < left ? q.kg : g0 + left;
                 pos += g1 - g0;
 
                 float acc0 = 0.0f, acc1 = 0.0f;
@@ -670,6 +787,12 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     if (tid == 0 && git == 0) TL_STAMP(g, 6);
                 }
                 if (tid == 0) TL_STAMP(g, 2);
+                if (pos >= sh.r1) {
+                    // the share's last stage is consumed: the limb buffer may be refilled for a later group while
+                    // this tile is finished (the fix-up waits for the other CTAs' partial sums)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&xfree[xb_i]);
+                }
 
                 // each thread of a quad covered blocks = t (mod 4): add the four
                 float v0 = acc0, v1 = acc1;
@@ -701,7 +824,8 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 }
                 if (!complete) {
                     // finisher: add the contributors' messages in CTA order (warp-uniform loop, bounded)
-                    const uint32_t c_last = q.cta_begin + owner_of((uint64_t)(tile + 1) * q.kg - 1, total, q.cta_count);
+                    // the tile's last CTA: walk on from this CTA (the next one or two, as a rule)
+                    const uint32_t c_last = MB ? tile_last_cta_inline(q, tile) : tile_last_cta_call(q, tile);
                     constexpr int CB = 4;
                     bool good = true;
                     for (uint32_t c0 = blockIdx.x + 1; c0 <= c_last && good; c0 += CB) {
@@ -790,9 +914,9 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                 }
                 if (tid == 0) TL_STAMP(g, 3);
             }
-            // the limb buffer may be refilled for a later group
+            // the projection buffer may be refilled for a later group
             __syncwarp();
-            if (lane == 0) mbar_arrive(&xfree[xb_i]);
+            if (lane == 0) mbar_arrive(&tfree[xb_i]);
         }
         if (!ok) {
             if (lane == 0) atomicOr(a.status, kDevErrBarrierTimeout);

@@ -5,6 +5,7 @@
 #include <cuda.h>
 
 #include "lq4_kernels.cuh"
+#include "lq4_step_share.h"
 
 namespace lq4 {
 
@@ -35,7 +36,8 @@ struct StepProblem {
     int32_t x_dtype;
     uint32_t cta_begin, cta_count;   // CTAs [cta_begin, cta_begin + cta_count) of the grid work on this problem in its group
     uint32_t dot_begin;        // first projection work item of this problem within its group
-    uint32_t pad_;
+    uint32_t charge;           // work units a CTA is charged for finishing a tile (see step_share_begin)
+    uint32_t pad_[2];
 };
 
 struct StepArgs {

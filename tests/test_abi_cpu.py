@@ -3,6 +3,7 @@ and rejects bad arguments before touching the device."""
 import ctypes as C
 import os
 import re
+import subprocess
 
 import numpy as np
 import pytest
@@ -234,6 +235,62 @@ int main() {
                    check=True)
     res = subprocess.run([str(exe)], capture_output=True, text=True)
     assert res.returncode == 0 and res.stdout.strip() == "0"
+
+
+def test_step_shares_cover_every_work_unit_once(tmp_path):
+    """The cut of a projection's work units into CTA shares (lq4_step_share.h): contiguous, monotone, complete,
+    and the owner function agrees with the cuts - for every charge, also where shares come out empty."""
+    src = tmp_path / "share.cpp"
+    src.write_text('''
+#include "lq4_step_share.h"
+#include <cstdio>
+#include <initializer_list>
+using namespace lq4;
+int main() {
+    long bad = 0, checks = 0;
+    for (uint32_t tiles : {1u, 2u, 3u, 8u, 40u, 136u})
+        for (uint32_t kg : {1u, 2u, 5u, 40u, 136u})
+            for (uint32_t charge : {0u, 1u, 3u, 5u, 9u})
+                for (uint32_t count = 1; count <= 148 && count <= tiles * kg; count += (count < 12 ? 1 : 7)) {
+                    const uint64_t total = (uint64_t)tiles * kg;
+                    bad += step_share_begin(0, tiles, kg, charge, count) != 0;
+                    bad += step_share_begin(count, tiles, kg, charge, count) != total;
+                    for (uint32_t c = 0; c < count; ++c)
+                        bad += step_share_begin(c, tiles, kg, charge, count) > step_share_begin(c + 1, tiles, kg, charge, count);
+                    for (uint64_t p = 0; p < total; ++p, ++checks) {
+                        const uint32_t o = step_share_owner(p, tiles, kg, charge, count);
+                        bad += !(o < count && step_share_begin(o, tiles, kg, charge, count) <= p &&
+                                 p < step_share_begin(o + 1, tiles, kg, charge, count));
+                    }
+                    if (step_share_fits32(tiles, kg, charge, count))
+                        for (uint32_t c = 0; c <= count; ++c)
+                            bad += step_share_begin_t<uint32_t>(c, tiles, kg, charge, count) != step_share_begin(c, tiles, kg, charge, count);
+                    for (uint32_t tile = 0; tile < tiles; ++tile) {      // the walk from a tile's first CTA to its last
+                        const uint64_t first = (uint64_t)tile * kg, last = first + kg - 1;
+                        const uint32_t f = step_share_owner(first, tiles, kg, charge, count);
+                        bad += step_share_last_t<uint64_t>(f, last, tiles, kg, charge, count) != step_share_owner(last, tiles, kg, charge, count);
+                        bad += step_share_last_t<uint32_t>(f, (uint32_t)last, tiles, kg, charge, count) != step_share_owner(last, tiles, kg, charge, count);
+                    }
+                    if (charge == 0)      // no charge: the even cut of the other decode kernels
+                        for (uint32_t c = 0; c <= count; ++c) bad += step_share_begin(c, tiles, kg, 0, count) != c * total / count;
+                }
+    // a CTA that starts a tile gets `charge` units less than one that does not (17408 -> 5120: 40 tiles x 136)
+    uint64_t with_start = 0, without = 0;
+    for (uint32_t c = 0; c < 61; ++c) {
+        const uint64_t r0 = step_share_begin(c, 40, 136, 5, 61), r1 = step_share_begin(c + 1, 40, 136, 5, 61);
+        const bool starts = (r0 % 136 == 0) || (r0 / 136 != (r1 - 1) / 136);
+        (starts ? with_start : without) = r1 - r0;
+    }
+    bad += !(without > with_start && without - with_start <= 6);
+    std::printf("%ld %ld\\n", bad, checks);
+    return bad != 0;
+}
+''')
+    exe = tmp_path / "share"
+    subprocess.run(["g++", "-std=c++17", "-O2", "-I", os.path.join(ROOT, "lattice_b200", "csrc"), str(src), "-o", str(exe)],
+                   check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0 and res.stdout.split()[0] == "0", res.stdout
 
 
 def test_step_sharded_and_option_entry_points_validate_without_a_device(L):
