@@ -383,7 +383,9 @@ def run_ours(args):
                 b0 = li * S + full_offs[si] + layers[li][si]["n0"]
                 return pay[b0: b0 + nls[si]]
 
-            def build(x_ext):
+            def build(x_ext, host=False, y_host=None):
+                # host: lq4_decode_step_host (x_ext may be pinned host memory); y_host: a pinned [layers * S] buffer
+                # the outputs are stored to directly (one GPU, independent sets: nothing reads them on the device)
                 groups = []
                 for li, projs in enumerate(layers):
                     grp = []
@@ -392,11 +394,16 @@ def run_ours(args):
                             x = x_ext[p["k"]]
                         else:
                             x = row_of(li - 1, 3) if p["k"] == 5120 else row_of(li - 1, 2)
-                        grp.append((x, p["qw"], p["lora"], y_of(li, si)))
+                        y = y_of(li, si)
+                        if y_host is not None:
+                            y = y_host[li * S + full_offs[si]: li * S + full_offs[si] + full_n[si]]
+                        grp.append((x, p["qw"], p["lora"], y))
                     groups.append(grp)
                 if flat:                          # nothing links the sets: the caller may as well hand them over as ONE group
                     groups = [[pr for grp in groups for pr in grp]]
-                return be.prepare_step(groups, sbuf, gathered=[pay[li * S:(li + 1) * S] for li in range(args.layers)])
+                if y_host is not None:
+                    return be.prepare_step(groups, host=True)
+                return be.prepare_step(groups, sbuf, gathered=[pay[li * S:(li + 1) * S] for li in range(args.layers)], host=host)
 
             run = build(xs)
 
@@ -458,10 +465,31 @@ def run_ours(args):
     batched = world == 1 and not step_mode
     if step_mode:
         # one pinned buffer in (the step's external inputs), one launch, one pinned buffer out (every set's rows)
+        # The public call is lq4_decode_step_host: the pinned inputs are staged in by a kernel chained in front of
+        # the step kernel, and (one GPU, independent sets) the step kernel stores the results straight into the
+        # pinned output buffer, so no copy-engine operation is left in the step.  Chained sets and N-sharded steps
+        # keep their outputs in the step buffer (later sets and the peers read them there) and copy them out.
         hx_cat = torch.randn(5120 + 17408).pin_memory()
-        dx_cat = torch.empty(5120 + 17408, device=dev)
         hy_step = torch.empty(args.layers * S).pin_memory()
-        e2e_step_call = build_step({5120: dx_cat[:5120].view(1, -1), 17408: dx_cat[5120:].view(1, -1)})
+        e2e_host_out = world == 1 and not args.chained
+        hx_views = {5120: hx_cat[:5120], 17408: hx_cat[5120:]}
+        e2e_step_call = build_step(hx_views, host=True, y_host=hy_step if e2e_host_out else None)
+        # checked once: the host call gives the bits of the device-buffer call on the same inputs
+        dx_chk = hx_cat.to(dev)
+        chk_call = build_step({5120: dx_chk[:5120].view(1, -1), 17408: dx_chk[5120:].view(1, -1)})
+        chk_call()
+        torch.cuda.synchronize()
+        want = pay.clone()
+        hy_step.fill_(float("nan"))
+        e2e_step_call()
+        if not e2e_host_out:
+            hy_step.copy_(pay, non_blocking=True)
+        torch.cuda.synchronize()
+        be.check_device_status()
+        if not torch.equal(want.cpu(), hy_step):
+            raise SystemExit("the host-buffer step differs from the device-buffer step")
+        step()                                    # the step buffer holds the timed variant's results again
+        torch.cuda.synchronize()
     if batched:
         xw = 5120 + 17408
         hx_all = torch.randn((args.layers, m, xw)).pin_memory()
@@ -486,9 +514,9 @@ def run_ours(args):
     def e2e_body():
         # host activations in (pinned -> device), the public call per set, host results out
         if step_mode:
-            dx_cat.copy_(hx_cat, non_blocking=True)
-            e2e_step_call()
-            hy_step.copy_(pay, non_blocking=True)
+            e2e_step_call()                       # reads the pinned inputs; writes the pinned outputs itself ...
+            if not e2e_host_out:
+                hy_step.copy_(pay, non_blocking=True)      # ... or leaves them in the step buffer
             return
         if batched:
             dx_all.copy_(hx_all, non_blocking=True)
@@ -520,7 +548,10 @@ def run_ours(args):
             with torch.cuda.graph(e2e_graph, stream=side):
                 e2e_body()
             e2e_info["mode"] = ("cuda-graph replay of the step's copies and kernels" +
-                                (" (one copy in, one copy out per step)" if batched or step_mode else "") + ", one wait per step")
+                                (" (one copy in, one copy out per step)" if batched else "") +
+                                (" (lq4_decode_step_host: stage-in kernel + step kernel" +
+                                 (", results stored to pinned host memory by the step kernel)" if e2e_host_out else ", one copy out)")
+                                 if step_mode else "") + ", one wait per step")
         except Exception as e:
             e2e_graph = None
             e2e_info["mode"] = "plain calls, one wait per step (graph capture failed: %r)" % (e,)

@@ -225,6 +225,20 @@ typedef struct {
 lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
                            void* stream);
 
+/* lq4_decode_step with HOST activations and outputs, the step-level counterpart of lq4_linear_host.  Every
+ * input that does not lie in the step buffer's payload is first copied into the library's workspace by a
+ * small stage-in kernel chained in front of the step kernel (programmatic launch: the step kernel's weight
+ * stream starts while the copy runs), so it may live in page-locked host memory that the device can address
+ * (cudaHostAlloc / cudaHostRegister under unified addressing; a device pointer works too).  Outputs are
+ * stored where y points by the step kernel itself, so they may live in such host memory as well: the
+ * results of an early group cross PCIe while the later groups compute, and no copy engine is involved in
+ * either direction (measured on B200: a copy node in front of and behind the kernel costs 14 us and 10 us of
+ * a 136 us step).  The host must not touch the inputs before the launch has completed, and reads the
+ * outputs after it has.  With world > 1 the outputs must lie in the step buffer as for lq4_decode_step.
+ * No counterpart in the reference, whose unified memory needs no copies. */
+lq4_status lq4_decode_step_host(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
+                                void* stream);
+
 /* ---- peer buffers for the fused all-gather ------------------------------------ */
 #define LQ4_PEER_HANDLE_BYTES 64
 /* Allocates (cudaMalloc, zero-filled) a buffer other processes on the same node can map:

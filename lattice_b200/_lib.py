@@ -90,6 +90,7 @@ SIGNATURES = {
     "lq4_linear_group": (C.c_int32, [C.c_void_p, C.POINTER(LinearArgs), C.c_uint32, C.c_void_p]),
     "lq4_step_buf_create": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p)]),
     "lq4_decode_step": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(StepDesc), C.c_void_p]),
+    "lq4_decode_step_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(StepDesc), C.c_void_p]),
     "lq4_peer_buf_create": (C.c_int32, [C.c_uint64, C.POINTER(C.c_void_p)]),
     "lq4_peer_buf_free": (None, [C.c_void_p]),
     "lq4_peer_buf_base": (C.c_void_p, [C.c_void_p]),

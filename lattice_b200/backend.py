@@ -129,9 +129,9 @@ class PreparedGroup:
 class PreparedStep:
     """Argument blocks of one ``lq4_decode_step`` call, reusable while its tensors live."""
 
-    def __init__(self, backend: "CudaQ4Backend", garr, ngroups: int, desc, keep):
+    def __init__(self, backend: "CudaQ4Backend", garr, ngroups: int, desc, keep, host: bool = False):
         self._be, self._garr, self._ngroups, self._desc, self._keep = backend, garr, ngroups, desc, keep
-        self._fn = _lib.lib().lq4_decode_step
+        self._fn = _lib.lib().lq4_decode_step_host if host else _lib.lib().lq4_decode_step
 
     def __call__(self) -> None:
         check(self._fn(self._be._ctx, C.cast(self._garr, C.c_void_p), self._ngroups,
@@ -561,13 +561,16 @@ class CudaQ4Backend:
         keep += [gather, wait_gather]
         return PreparedGroup(self, arr, n_prob, ys, keep)
 
-    def prepare_step(self, groups, step_buffer=None, gathered=None) -> "PreparedStep":
+    def prepare_step(self, groups, step_buffer=None, gathered=None, host: bool = False) -> "PreparedStep":
         """Builds the argument blocks of one ``lq4_decode_step`` call; calling the result launches it.
 
         ``groups`` is a list of groups, each a list of ``(x, qw, lora, y)`` with ``x`` ``[1, k]`` or ``[k]`` and
         ``y`` ``[n]`` (or ``[1, n]``) device tensors.  A later group's ``x`` may be a slice of
         ``step_buffer.payload`` where earlier groups' ``y`` slices lie.  ``gathered`` lists the payload slices
-        that must be complete on this rank when the launch completes."""
+        that must be complete on this rank when the launch completes.  ``host=True`` makes the call
+        ``lq4_decode_step_host``: inputs and outputs may then be pinned host tensors (``pin_memory=True``); the
+        inputs are staged in by a kernel chained in front of the step kernel, the outputs are stored by the step
+        kernel itself, and the caller synchronises before it reads them."""
         from ._lib import StepDesc, StepGroup, StepRange
         keep, garr = [], (StepGroup * max(len(groups), 1))()
         for gi, grp in enumerate(groups):
@@ -575,7 +578,8 @@ class CudaQ4Backend:
             for i, (x, qw, lora, y) in enumerate(grp):
                 k = x.numel()
                 self._require_k("decode_step", k)
-                assert x.is_cuda and y.is_cuda and y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
+                assert (x.is_cuda or (host and x.is_pinned())) and (y.is_cuda or (host and y.is_pinned()))
+                assert y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous()
                 assert k == qw.k and y.numel() == qw.n
                 arr[i] = LinearArgs(x.data_ptr(), self._dtype_of(x), 1, qw.n, k, qw.payload_ptr, y.data_ptr(), 0,
                                     C.pointer(lora) if lora is not None else None, None, _lib.PATH_AUTO, None, None)
@@ -590,7 +594,7 @@ class CudaQ4Backend:
                 rng[i] = StepRange(t.data_ptr(), t.numel())
             desc = StepDesc(C.pointer(step_buffer.desc), C.cast(rng, C.c_void_p).value, len(gathered or []))
             keep += [rng, step_buffer, gathered]
-        return PreparedStep(self, garr, len(groups), desc, keep)
+        return PreparedStep(self, garr, len(groups), desc, keep, host)
 
     def gather_wait(self, gather: GatherDesc) -> None:
         """Stream-ordered wait until every peer's results of the gathered launches issued so far are here."""

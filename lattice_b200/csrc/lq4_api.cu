@@ -969,14 +969,34 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
 
 }  // namespace
 
-lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
-                           void* stream) {
-    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
-    if (ngroups == 0) return LQ4_OK;
-    if (!groups) return fail(LQ4_ERR_NULL, "groups is NULL");
+namespace {
+
+// Copies up to kStepMaxProblems segments (whole 16-byte words) with plain loads and stores: the sources may be
+// page-locked host memory.  The dependent launch (the step kernel) is released at once; it waits for this grid
+// to complete before it reads an activation.
+struct StageArgs {
+    const uint4* src[kStepMaxProblems];
+    uint4* dst[kStepMaxProblems];
+    uint32_t words[kStepMaxProblems];
+    uint32_t count;
+};
+__global__ void __launch_bounds__(256) stage_in_kernel(const __grid_constant__ StageArgs a) {
+    pdl_launch_dependents();
+    const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nt = gridDim.x * blockDim.x;
+    for (uint32_t sgi = 0; sgi < a.count; ++sgi) {
+        const uint4* src = a.src[sgi];
+        uint4* dst = a.dst[sgi];
+        for (uint32_t i = tid; i < a.words[sgi]; i += nt) {
+            uint4 v;
+            // host memory can change between launches: a load that no cache of this GPU keeps
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i) : "memory");
+            dst[i] = v;
+        }
+    }
+}
+
+lq4_status collect_step(const lq4_step_group* groups, uint32_t ngroups, StepSpec* specs, uint32_t* gsize) {
     if (ngroups > (uint32_t)kStepMaxGroups) return fail(LQ4_ERR_NOSPACE, "a step holds at most 8 groups");
-    StepSpec specs[kStepMaxProblems];
-    uint32_t gsize[kStepMaxGroups];
     uint32_t np = 0;
     for (uint32_t g = 0; g < ngroups; ++g) {
         if (groups[g].count && !groups[g].args) return fail(LQ4_ERR_NULL, "a group's args is NULL");
@@ -985,7 +1005,82 @@ lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t 
         for (uint32_t i = 0; i < groups[g].count; ++i) { specs[np].a = groups[g].args[i]; specs[np].x_mul = nullptr; ++np; }
         gsize[g] = groups[g].count;
     }
+    return LQ4_OK;
+}
+
+}  // namespace
+
+lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
+                           void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (ngroups == 0) return LQ4_OK;
+    if (!groups) return fail(LQ4_ERR_NULL, "groups is NULL");
+    StepSpec specs[kStepMaxProblems];
+    uint32_t gsize[kStepMaxGroups];
+    lq4_status st;
+    if ((st = collect_step(groups, ngroups, specs, gsize))) return st;
     return step_core(ctx, specs, gsize, ngroups, step, (cudaStream_t)stream);
+}
+
+lq4_status lq4_decode_step_host(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
+                                void* stream) {
+    if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
+    if (ngroups == 0) return LQ4_OK;
+    if (!groups) return fail(LQ4_ERR_NULL, "groups is NULL");
+    StepSpec specs[kStepMaxProblems];
+    uint32_t gsize[kStepMaxGroups];
+    lq4_status st;
+    if ((st = collect_step(groups, ngroups, specs, gsize))) return st;
+    uint32_t np = 0;
+    for (uint32_t g = 0; g < ngroups; ++g) np += gsize[g];
+    cudaStream_t s = (cudaStream_t)stream;
+
+    // the inputs outside the step buffer, each distinct (pointer, bytes) once
+    const char* pay0 = nullptr;
+    const char* pay1 = nullptr;
+    if (step && step->bufs && step->bufs->rank < LQ4_MAX_PEERS && step->bufs->bases[step->bufs->rank]) {
+        lq4_peer_buf info{};
+        char* base = static_cast<char*>(step->bufs->bases[step->bufs->rank]);
+        if (peer_buf_info(base, &info)) { pay0 = base + 256; pay1 = pay0 + info.payload_bytes; }
+    }
+    StageArgs sg{};
+    size_t off[kStepMaxProblems], total = 0;
+    int seg_of[kStepMaxProblems];
+    for (uint32_t i = 0; i < np; ++i) {
+        const lq4_linear_args& a = specs[i].a;
+        seg_of[i] = -1;
+        if (a.m == 0 || a.n == 0) continue;
+        if (!a.x) return fail(LQ4_ERR_NULL, "x must be non-NULL");
+        if (!aligned(a.x, 16) || a.k % 32 != 0) return fail(LQ4_ERR_ALIGN, "a step needs 16-byte aligned x and k % 32 == 0");
+        const size_t bytes = (size_t)a.k * (a.x_dtype == LQ4_DTYPE_BF16 ? 2 : 4);
+        const char* x0 = static_cast<const char*>(a.x);
+        if (pay0 && x0 >= pay0 && x0 + bytes <= pay1) continue;      // written by an earlier group: read through the mailbox
+        for (uint32_t j = 0; j < sg.count; ++j)
+            if (sg.src[j] == reinterpret_cast<const uint4*>(a.x) && sg.words[j] == bytes / 16) seg_of[i] = (int)j;
+        if (seg_of[i] < 0) {
+            seg_of[i] = (int)sg.count;
+            sg.src[sg.count] = reinterpret_cast<const uint4*>(a.x);
+            sg.words[sg.count] = (uint32_t)(bytes / 16);
+            off[sg.count] = total;
+            total += (bytes + 255) / 256 * 256;
+            ++sg.count;
+        }
+    }
+    if (sg.count) {
+        if ((st = ensure(ctx, ctx->hx, total, false, s))) return st;
+        uint64_t words = 0;
+        for (uint32_t j = 0; j < sg.count; ++j) {
+            sg.dst[j] = reinterpret_cast<uint4*>(static_cast<char*>(ctx->hx.p) + off[j]);
+            words += sg.words[j];
+        }
+        for (uint32_t i = 0; i < np; ++i)
+            if (seg_of[i] >= 0) specs[i].a.x = sg.dst[seg_of[i]];
+        const uint64_t blocks = (words + 255) / 256;
+        stage_in_kernel<<<(unsigned)(blocks < 64 ? blocks : 64), 256, 0, s>>>(sg);
+        LQ4_CUDA(cudaGetLastError());
+        ctx->launches += 1;
+    }
+    return step_core(ctx, specs, gsize, ngroups, step, s);
 }
 
 lq4_status lq4_linear_host(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {

@@ -295,6 +295,7 @@ int main() {
 
 def test_step_sharded_and_option_entry_points_validate_without_a_device(L):
     assert L.lq4_decode_step(None, None, 0, None, None) == _lib.ERR_NULL
+    assert L.lq4_decode_step_host(None, None, 0, None, None) == _lib.ERR_NULL
     assert L.lq4_linear_sharded(None, None, None, None) == _lib.ERR_NULL
     assert L.lq4_ctx_set_option(None, _lib.OPT_PDL, 0) == _lib.ERR_NULL
     assert L.lq4_noalloc_check is not None

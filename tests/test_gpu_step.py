@@ -172,3 +172,63 @@ def test_step_refuses_what_it_cannot_order(be):
     assert _lib.lib().lq4_decode_step(be._ctx, C.byref(grp), 9, None, None) == _lib.ERR_NOSPACE
     assert _lib.lib().lq4_decode_step(None, C.byref(grp), 1, None, None) == _lib.ERR_NULL
     buf.close()
+
+
+def test_host_step_reads_pinned_inputs_and_writes_pinned_outputs(be):
+    """lq4_decode_step_host: inputs in page-locked host memory (staged in by a kernel chained in front of the
+    step kernel), outputs stored straight to page-locked host memory; the same bits as the device-buffer call,
+    also after the host has changed the inputs between two launches, and with a chained second group."""
+    from lattice_b200.sharded import StepBuffer
+    spec = [[(1024, 300, 16), (2048, 640, 8)], [(1024, 512, 4), (2048, 77, 0)]]
+    cases = [[make_case(3, 1, k, n, r, 2.0 * r, extra=400 + 10 * gi + i) for i, (k, n, r) in enumerate(grp)] for gi, grp in enumerate(spec)]
+    # both groups share one input per k, as the projections of a layer do (staged once per distinct pointer)
+    hx = {k: torch.from_numpy(np.ascontiguousarray(cases[0][i]["x"].reshape(-1))).pin_memory() for i, (k, _, _) in enumerate(spec[0])}
+    dx = {k: v.cuda() for k, v in hx.items()}
+    dev_groups, host_groups, outs, keep = [], [], [], []
+    for gi, grp in enumerate(spec):
+        dg, hg = [], []
+        for i, (k, n, r) in enumerate(grp):
+            qw, lora, kp = _problem(cases[gi][i])
+            keep += kp
+            yd = torch.full((n,), float("nan"), device="cuda")
+            yh = torch.full((n,), float("nan")).pin_memory()
+            dg.append((dx[k], qw, lora, yd))
+            hg.append((hx[k], qw, lora, yh))
+            outs.append((yd, yh))
+        dev_groups.append(dg)
+        host_groups.append(hg)
+    on_dev, on_host = be.prepare_step(dev_groups), be.prepare_step(host_groups, host=True)
+    on_dev()
+    before = be.launch_count
+    on_host()
+    assert be.launch_count - before == 2                    # stage-in kernel + step kernel
+    be.check_device_status()
+    for yd, yh in outs:
+        assert torch.equal(yd.cpu(), yh)
+    for i in range(2):                                      # group 0 runs on its own cases' inputs: against the oracle
+        assert tol_ratio(outs[i][1].numpy().reshape(1, -1), cases[0][i]["y_ref"]) <= 1.0
+    # new activations written by the host between launches are what the next launch reads
+    for k in hx:
+        hx[k].mul_(-0.5)
+        dx[k].copy_(hx[k])
+    on_dev()
+    on_host()
+    be.check_device_status()
+    for yd, yh in outs:
+        assert torch.equal(yd.cpu(), yh)
+    # a chained step: group 1 reads group 0's output through the step buffer; its own output goes to the host
+    c0 = make_case(3, 1, 1024, 512, 16, 32.0, extra=470)
+    c1 = make_case(3, 1, 512, 200, 8, 16.0, extra=471)
+    q0, l0, k0 = _problem(c0)
+    q1, l1, k1 = _problem(c1)
+    sb = StepBuffer(512)
+    hx0 = torch.from_numpy(np.ascontiguousarray(c0["x"].reshape(-1))).pin_memory()
+    mid = sb.payload[:512]
+    y_host = torch.full((200,), float("nan")).pin_memory()
+    y_dev = torch.full((200,), float("nan"), device="cuda")
+    chained_host = be.prepare_step([[(hx0, q0, l0, mid)], [(mid, q1, l1, y_host)]], sb, gathered=[], host=True)
+    chained_dev = be.prepare_step([[(hx0.cuda(), q0, l0, mid)], [(mid, q1, l1, y_dev)]], sb, gathered=[])
+    chained_dev()
+    chained_host()
+    be.check_device_status()
+    assert torch.equal(y_dev.cpu(), y_host)
