@@ -275,44 +275,38 @@ __device__ __forceinline__ void store_limbs_block(uint8_t* xs, float2* sx, uint3
     sx[blk] = make_float2(scale, sum);
 }
 
-// The converter warps' conversion of a share's k range(s) from plain memory, a block per thread and pass.
+// The converter warps' conversion of a share's k range(s) from plain memory, a block per thread and turn.  The
+// loop is kept small on purpose (one block's arithmetic, the next block's loads issued before it): these warps
+// share their schedulers' instruction caches with the consumers' stage loop.
 template <int NT>
 __device__ __forceinline__ void convert_blocks_plain(const StepProblem& q, uint8_t* xs, float2* sx, int ctid, const XRange& xr) {
     const uint32_t nblk = xr.noct / 4, nba = xr.na / 4, a0b = xr.a0 / 4, b0b = xr.b0 / 4;      // ranges are whole granules
-    constexpr int KB = 2;
-#pragma unroll 1
-    for (uint32_t i0 = 0; i0 < nblk; i0 += KB * NT) {
-        float v[KB][32];
+    auto load_block = [&](uint32_t i, float (&v)[32]) {
+        const uint32_t o = i < nba ? a0b + i : b0b + (i - nba);
 #pragma unroll
-        for (int u = 0; u < KB; ++u) {
-            const uint32_t i = i0 + u * NT + ctid;
-            const uint32_t o = i < nba ? a0b + i : b0b + (i - nba);
-            if (i < nblk) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) load8(q.x, q.x_dtype, (size_t)o * 32 + 8 * j, *reinterpret_cast<float(*)[8]>(&v[u][8 * j]));
-            }
-        }
+        for (int j = 0; j < 4; ++j) load8(q.x, q.x_dtype, (size_t)o * 32 + 8 * j, *reinterpret_cast<float(*)[8]>(&v[8 * j]));
         if (q.x_mul) {
 #pragma unroll
-            for (int u = 0; u < KB; ++u) {
-                const uint32_t i = i0 + u * NT + ctid;
-                const uint32_t o = i < nba ? a0b + i : b0b + (i - nba);
-                if (i < nblk) {
+            for (int j = 0; j < 4; ++j) {
+                float up[8];
+                load8(q.x_mul, LQ4_DTYPE_F32, (size_t)o * 32 + 8 * j, up);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float up[8];
-                        load8(q.x_mul, LQ4_DTYPE_F32, (size_t)o * 32 + 8 * j, up);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) v[u][8 * j + e] = silu_mul(v[u][8 * j + e], up[e]);
-                    }
-                }
+                for (int e = 0; e < 8; ++e) v[8 * j + e] = silu_mul(v[8 * j + e], up[e]);
             }
         }
+    };
+    float cur[32];
+    uint32_t i = ctid;
+    if (i < nblk) load_block(i, cur);
+#pragma unroll 1
+    for (; i < nblk; i += NT) {
+        float nxt[32];
 #pragma unroll
-        for (int u = 0; u < KB; ++u) {
-            const uint32_t i = i0 + u * NT + ctid;
-            if (i < nblk) store_limbs_block(xs, sx, i, v[u]);
-        }
+        for (int e = 0; e < 32; ++e) nxt[e] = 0.0f;
+        if (i + NT < nblk) load_block(i + NT, nxt);
+        store_limbs_block(xs, sx, i, cur);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) cur[e] = nxt[e];
     }
 }
 
@@ -892,25 +886,25 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
                     v0 += q.lscale * la;
                     v1 += q.lscale * lb2;
                 }
-                if (t == 0) {
-                    // plain f32 for whoever reads after the launch, a tagged mailbox entry on every rank for the
-                    // later groups of this launch (and for the final gather)
-                    if (rowa < q.n) {
-                        q.y[rowa] = v0;
-                        if (q.y_slot != kNoSlot) {
-                            const unsigned long long e = mbox_pack(v0, stag);
-                            char* own = reinterpret_cast<char*>(mb + q.y_slot + rowa);
-                            for (uint32_t r = 0; r < a.world; ++r) mbox_store(reinterpret_cast<unsigned long long*>(own + a.peer_mbox_off[r]), e);
-                        }
+                // Results: plain f32 for whoever reads after the launch, a tagged mailbox entry on every rank for the
+                // later groups of this launch (and for the final gather).
+                auto publish = [&](uint32_t row, float val) {
+                    q.y[row] = val;
+                    if (q.y_slot != kNoSlot) {
+                        const unsigned long long e = mbox_pack(val, stag);
+                        char* own = reinterpret_cast<char*>(mb + q.y_slot + row);
+                        for (uint32_t r = 0; r < a.world; ++r) mbox_store(reinterpret_cast<unsigned long long*>(own + a.peer_mbox_off[r]), e);
                     }
-                    if (rowb < q.n) {
-                        q.y[rowb] = v1;
-                        if (q.y_slot != kNoSlot) {
-                            const unsigned long long e = mbox_pack(v1, stag);
-                            char* own = reinterpret_cast<char*>(mb + q.y_slot + rowb);
-                            for (uint32_t r = 0; r < a.world; ++r) mbox_store(reinterpret_cast<unsigned long long*>(own + a.peer_mbox_off[r]), e);
-                        }
-                    }
+                };
+                if constexpr (!MB) {
+                    // every lane of a quad holds both sums: lane 0 stores the first row, lane 1 the second, so one
+                    // store instruction of the warp writes the warp's 16 consecutive rows (64 bytes of y, whole
+                    // packets when y is host memory behind PCIe); 0.7 % of the step on the plain-input instantiation
+                    const uint32_t row = t == 0 ? rowa : rowb;
+                    if (t < 2 && row < q.n) publish(row, t == 0 ? v0 : v1);
+                } else if (t == 0) {
+                    if (rowa < q.n) publish(rowa, v0);
+                    if (rowb < q.n) publish(rowb, v1);
                 }
                 if (tid == 0) TL_STAMP(g, 3);
             }
