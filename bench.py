@@ -568,7 +568,11 @@ def run_ours(args):
     # once; replay removes the per-call host cost).  --eager times plain calls instead.
     graph_info = {"mode": "eager"}
 
-    def make_graphed(fn):
+    # steps per captured graph of the headline leg: the largest divisor of --steps that is at most --graph-steps
+    head_graph_steps = max(d for d in range(1, max(1, args.graph_steps) + 1) if args.steps % d == 0)
+    graph_info["steps_per_replay"] = 1
+
+    def make_graphed(fn, graph_steps=1):
         if args.eager or (world > 1 and args.gather == "nccl"):
             # with NCCL collectives inside the step, capture is left out: a captured all-gather did
             # not complete on this pool, so such steps are timed as plain calls
@@ -586,9 +590,14 @@ def run_ours(args):
             g = torch.cuda.CUDAGraph()
             l0 = be.launch_count
             with torch.cuda.graph(g, stream=side):
-                fn()
-            per_step = be.launch_count - l0
-            graph_info["mode"] = "cuda-graph replay of one captured step"
+                for _ in range(graph_steps):
+                    fn()
+            per_step = (be.launch_count - l0) // graph_steps
+            graph_info["mode"] = ("cuda-graph replay of one captured step" if graph_steps == 1 else
+                                  f"cuda-graph replay of {graph_steps} consecutive captured steps (programmatic launch edges "
+                                  "between them: a step's weight stream starts while the step before it drains; its "
+                                  "activations are read after that step has completed)")
+            graph_info["steps_per_replay"] = graph_steps
             return g.replay, per_step
         except Exception as e:                      # capture not possible: fall back to plain calls
             graph_info["mode"] = "eager (graph capture failed: %r)" % (e,)
@@ -627,10 +636,11 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.25)                    # the first sample is there before the timed region starts
-    step_fn, per_step_launches = make_graphed(step)
+    step_fn, per_step_launches = make_graphed(step, head_graph_steps)
     note("launch mode: " + graph_info["mode"])
     t_host0 = time.time()
-    ms, launches = timed(step_fn, args.steps, args.warmup, per_step_launches)
+    spr = graph_info["steps_per_replay"]
+    ms, launches = timed(step_fn, args.steps // spr, -(-args.warmup // spr), per_step_launches * spr if per_step_launches is not None else None)
     t_host1 = time.time()
     note("device-timed leg done")
     clocks = sampler.window(t_host0, t_host1) if rank == 0 else None
@@ -1296,6 +1306,8 @@ def main():
                          "rank's buffer over NVLink); nccl = one NCCL all-gather per set; peer-nowait and none are "
                          "diagnostics (no waiting for the peers / no exchange at all): their values are not results")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of a CUDA-graph replay")
+    ap.add_argument("--graph-steps", type=int, default=10,
+                    help="consecutive steps captured in the replayed CUDA graph of the device-timed leg (1: one step per replay)")
     ap.add_argument("--verbose", action="store_true", help="progress notes on stderr")
     ap.add_argument("--only", default=None, help="gemm-slice | decode-up | decode-set | decode-step | mlp-block | lm-head: three launches of one case, for profiling")
     ap.add_argument("--no-aux", action="store_true")
