@@ -713,7 +713,8 @@ def run_ours(args):
             line.setdefault("aux", {})["copy_bandwidth_this_box"] = {"error": repr(e)}
         # the headline step replayed back to back for about two seconds: the rate a decode loop sustains once
         # clocks and power have settled, with the sampled SM clock and the rate binned by clock
-        line.setdefault("aux", {})["sustained"] = sustained_run(step_fn, per_step_bytes, sampler, hbm_peak)
+        line.setdefault("aux", {})["sustained"] = sustained_run(step_fn, per_step_bytes * spr, sampler, hbm_peak, chunk=max(1, 100 // spr))
+        line["aux"]["sustained"]["steps_per_replay"] = spr
     if rank == 0 and world == 1 and not args.no_aux:
         line["aux"].update(aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust, sampler))
         # the same decode set at other token counts and with the other launch mode, timed the same way

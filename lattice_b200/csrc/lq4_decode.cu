@@ -700,7 +700,8 @@ namespace dec {
 void split_ctas(const GemvParams* ps, uint32_t count, uint32_t grid, uint32_t* cta_begin, uint32_t tile_charge) {
     // fix-up and epilogue of a tile, in work units (a work unit streams in about 0.24 us).  Measured on the
     // large-layer set: 8 suits a launch per set, whose tail the next launch covers; the step kernel, where a
-    // CTA walks straight into the next group, is quickest with 3 (LQ4_TILE_CHARGE overrides both).
+    // CTA walks straight into the next group and the shares inside a problem carry a charge of their own,
+    // passes 5 (LQ4_TILE_CHARGE overrides both).
     static const int env_charge = [] {
         const char* e = getenv("LQ4_TILE_CHARGE");
         return e ? atoi(e) : -1;
