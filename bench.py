@@ -1113,15 +1113,15 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust, sampler=None):
         hbuf = torch.empty((1, inter), device=dev)
         res = {}
         from lattice_b200 import _lib as lq4lib
-        for what in ("block", "one_launch", "separate"):
-            be.set_option(lq4lib.OPT_MLP_ONE_LAUNCH, 1 if what == "one_launch" else 0)
+        for what in ("block", "two_launches", "separate"):
+            be.set_option(lq4lib.OPT_MLP_ONE_LAUNCH, 0 if what == "two_launches" else 1)
 
             def call(i):
                 qgu, qd = sets[i % copies]
-                if what == "block":              # default: grouped gate/up launch, then down_proj gating its own input
-                    be.mlp_block(x, qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2], gate_up=gu, out=y)
-                elif what == "one_launch":       # opt-in: the block as ONE lq4_decode_step launch (row in the library's step buffer)
+                if what == "block":              # default: the block as ONE lq4_decode_step launch (row in the library's step buffer)
                     be.mlp_block(x, qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2], out=y)
+                elif what == "two_launches":     # grouped gate/up launch into the caller's row, then down_proj gating its own input
+                    be.mlp_block(x, qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2], gate_up=gu, out=y)
                 else:
                     be.dispatch_gemm_q4_at(x, 0, qgu, 0, gu, 0, 1, inter, hidden, lora=descs[0])
                     be.dispatch_gemm_q4_at(x, 0, qgu, inter * (hidden // 32) * 20, gu, inter * 4, 1, inter, hidden, lora=descs[1])
@@ -1146,8 +1146,8 @@ def aux_measurements(be, dev, hbm_peak, tc_peak, tc_sust, sampler=None):
             res[what] = e0.elapsed_time(e1) * 1e3 / reps
         byts = 3 * inter * (hidden // 32) * 20 + 4 * rank * 3 * (hidden + inter)
         us = res["block"]
-        be.set_option(lq4lib.OPT_MLP_ONE_LAUNCH, 0)
-        out[name] = {"us_per_block": us, "us_one_launch_opt_in": res["one_launch"], "us_separate_calls": res["separate"], "GB/s": byts / us / 1e3,
+        be.set_option(lq4lib.OPT_MLP_ONE_LAUNCH, 1)
+        out[name] = {"us_per_block": us, "us_two_launches": res["two_launches"], "us_separate_calls": res["separate"], "GB/s": byts / us / 1e3,
                      "frac_hbm": byts / us / 1e3 / hbm_peak, "weight_copies": copies, "timing": "cuda-graph replay"}
 
     def clocked(fn, name, *a, **kw):

@@ -138,9 +138,9 @@ lq4_status lq4_ctx_reserve(lq4_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uin
 /* Synchronises `stream` and returns LQ4_ERR_DEVICE if any kernel launched through
  * this context gave up on a bounded wait since the last call; clears the flag. */
 lq4_status lq4_ctx_check(lq4_ctx* ctx, void* stream);
-/* Per-context switches.  LQ4_OPT_MLP_ONE_LAUNCH (default 0): lq4_mlp_block runs a one-token block whose
+/* Per-context switches.  LQ4_OPT_MLP_ONE_LAUNCH (default 1): lq4_mlp_block runs a one-token block whose
  * gate||up row lives in the library's workspace as ONE lq4_decode_step launch instead of two launches (measured
- * on B200, hidden 5120 / inter 17408: 47.9 us against 45.3 us, so it is off by default).  LQ4_OPT_PDL (default
+ * on B200, hidden 5120 / inter 17408: 42.5 us against 47.0 us).  LQ4_OPT_PDL (default
  * 1): programmatic dependent launch between consecutive kernels.  LQ4_OPT_ALLOW_GROW (default 1): 0 makes a call
  * whose workspace is too small return LQ4_ERR_NOSPACE instead of reallocating (after lq4_ctx_reserve, for
  * callers that must not hit cudaMalloc in the decode loop). */

@@ -62,7 +62,7 @@ struct lq4_ctx {
     cudaEvent_t ev_block[4] = {nullptr, nullptr, nullptr, nullptr}, ev_comm = nullptr;
     bool allow_grow = true;
     int pdl = 1;
-    int mlp_one_launch = 0;       // LQ4_OPT_MLP_ONE_LAUNCH
+    int mlp_one_launch = 1;       // LQ4_OPT_MLP_ONE_LAUNCH
 };
 
 struct lq4_weights {
@@ -333,7 +333,7 @@ lq4_status lq4_ctx_create(int32_t device, lq4_ctx** out) {
     const char* env = getenv("LQ4_DISABLE_PDL");
     if (env && env[0] == '1') ctx->pdl = 0;
     env = getenv("LQ4_MLP_ONE_LAUNCH");
-    if (env && env[0] == '1') ctx->mlp_one_launch = 1;
+    if (env && (env[0] == '0' || env[0] == '1')) ctx->mlp_one_launch = env[0] == '1';
     *out = ctx;
     return lq4_ctx_reserve(ctx, 16, 32768, 32768, 128);
 }
@@ -1161,10 +1161,11 @@ lq4_status lq4_mlp_block(lq4_ctx* ctx, const lq4_mlp_args* a, void* stream) {
         bool lora_ok = true;
         for (const lq4_lora_desc* l : {a->lora_gate, a->lora_up, a->lora_down})
             lora_ok = lora_ok && (!l || (l->rank <= (uint32_t)kGemvMaxRank && aligned(l->a, 16)));
+        const uint64_t need = 2ull * a->inter;
+        // without room for the row and with growth disabled the block runs as two launches (below)
+        if (lora_ok && !ctx->allow_grow && (!ctx->mlp_step || ctx->mlp_step->payload_bytes < need * 4)) lora_ok = false;
         if (lora_ok) {
-            const uint64_t need = 2ull * a->inter;
             if (!ctx->mlp_step || ctx->mlp_step->payload_bytes < need * 4) {
-                if (!ctx->allow_grow) return fail(LQ4_ERR_NOSPACE, "workspace too small and growth is disabled");
                 LQ4_CUDA(cudaStreamSynchronize(s));
                 if (ctx->mlp_step) { lq4_peer_buf_free(ctx->mlp_step); ctx->mlp_step = nullptr; }
                 if ((st = lq4_step_buf_create(need, &ctx->mlp_step))) return st;

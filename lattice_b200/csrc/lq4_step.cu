@@ -350,9 +350,12 @@ __device__ __forceinline__ void convert_activations(const StepArgs& a, const Ste
             }
         }
     } else {
+        // Octets per thread and sweep: 2 (1 with a gating row).  Larger sweeps save L2 round trips but their
+        // registers spill, and the spill code lands in the consumers' stage loop: with 4 (2) the whole
+        // instantiation ran 26 % slower on plain inputs and the chained bench step took 144 us instead of 112.
         const unsigned long long* xm = mb + q.x_slot;
-        if (q.xmul_slot != kNoSlot) prologue_from_mailbox<NT, 2, true>(a, xs, sx, xm, mb + q.xmul_slot, a0, na, b0, noct, ctid, stag, s_err);
-        else prologue_from_mailbox<NT, 4, false>(a, xs, sx, xm, nullptr, a0, na, b0, noct, ctid, stag, s_err);
+        if (q.xmul_slot != kNoSlot) prologue_from_mailbox<NT, 1, true>(a, xs, sx, xm, mb + q.xmul_slot, a0, na, b0, noct, ctid, stag, s_err);
+        else prologue_from_mailbox<NT, 2, false>(a, xs, sx, xm, nullptr, a0, na, b0, noct, ctid, stag, s_err);
     }
 }
 
@@ -1022,7 +1025,9 @@ static cudaError_t launch_step_t(const StepArgs& a, size_t smem, int grid, cudaS
 cudaError_t launch_decode_step(const StepArgs& a, size_t smem, int grid, cudaStream_t s) {
     bool mailbox_inputs = false;
     for (uint32_t i = 0; i < a.group_begin[a.ngroups]; ++i) mailbox_inputs = mailbox_inputs || a.p[i].x_slot != kNoSlot;
-    return mailbox_inputs ? launch_step_t<true>(a, smem, grid, s) : launch_step_t<false>(a, smem, grid, s);
+    // LQ4_STEP_FORCE_MB: run the mailbox-fed instantiation on plain inputs too (to compare the two builds' stage loops)
+    static const bool force_mb = getenv("LQ4_STEP_FORCE_MB") != nullptr;
+    return (mailbox_inputs || force_mb) ? launch_step_t<true>(a, smem, grid, s) : launch_step_t<false>(a, smem, grid, s);
 }
 
 }  // namespace lq4

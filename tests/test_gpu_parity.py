@@ -963,14 +963,14 @@ def test_mlp_block_matches_the_three_step_reference(be, m, hidden, inter, rank):
     bound = 1.0 if m <= 16 else 2.0
     ratio = tol_ratio(y.cpu().numpy(), y_ref)
     assert ratio <= bound, f"tolerance ratio {ratio}"
-    if m == 1 and inter % 128 == 0:
-        assert launches == 2          # gate and up rows in one grouped launch; down_proj gates its own input
-        # opt-in: the whole block as ONE persistent launch (down_proj reads silu(gate) * up through the mailbox)
-        be.set_option(_lib.OPT_MLP_ONE_LAUNCH, 1)
+    if m == 1 and inter % 128 == 0 and hidden % 128 == 0:
+        assert launches == 1          # the whole block as ONE persistent launch (down_proj reads silu(gate) * up through the mailbox)
+        # switched off: gate and up rows in one grouped launch; down_proj gates its own input
+        be.set_option(_lib.OPT_MLP_ONE_LAUNCH, 0)
         before = be.launch_count
         y1 = be.mlp_block(dev(x), qgu, qd, lora_gate=descs[0], lora_up=descs[1], lora_down=descs[2])
-        be.set_option(_lib.OPT_MLP_ONE_LAUNCH, 0)
-        assert be.launch_count - before == 1
+        be.set_option(_lib.OPT_MLP_ONE_LAUNCH, 1)
+        assert be.launch_count - before == 2
         be.check_device_status()
         assert tol_ratio(y1.cpu().numpy(), y_ref) <= bound
     # with a caller-provided scratch (one token: gate||up launch, then down_proj gating its own input) the
