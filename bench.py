@@ -44,7 +44,7 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC = {
     "grouped": {"bytes_per_launch": 138.64e6, "kernel": "decode_kernel<1, 8>", "source_hash": None},
     "per-projection": {"bytes_per_launch": None, "kernel": "decode_kernel<1, 1>", "source_hash": None},
-    "step": {"bytes_per_launch": 555.38e6, "kernel": "decode_step_kernel<false>", "source_hash": "6c7ff2b22150110b"},
+    "step": {"bytes_per_launch": 553.74e6, "kernel": "decode_step_kernel<false>", "source_hash": "ed2396357ff09d6d"},
 }
 
 
