@@ -232,3 +232,36 @@ def test_host_step_reads_pinned_inputs_and_writes_pinned_outputs(be):
     chained_host()
     be.check_device_status()
     assert torch.equal(y_dev.cpu(), y_host)
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_steps_match_the_oracle(be, seed):
+    """Seeded random steps (1-3 groups of 1-4 projections, ragged n, k from one to 34 granules per tile, adapters of
+    rank 0-64): every output against the oracle.  Exercises the cut of the work units into CTA shares where tiles
+    are few, shares are a handful of units and some CTAs get nothing."""
+    rng = np.random.default_rng(seed)
+    groups, checks, keep = [], [], []
+    e = 0
+    for _ in range(int(rng.integers(1, 4))):
+        g = []
+        for _ in range(int(rng.integers(1, 5))):
+            k = 128 * int(rng.choice([1, 2, 3, 8, 17, 34]))
+            n = int(rng.choice([1, 77, 128, 129, 640, 1000, 2500]))
+            r = int(rng.choice([0, 4, 16, 64]))
+            case = make_case(3, 1, k, n, r, 2.0 * max(r, 1), extra=600 + 37 * seed + e)
+            e += 1
+            qw, lora, kp = _problem(case)
+            keep += kp
+            y = torch.full((n,), float("nan"), device="cuda")
+            g.append((dev(case["x"]), qw, lora, y))
+            checks.append((y, case))
+        groups.append(g)
+    step = be.prepare_step(groups)
+    step()
+    be.check_device_status()
+    for y, case in checks:
+        assert tol_ratio(y.cpu().numpy().reshape(1, -1), case["y_ref"]) <= 1.0, (case["n"], case["k"], case["rank"])
+    first = [y.clone() for y, _ in checks]
+    step()
+    be.check_device_status()
+    assert all(torch.equal(a, y) for a, (y, _) in zip(first, checks))
