@@ -235,6 +235,8 @@ lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t 
  * either direction (measured on B200: a copy node in front of and behind the kernel costs 14 us and 10 us of
  * a 136 us step).  The host must not touch the inputs before the launch has completed, and reads the
  * outputs after it has.  With world > 1 the outputs must lie in the step buffer as for lq4_decode_step.
+ * The staging area grows on first use (which synchronises the stream and allocates): make one plain call
+ * before capturing this call into a CUDA graph.
  * No counterpart in the reference, whose buffers are zero-copy unified memory
  * (crates/inference/src/forward/metal.rs:4, StorageModeShared). */
 lq4_status lq4_decode_step_host(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t ngroups, const lq4_step_desc* step,
