@@ -523,6 +523,15 @@ lq4_status lq4_linear(lq4_ctx* ctx, const lq4_linear_args* a, void* stream) {
     return LQ4_OK;
 }
 
+namespace {
+struct StepSpec {
+    lq4_linear_args a;
+    const float* x_mul;      // gating row for this problem's input (silu(x) * x_mul), or NULL
+};
+lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize, uint32_t ngroups, const lq4_step_desc* step,
+                     cudaStream_t s);
+}  // namespace
+
 lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t count, void* stream) {
     if (!ctx) return fail(LQ4_ERR_NULL, "ctx is NULL");
     if (count == 0) return LQ4_OK;
@@ -544,6 +553,33 @@ lq4_status lq4_linear_group(lq4_ctx* ctx, const lq4_linear_args* args, uint32_t 
                           !(a.wait_gather && a.wait_gather->world > 1) && gemv_resident_fits(1, a.k, false);
         if (!fits) return lq4_linear(ctx, &a, stream);
         return run_gemv_mma(ctx, &a, a.x, a.x_dtype, nullptr, 1, a.y, a.ldy ? a.ldy : a.n, s, nullptr, true);
+    }
+    if (count > (uint32_t)kMaxGroup && count <= (uint32_t)kStepMaxProblems) {
+        // 9 to 24 one-token projections: one group of the step kernel (one persistent launch) when every
+        // problem qualifies for it; else problem by problem below
+        bool step_ok = true;
+        for (uint32_t i = 0; i < count && step_ok; ++i) {
+            const lq4_linear_args& a = args[i];
+            const uint32_t rank = a.lora ? a.lora->rank : 0;
+            step_ok = a.m == 1 && a.n > 0 && !a.rot && !a.gather && !a.wait_gather && (a.k % 128 == 0) && aligned(a.w, 16) &&
+                      aligned(a.x, 16) && rank <= (uint32_t)kGemvMaxRank && (!a.lora || aligned(a.lora->a, 16)) &&
+                      (a.path == LQ4_PATH_AUTO || a.path == LQ4_PATH_GEMV_MMA) && (a.ldy == 0 || a.ldy == a.n) &&
+                      gemv_resident_fits(1, a.k, false);
+            // no output may be another problem's input (a step orders its groups; a group's problems are independent)
+            for (uint32_t j = 0; j < count && step_ok; ++j) {
+                const char* y0 = reinterpret_cast<const char*>(args[j].y);
+                const char* x0 = static_cast<const char*>(a.x);
+                const size_t xb = (size_t)a.k * (a.x_dtype == LQ4_DTYPE_BF16 ? 2 : 4);
+                step_ok = !(x0 < y0 + (size_t)args[j].n * 4 && y0 < x0 + xb);
+            }
+        }
+        if (step_ok) {
+            StepSpec specs[kStepMaxProblems];
+            for (uint32_t i = 0; i < count; ++i) { specs[i].a = args[i]; specs[i].x_mul = nullptr; }
+            const uint32_t gsize[1] = {count};
+            st = step_core(ctx, specs, gsize, 1, nullptr, s);
+            if (st != LQ4_ERR_UNSUPPORTED) return st;      // (refused before anything was launched: e.g. a row too long for two limb buffers)
+        }
     }
     bool one_launch = count >= 2 && count <= (uint32_t)kMaxGroup;
     GemvParams ps[kMaxGroup];
@@ -738,11 +774,6 @@ lq4_status lq4_gather_wait(lq4_ctx* ctx, const lq4_gather_desc* g, void* stream)
 }
 
 namespace {
-
-struct StepSpec {
-    lq4_linear_args a;
-    const float* x_mul;      // gating row for this problem's input (silu(x) * x_mul), or NULL
-};
 
 // Core of lq4_decode_step: `specs` are the problems in group order, `gsize[g]` the size of group g.
 lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize, uint32_t ngroups, const lq4_step_desc* step,

@@ -446,10 +446,16 @@ def test_group_that_cannot_share_a_launch_runs_problem_by_problem(be):
     assert launches >= 3
     for y, c in zip(ys, cases):
         assert tol_ratio(y, c["y_ref"]) <= 1.0
-    # more problems than one launch takes
+    # nine one-token projections: more than the grouped kernel takes, one group of the step kernel
     many = [make_case(1, 1, 256, 128, extra=70 + i) for i in range(9)]
     ys, launches = _run_group(be, many)
-    assert launches == 9
+    assert launches == 1
+    for y, c in zip(ys, many):
+        assert tol_ratio(y, c["y_ref"]) <= 1.0
+    # nine two-token projections: more problems than one launch takes
+    many = [make_case(1, 2, 256, 128, extra=80 + i) for i in range(9)]
+    ys, launches = _run_group(be, many)
+    assert launches >= 9
     for y, c in zip(ys, many):
         assert tol_ratio(y, c["y_ref"]) <= 1.0
     assert be.linear_group([]) == []

@@ -265,3 +265,26 @@ def test_random_steps_match_the_oracle(be, seed):
     step()
     be.check_device_status()
     assert all(torch.equal(a, y) for a, (y, _) in zip(first, checks))
+
+
+def test_a_group_of_twelve_projections_is_one_launch(be):
+    """lq4_linear_group with 9 to 24 one-token projections runs them as one group of the step kernel: ONE launch,
+    every output against the oracle; a group that does not qualify (a rotated member) still runs problem by
+    problem with the same results."""
+    shapes = [(1024, 300, 16), (1024, 128, 0), (2048, 640, 8), (512, 1000, 16), (1024, 77, 4), (3072, 256, 16),
+              (1024, 512, 0), (2048, 129, 64), (512, 2500, 4), (1024, 640, 16), (2048, 300, 0), (1024, 1000, 8)]
+    problems, outs, checks, keep = [], [], [], []
+    for i, (k, n, r) in enumerate(shapes):
+        case = make_case(3, 1, k, n, r, 2.0 * max(r, 1), extra=700 + i)
+        qw, lora, kp = _problem(case)
+        keep += kp
+        y = torch.full((1, n), float("nan"), device="cuda")
+        problems.append((dev(case["x"]), qw, lora))
+        outs.append(y)
+        checks.append((y, case))
+    before = be.launch_count
+    be.linear_group(problems, outs)
+    assert be.launch_count - before == 1
+    be.check_device_status()
+    for y, case in checks:
+        assert tol_ratio(y.cpu().numpy().reshape(1, -1), case["y_ref"]) <= 1.0
