@@ -754,14 +754,15 @@ def run_ours(args):
                 continue
             var = make_step_variant(other == "chained", other == "flat")
             step_variants[other] = var
-            gfn, gl = make_graphed(var["run"])
-            nsteps = min(args.steps, 50)
-            gms, _ = timed(gfn, nsteps, 3, gl)
+            gfn, gl = make_graphed(var["run"], head_graph_steps)      # queued like the headline's steps
+            spr_v = graph_info["steps_per_replay"] if gl is not None else 1
+            nsteps = max(spr_v, min(args.steps, 50) // spr_v * spr_v)
+            gms, _ = timed(gfn, nsteps // spr_v, 3 if spr_v == 1 else 1, gl)
             be.check_device_status()
             v = per_step_bytes * nsteps / (gms * 1e-3) / 1e9
             if rank == 0:
                 line.setdefault("aux", {})[f"decode_step_M1_{other}"] = {
-                    "GB/s": v, "frac_hbm_per_gpu": v / world / hbm_peak, "us_per_step": gms * 1e3 / nsteps,
+                    "GB/s": v, "frac_hbm_per_gpu": v / world / hbm_peak, "us_per_step": gms * 1e3 / nsteps, "steps_per_graph_replay": spr_v,
                     "checked_before_timing": var["check"], "what": what[other]}
     if world > 1 and not args.no_aux:
         sharded = aux_sharded_prefill(be, dev, world, rank, tc_peak, tc_sust)      # every rank takes part
