@@ -237,6 +237,7 @@ lq4_status lq4_decode_step(lq4_ctx* ctx, const lq4_step_group* groups, uint32_t 
  * either direction (measured on B200: a copy node in front of and behind the kernel costs 14 us and 10 us of
  * a 136 us step).  The host must not touch the inputs before the launch has completed, and reads the
  * outputs after it has.  With world > 1 the outputs must lie in the step buffer as for lq4_decode_step.
+ * Pointers the device cannot address (pageable host memory) are refused with LQ4_ERR_UNSUPPORTED.
  * The staging area grows on first use (which synchronises the stream and allocates): make one plain call
  * before capturing this call into a CUDA graph.
  * No counterpart in the reference, whose buffers are zero-copy unified memory

@@ -1074,6 +1074,12 @@ lq4_status lq4_decode_step_host(lq4_ctx* ctx, const lq4_step_group* groups, uint
         char* base = static_cast<char*>(step->bufs->bases[step->bufs->rank]);
         if (peer_buf_info(base, &info)) { pay0 = base + 256; pay1 = pay0 + info.payload_bytes; }
     }
+    // Pageable host memory is not addressable by the device: refuse it here instead of faulting in a kernel.
+    auto device_can_address = [](const void* p) {
+        cudaPointerAttributes at{};
+        if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return false; }
+        return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeHost || at.type == cudaMemoryTypeManaged;
+    };
     StageArgs sg{};
     size_t off[kStepMaxProblems], total = 0;
     int seg_of[kStepMaxProblems];
@@ -1081,7 +1087,9 @@ lq4_status lq4_decode_step_host(lq4_ctx* ctx, const lq4_step_group* groups, uint
         const lq4_linear_args& a = specs[i].a;
         seg_of[i] = -1;
         if (a.m == 0 || a.n == 0) continue;
-        if (!a.x) return fail(LQ4_ERR_NULL, "x must be non-NULL");
+        if (!a.x || !a.y) return fail(LQ4_ERR_NULL, "x and y must be non-NULL");
+        if (!device_can_address(a.y) || !device_can_address(a.y + (a.n - 1)))
+            return fail(LQ4_ERR_UNSUPPORTED, "y must be device memory or page-locked host memory (cudaHostAlloc / cudaHostRegister)");
         if (!aligned(a.x, 16) || a.k % 32 != 0) return fail(LQ4_ERR_ALIGN, "a step needs 16-byte aligned x and k % 32 == 0");
         const size_t bytes = (size_t)a.k * (a.x_dtype == LQ4_DTYPE_BF16 ? 2 : 4);
         const char* x0 = static_cast<const char*>(a.x);
@@ -1089,6 +1097,8 @@ lq4_status lq4_decode_step_host(lq4_ctx* ctx, const lq4_step_group* groups, uint
         for (uint32_t j = 0; j < sg.count; ++j)
             if (sg.src[j] == reinterpret_cast<const uint4*>(a.x) && sg.words[j] == bytes / 16) seg_of[i] = (int)j;
         if (seg_of[i] < 0) {
+            if (!device_can_address(x0) || !device_can_address(x0 + bytes - 1))
+                return fail(LQ4_ERR_UNSUPPORTED, "x must be device memory or page-locked host memory (cudaHostAlloc / cudaHostRegister)");
             seg_of[i] = (int)sg.count;
             sg.src[sg.count] = reinterpret_cast<const uint4*>(a.x);
             sg.words[sg.count] = (uint32_t)(bytes / 16);

@@ -288,3 +288,23 @@ def test_a_group_of_twelve_projections_is_one_launch(be):
     be.check_device_status()
     for y, case in checks:
         assert tol_ratio(y.cpu().numpy().reshape(1, -1), case["y_ref"]) <= 1.0
+
+
+def test_host_step_refuses_pageable_memory(be):
+    """A pointer the device cannot address must not reach a kernel: pageable host tensors are refused."""
+    from lattice_b200 import _lib as L
+    from lattice_b200._lib import LinearArgs, StepGroup
+    case = make_case(3, 1, 1024, 128, 0, 0.0, extra=480)
+    qw, _, keep = _problem(case)
+    x_pinned = torch.from_numpy(np.ascontiguousarray(case["x"].reshape(-1))).pin_memory()
+    x_pageable = torch.from_numpy(np.ascontiguousarray(case["x"].reshape(-1)).copy())
+    y_pinned = torch.zeros(128).pin_memory()
+    y_pageable = torch.zeros(128)
+    for x, y in ((x_pageable, y_pinned), (x_pinned, y_pageable)):
+        arr = (LinearArgs * 1)()
+        arr[0] = LinearArgs(x.data_ptr(), L.DTYPE_F32, 1, 128, 1024, qw.payload_ptr, y.data_ptr(), 0, None, None, L.PATH_AUTO, None, None)
+        grp = (StepGroup * 1)()
+        grp[0] = StepGroup(C.cast(arr, C.c_void_p).value, 1)
+        rc = L.lib().lq4_decode_step_host(be._ctx, C.cast(grp, C.c_void_p), 1, None, None)
+        assert rc == L.ERR_UNSUPPORTED
+    be.check_device_status()
