@@ -10,7 +10,16 @@ token (M = 1) - repeated over `--layers` layers with distinct weights (4 x 131 M
 several times the 126 MB L2, so every launch streams its weights from HBM).  One step is one
 pass over all of them.  metric = weight-streaming rate in GB/s on ALGORITHMIC bytes
 (payload + LoRA factors + x + y, each once); with N GPUs the output rows of every projection
-are sharded over the ranks and the slices are all-gathered over NCCL.
+are sharded over the ranks and every rank ends the step with all ranks' columns (published
+into every rank's step buffer by the step kernel itself; `--gather nccl` uses an NCCL
+all-gather per set instead).
+
+A step is ONE lq4_decode_step launch (`--launch step`, the default).  The device-timed leg
+issues the K steps back to back as replays of a CUDA graph of up to `--graph-steps`
+consecutive steps (a decode loop's queue: a step's weight stream starts while the step before
+it drains); the end-to-end leg replays one step per graph through lq4_decode_step_host
+(pinned inputs staged in by a kernel, results stored to pinned memory by the step kernel) and
+waits for it every step.
 
 Data are seeded synthetic tensors of those shapes (no dataset exists for this path).
 The reference arm (--impl reference) times the CPU restatement of the reference's own
