@@ -63,6 +63,8 @@ struct lq4_ctx {
     bool allow_grow = true;
     int pdl = 1;
     int mlp_one_launch = 1;       // LQ4_OPT_MLP_ONE_LAUNCH
+    uint64_t alloc_gen = 0;       // bumped whenever a workspace buffer is reallocated (plans hold workspace pointers)
+    struct StepPlan* step_plan = nullptr;      // the last lq4_decode_step call's argument block, reused when the call repeats
 };
 
 struct lq4_weights {
@@ -93,6 +95,7 @@ lq4_status ensure(lq4_ctx* ctx, Buf& b, size_t bytes, bool zero, cudaStream_t s)
     LQ4_CUDA(cudaMalloc(&b.p, cap));
     if (zero) LQ4_CUDA(cudaMemsetAsync(b.p, 0, cap, s));      // on the caller's stream: ordered before the first launch that reads it
     b.cap = cap;
+    ++ctx->alloc_gen;
     return LQ4_OK;
 }
 
@@ -338,10 +341,13 @@ lq4_status lq4_ctx_create(int32_t device, lq4_ctx** out) {
     return lq4_ctx_reserve(ctx, 16, 32768, 32768, 128);
 }
 
+static void free_step_plan(struct StepPlan* p);      // (defined with the struct, beside lq4_decode_step)
+
 void lq4_ctx_destroy(lq4_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
+    free_step_plan(ctx->step_plan);
     for (Buf* b : {&ctx->xrot, &ctx->xs, &ctx->t, &ctx->tmsg, &ctx->partials, &ctx->hx, &ctx->hy, &ctx->gemm, &ctx->logits, &ctx->topk, &ctx->topk_ctr, &ctx->mlp, &ctx->mlp_h, &ctx->shard_send, &ctx->shard_recv})
         if (b->p) cudaFree(b->p);
     if (ctx->mlp_step) lq4_peer_buf_free(ctx->mlp_step);
@@ -775,6 +781,23 @@ lq4_status lq4_gather_wait(lq4_ctx* ctx, const lq4_gather_desc* g, void* stream)
 
 namespace {
 
+}  // namespace
+
+// A decode loop issues the same step again and again (same buffers, same weights): planning it (validation,
+// CTA shares, tensor maps, shared-memory plan: about 15 us of host time for sixteen projections) is done once and
+// the argument block is kept.  The key is every byte the plan depends on: the problems' argument structs and
+// adapter descriptors, the group sizes, the step descriptor with its buffer layout, the context's switches and
+// the generation of its workspace.
+struct StepPlan {
+    std::vector<uint8_t> key;
+    StepArgs args;
+    size_t smem = 0;
+    int grid = 0;
+};
+static void free_step_plan(StepPlan* p) { delete p; }
+
+namespace {
+
 // Core of lq4_decode_step: `specs` are the problems in group order, `gsize[g]` the size of group g.
 lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize, uint32_t ngroups, const lq4_step_desc* step,
                      cudaStream_t s) {
@@ -800,6 +823,34 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
             return fail(LQ4_ERR_SHAPE, "step: bases[rank] is not a step buffer created by lq4_step_buf_create in this process");
     } else if (step) {
         return fail(LQ4_ERR_NULL, "step->bufs is NULL");
+    }
+    thread_local std::vector<uint8_t> key;
+    key.clear();
+    auto put = [&](const void* p, size_t n) {
+        const uint8_t* b = static_cast<const uint8_t*>(p);
+        key.insert(key.end(), b, b + n);
+    };
+    put(&ngroups, sizeof(ngroups));
+    put(gsize, sizeof(uint32_t) * ngroups);
+    put(&ctx->pdl, sizeof(ctx->pdl));
+    put(&ctx->alloc_gen, sizeof(ctx->alloc_gen));
+    for (uint32_t i = 0; i < np; ++i) {
+        put(&specs[i].a, sizeof(lq4_linear_args));
+        put(&specs[i].x_mul, sizeof(specs[i].x_mul));
+        if (specs[i].a.lora) put(specs[i].a.lora, sizeof(lq4_lora_desc));
+    }
+    if (step) {
+        put(&step->n_gathered, sizeof(step->n_gathered));
+        if (step->gathered && step->n_gathered <= (uint32_t)kStepMaxRanges) put(step->gathered, sizeof(lq4_step_range) * step->n_gathered);
+        if (gd) put(gd, sizeof(lq4_gather_desc));
+        put(&info.payload_bytes, sizeof(info.payload_bytes));
+        put(&info.mailbox_off, sizeof(info.mailbox_off));
+        put(&info.mailbox_half, sizeof(info.mailbox_half));
+    }
+    if (ctx->step_plan && ctx->step_plan->key == key) {
+        LQ4_CUDA(launch_decode_step(ctx->step_plan->args, ctx->step_plan->smem, ctx->step_plan->grid, s));
+        ctx->launches += 1;
+        return LQ4_OK;
     }
     float* payload = base ? reinterpret_cast<float*>(base + 256) : nullptr;
     const uint64_t pfloats = base ? info.payload_bytes / 4 : 0;
@@ -954,11 +1005,9 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
     uint32_t cap_blocks = 0;
     for (uint32_t i = 0; i < np; ++i) {
         const StepProblem& q = sa.p[i];
-        uint64_t share = 0;
-        for (uint32_t c = 0; c < q.cta_count; ++c) {
-            const uint64_t len = step_share_begin(c + 1, q.tiles, q.kg, q.charge, q.cta_count) - step_share_begin(c, q.tiles, q.kg, q.charge, q.cta_count);
-            share = len > share ? len : share;
-        }
+        // no share is longer than the even cut of the stretched range (a share without a tile start is exactly that long)
+        const uint64_t totalv = (uint64_t)q.tiles * ((uint64_t)q.kg + q.charge);
+        const uint64_t share = (totalv + q.cta_count - 1) / q.cta_count;
         const uint32_t blocks = share >= q.kg ? q.kb : (uint32_t)share * kGemvGranuleBlocks;
         cap_blocks = blocks > cap_blocks ? blocks : cap_blocks;
     }
@@ -995,6 +1044,14 @@ lq4_status step_core(lq4_ctx* ctx, const StepSpec* specs, const uint32_t* gsize,
     }
     LQ4_CUDA(launch_decode_step(sa, smem, grid, s));
     ctx->launches += 1;
+    // keep the plan for the next call (the workspace may have grown while it was made: take the generation as it is now)
+    if (!ctx->step_plan) ctx->step_plan = new StepPlan();
+    const size_t gen_at = sizeof(ngroups) + sizeof(uint32_t) * ngroups + sizeof(ctx->pdl);
+    memcpy(key.data() + gen_at, &ctx->alloc_gen, sizeof(ctx->alloc_gen));
+    ctx->step_plan->key = key;
+    ctx->step_plan->args = sa;
+    ctx->step_plan->smem = smem;
+    ctx->step_plan->grid = grid;
     return LQ4_OK;
 }
 

@@ -308,3 +308,40 @@ def test_host_step_refuses_pageable_memory(be):
         rc = L.lib().lq4_decode_step_host(be._ctx, C.cast(grp, C.c_void_p), 1, None, None)
         assert rc == L.ERR_UNSUPPORTED
     be.check_device_status()
+
+
+def test_repeated_step_reuses_its_plan_and_a_changed_argument_replans(be):
+    """The library keeps the last step's argument block: the same call again gives the same bits, and a call that
+    differs in one pointer, one adapter scale or one group size is planned afresh (checked against the oracle)."""
+    from lattice_b200._lib import LoraDesc
+    c0 = make_case(3, 1, 1024, 300, 16, 32.0, extra=800)
+    c1 = make_case(3, 1, 2048, 640, 8, 16.0, extra=801)
+    q0, l0, k0 = _problem(c0)
+    q1, l1, k1 = _problem(c1)
+    x0, x1 = dev(c0["x"]), dev(c1["x"])
+    ya, yb = torch.zeros(300, device="cuda"), torch.zeros(640, device="cuda")
+    step = be.prepare_step([[(x0, q0, l0, ya), (x1, q1, l1, yb)]])
+    step(); step()
+    be.check_device_status()
+    assert tol_ratio(ya.cpu().numpy().reshape(1, -1), c0["y_ref"]) <= 1.0
+    assert tol_ratio(yb.cpu().numpy().reshape(1, -1), c1["y_ref"]) <= 1.0
+    # another output pointer for the first problem
+    ya2 = torch.full((300,), float("nan"), device="cuda")
+    be.prepare_step([[(x0, q0, l0, ya2), (x1, q1, l1, yb)]])()
+    be.check_device_status()
+    assert torch.equal(ya2, ya)
+    # the same pointers, the adapter's scale doubled in place: the result must follow
+    a, b, s = c0["lora"]
+    l0.scale = 2.0 * s
+    ya.fill_(float("nan"))
+    step()
+    be.check_device_status()
+    ref = oracle.q4_linear(c0["x"], None, 1, 300, 1024, lora=(a, b, 2.0 * s), w_f32=c0["w_deq"])
+    assert tol_ratio(ya.cpu().numpy().reshape(1, -1), ref) <= 1.0
+    l0.scale = s
+    # the same two problems as two groups of one
+    ya.fill_(float("nan")); yb.fill_(float("nan"))
+    be.prepare_step([[(x0, q0, l0, ya)], [(x1, q1, l1, yb)]])()
+    be.check_device_status()
+    assert tol_ratio(ya.cpu().numpy().reshape(1, -1), c0["y_ref"]) <= 1.0
+    assert tol_ratio(yb.cpu().numpy().reshape(1, -1), c1["y_ref"]) <= 1.0
